@@ -1,0 +1,106 @@
+"""The CPU oracle against the golden vectors produced by the reference's own
+``forward`` source (tests/golden/make_golden.py) and against itself."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import llama_ref as O
+
+GOLD = np.load(os.path.join(os.path.dirname(__file__), "golden", "llama_golden.npz"))
+
+
+def _uniform_weights(cfg, seed, dtype):
+    rng = np.random.default_rng(seed)
+    w = {}
+    for name, shape in sorted(O.weight_shapes(cfg).items()):
+        w[name] = rng.random(shape).astype(dtype)
+    return w, rng
+
+
+@pytest.mark.parametrize("tag,dt,tol", [("f32", np.float32, 2e-5), ("f64", np.float64, 1e-12)])
+def test_level0_shipped_shape(tag, dt, tol):
+    cfg = O.CONFIGS["c1"]
+    w, rng = _uniform_weights(cfg, 11, dt)
+    x = rng.random(cfg["dim"]).astype(dt)
+    kc = np.zeros((cfg["n_layers"], 1, cfg["dim"]), dt)
+    got = O.forward_token(x, cfg, w, kc, kc.copy())
+    np.testing.assert_allclose(got, GOLD[f"A_{tag}"], rtol=tol, atol=tol)
+
+
+def _tiny_case():
+    cfg = O.CONFIGS["tiny"]
+    wt = O.make_weights(cfg, 5, torch.float64, std=0.2, gains_one=False)
+    w = O.to_numpy(wt)
+    rng = np.random.default_rng(21)
+    x = rng.standard_normal(cfg["dim"])
+    kc = rng.standard_normal((cfg["n_layers"], 5, cfg["dim"]))
+    vc = rng.standard_normal((cfg["n_layers"], 5, cfg["dim"]))
+    return cfg, wt, w, x, kc, vc
+
+
+def test_level0_random_cache_and_empty_cache():
+    cfg, _, w, x, kc, vc = _tiny_case()
+    np.testing.assert_allclose(O.forward_token(x, cfg, w, kc, vc), GOLD["B_f64"], rtol=1e-12, atol=1e-12)
+    e = np.zeros((cfg["n_layers"], 0, cfg["dim"]))
+    np.testing.assert_allclose(O.forward_token(x, cfg, w, e, e.copy()), GOLD["C_f64"], rtol=1e-12, atol=1e-12)
+
+
+def test_level1_hidden_matches_reference_per_token():
+    cfg, wt, _, _, _, _ = _tiny_case()
+    tokens = O.make_tokens(cfg, 2, 12, 3)
+    _, aux = O.forward_sequence(tokens, cfg, wt, return_aux=True)
+    np.testing.assert_allclose(aux["xf"].numpy(), GOLD["D_hidden_f64"], rtol=1e-10, atol=1e-11)
+
+
+def test_level1_equals_level0_iterated():
+    cfg, wt, w, _, _, _ = _tiny_case()
+    tokens = O.make_tokens(cfg, 1, 9, 8)
+    logits, aux = O.forward_sequence(tokens, cfg, wt, return_aux=True)
+    L, d = cfg["n_layers"], cfg["dim"]
+    kc = np.zeros((L, 0, d))
+    vc = np.zeros((L, 0, d))
+    for t in range(9):
+        x = w["token_embedding_table"][int(tokens[0, t])]
+        h, nk, nv = O.forward_token(x, cfg, w, kc, vc, return_kv=True)
+        np.testing.assert_allclose(h, aux["xf"][0, t].numpy(), rtol=1e-10, atol=1e-11)
+        np.testing.assert_allclose(w["wcls"] @ h, logits[0, t].numpy(), rtol=1e-9, atol=1e-10)
+        kc = np.concatenate([kc, nk[:, None, :]], axis=1)
+        vc = np.concatenate([vc, nv[:, None, :]], axis=1)
+
+
+def test_level1_past_cache_equals_full_sequence():
+    cfg, wt, _, _, _, _ = _tiny_case()
+    tokens = O.make_tokens(cfg, 2, 10, 4)
+    full, aux = O.forward_sequence(tokens, cfg, wt, return_aux=True)
+    P = 7
+    part = O.forward_sequence(tokens[:, P:], cfg, wt, past_k=aux["k"][:, :, :P], past_v=aux["v"][:, :, :P])
+    np.testing.assert_allclose(part.numpy(), full[:, P:].numpy(), rtol=1e-10, atol=1e-11)
+
+
+def test_level2_vjp_matches_finite_differences():
+    cfg, wt, _, _, _, _ = _tiny_case()
+    tokens = O.make_tokens(cfg, 1, 6, 2)
+    g = torch.Generator().manual_seed(0)
+    dlogits = torch.randn(1, 6, cfg["vocab_size"], generator=g, dtype=torch.float64)
+    _, grads = O.vjp_sequence(tokens, cfg, wt, dlogits)
+    rng = np.random.default_rng(0)
+    for name in ("wq", "w2", "rms_ffn_weight", "wcls", "token_embedding_table", "wv"):
+        dirn = torch.from_numpy(rng.standard_normal(tuple(wt[name].shape)))
+        eps = 1e-6
+        wp = dict(wt); wp[name] = wt[name] + eps * dirn
+        wm = dict(wt); wm[name] = wt[name] - eps * dirn
+        fd = ((O.forward_sequence(tokens, cfg, wp) - O.forward_sequence(tokens, cfg, wm)) * dlogits).sum() / (2 * eps)
+        an = (grads[name] * dirn).sum()
+        assert abs(fd - an) <= 1e-6 * max(1.0, abs(an)), (name, float(fd), float(an))
+
+
+def test_fp32_vs_fp64_rounding_bound():
+    cfg = O.CONFIGS["tiny"]
+    w64 = O.make_weights(cfg, 9, torch.float64)
+    w32 = O.cast_weights(w64, torch.float32)
+    tokens = O.make_tokens(cfg, 2, 16, 1)
+    a = O.forward_sequence(tokens, cfg, w64)
+    b = O.forward_sequence(tokens, cfg, w32).double()
+    assert (a - b).abs().max() <= 1e-5 + 1e-4 * a.abs().max()
