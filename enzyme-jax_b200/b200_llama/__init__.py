@@ -1,0 +1,350 @@
+"""Host-side driver of the B200 llama path.
+
+Thin ``ctypes`` layer over ``libb200_llama.so`` (the C ABI declared in
+``include/b200_llama.h``).  PyTorch supplies device memory, streams and
+``torch.distributed``; every computation runs in the library's own sm_100a
+kernels.  There is no CPU fallback: loading fails loudly when the library has
+not been built, and every entry point raises :class:`B200Error` on a non-zero
+status.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+from ctypes import POINTER, byref, c_char_p, c_float, c_int32, c_size_t, c_uint32, c_void_p
+from typing import Dict, Optional
+
+import torch
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(os.path.dirname(_HERE), "lib", "libb200_llama.so")
+
+F32, BF16 = 0, 1
+LEAF_ORDER = (
+    "rms_att_weight", "rms_ffn_weight", "rms_final_weight", "token_embedding_table",
+    "w1", "w2", "w3", "wcls", "wk", "wo", "wq", "wv",
+)
+CONFIG_KEYS = ("dim", "hidden_dim", "n_layers", "n_heads", "n_kv_heads", "vocab_size", "seq_len")
+
+EXPORTS = (
+    "b200_last_error", "b200_version", "b200_device_status", "b200_plan_create", "b200_plan_destroy",
+    "b200_packed_weight_bytes", "b200_pack_weights", "b200_workspace_bytes", "b200_saved_bytes", "b200_forward",
+    "b200_backward", "b200_packed_grad_bytes", "b200_unpack_grads", "b200_allreduce_f32", "b200_decode_step",
+    "b200_gemm", "b200_rmsnorm", "b200_attention", "b200_comm_unique_id", "b200_comm_init_rank",
+    "b200_comm_destroy", "b200_launch_count", "b200_profile_enable", "b200_profile_read",
+)
+
+
+class B200Error(RuntimeError):
+    def __init__(self, status: int, message: str):
+        super().__init__(f"b200 status {status}: {message}")
+        self.status = status
+
+
+class _Config(ctypes.Structure):
+    _fields_ = [(k, c_int32) for k in CONFIG_KEYS] + [("dtype", c_int32), ("rope_theta", c_float), ("rms_eps", c_float)]
+
+
+_lib = None
+
+
+def lib() -> ctypes.CDLL:
+    """Loads the CUDA library; raises if it has not been built."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise RuntimeError(
+                f"{LIB_PATH} is missing: build it with `python enzyme-jax_b200/build.py` "
+                "(there is no fallback implementation)")
+        l = ctypes.CDLL(LIB_PATH)
+        l.b200_last_error.restype = c_char_p
+        l.b200_version.restype = c_char_p
+        for name in EXPORTS:
+            fn = getattr(l, name)
+            if name not in ("b200_last_error", "b200_version"):
+                fn.restype = c_int32
+        l.b200_launch_count.restype = ctypes.c_int64
+        l.b200_profile_enable.argtypes = [c_int32]
+        l.b200_profile_read.argtypes = [c_int32, POINTER(ctypes.c_double), POINTER(ctypes.c_double),
+                                        POINTER(ctypes.c_int64)]
+        l.b200_plan_create.argtypes = [POINTER(_Config), c_int32, c_int32, c_void_p, POINTER(c_void_p)]
+        l.b200_plan_destroy.argtypes = [c_void_p]
+        l.b200_packed_weight_bytes.argtypes = [c_void_p, c_int32, POINTER(c_size_t)]
+        l.b200_packed_grad_bytes.argtypes = [c_void_p, POINTER(c_size_t)]
+        l.b200_pack_weights.argtypes = [c_void_p, POINTER(c_void_p), c_int32, c_int32, c_void_p, c_void_p]
+        l.b200_workspace_bytes.argtypes = [c_void_p, c_int32, c_int32, c_int32, POINTER(c_size_t)]
+        l.b200_saved_bytes.argtypes = [c_void_p, c_int32, c_int32, POINTER(c_size_t)]
+        l.b200_forward.argtypes = [c_void_p, c_void_p, c_int32, c_int32, c_void_p, c_void_p, c_void_p, c_void_p,
+                                   c_void_p, c_size_t, c_void_p]
+        l.b200_backward.argtypes = [c_void_p, c_void_p, c_int32, c_int32, c_void_p, c_void_p, c_void_p, c_void_p,
+                                    c_int32, c_void_p, c_size_t, c_void_p]
+        l.b200_unpack_grads.argtypes = [c_void_p, c_void_p, POINTER(c_void_p), c_void_p]
+        l.b200_allreduce_f32.argtypes = [c_void_p, c_void_p, c_size_t, c_void_p]
+        l.b200_decode_step.argtypes = [c_void_p, c_void_p, c_void_p, c_int32, c_int32, c_void_p, c_void_p, c_void_p,
+                                       c_int32, c_int32, c_int32, c_void_p, c_void_p, c_void_p, c_size_t, c_void_p]
+        l.b200_gemm.argtypes = [c_void_p, c_void_p, c_void_p] + [c_int32] * 12 + [c_void_p]
+        l.b200_rmsnorm.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int32, c_int32, c_float, c_int32,
+                                   c_void_p]
+        l.b200_attention.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p] + [c_int32] * 9 + [c_void_p]
+        l.b200_device_status.argtypes = [c_void_p, POINTER(c_uint32)]
+        l.b200_comm_unique_id.argtypes = [c_void_p]
+        l.b200_comm_init_rank.argtypes = [c_void_p, c_int32, c_int32, POINTER(c_void_p)]
+        l.b200_comm_destroy.argtypes = [c_void_p]
+        _lib = l
+    return _lib
+
+
+def check(status: int) -> None:
+    if status != 0:
+        raise B200Error(status, lib().b200_last_error().decode("utf-8", "replace"))
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
+    return None if t is None else t.data_ptr()
+
+
+def _dt(dtype: torch.dtype) -> int:
+    if dtype == torch.float32:
+        return F32
+    if dtype == torch.bfloat16:
+        return BF16
+    raise B200Error(3, f"unsupported dtype {dtype}")
+
+
+def device_status() -> int:
+    """Reads and clears the device status word (synchronises the stream)."""
+    code = c_uint32(0)
+    check(lib().b200_device_status(_stream(), byref(code)))
+    return code.value
+
+
+def launch_count() -> int:
+    return int(lib().b200_launch_count())
+
+
+PROFILE_CLASSES = ("gemm_tcgen05", "gemm_ffma", "attention_fwd", "attention_bwd", "attention_decode")
+
+
+def profile_enable(on: bool) -> None:
+    check(lib().b200_profile_enable(int(on)))
+
+
+def profile_read() -> Dict[str, Dict[str, float]]:
+    """Per kernel class: summed ms, summed algorithmic work, launches (synchronises the recorded events)."""
+    out = {}
+    for i, name in enumerate(PROFILE_CLASSES):
+        ms, work, n = ctypes.c_double(0), ctypes.c_double(0), ctypes.c_int64(0)
+        check(lib().b200_profile_read(i, byref(ms), byref(work), byref(n)))
+        out[name] = {"ms": ms.value, "work": work.value, "launches": int(n.value)}
+    return out
+
+
+# --------------------------------------------------------------------------
+# single kernels
+# --------------------------------------------------------------------------
+
+def gemm(a: torch.Tensor, b: torch.Tensor, *, ta=False, tb=False, out_dtype=None, impl=0,
+         out: Optional[torch.Tensor] = None, accumulate=False) -> torch.Tensor:
+    """Y = op(a) @ op(b)^T with fp32 accumulation.  a is [M,K] ([K,M] with ta), b is [N,K] ([K,N] with tb)."""
+    M, K = (a.shape[1], a.shape[0]) if ta else (a.shape[0], a.shape[1])
+    N = b.shape[1] if tb else b.shape[0]
+    out_dtype = out_dtype or a.dtype
+    if out is None:
+        out = torch.empty(M, N, dtype=out_dtype, device=a.device)
+    check(lib().b200_gemm(a.data_ptr(), b.data_ptr(), out.data_ptr(), M, N, K, a.stride(0), b.stride(0),
+                          out.stride(0), int(ta), int(tb), _dt(a.dtype), _dt(out.dtype), int(accumulate), impl,
+                          _stream()))
+    return out
+
+
+def rmsnorm(x: torch.Tensor, gain: torch.Tensor, eps: float = 1e-5, out_dtype=torch.float32):
+    rows, dim = x.shape
+    y = torch.empty(rows, dim, dtype=out_dtype, device=x.device)
+    rinv = torch.empty(rows, dtype=torch.float32, device=x.device)
+    check(lib().b200_rmsnorm(x.data_ptr(), gain.data_ptr(), y.data_ptr(), rinv.data_ptr(), rows, dim, eps,
+                             _dt(out_dtype), _stream()))
+    return y, rinv
+
+
+def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, batch: int, seq: int, n_heads: int, impl=0):
+    """Causal attention; q,k,v are [batch*seq, n_heads*head_size] (possibly strided row views)."""
+    T, d = q.shape
+    hs = d // n_heads
+    o = torch.empty(T, d, dtype=q.dtype, device=q.device)
+    lse = torch.empty(batch, n_heads, seq, dtype=torch.float32, device=q.device)
+    check(lib().b200_attention(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr(), batch, seq,
+                               n_heads, hs, q.stride(0), k.stride(0), o.stride(0), _dt(q.dtype), impl, _stream()))
+    return o, lse
+
+
+# --------------------------------------------------------------------------
+# communicator
+# --------------------------------------------------------------------------
+
+class Comm:
+    """NCCL communicator created from a unique id that rank 0 shares through
+    ``torch.distributed`` (any backend: the id is 128 bytes of host data)."""
+
+    def __init__(self, rank: int, world: int, group=None):
+        import torch.distributed as dist
+        ident = ctypes.create_string_buffer(128)
+        if rank == 0:
+            check(lib().b200_comm_unique_id(ident))
+        box = [ident.raw]
+        dist.broadcast_object_list(box, src=0, group=group)
+        ident = ctypes.create_string_buffer(box[0], 128)
+        handle = c_void_p()
+        check(lib().b200_comm_init_rank(ident, rank, world, byref(handle)))
+        self.handle, self.rank, self.world = handle, rank, world
+
+    def allreduce_f32(self, t: torch.Tensor) -> None:
+        check(lib().b200_allreduce_f32(self.handle, t.data_ptr(), t.numel(), _stream()))
+
+    def destroy(self) -> None:
+        if self.handle:
+            check(lib().b200_comm_destroy(self.handle))
+            self.handle = None
+
+
+# --------------------------------------------------------------------------
+# plan
+# --------------------------------------------------------------------------
+
+class Plan:
+    """A model on the current CUDA device: config, packed weights, buffers."""
+
+    def __init__(self, config: Dict[str, int], dtype: torch.dtype = torch.bfloat16, *, tp_rank: int = 0,
+                 tp_size: int = 1, comm: Optional[Comm] = None, rope_theta: float = 10000.0, rms_eps: float = 1e-5):
+        if not torch.cuda.is_available():
+            raise RuntimeError("the B200 llama path needs a CUDA device; there is no CPU implementation")
+        self.config = dict(config)
+        self.dtype = dtype
+        self.tp_rank, self.tp_size, self.comm = tp_rank, tp_size, comm
+        self.device = torch.device("cuda", torch.cuda.current_device())
+        c = _Config(*[int(config[k]) for k in CONFIG_KEYS], _dt(dtype), rope_theta, rms_eps)
+        self._h = c_void_p()
+        check(lib().b200_plan_create(byref(c), tp_rank, tp_size, comm.handle if comm else None, byref(self._h)))
+        self.packed: Optional[torch.Tensor] = None
+        self.with_transposed = False
+        self._ws: Optional[torch.Tensor] = None
+        self.vocab_local = config["vocab_size"] // tp_size
+        self.d_local = config["dim"] // tp_size
+
+    def close(self) -> None:
+        if self._h:
+            lib().b200_plan_destroy(self._h)
+            self._h = c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    # ---- buffers ---------------------------------------------------------
+    def _bytes(self, fn, *args) -> int:
+        n = c_size_t(0)
+        check(fn(self._h, *args, byref(n)))
+        return n.value
+
+    def workspace(self, mode: int, batch: int, seq: int) -> torch.Tensor:
+        need = self._bytes(lib().b200_workspace_bytes, mode, batch, seq)
+        if self._ws is None or self._ws.numel() < need:
+            self._ws = None
+            self._ws = torch.empty(need, dtype=torch.uint8, device=self.device)
+        return self._ws
+
+    def saved_bytes(self, batch: int, seq: int) -> int:
+        return self._bytes(lib().b200_saved_bytes, batch, seq)
+
+    def grad_bytes(self) -> int:
+        return self._bytes(lib().b200_packed_grad_bytes)
+
+    # ---- weights ---------------------------------------------------------
+    def pack_weights(self, weights: Dict[str, torch.Tensor], with_transposed: bool = False) -> None:
+        """``weights``: the reference's weight dict (full, unsharded leaves) on this device."""
+        leaves = []
+        dts = set()
+        for name in LEAF_ORDER:
+            t = weights[name]
+            if not t.is_cuda or not t.is_contiguous():
+                raise B200Error(1, f"leaf {name} must be a contiguous CUDA tensor")
+            leaves.append(t)
+            dts.add(t.dtype)
+        if len(dts) != 1:
+            raise B200Error(3, "all leaves must share one dtype")
+        n = self._bytes(lib().b200_packed_weight_bytes, int(with_transposed))
+        self.packed = torch.empty(n, dtype=torch.uint8, device=self.device)
+        arr = (c_void_p * len(leaves))(*[t.data_ptr() for t in leaves])
+        check(lib().b200_pack_weights(self._h, arr, _dt(dts.pop()), int(with_transposed), self.packed.data_ptr(),
+                                      _stream()))
+        self.with_transposed = with_transposed
+
+    # ---- forward / backward ---------------------------------------------
+    def forward(self, tokens: torch.Tensor, *, saved: Optional[torch.Tensor] = None,
+                kv_out: Optional[torch.Tensor] = None, logits: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """tokens int32 [B,S] on the device -> fp32 logits [B,S,V/tp]."""
+        B, S = tokens.shape
+        if tokens.dtype != torch.int32 or not tokens.is_cuda:
+            raise B200Error(3, "tokens must be an int32 CUDA tensor")
+        if logits is None:
+            logits = torch.empty(B, S, self.vocab_local, dtype=torch.float32, device=self.device)
+        ws = self.workspace(1 if saved is not None else 0, B, S)
+        check(lib().b200_forward(self._h, tokens.data_ptr(), B, S, self.packed.data_ptr(), logits.data_ptr(),
+                                 _ptr(saved), _ptr(kv_out), ws.data_ptr(), ws.numel(), _stream()))
+        return logits
+
+    def new_saved(self, batch: int, seq: int) -> torch.Tensor:
+        return torch.empty(self.saved_bytes(batch, seq), dtype=torch.uint8, device=self.device)
+
+    def new_grads(self) -> torch.Tensor:
+        return torch.zeros(self.grad_bytes() // 4, dtype=torch.float32, device=self.device)
+
+    def backward(self, tokens: torch.Tensor, dlogits: torch.Tensor, saved: torch.Tensor, grads: torch.Tensor,
+                 accumulate: bool = False) -> torch.Tensor:
+        if not self.with_transposed:
+            raise B200Error(1, "backward needs weights packed with with_transposed=True")
+        B, S = tokens.shape
+        ws = self.workspace(2, B, S)
+        check(lib().b200_backward(self._h, tokens.data_ptr(), B, S, self.packed.data_ptr(), dlogits.data_ptr(),
+                                  saved.data_ptr(), grads.data_ptr(), int(accumulate), ws.data_ptr(), ws.numel(),
+                                  _stream()))
+        return grads
+
+    def unpack_grads(self, grads: torch.Tensor) -> Dict[str, torch.Tensor]:
+        cfg = self.config
+        L, d, h, V = cfg["n_layers"], cfg["dim"], cfg["hidden_dim"], cfg["vocab_size"]
+        shapes = {
+            "rms_att_weight": (L, d), "rms_ffn_weight": (L, d), "rms_final_weight": (d,),
+            "token_embedding_table": (V, d), "w1": (L, h, d), "w2": (L, d, h), "w3": (L, h, d), "wcls": (V, d),
+            "wk": (L, d, d), "wo": (L, d, d), "wq": (L, d, d), "wv": (L, d, d),
+        }
+        out = {k: torch.empty(shapes[k], dtype=torch.float32, device=self.device) for k in LEAF_ORDER}
+        arr = (c_void_p * len(LEAF_ORDER))(*[out[k].data_ptr() for k in LEAF_ORDER])
+        check(lib().b200_unpack_grads(self._h, grads.data_ptr(), arr, _stream()))
+        return out
+
+    # ---- decode ----------------------------------------------------------
+    def new_kv_pages(self, n_pages: int, page_size: int) -> torch.Tensor:
+        L = self.config["n_layers"]
+        return torch.zeros(L, 2, n_pages, page_size, self.d_local, dtype=self.dtype, device=self.device)
+
+    def decode_step(self, pos: int, kv_pages: torch.Tensor, page_table: torch.Tensor, *,
+                    tokens: Optional[torch.Tensor] = None, x: Optional[torch.Tensor] = None,
+                    want_hidden: bool = False, want_logits: bool = True,
+                    logits: Optional[torch.Tensor] = None):
+        B = (tokens if tokens is not None else x).shape[0]
+        n_pages, page_size = kv_pages.shape[2], kv_pages.shape[3]
+        hidden = torch.empty(B, self.config["dim"], dtype=torch.float32, device=self.device) if want_hidden else None
+        if want_logits and logits is None:
+            logits = torch.empty(B, self.vocab_local, dtype=torch.float32, device=self.device)
+        ws = self.workspace(3, B, pos + 1)
+        check(lib().b200_decode_step(self._h, _ptr(tokens), _ptr(x), B, pos, self.packed.data_ptr(),
+                                     kv_pages.data_ptr(), page_table.data_ptr(), n_pages, page_size,
+                                     page_table.shape[1], _ptr(hidden), _ptr(logits) if want_logits else None,
+                                     ws.data_ptr(), ws.numel(), _stream()))
+        return hidden, (logits if want_logits else None)

@@ -1,0 +1,191 @@
+// Decode attention over the paged KV cache: one query row per (sequence, head)
+// against `ctx` cached rows (test/llama.py:177-209 of the reference, where the
+// cache holds pos rows plus the new one).
+//
+// Pass 1: CTA (split, head, sequence) of 4 warps walks its slice of the context
+// 32 keys at a time per warp.  For q.k each lane owns one key and streams that
+// key's row in 16-byte pieces; for p.v the lanes own head dimensions and the
+// probabilities are broadcast by shuffle.  Each CTA leaves (acc[hs], max, sum)
+// in scratch.  Pass 2 merges the splits.  HBM-bound: every cached byte is read
+// exactly once per step.
+#include "attention.cuh"
+
+namespace b200 {
+
+namespace {
+
+constexpr int DW = 4;  // warps per CTA
+
+template <typename T>
+__device__ __forceinline__ const T* page_row(const T* base, const int32_t* table, int u, int page_size, int d_local) {
+  const int page = table[u / page_size];
+  return base + ((size_t)page * page_size + (u % page_size)) * d_local;
+}
+
+template <typename T, int HS>
+__global__ void __launch_bounds__(DW * 32)
+    attn_decode_kernel(const T* __restrict__ q, const T* __restrict__ kpages, const T* __restrict__ vpages,
+                       const int32_t* __restrict__ page_table, float* __restrict__ scratch, int ctx, int n_heads,
+                       int ldq, int page_size, int max_pages, int d_local, int n_splits, float scale) {
+  constexpr int DPL = (HS + 31) / 32;  // head dims per lane in the p.v phase
+  __shared__ float qs[HS];
+  __shared__ float part_acc[DW][HS];
+  __shared__ float part_m[DW], part_l[DW];
+  const int split = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int32_t* table = page_table + (size_t)b * max_pages;
+  for (int i = threadIdx.x; i < HS; i += blockDim.x) qs[i] = to_f32(q[(size_t)b * ldq + h * HS + i]) * scale;
+  __syncthreads();
+
+  const int per = (ctx + n_splits - 1) / n_splits;
+  const int c0 = split * per, c1 = min(ctx, c0 + per);
+  float m = -INFINITY, l = 0.f, acc[DPL];
+#pragma unroll
+  for (int i = 0; i < DPL; ++i) acc[i] = 0.f;
+
+  for (int u0 = c0 + warp * 32; u0 < c1; u0 += DW * 32) {
+    const int u = u0 + lane;
+    float s = -INFINITY;
+    if (u < c1) {
+      const T* kr = page_row(kpages, table, u, page_size, d_local) + h * HS;
+      float d = 0.f;
+#pragma unroll
+      for (int e = 0; e < HS; e += 8) {
+        float kv[8];
+        load8(kr + e, kv);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) d = fmaf(qs[e + i], kv[i], d);
+      }
+      s = d;
+    }
+    const float bm = warp_max(s);
+    const float nm = fmaxf(m, bm);
+    const float corr = __expf(m - nm);
+    const float p = (u < c1) ? __expf(s - nm) : 0.f;
+    l = l * corr + warp_sum(p);
+#pragma unroll
+    for (int i = 0; i < DPL; ++i) acc[i] *= corr;
+    const int n = min(32, c1 - u0);
+    for (int j = 0; j < n; ++j) {
+      const float pj = __shfl_sync(0xffffffffu, p, j);
+      const T* vr = page_row(vpages, table, u0 + j, page_size, d_local) + h * HS;
+#pragma unroll
+      for (int i = 0; i < DPL; ++i) {
+        const int e = lane + 32 * i;
+        if (e < HS) acc[i] = fmaf(pj, to_f32(vr[e]), acc[i]);
+      }
+    }
+    m = nm;
+  }
+  // merge the warps of this CTA
+#pragma unroll
+  for (int i = 0; i < DPL; ++i) {
+    const int e = lane + 32 * i;
+    if (e < HS) part_acc[warp][e] = acc[i];
+  }
+  if (lane == 0) { part_m[warp] = m; part_l[warp] = l; }
+  __syncthreads();
+  float gm = -INFINITY;
+#pragma unroll
+  for (int w = 0; w < DW; ++w) gm = fmaxf(gm, part_m[w]);
+  float* out = scratch + (((size_t)b * n_heads + h) * n_splits + split) * (HS + 2);
+  for (int e = threadIdx.x; e < HS; e += blockDim.x) {
+    float a = 0.f;
+#pragma unroll
+    for (int w = 0; w < DW; ++w)
+      if (part_m[w] > -INFINITY) a += part_acc[w][e] * __expf(part_m[w] - gm);
+    out[e] = a;
+  }
+  if (threadIdx.x == 0) {
+    float gl = 0.f;
+#pragma unroll
+    for (int w = 0; w < DW; ++w)
+      if (part_m[w] > -INFINITY) gl += part_l[w] * __expf(part_m[w] - gm);
+    out[HS] = gm;
+    out[HS + 1] = gl;
+  }
+}
+
+template <typename T, int HS>
+__global__ void attn_decode_combine_kernel(const float* __restrict__ scratch, T* __restrict__ o, int n_heads, int ldo,
+                                           int n_splits) {
+  const int h = blockIdx.x, b = blockIdx.y;
+  const float* base = scratch + ((size_t)b * n_heads + h) * n_splits * (HS + 2);
+  float gm = -INFINITY;
+  for (int s = 0; s < n_splits; ++s) gm = fmaxf(gm, base[(size_t)s * (HS + 2) + HS]);
+  float gl = 0.f;
+  for (int s = 0; s < n_splits; ++s) {
+    const float ms = base[(size_t)s * (HS + 2) + HS];
+    if (ms > -INFINITY) gl += base[(size_t)s * (HS + 2) + HS + 1] * __expf(ms - gm);
+  }
+  for (int e = threadIdx.x; e < HS; e += blockDim.x) {
+    float a = 0.f;
+    for (int s = 0; s < n_splits; ++s) {
+      const float ms = base[(size_t)s * (HS + 2) + HS];
+      if (ms > -INFINITY) a += base[(size_t)s * (HS + 2) + e] * __expf(ms - gm);
+    }
+    o[(size_t)b * ldo + h * HS + e] = from_f32<T>(a / gl);
+  }
+}
+
+template <typename T, int HS>
+int32_t launch_hs(const AttnDecodeArgs& a, cudaStream_t stream) {
+  const size_t page_elems = (size_t)a.n_pages * a.page_size * a.d_local;
+  const T* kp = reinterpret_cast<const T*>(a.kv_pages);
+  const T* vp = kp + page_elems;
+  dim3 grid(a.n_splits, a.n_heads, a.batch);
+  attn_decode_kernel<T, HS><<<grid, DW * 32, 0, stream>>>((const T*)a.q, kp, vp, a.page_table, a.scratch, a.ctx,
+                                                          a.n_heads, a.ldq, a.page_size, a.max_pages, a.d_local,
+                                                          a.n_splits, 1.f / sqrtf((float)HS));
+  B200_LAUNCH_OK("attn_decode_kernel");
+  dim3 grid2(a.n_heads, a.batch);
+  attn_decode_combine_kernel<T, HS><<<grid2, HS < 32 ? 32 : HS, 0, stream>>>(a.scratch, (T*)a.o, a.n_heads, a.ldo,
+                                                                             a.n_splits);
+  B200_LAUNCH_OK("attn_decode_combine_kernel");
+  return B200_OK;
+}
+
+template <typename T>
+int32_t launch_t(const AttnDecodeArgs& a, cudaStream_t stream) {
+  switch (a.head_size) {
+    case 16: return launch_hs<T, 16>(a, stream);
+    case 32: return launch_hs<T, 32>(a, stream);
+    case 48: return launch_hs<T, 48>(a, stream);
+    case 64: return launch_hs<T, 64>(a, stream);
+    case 128: return launch_hs<T, 128>(a, stream);
+  }
+  return fail(B200_ERR_BAD_SHAPE, "decode attention: head size %d is not one of 16/32/48/64/128", a.head_size);
+}
+
+}  // namespace
+
+size_t decode_scratch_floats(int batch, int n_heads, int head_size, int n_splits) {
+  return (size_t)batch * n_heads * n_splits * (head_size + 2);
+}
+
+int decode_pick_splits(int batch, int n_heads, int ctx) {
+  const int want = 2 * sm_count();
+  int s = cdiv(want, batch * n_heads);
+  const int max_s = ctx / 128 > 0 ? ctx / 128 : 1;
+  if (s > max_s) s = max_s;
+  if (s < 1) s = 1;
+  if (s > 64) s = 64;
+  return s;
+}
+
+int32_t launch_attn_decode(const AttnDecodeArgs& a, cudaStream_t stream) {
+  if (a.batch <= 0 || a.ctx <= 0 || a.n_heads <= 0 || a.n_splits <= 0)
+    return fail(B200_ERR_BAD_SHAPE, "decode attention: empty problem");
+  if (a.d_local % 8 || a.head_size % 8) return fail(B200_ERR_BAD_SHAPE, "decode attention: row width must be a multiple of 8");
+  if (cdiv(a.ctx, a.page_size) > a.max_pages)
+    return fail(B200_ERR_BAD_SHAPE, "decode attention: context %d needs more than %d pages of %d rows", a.ctx,
+                a.max_pages, a.page_size);
+  if (!a.scratch) return fail(B200_ERR_INVALID_ARG, "decode attention: scratch is null");
+  const double es = a.dtype == B200_BF16 ? 2.0 : 4.0;
+  ProfScope prof(PROF_ATTN_DECODE, 2.0 * a.batch * (double)a.ctx * a.n_heads * a.head_size * es, stream);
+  if (a.dtype == B200_F32) return launch_t<float>(a, stream);
+  if (a.dtype == B200_BF16) return launch_t<bf16>(a, stream);
+  return fail(B200_ERR_BAD_DTYPE, "decode attention: unsupported dtype %d", a.dtype);
+}
+
+}  // namespace b200

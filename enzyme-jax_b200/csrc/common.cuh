@@ -1,0 +1,124 @@
+// Shared helpers for the llama path kernels: status/error plumbing, numeric
+// type traits, vector loads, warp reductions.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+
+#include "../../include/b200_llama.h"
+
+namespace b200 {
+
+// ---- host-side error plumbing --------------------------------------------
+void set_error(const char* fmt, ...);
+int32_t fail(int32_t code, const char* fmt, ...);
+
+#define B200_CUDA_OK(expr)                                                              \
+  do {                                                                                  \
+    cudaError_t _e = (expr);                                                            \
+    if (_e != cudaSuccess)                                                              \
+      return ::b200::fail(B200_ERR_CUDA, "%s failed: %s (%s:%d)", #expr,                \
+                          cudaGetErrorString(_e), __FILE__, __LINE__);                  \
+  } while (0)
+
+#define B200_LAUNCH_OK(name)                                                            \
+  do {                                                                                  \
+    ::b200::count_launch();                                                             \
+    cudaError_t _e = cudaGetLastError();                                                \
+    if (_e != cudaSuccess)                                                              \
+      return ::b200::fail(B200_ERR_CUDA, "launch of %s failed: %s", name,               \
+                          cudaGetErrorString(_e));                                      \
+  } while (0)
+
+#define B200_TRY(expr)                  \
+  do {                                  \
+    int32_t _s = (expr);                \
+    if (_s != B200_OK) return _s;       \
+  } while (0)
+
+void count_launch();
+
+// Event-pair profiling of kernel classes (off unless enabled through the ABI).
+enum ProfClass : int { PROF_GEMM_TC = 0, PROF_GEMM_SIMT = 1, PROF_ATTN_FWD = 2, PROF_ATTN_BWD = 3, PROF_ATTN_DECODE = 4, PROF_NUM = 5 };
+struct ProfScope {
+  int slot = -1;
+  cudaStream_t stream;
+  ProfScope(int cls, double work, cudaStream_t s);
+  ~ProfScope();
+};
+
+// Device word that kernels with bounded waits OR their failure code into.
+uint32_t* device_status_word();  // lazily allocated per device, never on a hot path
+
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
+inline int cdiv(int a, int b) { return (a + b - 1) / b; }
+int sm_count();
+
+// ---- numeric helpers -------------------------------------------------------
+using bf16 = __nv_bfloat16;
+
+template <typename T> struct DTypeOf;
+template <> struct DTypeOf<float> { static constexpr int value = B200_F32; };
+template <> struct DTypeOf<bf16> { static constexpr int value = B200_BF16; };
+
+__device__ __forceinline__ float to_f32(float v) { return v; }
+__device__ __forceinline__ float to_f32(bf16 v) { return __bfloat162float(v); }
+template <typename T> __device__ __forceinline__ T from_f32(float v);
+template <> __device__ __forceinline__ float from_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ bf16 from_f32<bf16>(float v) { return __float2bfloat16_rn(v); }
+
+// Loads 8 consecutive elements as fp32 (16 B for bf16, 32 B for fp32).
+__device__ __forceinline__ void load8(const float* p, float (&v)[8]) {
+  float4 a = *reinterpret_cast<const float4*>(p);
+  float4 b = *reinterpret_cast<const float4*>(p + 4);
+  v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+}
+__device__ __forceinline__ void load8(const bf16* p, float (&v)[8]) {
+  uint4 raw = *reinterpret_cast<const uint4*>(p);
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    float2 f = __bfloat1622float2(h[i]);
+    v[2 * i] = f.x;
+    v[2 * i + 1] = f.y;
+  }
+}
+__device__ __forceinline__ void store8(float* p, const float (&v)[8]) {
+  *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+  *reinterpret_cast<float4*>(p + 4) = make_float4(v[4], v[5], v[6], v[7]);
+}
+__device__ __forceinline__ void store8(bf16* p, const float (&v)[8]) {
+  uint4 raw;
+  __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&raw);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+  *reinterpret_cast<uint4*>(p) = raw;
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// Block-wide sum for blocks of up to 1024 threads; `red` is 32 floats of shared memory.
+__device__ __forceinline__ float block_sum(float v, float* red) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+  v = warp_sum(v);
+  __syncthreads();
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  float t = (lane < nw) ? red[lane] : 0.f;
+  t = warp_sum(t);
+  return t;
+}
+
+}  // namespace b200

@@ -1,0 +1,287 @@
+// tcgen05 / TMEM GEMM for sm_100a:  Y[M,N] = A[M,K] * B[N,K]^T, bf16 operands,
+// fp32 accumulation in tensor memory, fused epilogues.
+//
+// One persistent CTA per SM walks output tiles of 128 x BN.  Warp roles:
+//   warp 0      TMA producer: cp.async.bulk.tensor 2-D boxes (64 K-elements =
+//               128 B wide, 128-byte swizzle) of A and B into a ring of stages
+//   warp 1      allocates TMEM; one lane issues tcgen05.mma (128 x BN x 16 per
+//               instruction) from shared-memory descriptors into one of two
+//               TMEM accumulators and commits to mbarriers
+//   warps 2..5  epilogue: tcgen05.ld the finished accumulator (lane = row),
+//               apply the fused epilogue, store; runs while the next tile's
+//               main loop fills the other accumulator
+// All waits are bounded; a wait that runs out sets the device status word and
+// the CTA unwinds (frees TMEM, returns).
+#include <cuda.h>
+
+#include <mutex>
+
+#include "gemm_epilogue.cuh"
+#include "ptx_sm100.cuh"
+
+namespace b200 {
+
+namespace {
+
+constexpr int TBM = 128;      // tile rows (TMEM lanes)
+constexpr int TBK = 64;       // K elements per stage (128 bytes of bf16)
+constexpr int UMMA_K = 16;    // K per tcgen05.mma for 16-bit operands
+constexpr int TC_THREADS = 192;
+
+template <int BN> struct TcCfg {
+  static constexpr int kStages = (BN >= 256) ? 4 : 6;
+  static constexpr int kABytes = TBM * TBK * 2;
+  static constexpr int kBBytes = BN * TBK * 2;
+  static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kTmemCols = 2 * BN;
+  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
+};
+
+enum : uint32_t {
+  ST_PRODUCER_TIMEOUT = 1u << 0,
+  ST_MMA_TIMEOUT = 1u << 1,
+  ST_EPILOGUE_TIMEOUT = 1u << 2,
+};
+
+template <int BN, int KIND, typename TOut>
+__global__ void __launch_bounds__(TC_THREADS, 1)
+    gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, int M, int N,
+                   int K, EpiParams ep, uint32_t* status) {
+  using Cfg = TcCfg<BN>;
+  constexpr int S = Cfg::kStages;
+  extern __shared__ uint8_t smem_raw[];
+  // Stage buffers must sit on 1024-byte boundaries for the 128-byte swizzle.
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + S * Cfg::kStageBytes);
+  uint64_t* full_bar = bars;                 // [S]   TMA bytes landed
+  uint64_t* empty_bar = bars + S;            // [S]   MMAs reading the stage are done
+  uint64_t* acc_full = bars + 2 * S;         // [2]   accumulator complete
+  uint64_t* acc_empty = bars + 2 * S + 2;    // [2]   accumulator drained by the epilogue
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * S + 4);
+  volatile uint32_t* abort_flag = tmem_slot + 1;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int m_tiles = (M + TBM - 1) / TBM;
+  const int n_tiles = (N + BN - 1) / BN;
+  const int num_tiles = m_tiles * n_tiles;
+  const int num_kb = (K + TBK - 1) / TBK;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < S; ++i) {
+      ptx::mbar_init(&full_bar[i], 1);
+      ptx::mbar_init(&empty_bar[i], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      ptx::mbar_init(&acc_full[i], 1);
+      ptx::mbar_init(&acc_empty[i], 4);
+    }
+    *abort_flag = 0u;
+    ptx::fence_barrier_init();
+    ptx::tma_prefetch_desc(&tmA);
+    ptx::tma_prefetch_desc(&tmB);
+  }
+  if (warp == 1) {
+    ptx::tmem_alloc(tmem_slot, Cfg::kTmemCols);
+    ptx::tmem_relinquish();
+  }
+  ptx::tc_fence_before_sync();
+  __syncthreads();
+  ptx::tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        const int m0 = (tile % m_tiles) * TBM, n0 = (tile / m_tiles) * BN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          ok = ptx::mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag, status, ST_PRODUCER_TIMEOUT);
+          if (!ok) break;
+          uint8_t* sa = smem + stage * Cfg::kStageBytes;
+          ptx::mbar_arrive_expect_tx(&full_bar[stage], Cfg::kStageBytes);
+          ptx::tma_load_2d(sa, &tmA, kb * TBK, m0, &full_bar[stage]);
+          ptx::tma_load_2d(sa + Cfg::kABytes, &tmB, kb * TBK, n0, &full_bar[stage]);
+          if (++stage == S) { stage = 0; phase ^= 1u; }
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc = ptx::idesc_bf16_f32(TBM, BN);
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        ok = ptx::mbar_wait(&acc_empty[acc], acc_phase ^ 1u, abort_flag, status, ST_MMA_TIMEOUT);
+        if (!ok) break;
+        ptx::tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
+        for (int kb = 0; kb < num_kb; ++kb) {
+          ok = ptx::mbar_wait(&full_bar[stage], phase, abort_flag, status, ST_MMA_TIMEOUT);
+          if (!ok) break;
+          ptx::tc_fence_after_sync();
+          const uint32_t sa = ptx::smem_u32(smem + stage * Cfg::kStageBytes);
+          const uint64_t adesc = ptx::smem_desc_sw128(sa);
+          const uint64_t bdesc = ptx::smem_desc_sw128(sa + Cfg::kABytes);
+#pragma unroll
+          for (int k = 0; k < TBK / UMMA_K; ++k) {
+            // advancing K by 16 elements = 32 bytes = 2 units of the encoded start address
+            ptx::mma_bf16_ss(d_tmem, adesc + (uint64_t)(2 * k), bdesc + (uint64_t)(2 * k), idesc,
+                             (kb > 0 || k > 0) ? 1u : 0u);
+          }
+          ptx::mma_commit(&empty_bar[stage]);
+          if (++stage == S) { stage = 0; phase ^= 1u; }
+        }
+        if (!ok) break;
+        ptx::mma_commit(&acc_full[acc]);
+        acc ^= 1;
+        if (acc == 0) acc_phase ^= 1u;
+      }
+    }
+    __syncwarp();
+  } else {
+    const int q = warp & 3;  // TMEM lane quarter this warp may read
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+      const int m0 = (tile % m_tiles) * TBM, n0 = (tile / m_tiles) * BN;
+      ok = ptx::mbar_wait(&acc_full[acc], acc_phase, abort_flag, status, ST_EPILOGUE_TIMEOUT);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      ptx::tc_fence_after_sync();
+      const int m = m0 + q * 32 + lane;
+      const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN);
+#pragma unroll 2
+      for (int c = 0; c < BN; c += 16) {
+        float v[16];
+        ptx::tmem_ld16(taddr + (uint32_t)c, v);
+        ptx::tmem_ld_wait();
+        if (m < M && n0 + c < N) epi_apply16<KIND, TOut>(ep, m, n0 + c, v);
+      }
+      ptx::tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) ptx::mbar_arrive(&acc_empty[acc]);
+      acc ^= 1;
+      if (acc == 0) acc_phase ^= 1u;
+    }
+  }
+
+  ptx::tc_fence_before_sync();
+  __syncthreads();
+  if (*abort_flag) {
+    // Give copies that may still be in flight time to land before the CTA's
+    // shared memory is released.
+    for (int i = 0; i < 1000; ++i) __nanosleep(1000);
+  }
+  if (warp == 1) {
+    ptx::tc_fence_after_sync();
+    ptx::tmem_dealloc(tmem_base, Cfg::kTmemCols);
+  }
+}
+
+// ---- host side ---------------------------------------------------------------
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  });
+  return fn;
+}
+
+// 2-D bf16 row-major [rows, cols] with leading dimension ld; box = 64 x box_rows.
+int32_t make_map(CUtensorMap* map, const void* base, int rows, int cols, int ld, int box_rows) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return fail(B200_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+  cuuint32_t box[2] = {(cuuint32_t)TBK, (cuuint32_t)box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(B200_ERR_CUDA, "cuTensorMapEncodeTiled failed with %d", (int)r);
+  return B200_OK;
+}
+
+template <int BN, int KIND, typename TOut>
+int32_t launch_cfg(const GemmArgs& g, cudaStream_t stream) {
+  using Cfg = TcCfg<BN>;
+  CUtensorMap tmA, tmB;
+  B200_TRY(make_map(&tmA, g.A, g.M, g.K, g.lda, TBM));
+  B200_TRY(make_map(&tmB, g.B, g.N, g.K, g.ldb, BN));
+  auto kern = gemm_tc_kernel<BN, KIND, TOut>;
+  static bool attr_set = false;  // per instantiation
+  if (!attr_set) {
+    B200_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
+    attr_set = true;
+  }
+  const int tiles = cdiv(g.M, TBM) * cdiv(g.N, BN);
+  const int grid = tiles < sm_count() ? tiles : sm_count();
+  kern<<<grid, TC_THREADS, Cfg::kSmemBytes, stream>>>(tmA, tmB, g.M, g.N, g.K, g.epi, device_status_word());
+  B200_LAUNCH_OK("gemm_tc_kernel");
+  return B200_OK;
+}
+
+template <int KIND, typename TOut>
+int32_t launch_bn(const GemmArgs& g, cudaStream_t stream) {
+  // Wide tiles when they still fill the machine, narrower ones otherwise.
+  const int sms = sm_count();
+  const long t256 = (long)cdiv(g.M, TBM) * cdiv(g.N, 256);
+  if (g.N % 256 == 0 && t256 >= 2L * sms) return launch_cfg<256, KIND, TOut>(g, stream);
+  const long t128 = (long)cdiv(g.M, TBM) * cdiv(g.N, 128);
+  if (t128 >= sms || g.N >= 128) return launch_cfg<128, KIND, TOut>(g, stream);
+  return launch_cfg<64, KIND, TOut>(g, stream);
+}
+
+template <typename TOut>
+int32_t launch_kind(const GemmArgs& g, cudaStream_t stream) {
+  switch (g.kind) {
+    case EPI_STORE: return launch_bn<EPI_STORE, TOut>(g, stream);
+    case EPI_ROPE: return launch_bn<EPI_ROPE, TOut>(g, stream);
+    case EPI_RESID: return launch_bn<EPI_RESID, TOut>(g, stream);
+    case EPI_SWIGLU: return launch_bn<EPI_SWIGLU, TOut>(g, stream);
+  }
+  return fail(B200_ERR_INVALID_ARG, "unknown epilogue kind %d", g.kind);
+}
+
+}  // namespace
+
+bool gemm_tc_supports(const GemmArgs& g) {
+  return g.in_dtype == B200_BF16 && !g.ta && !g.tb && g.M > 0 && g.N > 0 && g.K > 0 && g.N % 16 == 0 &&
+         g.lda % 8 == 0 && g.ldb % 8 == 0 && g.K % 8 == 0 && aligned16(g.A) && aligned16(g.B) &&
+         aligned16(g.epi.out) && g.epi.ldo % 8 == 0;
+}
+
+int32_t launch_gemm_tc(const GemmArgs& g, cudaStream_t stream) {
+  if (!gemm_tc_supports(g))
+    return fail(B200_ERR_UNSUPPORTED,
+                "tcgen05 gemm needs bf16 K-major operands, 16-byte aligned rows and N %% 16 == 0 (M=%d N=%d K=%d)",
+                g.M, g.N, g.K);
+  if (g.out_dtype == B200_BF16) return launch_kind<bf16>(g, stream);
+  if (g.out_dtype == B200_F32) return launch_kind<float>(g, stream);
+  return fail(B200_ERR_BAD_DTYPE, "gemm: unsupported output dtype %d", g.out_dtype);
+}
+
+int32_t launch_gemm(const GemmArgs& g, int impl, cudaStream_t stream) {
+  const bool tc = impl == 1 || (impl != 2 && gemm_tc_supports(g));
+  ProfScope prof(tc ? PROF_GEMM_TC : PROF_GEMM_SIMT, 2.0 * g.M * (double)g.N * g.K, stream);
+  return tc ? launch_gemm_tc(g, stream) : launch_gemm_simt(g, stream);
+}
+
+}  // namespace b200

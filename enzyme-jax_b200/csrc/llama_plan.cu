@@ -1,0 +1,484 @@
+// Host side of the llama path: error plumbing, plan creation, packed weight
+// layout, and the forward kernel sequence (test/llama.py:35-238 of the
+// reference, applied to whole sequences).
+#include <stdarg.h>
+#include <stdlib.h>
+#include <string.h>
+
+#include <atomic>
+#include <mutex>
+#include <vector>
+
+#include "attention.cuh"
+#include "elementwise.cuh"
+#include "gemm_epilogue.cuh"
+#include "plan.cuh"
+
+namespace b200 {
+
+// ---- errors -------------------------------------------------------------------
+static thread_local char g_err[512] = "";
+
+void set_error(const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof(g_err), fmt, ap);
+  va_end(ap);
+}
+
+int32_t fail(int32_t code, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof(g_err), fmt, ap);
+  va_end(ap);
+  return code;
+}
+
+int env_int(const char* name, int dflt) {
+  const char* v = getenv(name);
+  return (v && *v) ? atoi(v) : dflt;
+}
+
+// ---- launch counter and event profiler -----------------------------------------
+static std::atomic<long long> g_launches{0};
+void count_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
+
+struct ProfSample { cudaEvent_t a, b; int cls; double work; };
+static std::mutex g_prof_mu;
+static std::vector<ProfSample> g_prof;
+static size_t g_prof_used = 0;
+static std::atomic<int> g_prof_on{0};
+
+ProfScope::ProfScope(int cls, double work, cudaStream_t s) : stream(s) {
+  if (!g_prof_on.load(std::memory_order_relaxed)) return;
+  std::lock_guard<std::mutex> lk(g_prof_mu);
+  if (g_prof_used == g_prof.size()) {
+    ProfSample ps;
+    if (cudaEventCreate(&ps.a) != cudaSuccess || cudaEventCreate(&ps.b) != cudaSuccess) return;
+    g_prof.push_back(ps);
+  }
+  slot = (int)g_prof_used++;
+  g_prof[slot].cls = cls;
+  g_prof[slot].work = work;
+  cudaEventRecord(g_prof[slot].a, stream);
+}
+ProfScope::~ProfScope() {
+  if (slot < 0) return;
+  std::lock_guard<std::mutex> lk(g_prof_mu);
+  cudaEventRecord(g_prof[slot].b, stream);
+}
+
+// ---- per-device state ---------------------------------------------------------
+static std::mutex g_mu;
+static uint32_t* g_status[64] = {nullptr};
+static int g_sms[64] = {0};
+
+uint32_t* device_status_word() {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  std::lock_guard<std::mutex> lk(g_mu);
+  if (!g_status[dev]) {
+    uint32_t* p = nullptr;
+    if (cudaMalloc(&p, 256) != cudaSuccess) return nullptr;
+    cudaMemset(p, 0, 256);
+    g_status[dev] = p;
+  }
+  return g_status[dev];
+}
+
+int sm_count() {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+  if (!g_sms[dev]) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+    g_sms[dev] = n;
+  }
+  return g_sms[dev];
+}
+
+// ---- layouts --------------------------------------------------------------------
+void build_layout(const B200Plan& p, size_t es, bool with_t, PackedLayout* out) {
+  Arena a(nullptr);
+  auto take = [&](size_t bytes) { size_t off = a.used; a.take(bytes); return off; };
+  out->layer.assign(p.L, LayerOffsets{});
+  out->g_att = take((size_t)p.L * p.d * 4);
+  out->g_ffn = take((size_t)p.L * p.d * 4);
+  out->g_final = take((size_t)p.d * 4);
+  out->emb = take((size_t)p.V * p.d * es);
+  for (int l = 0; l < p.L; ++l) {
+    LayerOffsets& o = out->layer[l];
+    o.wqkv = take((size_t)3 * p.d_loc * p.d * es);
+    o.wo = take((size_t)p.d * p.d_loc * es);
+    o.w13 = take((size_t)2 * p.h_loc * p.d * es);
+    o.w2 = take((size_t)p.d * p.h_loc * es);
+  }
+  out->wcls = take((size_t)p.V_loc * p.d * es);
+  if (with_t) {
+    for (int l = 0; l < p.L; ++l) {
+      LayerOffsets& o = out->layer[l];
+      o.wqkv_t = take((size_t)3 * p.d_loc * p.d * es);
+      o.wo_t = take((size_t)p.d * p.d_loc * es);
+      o.w13_t = take((size_t)2 * p.h_loc * p.d * es);
+      o.w2_t = take((size_t)p.d * p.h_loc * es);
+    }
+    out->wcls_t = take((size_t)p.V_loc * p.d * es);
+  }
+  out->total = a.used;
+}
+
+void carve_forward(const B200Plan& p, Arena& a, int B, int S, bool keep, FwdActs* out) {
+  const size_t T = (size_t)B * S, es = p.esize;
+  out->layer.assign(p.L, LayerActs{});
+  auto carve_one = [&](LayerActs& la, float* x_in) {
+    la.x_in = x_in ? x_in : a.take<float>(T * p.d * 4);
+    la.xb = a.take(T * p.d * es);
+    la.rinv1 = a.take<float>(T * 4);
+    la.qkv = a.take(T * 3 * p.d_loc * es);
+    la.o = a.take(T * p.d_loc * es);
+    la.lse = a.take<float>((size_t)B * p.H_loc * S * 4);
+    la.xb2 = a.take(T * p.d * es);
+    la.rinv2 = a.take<float>(T * 4);
+    la.hg = a.take(T * p.h_loc * es);
+  };
+  if (!keep) {
+    LayerActs la;
+    carve_one(la, nullptr);
+    la.x_mid = la.x_in;
+    la.x_out = la.x_in;
+    la.xb2 = la.xb;  // the two normed buffers are never live together
+    for (int l = 0; l < p.L; ++l) out->layer[l] = la;
+    out->fin.x_last = la.x_in;
+    out->fin.rinv_f = la.rinv1;
+    out->fin.xf = la.xb;
+    return;
+  }
+  float* x_next = nullptr;
+  for (int l = 0; l < p.L; ++l) {
+    LayerActs& la = out->layer[l];
+    carve_one(la, x_next);
+    la.x_mid = a.take<float>(T * p.d * 4);
+    la.gate = a.take(T * p.h_loc * es);
+    la.up = a.take(T * p.h_loc * es);
+    la.x_out = a.take<float>(T * p.d * 4);
+    x_next = la.x_out;
+  }
+  out->fin.x_last = x_next;
+  out->fin.rinv_f = a.take<float>(T * 4);
+  out->fin.xf = a.take(T * p.d * es);
+}
+
+// ---- forward ---------------------------------------------------------------------
+static int32_t gemm(const B200Plan& p, const void* A, int lda, const void* B, int ldb, int M, int N, int K, int kind,
+                    int out_dtype, const EpiParams& epi, cudaStream_t stream) {
+  GemmArgs g;
+  g.A = A; g.B = B; g.M = M; g.N = N; g.K = K; g.lda = lda; g.ldb = ldb;
+  g.in_dtype = p.dtype; g.out_dtype = out_dtype; g.kind = kind; g.epi = epi;
+  return launch_gemm(g, p.gemm_impl, stream);
+}
+
+// Row-parallel projection followed by the residual add: fused when the model is
+// on one GPU; with tensor parallelism the partial products are summed over the
+// ranks first (one all-reduce per block) and then added.
+static int32_t proj_residual(const B200Plan& p, const void* A, int lda, const void* W, int ldw, int T, int K,
+                             const float* x_in, float* x_out, void* tp_tmp, cudaStream_t stream) {
+  EpiParams e;
+  if (p.tp_size == 1) {
+    e.out = x_out; e.ldo = p.d; e.resid_in = x_in;
+    return gemm(p, A, lda, W, ldw, T, p.d, K, EPI_RESID, B200_F32, e, stream);
+  }
+  e.out = tp_tmp; e.ldo = p.d;
+  B200_TRY(gemm(p, A, lda, W, ldw, T, p.d, K, EPI_STORE, p.dtype, e, stream));
+  B200_TRY(comm_allreduce(p.comm, tp_tmp, (size_t)T * p.d, p.dtype, stream));
+  if (x_out != x_in)
+    B200_CUDA_OK(cudaMemcpyAsync(x_out, x_in, (size_t)T * p.d * 4, cudaMemcpyDeviceToDevice, stream));
+  return launch_add_to_f32(x_out, tp_tmp, p.dtype, (size_t)T * p.d, stream);
+}
+
+static int32_t forward_impl(B200Plan* p, const int32_t* tokens, int B, int S, const uint8_t* w, const PackedLayout& wl,
+                            float* logits, void* saved, void* kv_out, void* ws, size_t ws_bytes,
+                            cudaStream_t stream) {
+  const int T = B * S;
+  const bool keep = saved != nullptr;
+  Arena wa(ws);
+  FwdActs acts;
+  if (keep) {
+    Arena sa(saved);
+    carve_forward(*p, sa, B, S, true, &acts);
+  } else {
+    carve_forward(*p, wa, B, S, false, &acts);
+  }
+  void* tp_tmp = p->tp_size > 1 ? wa.take((size_t)T * p->d * p->esize) : nullptr;
+  if (wa.used > ws_bytes) return fail(B200_ERR_WORKSPACE, "forward needs %zu workspace bytes, got %zu", wa.used, ws_bytes);
+
+  const float* g_att = reinterpret_cast<const float*>(w + wl.g_att);
+  const float* g_ffn = reinterpret_cast<const float*>(w + wl.g_ffn);
+  const float* g_fin = reinterpret_cast<const float*>(w + wl.g_final);
+  const float eps = p->cfg.rms_eps;
+  const int d = p->d, dl = p->d_loc, hl = p->h_loc;
+
+  B200_TRY(launch_embed(tokens, w + wl.emb, p->dtype, acts.layer[0].x_in, T, d, p->V, stream));
+  for (int l = 0; l < p->L; ++l) {
+    const LayerActs& a = acts.layer[l];
+    const LayerOffsets& o = wl.layer[l];
+    B200_TRY(launch_rmsnorm(a.x_in, g_att + (size_t)l * d, a.xb, a.rinv1, T, d, eps, p->dtype, stream));
+    {  // q,k,v = xb Wqkv^T with the pair rotation of q and k fused (test/llama.py:149-168)
+      EpiParams e;
+      e.out = a.qkv; e.ldo = 3 * dl;
+      e.rope_cos = p->rope_cos; e.rope_sin = p->rope_sin;
+      e.seq_len = S; e.pos_base = 0; e.head_size = p->hs; e.rope_cols = 2 * dl;
+      B200_TRY(gemm(*p, a.xb, d, w + o.wqkv, d, T, 3 * dl, d, EPI_ROPE, p->dtype, e, stream));
+    }
+    if (kv_out) {
+      // kv_out [L, 2, B, S, d_loc]: rotated keys and values of this layer
+      uint8_t* dst = reinterpret_cast<uint8_t*>(kv_out) + (size_t)l * 2 * T * dl * p->esize;
+      const uint8_t* src = reinterpret_cast<const uint8_t*>(a.qkv);
+      for (int part = 0; part < 2; ++part)
+        B200_CUDA_OK(cudaMemcpy2DAsync(dst + (size_t)part * T * dl * p->esize, (size_t)dl * p->esize,
+                                       src + (size_t)(1 + part) * dl * p->esize, (size_t)3 * dl * p->esize,
+                                       (size_t)dl * p->esize, T, cudaMemcpyDeviceToDevice, stream));
+    }
+    {
+      AttnArgs at;
+      const uint8_t* base = reinterpret_cast<const uint8_t*>(a.qkv);
+      at.q = base; at.k = base + (size_t)dl * p->esize; at.v = base + (size_t)2 * dl * p->esize;
+      at.o = a.o; at.lse = a.lse;
+      at.batch = B; at.seq = S; at.n_heads = p->H_loc; at.head_size = p->hs;
+      at.ldq = 3 * dl; at.ldkv = 3 * dl; at.ldo = dl; at.dtype = p->dtype;
+      B200_TRY(launch_attn_fwd(at, p->attn_impl, stream));
+    }
+    B200_TRY(proj_residual(*p, a.o, dl, w + o.wo, dl, T, dl, a.x_in, a.x_mid, tp_tmp, stream));
+    B200_TRY(launch_rmsnorm(a.x_mid, g_ffn + (size_t)l * d, a.xb2, a.rinv2, T, d, eps, p->dtype, stream));
+    {  // hg = silu(xb2 W1^T) * (xb2 W3^T) from the interleaved [W1;W3] product (test/llama.py:224-229)
+      EpiParams e;
+      e.out = a.hg; e.ldo = hl; e.out_gate = a.gate; e.out_up = a.up;
+      B200_TRY(gemm(*p, a.xb2, d, w + o.w13, d, T, 2 * hl, d, EPI_SWIGLU, p->dtype, e, stream));
+    }
+    B200_TRY(proj_residual(*p, a.hg, hl, w + o.w2, hl, T, hl, a.x_mid, a.x_out, tp_tmp, stream));
+  }
+  B200_TRY(launch_rmsnorm(acts.fin.x_last, g_fin, acts.fin.xf, acts.fin.rinv_f, T, d, eps, p->dtype, stream));
+  if (logits) {
+    EpiParams e;
+    e.out = logits; e.ldo = p->V_loc;
+    B200_TRY(gemm(*p, acts.fin.xf, d, w + wl.wcls, d, T, p->V_loc, d, EPI_STORE, B200_F32, e, stream));
+  }
+  return B200_OK;
+}
+
+int32_t launch_attn_fwd(const AttnArgs& a, int impl, cudaStream_t stream) {
+  // causal: half of the 4*S^2*hs flops per (batch, head)
+  ProfScope prof(PROF_ATTN_FWD, 2.0 * a.batch * a.n_heads * (double)a.seq * a.seq * a.head_size, stream);
+  if (impl == 2) return launch_attn_fwd_simt(a, stream);
+  if (impl == 1) return launch_attn_fwd_mma(a, stream);
+  if (attn_fwd_mma_supports(a)) return launch_attn_fwd_mma(a, stream);
+  return launch_attn_fwd_simt(a, stream);
+}
+
+static int32_t check_plan_call(const B200Plan* p, int B, int S) {
+  if (!p) return fail(B200_ERR_INVALID_ARG, "plan is null");
+  if (B <= 0 || S <= 0) return fail(B200_ERR_BAD_SHAPE, "batch=%d seq=%d must be positive", B, S);
+  if (S > p->cfg.seq_len) return fail(B200_ERR_BAD_SHAPE, "seq=%d exceeds the plan's seq_len=%d", S, p->cfg.seq_len);
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev != p->device)
+    return fail(B200_ERR_INVALID_ARG, "plan was created on device %d, current device is %d", p->device, dev);
+  return B200_OK;
+}
+
+}  // namespace b200
+
+using namespace b200;
+
+extern "C" {
+
+const char* b200_last_error(void) { return g_err; }
+const char* b200_version(void) { return "0.1"; }
+int64_t b200_launch_count(void) { return g_launches.load(); }
+
+int32_t b200_profile_enable(int32_t on) {
+  std::lock_guard<std::mutex> lk(g_prof_mu);
+  if (on) g_prof_used = 0;
+  g_prof_on.store(on ? 1 : 0);
+  return B200_OK;
+}
+
+int32_t b200_profile_read(int32_t cls, double* total_ms, double* total_work, int64_t* launches) {
+  if (cls < 0 || cls >= PROF_NUM) return fail(B200_ERR_INVALID_ARG, "unknown kernel class %d", cls);
+  std::lock_guard<std::mutex> lk(g_prof_mu);
+  double ms = 0, work = 0;
+  int64_t n = 0;
+  for (size_t i = 0; i < g_prof_used; ++i) {
+    if (g_prof[i].cls != cls) continue;
+    B200_CUDA_OK(cudaEventSynchronize(g_prof[i].b));
+    float t = 0.f;
+    B200_CUDA_OK(cudaEventElapsedTime(&t, g_prof[i].a, g_prof[i].b));
+    ms += t; work += g_prof[i].work; ++n;
+  }
+  if (total_ms) *total_ms = ms;
+  if (total_work) *total_work = work;
+  if (launches) *launches = n;
+  return B200_OK;
+}
+
+int32_t b200_device_status(b200_stream_t stream, uint32_t* code) {
+  uint32_t* word = device_status_word();
+  if (!word) return fail(B200_ERR_CUDA, "no device status word");
+  uint32_t host = 0;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  B200_CUDA_OK(cudaMemcpyAsync(&host, word, 4, cudaMemcpyDeviceToHost, s));
+  B200_CUDA_OK(cudaStreamSynchronize(s));
+  if (host) {
+    B200_CUDA_OK(cudaMemsetAsync(word, 0, 4, s));
+    B200_CUDA_OK(cudaStreamSynchronize(s));
+  }
+  if (code) *code = host;
+  if (host) return fail(B200_ERR_TIMEOUT, "a bounded device-side wait ran out (status word 0x%x)", host);
+  return B200_OK;
+}
+
+int32_t b200_plan_create(const B200LlamaConfig* cfg, int32_t tp_rank, int32_t tp_size, void* comm, B200Plan** out) {
+  if (!cfg || !out) return fail(B200_ERR_INVALID_ARG, "cfg and out must not be null");
+  *out = nullptr;
+  if (cfg->dim <= 0 || cfg->hidden_dim <= 0 || cfg->n_layers <= 0 || cfg->n_heads <= 0 || cfg->vocab_size <= 0 ||
+      cfg->seq_len <= 0)
+    return fail(B200_ERR_BAD_SHAPE, "config sizes must be positive");
+  if (cfg->n_kv_heads != cfg->n_heads)
+    return fail(B200_ERR_UNSUPPORTED, "n_kv_heads (%d) must equal n_heads (%d), as in the reference model",
+                cfg->n_kv_heads, cfg->n_heads);
+  if (cfg->dim % cfg->n_heads) return fail(B200_ERR_BAD_SHAPE, "dim %% n_heads != 0");
+  if (cfg->dtype != B200_F32 && cfg->dtype != B200_BF16) return fail(B200_ERR_BAD_DTYPE, "dtype must be fp32 or bf16");
+  if (tp_size < 1 || tp_rank < 0 || tp_rank >= tp_size) return fail(B200_ERR_INVALID_ARG, "bad tensor-parallel rank %d of %d", tp_rank, tp_size);
+  if (tp_size > 1 && !comm) return fail(B200_ERR_INVALID_ARG, "tensor parallelism needs a communicator");
+  const int hs = cfg->dim / cfg->n_heads;
+  if (hs != 16 && hs != 32 && hs != 48 && hs != 64 && hs != 128)
+    return fail(B200_ERR_BAD_SHAPE, "head size %d is not one of 16/32/48/64/128", hs);
+  if (cfg->n_heads % tp_size || cfg->hidden_dim % (16 * tp_size) || cfg->vocab_size % (16 * tp_size) ||
+      (cfg->dim / tp_size) % 16 || cfg->dim % 16)
+    return fail(B200_ERR_BAD_SHAPE, "dim, hidden_dim, vocab (per rank) must be multiples of 16 and heads divisible by tp_size");
+  int dev = 0;
+  B200_CUDA_OK(cudaGetDevice(&dev));
+  int major = 0;
+  B200_CUDA_OK(cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev));
+  if (major != 10) return fail(B200_ERR_ARCH, "device %d has compute capability %d.x; this library is sm_100a only", dev, major);
+
+  B200Plan* p = new B200Plan();
+  p->cfg = *cfg;
+  p->tp_rank = tp_rank; p->tp_size = tp_size; p->comm = comm;
+  p->d = cfg->dim; p->h = cfg->hidden_dim; p->L = cfg->n_layers; p->H = cfg->n_heads; p->hs = hs; p->V = cfg->vocab_size;
+  p->d_loc = p->d / tp_size; p->h_loc = p->h / tp_size; p->V_loc = p->V / tp_size; p->H_loc = p->H / tp_size;
+  p->dtype = cfg->dtype;
+  p->esize = cfg->dtype == B200_BF16 ? 2 : 4;
+  p->device = dev;
+  p->gemm_impl = env_int("B200_GEMM_IMPL", 0);
+  p->attn_impl = env_int("B200_ATTN_IMPL", 0);
+  build_layout(*p, p->esize, false, &p->wl);
+  build_layout(*p, p->esize, true, &p->wlt);
+  build_layout(*p, 4, false, &p->gl);
+  const size_t tb = (size_t)cfg->seq_len * (hs / 2) * 4;
+  if (cudaMalloc(&p->rope_cos, tb) != cudaSuccess || cudaMalloc(&p->rope_sin, tb) != cudaSuccess) {
+    cudaFree(p->rope_cos);
+    delete p;
+    return fail(B200_ERR_CUDA, "cannot allocate the rotation tables");
+  }
+  int32_t st = launch_rope_table(p->rope_cos, p->rope_sin, cfg->seq_len, hs, cfg->rope_theta, 0);
+  if (st == B200_OK && cudaStreamSynchronize(0) != cudaSuccess) st = fail(B200_ERR_CUDA, "rotation table kernel failed");
+  if (st != B200_OK) {
+    cudaFree(p->rope_cos); cudaFree(p->rope_sin);
+    delete p;
+    return st;
+  }
+  device_status_word();
+  *out = p;
+  return B200_OK;
+}
+
+int32_t b200_plan_destroy(B200Plan* p) {
+  if (!p) return B200_OK;
+  cudaFree(p->rope_cos);
+  cudaFree(p->rope_sin);
+  delete p;
+  return B200_OK;
+}
+
+int32_t b200_packed_weight_bytes(const B200Plan* p, int32_t with_t, size_t* bytes) {
+  if (!p || !bytes) return fail(B200_ERR_INVALID_ARG, "null argument");
+  *bytes = with_t ? p->wlt.total : p->wl.total;
+  return B200_OK;
+}
+
+int32_t b200_packed_grad_bytes(const B200Plan* p, size_t* bytes) {
+  if (!p || !bytes) return fail(B200_ERR_INVALID_ARG, "null argument");
+  *bytes = p->gl.total;
+  return B200_OK;
+}
+
+int32_t b200_pack_weights(const B200Plan* p, const void* const* leaves, int32_t ld, int32_t with_t, void* packed,
+                          b200_stream_t stream_) {
+  if (!p || !leaves || !packed) return fail(B200_ERR_INVALID_ARG, "null argument");
+  for (int i = 0; i < B200_NUM_LEAVES; ++i) {
+    if (!leaves[i]) return fail(B200_ERR_INVALID_ARG, "leaf %d is null", i);
+    if (!aligned16(leaves[i])) return fail(B200_ERR_MISALIGNED, "leaf %d is not 16-byte aligned", i);
+  }
+  if (ld != B200_F32 && ld != B200_BF16) return fail(B200_ERR_BAD_DTYPE, "leaf dtype must be fp32 or bf16");
+  if (!aligned16(packed)) return fail(B200_ERR_MISALIGNED, "packed buffer is not 16-byte aligned");
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream_);
+  const PackedLayout& wl = with_t ? p->wlt : p->wl;
+  uint8_t* w = reinterpret_cast<uint8_t*>(packed);
+  const size_t les = ld == B200_BF16 ? 2 : 4;
+  const int d = p->d, h = p->h, dl = p->d_loc, hl = p->h_loc, Vl = p->V_loc, L = p->L, r = p->tp_rank, dt = p->dtype;
+  auto leaf = [&](int i, size_t elem_off) { return reinterpret_cast<const uint8_t*>(leaves[i]) + elem_off * les; };
+  auto plain = [&](const void* src, int sld, void* dst, int dld, int rows, int cols, int ddt) {
+    return launch_copy_rows(src, ld, sld, dst, ddt, dld, rows, cols, rows, rows, 0, s);
+  };
+  B200_TRY(plain(leaf(B200_LEAF_RMS_ATT, 0), d, w + wl.g_att, d, L, d, B200_F32));
+  B200_TRY(plain(leaf(B200_LEAF_RMS_FFN, 0), d, w + wl.g_ffn, d, L, d, B200_F32));
+  B200_TRY(plain(leaf(B200_LEAF_RMS_FINAL, 0), d, w + wl.g_final, d, 1, d, B200_F32));
+  B200_TRY(plain(leaf(B200_LEAF_TOK_EMB, 0), d, w + wl.emb, d, p->V, d, dt));
+  for (int l = 0; l < L; ++l) {
+    const LayerOffsets& o = wl.layer[l];
+    const size_t dd = (size_t)l * d * d, hd = (size_t)l * h * d;
+    const int qkv_leaf[3] = {B200_LEAF_WQ, B200_LEAF_WK, B200_LEAF_WV};
+    for (int j = 0; j < 3; ++j)  // head rows of this rank, q then k then v
+      B200_TRY(plain(leaf(qkv_leaf[j], dd + (size_t)r * dl * d), d, w + o.wqkv + (size_t)j * dl * d * p->esize, d, dl,
+                     d, dt));
+    // wo [d, d]: columns of this rank's heads
+    B200_TRY(plain(leaf(B200_LEAF_WO, dd + (size_t)r * dl), d, w + o.wo, dl, d, dl, dt));
+    // w1/w3 rows of this rank, interleaved in groups of 8: [8 of w1 | 8 of w3 | ...]
+    B200_TRY(launch_copy_rows(leaf(B200_LEAF_W1, hd + (size_t)r * hl * d), ld, d, w + o.w13, dt, d, hl, d, 8, 16, 0, s));
+    B200_TRY(launch_copy_rows(leaf(B200_LEAF_W3, hd + (size_t)r * hl * d), ld, d, w + o.w13, dt, d, hl, d, 8, 16, 8, s));
+    // w2 [d, h]: columns of this rank's hidden units
+    B200_TRY(plain(leaf(B200_LEAF_W2, hd + (size_t)r * hl), h, w + o.w2, hl, d, hl, dt));
+    if (with_t) {
+      B200_TRY(launch_transpose(w + o.wqkv, dt, d, w + o.wqkv_t, dt, 3 * dl, 3 * dl, d, s));
+      B200_TRY(launch_transpose(w + o.wo, dt, dl, w + o.wo_t, dt, d, d, dl, s));
+      B200_TRY(launch_transpose(w + o.w13, dt, d, w + o.w13_t, dt, 2 * hl, 2 * hl, d, s));
+      B200_TRY(launch_transpose(w + o.w2, dt, hl, w + o.w2_t, dt, d, d, hl, s));
+    }
+  }
+  B200_TRY(plain(leaf(B200_LEAF_WCLS, (size_t)r * Vl * d), d, w + wl.wcls, d, Vl, d, dt));
+  if (with_t) B200_TRY(launch_transpose(w + wl.wcls, dt, d, w + wl.wcls_t, dt, Vl, Vl, d, s));
+  return B200_OK;
+}
+
+int32_t b200_saved_bytes(const B200Plan* p, int32_t B, int32_t S, size_t* bytes) {
+  if (!p || !bytes) return fail(B200_ERR_INVALID_ARG, "null argument");
+  if (B <= 0 || S <= 0) return fail(B200_ERR_BAD_SHAPE, "batch and seq must be positive");
+  Arena a(nullptr);
+  FwdActs acts;
+  carve_forward(*p, a, B, S, true, &acts);
+  *bytes = a.used;
+  return B200_OK;
+}
+
+int32_t b200_forward(B200Plan* p, const int32_t* tokens, int32_t B, int32_t S, const void* packed_w, float* logits,
+                     void* saved, void* kv_out, void* ws, size_t ws_bytes, b200_stream_t stream) {
+  B200_TRY(check_plan_call(p, B, S));
+  if (!tokens || !packed_w || !ws) return fail(B200_ERR_INVALID_ARG, "tokens, weights and workspace must not be null");
+  if (!aligned16(ws) || !aligned16(packed_w) || (logits && !aligned16(logits)) || (saved && !aligned16(saved)))
+    return fail(B200_ERR_MISALIGNED, "buffers must be 16-byte aligned");
+  // The backward pass contracts against the transposed copies, which sit
+  // behind the plain weights in both layouts, so either packing serves here.
+  return forward_impl(p, tokens, B, S, reinterpret_cast<const uint8_t*>(packed_w), p->wl, logits, saved, kv_out, ws,
+                      ws_bytes, reinterpret_cast<cudaStream_t>(stream));
+}
+
+}  // extern "C"

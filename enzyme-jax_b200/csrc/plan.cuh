@@ -1,0 +1,99 @@
+// Launch plan of the llama path: shapes, tensor-parallel shard sizes, the layout
+// of the packed weight / gradient buffers, and the carving of the caller's
+// workspace and saved-activation buffers.
+#pragma once
+
+#include <stddef.h>
+
+#include <vector>
+
+#include "common.cuh"
+
+namespace b200 {
+
+struct LayerOffsets {
+  size_t wqkv, wo, w13, w2;          // byte offsets of the matrices
+  size_t wqkv_t, wo_t, w13_t, w2_t;  // transposed copies (weights only)
+};
+
+struct PackedLayout {
+  size_t g_att = 0, g_ffn = 0, g_final = 0;  // fp32 gains
+  size_t emb = 0;
+  std::vector<LayerOffsets> layer;
+  size_t wcls = 0, wcls_t = 0;
+  size_t total = 0;
+};
+
+// Carves consecutive 256-byte aligned regions out of a caller buffer; with a
+// null base it only counts.
+struct Arena {
+  uint8_t* base;
+  size_t used = 0;
+  explicit Arena(void* b) : base(reinterpret_cast<uint8_t*>(b)) {}
+  template <typename T = void> T* take(size_t bytes) {
+    T* p = base ? reinterpret_cast<T*>(base + used) : nullptr;
+    used += align_up(bytes, 256);
+    return p;
+  }
+};
+
+// Activations of one layer: slices of the saved buffer when the forward keeps
+// them for the backward pass, else workspace regions shared by all layers.
+struct LayerActs {
+  float* x_in = nullptr;   // [T,d] residual stream entering the layer
+  void* xb = nullptr;      // [T,d] normed input of the attention block
+  float* rinv1 = nullptr;  // [T]
+  void* qkv = nullptr;     // [T,3*d_loc] rotated q,k and v
+  void* o = nullptr;       // [T,d_loc] attention output
+  float* lse = nullptr;    // [B,H_loc,S]
+  float* x_mid = nullptr;  // [T,d] residual stream after attention
+  void* xb2 = nullptr;     // [T,d]
+  float* rinv2 = nullptr;  // [T]
+  void* gate = nullptr;    // [T,h_loc]
+  void* up = nullptr;      // [T,h_loc]
+  void* hg = nullptr;      // [T,h_loc]
+  float* x_out = nullptr;  // [T,d] residual stream leaving the layer
+};
+struct FinalActs {
+  float* x_last = nullptr;
+  float* rinv_f = nullptr;
+  void* xf = nullptr;
+};
+struct FwdActs {
+  std::vector<LayerActs> layer;
+  FinalActs fin;
+};
+
+}  // namespace b200
+
+struct B200Plan {
+  B200LlamaConfig cfg;
+  int tp_rank = 0, tp_size = 1;
+  void* comm = nullptr;
+  int d = 0, h = 0, L = 0, H = 0, hs = 0, V = 0;
+  int d_loc = 0, h_loc = 0, V_loc = 0, H_loc = 0;
+  int esize = 2;
+  int dtype = B200_BF16;
+  int device = 0;
+  int gemm_impl = 0, attn_impl = 0;
+  float* rope_cos = nullptr;  // [seq_len, hs/2], owned by the plan
+  float* rope_sin = nullptr;
+  b200::PackedLayout wl;   // weights
+  b200::PackedLayout wlt;  // weights followed by transposed copies
+  b200::PackedLayout gl;   // gradients (everything fp32)
+};
+
+namespace b200 {
+
+void build_layout(const B200Plan& p, size_t mat_esize, bool with_t, PackedLayout* out);
+// Carves the activations of a forward over T = B*S tokens.  keep: per-layer
+// buffers (the saved-activation layout); otherwise one shared set.
+void carve_forward(const B200Plan& p, Arena& a, int B, int S, bool keep, FwdActs* out);
+
+int32_t comm_allreduce(void* comm, void* data, size_t count, int dtype, cudaStream_t stream);
+
+// Environment knobs (read once at plan creation): B200_GEMM_IMPL and
+// B200_ATTN_IMPL select 0 = pick, 1 = tensor-core kernels, 2 = CUDA-core kernels.
+int env_int(const char* name, int dflt);
+
+}  // namespace b200

@@ -1,0 +1,226 @@
+/* C ABI of the B200-native llama forward / VJP path.
+ *
+ * This is the boundary an XLA typed-FFI handler (api_version 4) binds to.  The
+ * reference registers such handlers with
+ *   Ffi::Bind().Ctx<PlatformStream<CUstream>>().Attr<T>(..).Arg<AnyBuffer>()..Ret<AnyBuffer>()
+ * (src/enzyme_ad/jax/xla_ffi/cuda/blas.cc:286-314) and
+ *   XLA_FFI_REGISTER_HANDLER(GetXlaFfiApi(), name, "CUDA", handler)
+ * (src/enzyme_ad/jax/xla_ffi/register.cc:21-27).  Each entry point below is
+ * what such a handler calls after unpacking its buffers: plain device pointers,
+ * sizes, a stream; no framework types.
+ *
+ * Conventions (matching the reference's handler rules):
+ *  - the caller owns every buffer, outputs and scratch included
+ *    (primitives.py:712-727 appends an i8[tmpBuf] result as scratch);
+ *  - work is enqueued on the given stream and the call returns without
+ *    synchronising (gpu.cc:122-125,153);
+ *  - the return value is a status code, 0 on success; b200_last_error() gives
+ *    the thread-local message (the handler maps it to ffi::Error, as
+ *    blas.cc:80-115 does for cuBLAS failures).
+ *  - nothing here falls back to a CPU implementation.
+ */
+#ifndef B200_LLAMA_H_
+#define B200_LLAMA_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define B200_API __attribute__((visibility("default")))
+
+typedef void* b200_stream_t; /* cudaStream_t / CUstream */
+
+enum B200Status {
+  B200_OK = 0,
+  B200_ERR_INVALID_ARG = 1,   /* null pointer, negative size */
+  B200_ERR_BAD_SHAPE = 2,     /* shape the kernels do not cover */
+  B200_ERR_BAD_DTYPE = 3,
+  B200_ERR_MISALIGNED = 4,    /* pointer or stride not 16-byte aligned */
+  B200_ERR_WORKSPACE = 5,     /* workspace smaller than b200_workspace_bytes */
+  B200_ERR_ARCH = 6,          /* device is not sm_100 */
+  B200_ERR_CUDA = 7,
+  B200_ERR_NCCL = 8,
+  B200_ERR_TIMEOUT = 9,       /* a bounded device-side wait ran out */
+  B200_ERR_UNSUPPORTED = 10
+};
+
+enum B200DType { B200_F32 = 0, B200_BF16 = 1 };
+
+/* Model description: the keys of the reference's config dict
+ * (test/llama.py:246-254) plus the numeric type and the two constants the
+ * reference hard-codes (theta at test/llama.py:129, eps at :9). */
+typedef struct B200LlamaConfig {
+  int32_t dim;
+  int32_t hidden_dim;
+  int32_t n_layers;
+  int32_t n_heads;
+  int32_t n_kv_heads; /* must equal n_heads, as in the reference (test/llama.py:162) */
+  int32_t vocab_size;
+  int32_t seq_len;    /* maximum sequence length */
+  int32_t dtype;      /* B200DType of weights and activations; accumulation, the
+                         residual stream, logits and gradients are always fp32 */
+  float rope_theta;
+  float rms_eps;
+} B200LlamaConfig;
+
+typedef struct B200Plan B200Plan;
+
+/* Order of the weight leaves everywhere in this ABI: the sorted key order in
+ * which JAX flattens the reference's weight dict (primitives.py:1537-1569
+ * flattens args with tree_flatten), with the embedding leaf the reference
+ * names at test/llama.py:109-112 in its sorted place. */
+enum B200Leaf {
+  B200_LEAF_RMS_ATT = 0,   /* [L, d]        */
+  B200_LEAF_RMS_FFN = 1,   /* [L, d]        */
+  B200_LEAF_RMS_FINAL = 2, /* [d]           */
+  B200_LEAF_TOK_EMB = 3,   /* [V, d]        */
+  B200_LEAF_W1 = 4,        /* [L, h, d]     */
+  B200_LEAF_W2 = 5,        /* [L, d, h]     */
+  B200_LEAF_W3 = 6,        /* [L, h, d]     */
+  B200_LEAF_WCLS = 7,      /* [V, d]        */
+  B200_LEAF_WK = 8,        /* [L, d, d]     */
+  B200_LEAF_WO = 9,        /* [L, d, d]     */
+  B200_LEAF_WQ = 10,       /* [L, d, d]     */
+  B200_LEAF_WV = 11,       /* [L, d, d]     */
+  B200_NUM_LEAVES = 12
+};
+
+/* ---- library / device ---------------------------------------------------- */
+
+/* Thread-local message of the last failing call on this thread.  Replaces the
+ * ffi::Error text of xla_ffi/cuda/blas.cc:80-115. */
+B200_API const char* b200_last_error(void);
+
+/* Version string "major.minor". */
+B200_API const char* b200_version(void);
+
+/* Reads and clears the device-side status word that kernels with bounded
+ * waits set when a wait runs out.  Synchronises the stream (the one place that
+ * does, like xla_throw_error in xla_ffi/cuda/throw_error.cc:20-31).  Returns
+ * B200_OK or B200_ERR_TIMEOUT; *code receives the raw word. */
+B200_API int32_t b200_device_status(b200_stream_t stream, uint32_t* code);
+
+/* Number of kernels this library has launched in this process. */
+B200_API int64_t b200_launch_count(void);
+
+/* Per-kernel timing with CUDA events on the launching stream, the counterpart
+ * of the reference's profiler-based step timing (test/xprof_utils.py:71-157).
+ * b200_profile_enable(1) clears earlier samples and brackets every GEMM and
+ * attention launch with an event pair; b200_profile_read synchronises those
+ * events and returns, for one kernel class (0 tcgen05 GEMM, 1 FFMA GEMM,
+ * 2 attention forward, 3 attention backward, 4 decode attention), the summed
+ * milliseconds, the summed algorithmic work (flops; bytes for class 4) and
+ * the launch count.  Off by default; costs two event records per launch. */
+B200_API int32_t b200_profile_enable(int32_t on);
+B200_API int32_t b200_profile_read(int32_t kernel_class, double* total_ms, double* total_work, int64_t* launches);
+
+/* ---- plan ---------------------------------------------------------------- */
+
+/* Creates the launch plan for one model on the current device.  tp_size > 1
+ * shards heads, hidden units and vocabulary rows Megatron-style over the ranks
+ * of `comm` (a handle from b200_comm_init_rank, or NULL when tp_size == 1).
+ * Replaces the compile step the reference performs for a jitted function
+ * (primitives.py:536-783: lowering + pass pipeline); there is no IR here, the
+ * plan is the fixed kernel sequence for this model. */
+B200_API int32_t b200_plan_create(const B200LlamaConfig* cfg, int32_t tp_rank, int32_t tp_size,
+                                  void* comm, B200Plan** out);
+B200_API int32_t b200_plan_destroy(B200Plan* plan);
+
+/* Bytes of the packed weight buffer for this rank; with_transposed != 0 adds
+ * the transposed copies the backward pass contracts against. */
+B200_API int32_t b200_packed_weight_bytes(const B200Plan* plan, int32_t with_transposed, size_t* bytes);
+
+/* Packs the 12 leaves (device pointers, B200Leaf order, element type
+ * leaf_dtype, full unsharded shapes) into the layout the kernels read:
+ * Wq/Wk/Wv rows concatenated, W1/W3 rows interleaved in groups of 8, this
+ * rank's shard only.  Stands in for the layout assignment XLA performs on the
+ * custom call's operand_layouts (Passes/LowerEnzymeXLABLAS.cpp:463-479). */
+B200_API int32_t b200_pack_weights(const B200Plan* plan, const void* const* leaves, int32_t leaf_dtype,
+                                   int32_t with_transposed, void* packed, b200_stream_t stream);
+
+/* mode: 0 forward (inference), 1 forward keeping activations for backward,
+ * 2 backward, 3 decode step. */
+B200_API int32_t b200_workspace_bytes(const B200Plan* plan, int32_t mode, int32_t batch, int32_t seq, size_t* bytes);
+B200_API int32_t b200_saved_bytes(const B200Plan* plan, int32_t batch, int32_t seq, size_t* bytes);
+
+/* ---- forward / backward / decode ----------------------------------------- */
+
+/* Full causal forward (the reference's `forward`, test/llama.py:35-238,
+ * applied to every position of `batch` sequences, with the embedding lookup
+ * and the logits projection of test/llama.py:109-113,236 enabled).
+ *   tokens  int32 [batch, seq]
+ *   logits  fp32  [batch*seq, vocab/tp_size]  (this rank's vocabulary rows)
+ *   saved   NULL, or b200_saved_bytes() bytes that receive the activations
+ *           b200_backward needs
+ *   kv_out  NULL, or [L, 2, batch, seq, d/tp] receiving rotated K and V */
+B200_API int32_t b200_forward(B200Plan* plan, const int32_t* tokens, int32_t batch, int32_t seq,
+                              const void* packed_w, float* logits, void* saved, void* kv_out,
+                              void* workspace, size_t workspace_bytes, b200_stream_t stream);
+
+/* Reverse mode of b200_forward with respect to every weight leaf (what
+ * jax.vjp through the reference's enzyme_vjp rule, primitives.py:1381-1469,
+ * returns for the weight arguments).
+ *   dlogits fp32 [batch*seq, vocab]
+ *   grads   fp32, packed like the weights (b200_packed_weight_bytes without
+ *           transposes, counted in fp32); accumulate != 0 adds into it
+ * Use b200_unpack_grads to obtain per-leaf gradients. */
+B200_API int32_t b200_backward(B200Plan* plan, const int32_t* tokens, int32_t batch, int32_t seq,
+                               const void* packed_w, const float* dlogits, const void* saved,
+                               float* grads, int32_t accumulate, void* workspace, size_t workspace_bytes,
+                               b200_stream_t stream);
+B200_API int32_t b200_packed_grad_bytes(const B200Plan* plan, size_t* bytes);
+B200_API int32_t b200_unpack_grads(const B200Plan* plan, const float* grads, float* const* leaves,
+                                   b200_stream_t stream);
+
+/* Sums `count` floats over the ranks of the communicator in place (the
+ * data-parallel gradient exchange). */
+B200_API int32_t b200_allreduce_f32(void* comm, float* data, size_t count, b200_stream_t stream);
+
+/* One decode step for `batch` sequences that all hold `pos` cached positions
+ * (the reference's single-token `forward`, test/llama.py:35-238, where
+ * pos = key_cache.shape[1]).
+ *   tokens     int32 [batch], or NULL when x_in is given
+ *   x_in       NULL, or fp32 [batch, d] residual vectors (the reference's `x`)
+ *   kv_pages   the paged cache: [L, 2, n_pages, page_size, d/tp] of the config
+ *              dtype; the step appends row `pos` of every sequence
+ *   page_table int32 [batch, max_pages]: page index of each sequence's pages
+ *   hidden_out NULL, or fp32 [batch, d]: final-normed hidden state (what the
+ *              reference returns, test/llama.py:235-238)
+ *   logits     NULL, or fp32 [batch, vocab/tp] */
+B200_API int32_t b200_decode_step(B200Plan* plan, const int32_t* tokens, const float* x_in, int32_t batch,
+                                  int32_t pos, const void* packed_w, void* kv_pages, const int32_t* page_table,
+                                  int32_t n_pages, int32_t page_size, int32_t max_pages, float* hidden_out,
+                                  float* logits, void* workspace, size_t workspace_bytes, b200_stream_t stream);
+
+/* ---- single kernels (unit-testable pieces of the path) ------------------- */
+
+/* Y[M,N] = A[M,K] * B[N,K]^T with fp32 accumulation; dtype of A and B is
+ * in_dtype, of Y out_dtype.  impl: 0 = pick, 1 = tcgen05/TMEM (bf16 only),
+ * 2 = FFMA.  ta/tb != 0 read the operand as its transpose ([K,M] / [K,N]). */
+B200_API int32_t b200_gemm(const void* A, const void* B, void* Y, int32_t M, int32_t N, int32_t K,
+                           int32_t lda, int32_t ldb, int32_t ldy, int32_t ta, int32_t tb, int32_t in_dtype,
+                           int32_t out_dtype, int32_t accumulate, int32_t impl, b200_stream_t stream);
+
+/* y = gain * x * rsqrt(mean(x^2) + eps) per row (test/llama.py:6-10). */
+B200_API int32_t b200_rmsnorm(const float* x, const float* gain, void* y, float* rinv_or_null, int32_t rows,
+                              int32_t dim, float eps, int32_t out_dtype, b200_stream_t stream);
+
+/* Causal attention over [batch, seq] with heads side by side in the rows:
+ * q,k,v,o [batch*seq, ld] (test/llama.py:177-209); lse fp32 [batch, H, seq] or NULL. */
+B200_API int32_t b200_attention(const void* q, const void* k, const void* v, void* o, float* lse, int32_t batch,
+                                int32_t seq, int32_t n_heads, int32_t head_size, int32_t ldq, int32_t ldkv,
+                                int32_t ldo, int32_t dtype, int32_t impl, b200_stream_t stream);
+
+/* ---- communicator (NCCL over NVLink) -------------------------------------- */
+
+B200_API int32_t b200_comm_unique_id(void* id128 /* 128 bytes out */);
+B200_API int32_t b200_comm_init_rank(const void* id128, int32_t rank, int32_t world, void** comm);
+B200_API int32_t b200_comm_destroy(void* comm);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200_LLAMA_H_ */

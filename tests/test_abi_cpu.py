@@ -1,0 +1,49 @@
+"""The C-ABI library loads without a GPU and exports every symbol the header
+declares; argument checks that precede any CUDA call answer with status codes."""
+import ctypes
+import os
+import re
+
+import b200_llama as B
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _declared():
+    text = open(os.path.join(ROOT, "include", "b200_llama.h")).read()
+    return sorted(set(re.findall(r"B200_API[^;(]*?\b(b200_\w+)\s*\(", text)))
+
+
+def test_every_declared_symbol_is_exported():
+    lib = B.lib()
+    names = _declared()
+    assert len(names) >= 20
+    for n in names:
+        assert hasattr(lib, n), n
+    assert sorted(B.EXPORTS) == names
+
+
+def test_version_and_error_string():
+    lib = B.lib()
+    assert lib.b200_version() == b"0.1"
+    assert lib.b200_plan_create(None, 0, 1, None, None) == 1
+    assert b"null" in lib.b200_last_error()
+
+
+def test_null_arguments_are_rejected_before_any_launch():
+    lib = B.lib()
+    n = ctypes.c_size_t(0)
+    assert lib.b200_packed_weight_bytes(None, 0, ctypes.byref(n)) == 1
+    assert lib.b200_workspace_bytes(None, 0, 1, 1, ctypes.byref(n)) == 1
+    assert lib.b200_gemm(None, None, None, 1, 16, 16, 16, 16, 16, 0, 0, 1, 1, 0, 0, None) == 1
+    assert lib.b200_comm_unique_id(None) == 1
+    assert lib.b200_backward(None, None, 1, 1, None, None, None, None, 0, None, 0, None) == 1
+
+
+def test_plan_needs_a_device():
+    import pytest
+    import torch
+    if torch.cuda.is_available():
+        pytest.skip("CUDA present")
+    with pytest.raises(RuntimeError):
+        B.Plan(dict(dim=64, hidden_dim=128, n_layers=1, n_heads=2, n_kv_heads=2, vocab_size=96, seq_len=8))
