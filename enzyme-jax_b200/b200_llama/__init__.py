@@ -32,6 +32,7 @@ EXPORTS = (
     "b200_backward", "b200_packed_grad_bytes", "b200_unpack_grads", "b200_allreduce_f32", "b200_decode_step",
     "b200_gemm", "b200_rmsnorm", "b200_attention", "b200_comm_unique_id", "b200_comm_init_rank",
     "b200_comm_destroy", "b200_launch_count", "b200_profile_enable", "b200_profile_read",
+    "b200_attention_decode_scratch_bytes", "b200_attention_decode",
 )
 
 
@@ -86,6 +87,8 @@ def lib() -> ctypes.CDLL:
         l.b200_rmsnorm.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int32, c_int32, c_float, c_int32,
                                    c_void_p]
         l.b200_attention.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p] + [c_int32] * 9 + [c_void_p]
+        l.b200_attention_decode_scratch_bytes.argtypes = [c_int32] * 4 + [POINTER(c_size_t)]
+        l.b200_attention_decode.argtypes = [c_void_p] * 5 + [c_size_t] + [c_int32] * 10 + [c_void_p]
         l.b200_device_status.argtypes = [c_void_p, POINTER(c_uint32)]
         l.b200_comm_unique_id.argtypes = [c_void_p]
         l.b200_comm_init_rank.argtypes = [c_void_p, c_int32, c_int32, POINTER(c_void_p)]
@@ -179,6 +182,23 @@ def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, batch: int, seq
     check(lib().b200_attention(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr(), batch, seq,
                                n_heads, hs, q.stride(0), k.stride(0), o.stride(0), _dt(q.dtype), impl, _stream()))
     return o, lse
+
+
+def attention_decode(q: torch.Tensor, kv_layer: torch.Tensor, page_table: torch.Tensor, ctx: int, n_heads: int,
+                     scratch: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Decode attention of q [batch, n_heads*hs] over one layer of a paged cache [2, n_pages, page_size, d]."""
+    batch, d = q.shape
+    hs = d // n_heads
+    n_pages, page_size = kv_layer.shape[1], kv_layer.shape[2]
+    o = torch.empty(batch, d, dtype=q.dtype, device=q.device)
+    if scratch is None:
+        n = c_size_t(0)
+        check(lib().b200_attention_decode_scratch_bytes(batch, n_heads, hs, ctx, byref(n)))
+        scratch = torch.empty(n.value, dtype=torch.uint8, device=q.device)
+    check(lib().b200_attention_decode(q.data_ptr(), kv_layer.data_ptr(), page_table.data_ptr(), o.data_ptr(),
+                                      scratch.data_ptr(), scratch.numel(), batch, ctx, n_heads, hs, q.stride(0),
+                                      o.stride(0), n_pages, page_size, page_table.shape[1], _dt(q.dtype), _stream()))
+    return o
 
 
 # --------------------------------------------------------------------------

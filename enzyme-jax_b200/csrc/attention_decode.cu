@@ -189,3 +189,36 @@ int32_t launch_attn_decode(const AttnDecodeArgs& a, cudaStream_t stream) {
 }
 
 }  // namespace b200
+
+using namespace b200;
+
+extern "C" {
+
+int32_t b200_attention_decode_scratch_bytes(int32_t batch, int32_t n_heads, int32_t head_size, int32_t ctx,
+                                            size_t* bytes) {
+  if (!bytes) return fail(B200_ERR_INVALID_ARG, "bytes is null");
+  if (batch <= 0 || n_heads <= 0 || head_size <= 0 || ctx <= 0) return fail(B200_ERR_BAD_SHAPE, "sizes must be positive");
+  *bytes = decode_scratch_floats(batch, n_heads, head_size, decode_pick_splits(batch, n_heads, ctx)) * sizeof(float);
+  return B200_OK;
+}
+
+int32_t b200_attention_decode(const void* q, const void* kv_pages, const int32_t* page_table, void* o, void* scratch,
+                              size_t scratch_bytes, int32_t batch, int32_t ctx, int32_t n_heads, int32_t head_size,
+                              int32_t ldq, int32_t ldo, int32_t n_pages, int32_t page_size, int32_t max_pages,
+                              int32_t dtype, b200_stream_t stream) {
+  if (!q || !kv_pages || !page_table || !o || !scratch) return fail(B200_ERR_INVALID_ARG, "null operand");
+  if (!aligned16(q) || !aligned16(kv_pages) || !aligned16(o) || !aligned16(scratch))
+    return fail(B200_ERR_MISALIGNED, "operands must be 16-byte aligned");
+  if (batch <= 0 || ctx <= 0 || n_heads <= 0 || n_pages <= 0 || page_size <= 0 || max_pages <= 0)
+    return fail(B200_ERR_BAD_SHAPE, "sizes must be positive");
+  AttnDecodeArgs a;
+  a.q = q; a.kv_pages = kv_pages; a.page_table = page_table; a.o = o; a.scratch = reinterpret_cast<float*>(scratch);
+  a.batch = batch; a.ctx = ctx; a.n_heads = n_heads; a.head_size = head_size; a.ldq = ldq; a.ldo = ldo;
+  a.n_pages = n_pages; a.page_size = page_size; a.max_pages = max_pages; a.d_local = n_heads * head_size;
+  a.dtype = dtype; a.n_splits = decode_pick_splits(batch, n_heads, ctx);
+  if (decode_scratch_floats(batch, n_heads, head_size, a.n_splits) * sizeof(float) > scratch_bytes)
+    return fail(B200_ERR_WORKSPACE, "decode attention scratch too small: %zu bytes given", scratch_bytes);
+  return launch_attn_decode(a, reinterpret_cast<cudaStream_t>(stream));
+}
+
+}  // extern "C"

@@ -27,6 +27,7 @@ constexpr int TBM = 128;      // tile rows (TMEM lanes)
 constexpr int TBK = 64;       // K elements per stage (128 bytes of bf16)
 constexpr int UMMA_K = 16;    // K per tcgen05.mma for 16-bit operands
 constexpr int TC_THREADS = 192;
+constexpr int kMnBoxBytes = 64 * TBK * 2;  // one TMA box of an MN-major operand: TBK rows of 64 elements
 
 template <int BN> struct TcCfg {
   static constexpr int kStages = (BN >= 256) ? 4 : 6;
@@ -43,7 +44,7 @@ enum : uint32_t {
   ST_EPILOGUE_TIMEOUT = 1u << 2,
 };
 
-template <int BN, int KIND, typename TOut>
+template <int BN, int KIND, typename TOut, bool AMN, bool BMN>
 __global__ void __launch_bounds__(TC_THREADS, 1)
     gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, int M, int N,
                    int K, EpiParams ep, uint32_t* status) {
@@ -101,8 +102,20 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
           if (!ok) break;
           uint8_t* sa = smem + stage * Cfg::kStageBytes;
           ptx::mbar_arrive_expect_tx(&full_bar[stage], Cfg::kStageBytes);
-          ptx::tma_load_2d(sa, &tmA, kb * TBK, m0, &full_bar[stage]);
-          ptx::tma_load_2d(sa + Cfg::kABytes, &tmB, kb * TBK, n0, &full_bar[stage]);
+          if constexpr (!AMN) {
+            ptx::tma_load_2d(sa, &tmA, kb * TBK, m0, &full_bar[stage]);
+          } else {  // operand stored [K, M]: one 64-wide box per 64 rows of the tile
+#pragma unroll
+            for (int i = 0; i < TBM / 64; ++i)
+              ptx::tma_load_2d(sa + i * kMnBoxBytes, &tmA, m0 + 64 * i, kb * TBK, &full_bar[stage]);
+          }
+          if constexpr (!BMN) {
+            ptx::tma_load_2d(sa + Cfg::kABytes, &tmB, kb * TBK, n0, &full_bar[stage]);
+          } else {
+#pragma unroll
+            for (int i = 0; i < BN / 64; ++i)
+              ptx::tma_load_2d(sa + Cfg::kABytes + i * kMnBoxBytes, &tmB, n0 + 64 * i, kb * TBK, &full_bar[stage]);
+          }
           if (++stage == S) { stage = 0; phase ^= 1u; }
         }
       }
@@ -110,7 +123,10 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
     __syncwarp();
   } else if (warp == 1) {
     if (lane == 0) {
-      constexpr uint32_t idesc = ptx::idesc_bf16_f32(TBM, BN);
+      constexpr uint32_t idesc = ptx::idesc_bf16_f32(TBM, BN) | (AMN ? (1u << 15) : 0u) | (BMN ? (1u << 16) : 0u);
+      // encoded (16-byte units) start-address step per 16 K-elements
+      constexpr uint64_t a_step = AMN ? (16 * 128) / 16 : 2;
+      constexpr uint64_t b_step = BMN ? (16 * 128) / 16 : 2;
       int stage = 0;
       uint32_t phase = 0;
       int acc = 0;
@@ -126,13 +142,14 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
           if (!ok) break;
           ptx::tc_fence_after_sync();
           const uint32_t sa = ptx::smem_u32(smem + stage * Cfg::kStageBytes);
-          const uint64_t adesc = ptx::smem_desc_sw128(sa);
-          const uint64_t bdesc = ptx::smem_desc_sw128(sa + Cfg::kABytes);
+          const uint64_t adesc = AMN ? ptx::smem_desc_sw128_mn(sa, kMnBoxBytes) : ptx::smem_desc_sw128(sa);
+          const uint64_t bdesc = BMN ? ptx::smem_desc_sw128_mn(sa + Cfg::kABytes, kMnBoxBytes)
+                                     : ptx::smem_desc_sw128(sa + Cfg::kABytes);
 #pragma unroll
           for (int k = 0; k < TBK / UMMA_K; ++k) {
-            // advancing K by 16 elements = 32 bytes = 2 units of the encoded start address
-            ptx::mma_bf16_ss(d_tmem, adesc + (uint64_t)(2 * k), bdesc + (uint64_t)(2 * k), idesc,
-                             (kb > 0 || k > 0) ? 1u : 0u);
+            // K-major: 16 elements further along a 128-byte row = 32 bytes;
+            // MN-major: 16 rows of 128 bytes further down.
+            ptx::mma_bf16_ss(d_tmem, adesc + a_step * k, bdesc + b_step * k, idesc, (kb > 0 || k > 0) ? 1u : 0u);
           }
           ptx::mma_commit(&empty_bar[stage]);
           if (++stage == S) { stage = 0; phase ^= 1u; }
@@ -219,13 +236,17 @@ int32_t make_map(CUtensorMap* map, const void* base, int rows, int cols, int ld,
   return B200_OK;
 }
 
-template <int BN, int KIND, typename TOut>
+template <int BN, int KIND, typename TOut, bool AMN, bool BMN>
 int32_t launch_cfg(const GemmArgs& g, cudaStream_t stream) {
   using Cfg = TcCfg<BN>;
   CUtensorMap tmA, tmB;
-  B200_TRY(make_map(&tmA, g.A, g.M, g.K, g.lda, TBM));
-  B200_TRY(make_map(&tmB, g.B, g.N, g.K, g.ldb, BN));
-  auto kern = gemm_tc_kernel<BN, KIND, TOut>;
+  // K-major operand: [rows = M or N, cols = K], box 64 (K) x tile rows.
+  // MN-major operand: stored [K, M or N], box 64 (M or N) x TBK rows of K.
+  if (AMN) B200_TRY(make_map(&tmA, g.A, g.K, g.M, g.lda, TBK));
+  else B200_TRY(make_map(&tmA, g.A, g.M, g.K, g.lda, TBM));
+  if (BMN) B200_TRY(make_map(&tmB, g.B, g.K, g.N, g.ldb, TBK));
+  else B200_TRY(make_map(&tmB, g.B, g.N, g.K, g.ldb, BN));
+  auto kern = gemm_tc_kernel<BN, KIND, TOut, AMN, BMN>;
   static bool attr_set = false;  // per instantiation
   if (!attr_set) {
     B200_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
@@ -238,24 +259,30 @@ int32_t launch_cfg(const GemmArgs& g, cudaStream_t stream) {
   return B200_OK;
 }
 
-template <int KIND, typename TOut>
+template <int KIND, typename TOut, bool AMN, bool BMN>
 int32_t launch_bn(const GemmArgs& g, cudaStream_t stream) {
   // Wide tiles when they still fill the machine, narrower ones otherwise.
   const int sms = sm_count();
   const long t256 = (long)cdiv(g.M, TBM) * cdiv(g.N, 256);
-  if (g.N % 256 == 0 && t256 >= 2L * sms) return launch_cfg<256, KIND, TOut>(g, stream);
+  if (g.N % 256 == 0 && t256 >= 2L * sms) return launch_cfg<256, KIND, TOut, AMN, BMN>(g, stream);
   const long t128 = (long)cdiv(g.M, TBM) * cdiv(g.N, 128);
-  if (t128 >= sms || g.N >= 128) return launch_cfg<128, KIND, TOut>(g, stream);
-  return launch_cfg<64, KIND, TOut>(g, stream);
+  if (t128 >= sms || g.N >= 128) return launch_cfg<128, KIND, TOut, AMN, BMN>(g, stream);
+  return launch_cfg<64, KIND, TOut, AMN, BMN>(g, stream);
 }
 
 template <typename TOut>
 int32_t launch_kind(const GemmArgs& g, cudaStream_t stream) {
+  if (g.ta || g.tb) {
+    if (g.kind != EPI_STORE) return fail(B200_ERR_UNSUPPORTED, "fused epilogues need both operands K-major");
+    if (g.ta && g.tb) return launch_bn<EPI_STORE, TOut, true, true>(g, stream);
+    if (g.ta) return launch_bn<EPI_STORE, TOut, true, false>(g, stream);
+    return launch_bn<EPI_STORE, TOut, false, true>(g, stream);
+  }
   switch (g.kind) {
-    case EPI_STORE: return launch_bn<EPI_STORE, TOut>(g, stream);
-    case EPI_ROPE: return launch_bn<EPI_ROPE, TOut>(g, stream);
-    case EPI_RESID: return launch_bn<EPI_RESID, TOut>(g, stream);
-    case EPI_SWIGLU: return launch_bn<EPI_SWIGLU, TOut>(g, stream);
+    case EPI_STORE: return launch_bn<EPI_STORE, TOut, false, false>(g, stream);
+    case EPI_ROPE: return launch_bn<EPI_ROPE, TOut, false, false>(g, stream);
+    case EPI_RESID: return launch_bn<EPI_RESID, TOut, false, false>(g, stream);
+    case EPI_SWIGLU: return launch_bn<EPI_SWIGLU, TOut, false, false>(g, stream);
   }
   return fail(B200_ERR_INVALID_ARG, "unknown epilogue kind %d", g.kind);
 }
@@ -263,15 +290,17 @@ int32_t launch_kind(const GemmArgs& g, cudaStream_t stream) {
 }  // namespace
 
 bool gemm_tc_supports(const GemmArgs& g) {
-  return g.in_dtype == B200_BF16 && !g.ta && !g.tb && g.M > 0 && g.N > 0 && g.K > 0 && g.N % 16 == 0 &&
-         g.lda % 8 == 0 && g.ldb % 8 == 0 && g.K % 8 == 0 && aligned16(g.A) && aligned16(g.B) &&
-         aligned16(g.epi.out) && g.epi.ldo % 8 == 0;
+  if ((g.ta || g.tb) && g.kind != EPI_STORE) return false;
+  // TMA needs 16-byte aligned bases and row pitches; the extent of the
+  // contiguous dimension needs no alignment (out-of-range elements read zero).
+  return g.in_dtype == B200_BF16 && g.M > 0 && g.N > 0 && g.K > 0 && g.N % 16 == 0 && g.lda % 8 == 0 &&
+         g.ldb % 8 == 0 && aligned16(g.A) && aligned16(g.B) && aligned16(g.epi.out) && g.epi.ldo % 8 == 0;
 }
 
 int32_t launch_gemm_tc(const GemmArgs& g, cudaStream_t stream) {
   if (!gemm_tc_supports(g))
     return fail(B200_ERR_UNSUPPORTED,
-                "tcgen05 gemm needs bf16 K-major operands, 16-byte aligned rows and N %% 16 == 0 (M=%d N=%d K=%d)",
+                "tcgen05 gemm needs bf16 operands, 16-byte aligned rows and N %% 16 == 0 (M=%d N=%d K=%d)",
                 g.M, g.N, g.K);
   if (g.out_dtype == B200_BF16) return launch_kind<bf16>(g, stream);
   if (g.out_dtype == B200_F32) return launch_kind<float>(g, stream);

@@ -143,7 +143,22 @@ __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t smem_addr) {
   return d;
 }
 
-// Instruction descriptor: bf16 x bf16 -> fp32, both operands K-major, M x N tile.
+// Same for an MN-major tile (the M or N index is contiguous in memory): TMA
+// boxes of 64 elements x R rows of K, each row 128 B, 128-byte swizzle.  Eight
+// K-rows form a 1024-byte group (stride byte offset); the next 64 elements of
+// M/N live in the next box, `box_bytes` further (leading byte offset).
+__device__ __forceinline__ uint64_t smem_desc_sw128_mn(uint32_t smem_addr, uint32_t box_bytes) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_addr & 0x3FFFFu) >> 4);
+  d |= (uint64_t)((box_bytes >> 4) & 0x3FFFu) << 16;
+  d |= (uint64_t)(1024 >> 4) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)2 << 61;
+  return d;
+}
+
+// Instruction descriptor: bf16 x bf16 -> fp32, both operands K-major, M x N tile
+// (bit 15 / bit 16 select an MN-major A / B operand).
 __host__ __device__ constexpr uint32_t idesc_bf16_f32(int M, int N) {
   return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
 }

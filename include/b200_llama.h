@@ -214,6 +214,21 @@ B200_API int32_t b200_attention(const void* q, const void* k, const void* v, voi
                                 int32_t seq, int32_t n_heads, int32_t head_size, int32_t ldq, int32_t ldkv,
                                 int32_t ldo, int32_t dtype, int32_t impl, b200_stream_t stream);
 
+/* Decode attention over the paged cache (test/llama.py:177-209 with a cache of
+ * ctx rows): one query row per (sequence, head).
+ *   q          [batch, ldq] of `dtype`
+ *   kv_pages   one layer of the cache: [2, n_pages, page_size, n_heads*head_size]
+ *   page_table int32 [batch, max_pages]
+ *   o          [batch, ldo]
+ *   scratch    caller-owned, b200_attention_decode_scratch_bytes() bytes: the
+ *              per-split partial results between the two kernels */
+B200_API int32_t b200_attention_decode_scratch_bytes(int32_t batch, int32_t n_heads, int32_t head_size, int32_t ctx,
+                                                     size_t* bytes);
+B200_API int32_t b200_attention_decode(const void* q, const void* kv_pages, const int32_t* page_table, void* o,
+                                       void* scratch, size_t scratch_bytes, int32_t batch, int32_t ctx,
+                                       int32_t n_heads, int32_t head_size, int32_t ldq, int32_t ldo, int32_t n_pages,
+                                       int32_t page_size, int32_t max_pages, int32_t dtype, b200_stream_t stream);
+
 /* ---- communicator (NCCL over NVLink) -------------------------------------- */
 
 B200_API int32_t b200_comm_unique_id(void* id128 /* 128 bytes out */);

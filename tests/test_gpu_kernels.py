@@ -79,7 +79,7 @@ def test_gemm_rejects_bad_arguments():
         B.gemm(a, torch.zeros(8, 16, device=DEV, dtype=torch.bfloat16))  # N not a multiple of 16
     assert e.value.status == 2
     with pytest.raises(B.B200Error):
-        B.gemm(a, a, ta=True, impl=1)  # tensor-core kernel does not take transposed operands
+        B.gemm(a.float(), a.float(), impl=1)  # the tensor-core kernel is bf16 only
 
 
 @pytest.mark.parametrize("rows,dim", [(7, 64), (256, 288), (1000, 768), (64, 4096)])
@@ -120,3 +120,50 @@ def test_attention_forward(impl, B_, S, H, hs, dtype):
     tol = 2e-5 if dtype == torch.float32 else 1e-2
     assert torch.allclose(o.double(), ro, rtol=tol, atol=tol)
     assert torch.allclose(lse.double(), rl, rtol=1e-4, atol=1e-4 if dtype == torch.float32 else 2e-2)
+
+
+def _decode_case(batch, ctx, H, hs, dtype, page, seed=0):
+    g = torch.Generator().manual_seed(seed)
+    d = H * hs
+    max_pages = (ctx + page - 1) // page
+    n_pages = batch * max_pages + 3
+    kv = torch.randn(2, n_pages, page, d, generator=g).to(dtype).to(DEV)
+    q = torch.randn(batch, d, generator=g).to(dtype).to(DEV)
+    table = torch.randperm(n_pages, generator=g)[: batch * max_pages].view(batch, max_pages).int().to(DEV)
+    return q, kv, table
+
+
+def _decode_ref(q, kv, table, ctx, H):
+    batch, d = q.shape
+    hs = d // H
+    page = kv.shape[2]
+    out = torch.empty(batch, d, dtype=torch.float64)
+    for b in range(batch):
+        rows = [(int(table[b, u // page]), u % page) for u in range(ctx)]
+        k = torch.stack([kv[0, p, r] for p, r in rows]).double().cpu().view(ctx, H, hs)
+        v = torch.stack([kv[1, p, r] for p, r in rows]).double().cpu().view(ctx, H, hs)
+        qq = q[b].double().cpu().view(H, hs)
+        att = torch.softmax(torch.einsum("he,uhe->hu", qq, k) / math.sqrt(hs), -1)
+        out[b] = torch.einsum("hu,uhe->he", att, v).reshape(d)
+    return out
+
+
+@pytest.mark.parametrize("batch,ctx,H,hs,dtype,page", [(1, 6, 6, 48, torch.float32, 16), (2, 700, 2, 64, torch.bfloat16, 64),
+                                                       (3, 333, 4, 128, torch.bfloat16, 32), (64, 130, 8, 128, torch.bfloat16, 128)])
+def test_attention_decode_paged(batch, ctx, H, hs, dtype, page):
+    q, kv, table = _decode_case(batch, ctx, H, hs, dtype, page)
+    o = B.attention_decode(q, kv, table, ctx, H)
+    ref = _decode_ref(q, kv, table, ctx, H)
+    tol = 2e-5 if dtype == torch.float32 else 1e-2
+    assert torch.allclose(o.double().cpu(), ref, rtol=tol, atol=tol)
+
+
+@pytest.mark.parametrize("ta,tb", [(True, False), (False, True), (True, True)])
+@pytest.mark.parametrize("M,N,K", [(128, 128, 64), (256, 256, 192), (2304, 768, 1024), (200, 144, 136)])
+def test_gemm_tensor_core_transposed_operands(ta, tb, M, N, K):
+    a = _ints((K, M) if ta else (M, K), 3)
+    b = _ints((K, N) if tb else (N, K), 4)
+    y = B.gemm(a, b, ta=ta, tb=tb, out_dtype=torch.float32, impl=1)
+    ref = (a.float().T if ta else a.float()) @ (b.float() if tb else b.float().T)
+    assert B.device_status() == 0
+    assert torch.equal(y, ref)
