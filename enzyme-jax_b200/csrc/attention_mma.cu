@@ -1,13 +1,368 @@
-// Tensor-core causal attention forward (bf16, head sizes 64 and 128).
+// Causal attention forward on the 5th-generation tensor cores (bf16, head size
+// 64 or 128): test/llama.py:177-209 of the reference for every query position,
+// flash-style (the score matrix never leaves the SM).
+//
+// A CTA owns 128 query rows of one (batch, head) and walks the key/value blocks
+// of 128 rows it may attend to.  Warp roles:
+//   warp 0      TMA producer: Q once, then K_j / V_j into a 2-stage ring
+//   warp 1      one lane issues tcgen05.mma:  S = Q K_j^T  (fp32, TMEM columns
+//               0..127) and, once the probabilities are in shared memory,
+//               O_j = P_j V_j (TMEM columns 128..128+hs)
+//   warps 2..5  softmax, one thread per query row: read S from TMEM, mask the
+//               diagonal block, running max / sum in fp32, write P as bf16 into
+//               shared memory in the swizzled K-major layout the MMA reads, then
+//               fold O_j into the fp32 output row kept in registers
+// V is consumed as an MN-major operand straight from its row-major layout.
+// TMEM use is 256 columns so that two CTAs share an SM and one CTA's softmax
+// overlaps the other's MMAs.  All waits are bounded.
+#include <cuda.h>
+
+#include <mutex>
+
 #include "attention.cuh"
+#include "ptx_sm100.cuh"
 
 namespace b200 {
 
-bool attn_fwd_mma_supports(const AttnArgs& a) { (void)a; return false; }
+namespace {
+
+constexpr int AQ = 128;   // query rows per CTA
+constexpr int AK = 128;   // keys per block
+constexpr int A_THREADS = 192;
+constexpr int SUB = 128 * 128;  // bytes of one [128 rows x 64 columns] bf16 sub-tile
+
+enum : uint32_t { ST_ATTN_TIMEOUT = 1u << 4, ST_ATTN_ALIGN = 1u << 5 };
+
+template <int HS> struct ACfg {
+  static constexpr int kSubs = HS / 64;               // 64-column sub-tiles per row block
+  static constexpr int kTileBytes = kSubs * SUB;      // Q, K_j or V_j
+  static constexpr int kStages = 2;
+  static constexpr int kPBytes = 2 * SUB;             // P: 128 rows x 128 keys
+  static constexpr int kQOff = 0;
+  static constexpr int kKOff = kTileBytes;
+  static constexpr int kVOff = kKOff + kStages * kTileBytes;
+  static constexpr int kPOff = kVOff + kStages * kTileBytes;
+  static constexpr int kBarOff = kPOff + kPBytes;
+  static constexpr int kSmemBytes = kBarOff + 256;
+  static constexpr int kTmemCols = 256;
+  static constexpr int kOCol = 128;
+};
+
+__device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* map, int x, int y, int z, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];" ::
+          "r"(ptx::smem_u32(dst)),
+      "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(z), "r"(ptx::smem_u32(bar))
+      : "memory");
+}
+
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
+  uint32_t r[32];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+#pragma unroll
+  for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+template <int HS>
+__global__ void __launch_bounds__(A_THREADS)
+    attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                       const __grid_constant__ CUtensorMap tmV, bf16* __restrict__ o, float* __restrict__ lse, int seq,
+                       int n_heads, int ldo, float scale, uint32_t* status) {
+  using C = ACfg<HS>;
+  extern __shared__ __align__(1024) uint8_t smem[];
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::kBarOff);
+  uint64_t* q_full = bars;          // Q landed
+  uint64_t* kv_full = bars + 1;     // [2] K_j and V_j landed
+  uint64_t* kv_empty = bars + 3;    // [2] both MMAs of block j are done with the stage
+  uint64_t* s_full = bars + 5;      // S_j complete in TMEM
+  uint64_t* s_empty = bars + 6;     // softmax has read S_j
+  uint64_t* p_full = bars + 7;      // P_j is in shared memory
+  uint64_t* o_full = bars + 8;      // O_j complete in TMEM (P_j and the stage are free)
+  uint64_t* o_empty = bars + 9;     // softmax has read O_j
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 10);
+  volatile uint32_t* abort_flag = tmem_slot + 1;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int qt = (int)gridDim.x - 1 - (int)blockIdx.x;  // long tiles first
+  const int h = blockIdx.y, b = blockIdx.z;
+  const int t0 = qt * AQ;
+  const int n_blocks = qt + 1;  // key blocks 0..qt
+
+  if (threadIdx.x == 0) {
+    if (ptx::smem_u32(smem) & 1023u) {
+      atomicOr(status, ST_ATTN_ALIGN);
+      *abort_flag = 1u;
+    } else {
+      *abort_flag = 0u;
+    }
+    ptx::mbar_init(q_full, 1);
+    for (int i = 0; i < 2; ++i) {
+      ptx::mbar_init(&kv_full[i], 1);
+      ptx::mbar_init(&kv_empty[i], 1);
+    }
+    ptx::mbar_init(s_full, 1);
+    ptx::mbar_init(s_empty, 128);
+    ptx::mbar_init(p_full, 128);
+    ptx::mbar_init(o_full, 1);
+    ptx::mbar_init(o_empty, 128);
+    ptx::fence_barrier_init();
+    ptx::tma_prefetch_desc(&tmQ);
+    ptx::tma_prefetch_desc(&tmK);
+    ptx::tma_prefetch_desc(&tmV);
+  }
+  if (warp == 1) {
+    ptx::tmem_alloc(tmem_slot, C::kTmemCols);
+    ptx::tmem_relinquish();
+  }
+  ptx::tc_fence_before_sync();
+  __syncthreads();
+  ptx::tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+  const bool aborted = *abort_flag != 0u;
+
+  if (aborted) {
+    // fall through to the common exit
+  } else if (warp == 0) {
+    if (lane == 0) {
+      ptx::mbar_arrive_expect_tx(q_full, C::kTileBytes);
+#pragma unroll
+      for (int s = 0; s < C::kSubs; ++s) tma_load_3d(smem + C::kQOff + s * SUB, &tmQ, h * HS + 64 * s, t0, b, q_full);
+      bool ok = true;
+      for (int j = 0; j < n_blocks && ok; ++j) {
+        const int st = j & 1;
+        const uint32_t ph = (uint32_t)(j >> 1) & 1u;
+        ok = ptx::mbar_wait(&kv_empty[st], ph ^ 1u, abort_flag, status, ST_ATTN_TIMEOUT);
+        if (!ok) break;
+        ptx::mbar_arrive_expect_tx(&kv_full[st], 2 * C::kTileBytes);
+#pragma unroll
+        for (int s = 0; s < C::kSubs; ++s) {
+          tma_load_3d(smem + C::kKOff + st * C::kTileBytes + s * SUB, &tmK, h * HS + 64 * s, j * AK, b, &kv_full[st]);
+          tma_load_3d(smem + C::kVOff + st * C::kTileBytes + s * SUB, &tmV, h * HS + 64 * s, j * AK, b, &kv_full[st]);
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc_s = ptx::idesc_bf16_f32(AQ, AK);
+      constexpr uint32_t idesc_o = ptx::idesc_bf16_f32(AQ, HS) | (1u << 16);  // V is MN-major
+      const uint32_t q_addr = ptx::smem_u32(smem + C::kQOff);
+      const uint32_t p_addr = ptx::smem_u32(smem + C::kPOff);
+      bool ok = ptx::mbar_wait(q_full, 0, abort_flag, status, ST_ATTN_TIMEOUT);
+      for (int j = 0; j < n_blocks && ok; ++j) {
+        const int st = j & 1;
+        const uint32_t ph = (uint32_t)(j >> 1) & 1u;
+        const uint32_t jp = (uint32_t)j & 1u;
+        ok = ptx::mbar_wait(&kv_full[st], ph, abort_flag, status, ST_ATTN_TIMEOUT) &&
+             ptx::mbar_wait(s_empty, jp ^ 1u, abort_flag, status, ST_ATTN_TIMEOUT);
+        if (!ok) break;
+        ptx::tc_fence_after_sync();
+        const uint32_t k_addr = ptx::smem_u32(smem + C::kKOff + st * C::kTileBytes);
+        const uint32_t v_addr = ptx::smem_u32(smem + C::kVOff + st * C::kTileBytes);
+#pragma unroll
+        for (int k = 0; k < HS / 16; ++k) {  // S = Q K^T, contraction over the head dimension
+          const uint32_t off = (uint32_t)((k >> 2) * SUB + (k & 3) * 32);
+          ptx::mma_bf16_ss(tmem_base, ptx::smem_desc_sw128(q_addr + off), ptx::smem_desc_sw128(k_addr + off), idesc_s,
+                           k > 0 ? 1u : 0u);
+        }
+        ptx::mma_commit(s_full);
+        ok = ptx::mbar_wait(p_full, jp, abort_flag, status, ST_ATTN_TIMEOUT) &&
+             ptx::mbar_wait(o_empty, jp ^ 1u, abort_flag, status, ST_ATTN_TIMEOUT);
+        if (!ok) break;
+        ptx::tc_fence_after_sync();
+#pragma unroll
+        for (int k = 0; k < AK / 16; ++k) {  // O_j = P V, contraction over the 128 keys of the block
+          const uint32_t poff = (uint32_t)((k >> 2) * SUB + (k & 3) * 32);
+          ptx::mma_bf16_ss(tmem_base + C::kOCol, ptx::smem_desc_sw128(p_addr + poff),
+                           ptx::smem_desc_sw128_mn(v_addr + (uint32_t)(k * 16 * 128), SUB), idesc_o, k > 0 ? 1u : 0u);
+        }
+        ptx::mma_commit(o_full);
+        ptx::mma_commit(&kv_empty[st]);
+      }
+    }
+    __syncwarp();
+  } else {
+    const int qd = warp & 3;
+    const int row = qd * 32 + lane;  // row of the tile == TMEM lane
+    const int t = t0 + row;
+    const uint32_t t_s = tmem_base + ((uint32_t)(qd * 32) << 16);
+    const uint32_t t_o = t_s + C::kOCol;
+    const float sl2 = scale * 1.4426950408889634f;  // scores are scaled inside the exp2
+    uint8_t* p_row = smem + C::kPOff + row * 128;
+    float acc[HS];
+#pragma unroll
+    for (int i = 0; i < HS; ++i) acc[i] = 0.f;
+    float m = -INFINITY, l = 0.f;
+    bool ok = true;
+    for (int j = 0; j < n_blocks; ++j) {
+      const uint32_t jp = (uint32_t)j & 1u;
+      ok = ptx::mbar_wait(s_full, jp, abort_flag, status, ST_ATTN_TIMEOUT);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      ptx::tc_fence_after_sync();
+      const bool diag = (j == qt);
+      const int u0 = j * AK;
+      // pass 1: row maximum
+      float bm = -INFINITY;
+#pragma unroll
+      for (int c = 0; c < AK; c += 32) {
+        float v[32];
+        tmem_ld32(t_s + (uint32_t)c, v);
+        ptx::tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const float s = (diag && (u0 + c + i > t)) ? -INFINITY : v[i];
+          bm = fmaxf(bm, s);
+        }
+      }
+      const float nm = fmaxf(m, bm);
+      const float corr = exp2f((m - nm) * sl2);
+      const float nms = nm * sl2;
+      // pass 2: probabilities -> bf16 -> shared memory (swizzled K-major tile)
+      float rs = 0.f;
+#pragma unroll
+      for (int c = 0; c < AK; c += 32) {
+        float v[32];
+        tmem_ld32(t_s + (uint32_t)c, v);
+        ptx::tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const float s = (diag && (u0 + c + i > t)) ? -INFINITY : v[i];
+          v[i] = exp2f(fmaf(s, sl2, -nms));
+          rs += v[i];
+        }
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {  // four 16-byte pieces of 8 keys
+          const int ch = (c >> 3) + g;  // piece index 0..15 within the row of 128 keys
+          uint4 raw;
+          __nv_bfloat162* hp = reinterpret_cast<__nv_bfloat162*>(&raw);
+#pragma unroll
+          for (int i = 0; i < 4; ++i) hp[i] = __floats2bfloat162_rn(v[g * 8 + 2 * i], v[g * 8 + 2 * i + 1]);
+          *reinterpret_cast<uint4*>(p_row + (ch >> 3) * SUB + (((ch & 7) ^ (row & 7)) << 4)) = raw;
+        }
+      }
+      ptx::tc_fence_before_sync();
+      ptx::mbar_arrive(s_empty);
+      ptx::fence_proxy_async();  // make the generic-proxy writes of P visible to the MMA's async proxy
+      ptx::mbar_arrive(p_full);
+      l = l * corr + rs;
+#pragma unroll
+      for (int i = 0; i < HS; ++i) acc[i] *= corr;
+      m = nm;
+      ok = ptx::mbar_wait(o_full, jp, abort_flag, status, ST_ATTN_TIMEOUT);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      ptx::tc_fence_after_sync();
+#pragma unroll
+      for (int c = 0; c < HS; c += 32) {
+        float v[32];
+        tmem_ld32(t_o + (uint32_t)c, v);
+        ptx::tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) acc[c + i] += v[i];
+      }
+      ptx::tc_fence_before_sync();
+      ptx::mbar_arrive(o_empty);
+    }
+    if (ok && t < seq) {
+      const float inv = 1.f / l;
+      bf16* dst = o + ((size_t)b * seq + t) * ldo + h * HS;
+#pragma unroll
+      for (int c = 0; c < HS; c += 8) {
+        float v[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[i] = acc[c + i] * inv;
+        store8(dst + c, v);
+      }
+      if (lse) lse[((size_t)b * n_heads + h) * seq + t] = m * scale + __logf(l);
+    }
+  }
+
+  ptx::tc_fence_before_sync();
+  __syncthreads();
+  if (*abort_flag) {
+    for (int i = 0; i < 1000; ++i) __nanosleep(1000);
+  }
+  if (warp == 1) {
+    ptx::tc_fence_after_sync();
+    ptx::tmem_dealloc(tmem_base, C::kTmemCols);
+  }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  });
+  return fn;
+}
+
+// [batch][seq][cols] bf16 with row pitch ld; box = 64 columns x 128 rows of one sequence.
+int32_t make_map3(CUtensorMap* map, const void* base, int batch, int seq, int cols, int ld) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return fail(B200_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+  cuuint64_t dims[3] = {(cuuint64_t)cols, (cuuint64_t)seq, (cuuint64_t)batch};
+  cuuint64_t strides[2] = {(cuuint64_t)ld * 2, (cuuint64_t)seq * ld * 2};
+  cuuint32_t box[3] = {64, 128, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(B200_ERR_CUDA, "cuTensorMapEncodeTiled (attention) failed with %d", (int)r);
+  return B200_OK;
+}
+
+template <int HS>
+int32_t launch_hs(const AttnArgs& a, cudaStream_t stream) {
+  using C = ACfg<HS>;
+  CUtensorMap tq, tk, tv;
+  const int cols = a.n_heads * HS;
+  B200_TRY(make_map3(&tq, a.q, a.batch, a.seq, cols, a.ldq));
+  B200_TRY(make_map3(&tk, a.k, a.batch, a.seq, cols, a.ldkv));
+  B200_TRY(make_map3(&tv, a.v, a.batch, a.seq, cols, a.ldkv));
+  auto kern = attn_fwd_tc_kernel<HS>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    B200_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes));
+    attr_set = true;
+  }
+  dim3 grid(cdiv(a.seq, AQ), a.n_heads, a.batch);
+  kern<<<grid, A_THREADS, C::kSmemBytes, stream>>>(tq, tk, tv, (bf16*)a.o, a.lse, a.seq, a.n_heads, a.ldo,
+                                                   1.f / sqrtf((float)HS), device_status_word());
+  B200_LAUNCH_OK("attn_fwd_tc_kernel");
+  return B200_OK;
+}
+
+}  // namespace
+
+bool attn_fwd_mma_supports(const AttnArgs& a) {
+  return a.dtype == B200_BF16 && (a.head_size == 64 || a.head_size == 128) && a.ldq % 8 == 0 && a.ldkv % 8 == 0 &&
+         a.ldo % 8 == 0 && aligned16(a.q) && aligned16(a.k) && aligned16(a.v) && aligned16(a.o) && a.batch > 0 &&
+         a.seq > 0 && a.n_heads > 0;
+}
 
 int32_t launch_attn_fwd_mma(const AttnArgs& a, cudaStream_t stream) {
-  (void)a; (void)stream;
-  return fail(B200_ERR_UNSUPPORTED, "tensor-core attention does not cover this problem");
+  if (!attn_fwd_mma_supports(a))
+    return fail(B200_ERR_UNSUPPORTED, "tensor-core attention needs bf16, head size 64 or 128 and 16-byte aligned rows");
+  if (a.head_size == 64) return launch_hs<64>(a, stream);
+  return launch_hs<128>(a, stream);
 }
 
 }  // namespace b200

@@ -109,7 +109,8 @@ def _attn_ref(q, k, v, B_, S, H):
 @pytest.mark.parametrize("impl", [0, 2])
 @pytest.mark.parametrize("B_,S,H,hs,dtype", [(1, 256, 6, 48, torch.float32), (2, 100, 2, 32, torch.float32),
                                              (2, 256, 4, 64, torch.bfloat16), (1, 384, 2, 128, torch.bfloat16),
-                                             (3, 33, 2, 16, torch.bfloat16)])
+                                             (3, 33, 2, 16, torch.bfloat16), (2, 200, 3, 64, torch.bfloat16),
+                                             (2, 1024, 2, 64, torch.bfloat16), (2, 300, 2, 128, torch.bfloat16)])
 def test_attention_forward(impl, B_, S, H, hs, dtype):
     g = torch.Generator().manual_seed(2)
     qkv = torch.randn(B_ * S, 3 * H * hs, generator=g).to(dtype).to(DEV)
