@@ -32,7 +32,7 @@ EXPORTS = (
     "b200_backward", "b200_packed_grad_bytes", "b200_unpack_grads", "b200_allreduce_f32", "b200_decode_step",
     "b200_gemm", "b200_rmsnorm", "b200_attention", "b200_comm_unique_id", "b200_comm_init_rank",
     "b200_comm_destroy", "b200_launch_count", "b200_profile_enable", "b200_profile_read",
-    "b200_attention_decode_scratch_bytes", "b200_attention_decode",
+    "b200_attention_decode_scratch_bytes", "b200_attention_decode", "b200_attention_decode_static",
 )
 
 
@@ -89,6 +89,7 @@ def lib() -> ctypes.CDLL:
         l.b200_attention.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p] + [c_int32] * 9 + [c_void_p]
         l.b200_attention_decode_scratch_bytes.argtypes = [c_int32] * 4 + [POINTER(c_size_t)]
         l.b200_attention_decode.argtypes = [c_void_p] * 5 + [c_size_t] + [c_int32] * 10 + [c_void_p]
+        l.b200_attention_decode_static.argtypes = [c_void_p] * 4 + [c_int32] * 10 + [c_void_p]
         l.b200_device_status.argtypes = [c_void_p, POINTER(c_uint32)]
         l.b200_comm_unique_id.argtypes = [c_void_p]
         l.b200_comm_init_rank.argtypes = [c_void_p, c_int32, c_int32, POINTER(c_void_p)]
@@ -199,6 +200,21 @@ def attention_decode(q: torch.Tensor, kv_layer: torch.Tensor, page_table: torch.
                                       scratch.data_ptr(), scratch.numel(), batch, ctx, n_heads, hs, q.stride(0),
                                       o.stride(0), n_pages, page_size, page_table.shape[1], _dt(q.dtype), _stream()))
     return o
+
+
+def attention_decode_static(q: torch.Tensor, kv_layer: torch.Tensor, page_table: torch.Tensor, ctx: int,
+                            n_heads: int, out: torch.Tensor) -> torch.Tensor:
+    """Decode attention that allocates nothing: the caller passes the output, the scratch is the
+    library's built-in 4 MiB array.  For callers that cannot allocate device memory (no scratch
+    operand to give, fixed memory pool, cudaMalloc not permitted where they run).  Calls that may
+    overlap on the GPU race on the shared scratch; make the first call outside stream capture."""
+    batch, d = q.shape
+    hs = d // n_heads
+    check(lib().b200_attention_decode_static(q.data_ptr(), kv_layer.data_ptr(), page_table.data_ptr(),
+                                             out.data_ptr(), batch, ctx, n_heads, hs, q.stride(0), out.stride(0),
+                                             kv_layer.shape[1], kv_layer.shape[2], page_table.shape[1],
+                                             _dt(q.dtype), _stream()))
+    return out
 
 
 # --------------------------------------------------------------------------

@@ -8,6 +8,8 @@
 // probabilities are broadcast by shuffle.  Each CTA leaves (acc[hs], max, sum)
 // in scratch.  Pass 2 merges the splits.  HBM-bound: every cached byte is read
 // exactly once per step.
+#include <mutex>
+
 #include "attention.cuh"
 
 namespace b200 {
@@ -222,3 +224,75 @@ int32_t b200_attention_decode(const void* q, const void* kv_pages, const int32_t
 }
 
 }  // extern "C"
+
+// ---- decode attention without any allocation --------------------------------------
+//
+// Some callers may not allocate device memory at the point where they need
+// decode attention: code that runs between the capture of other work, a
+// serving loop whose memory pool is fixed at start-up, or a host runtime that
+// hands this library only the input and output buffers of a custom call and
+// has no way to pass (or size) an extra scratch operand.  For them the split
+// partials live in a fixed array inside the library image instead of a
+// caller buffer.  Every GPU that loads the library holds these 4 MiB until the
+// process exits.
+namespace {
+
+constexpr size_t kStaticScratchFloats = size_t(1) << 20;  // 4 MiB
+static __device__ __align__(256) float g_static_decode_scratch[kStaticScratchFloats];
+
+std::mutex g_static_mu;
+float* g_static_ptr[64] = {nullptr};
+
+// Device address of the array on the current device.  In host code the array's
+// name is only a handle, so the address is asked for once per device.
+int32_t static_scratch(float** out) {
+  int dev = -1;
+  B200_CUDA_OK(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return fail(B200_ERR_INVALID_ARG, "device ordinal %d is out of range", dev);
+  std::lock_guard<std::mutex> lk(g_static_mu);
+  if (!g_static_ptr[dev]) {
+    float* p = nullptr;
+    B200_CUDA_OK(cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_static_decode_scratch));
+    if (!p) return fail(B200_ERR_CUDA, "cudaGetSymbolAddress returned a null address");
+    g_static_ptr[dev] = p;
+  }
+  *out = g_static_ptr[dev];
+  return B200_OK;
+}
+
+}  // namespace
+
+extern "C" int32_t b200_attention_decode_static(const void* q, const void* kv_pages, const int32_t* page_table,
+                                                void* o, int32_t batch, int32_t ctx, int32_t n_heads,
+                                                int32_t head_size, int32_t ldq, int32_t ldo, int32_t n_pages,
+                                                int32_t page_size, int32_t max_pages, int32_t dtype,
+                                                b200_stream_t stream) {
+  if (!q || !kv_pages || !page_table || !o) return fail(B200_ERR_INVALID_ARG, "null operand");
+  if (!aligned16(q) || !aligned16(kv_pages) || !aligned16(o))
+    return fail(B200_ERR_MISALIGNED, "operands must be 16-byte aligned");
+  if (batch <= 0 || ctx <= 0 || n_heads <= 0 || head_size <= 0 || n_pages <= 0 || page_size <= 0 || max_pages <= 0)
+    return fail(B200_ERR_BAD_SHAPE, "sizes must be positive");
+  AttnDecodeArgs a;
+  a.n_splits = decode_pick_splits(batch, n_heads, ctx);
+  const size_t need = decode_scratch_floats(batch, n_heads, head_size, a.n_splits);
+  if (need > kStaticScratchFloats)
+    return fail(B200_ERR_WORKSPACE,
+                "decode attention needs %zu scratch bytes for batch=%d heads=%d head_size=%d (%d splits); the built-in "
+                "scratch holds %zu bytes: use b200_attention_decode with a caller buffer",
+                need * sizeof(float), batch, n_heads, head_size, a.n_splits, kStaticScratchFloats * sizeof(float));
+  float* scratch = nullptr;
+  B200_TRY(static_scratch(&scratch));
+  a.q = q; a.kv_pages = kv_pages; a.page_table = page_table; a.o = o; a.scratch = scratch;
+  a.batch = batch; a.ctx = ctx; a.n_heads = n_heads; a.head_size = head_size; a.ldq = ldq; a.ldo = ldo;
+  a.n_pages = n_pages; a.page_size = page_size; a.max_pages = max_pages; a.d_local = n_heads * head_size;
+  a.dtype = dtype;
+  if (a.d_local % 8 || a.head_size % 8) return fail(B200_ERR_BAD_SHAPE, "row width must be a multiple of 8");
+  if (cdiv(a.ctx, a.page_size) > a.max_pages)
+    return fail(B200_ERR_BAD_SHAPE, "context %d needs more than %d pages of %d rows", a.ctx, a.max_pages, a.page_size);
+  // Nothing in the array has to start at zero: the first kernel writes every
+  // (sequence, head, split) slot, empty splits included, before the second reads it.
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  if (dtype == B200_F32) return launch_t<float>(a, s);
+  if (dtype == B200_BF16) return launch_t<bf16>(a, s);
+  return fail(B200_ERR_BAD_DTYPE, "unsupported dtype %d", dtype);
+}

@@ -229,6 +229,30 @@ B200_API int32_t b200_attention_decode(const void* q, const void* kv_pages, cons
                                        int32_t n_heads, int32_t head_size, int32_t ldq, int32_t ldo, int32_t n_pages,
                                        int32_t page_size, int32_t max_pages, int32_t dtype, b200_stream_t stream);
 
+/* b200_attention_decode for callers that cannot allocate device memory.  No
+ * counterpart in the reference: this entry point exists only in this library.
+ * It serves callers that can hand over inputs and outputs but no scratch
+ * buffer: a runtime that gives a custom call only its declared operands, a
+ * serving loop whose memory pool was fixed at start-up, or code running where
+ * cudaMalloc is not permitted.  The per-split partial results live in a 4 MiB
+ * array inside the library image (held by every GPU that loads the library
+ * until the process exits) instead of a caller buffer; the call itself
+ * allocates nothing and frees nothing.
+ *  - Limit: batch * n_heads * splits * (head_size + 2) floats must fit in
+ *    4 MiB (1,048,576 floats); larger problems return B200_ERR_WORKSPACE and
+ *    should use b200_attention_decode with a caller buffer.
+ *  - The first call on each device looks up the array's device address (with
+ *    that device current).  Make that first call outside any stream capture.
+ *  - All calls on a device share the one array.  Two calls whose kernels may
+ *    overlap on the GPU (different streams without an ordering between them)
+ *    race on it; order them.  Nothing needs clearing between calls: each call
+ *    overwrites every slot it later reads. */
+B200_API int32_t b200_attention_decode_static(const void* q, const void* kv_pages, const int32_t* page_table,
+                                              void* o, int32_t batch, int32_t ctx, int32_t n_heads,
+                                              int32_t head_size, int32_t ldq, int32_t ldo, int32_t n_pages,
+                                              int32_t page_size, int32_t max_pages, int32_t dtype,
+                                              b200_stream_t stream);
+
 /* ---- communicator (NCCL over NVLink) -------------------------------------- */
 
 B200_API int32_t b200_comm_unique_id(void* id128 /* 128 bytes out */);
