@@ -225,6 +225,9 @@ def timed(fn, steps, world, dist):
 
 def run_prefill(args, rank, world, local, B, dist):
     cfg, dname, batch, seq, desc = WORKLOADS[args.workload]
+    if args.batch > 0:
+        batch = args.batch
+        desc += f" [batch overridden to {batch}]"
     dtype = torch.bfloat16 if dname == "bf16" else torch.float32
     dev = torch.device("cuda", local)
     pk = peaks()
@@ -333,6 +336,7 @@ def main():
     ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--batch", type=int, default=0, help="override the batch per rank (profiling on a small case)")
     args = ap.parse_args()
 
     rank = int(os.environ.get("RANK", "0"))
