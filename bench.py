@@ -197,10 +197,7 @@ def synth_weights(cfg, dtype, device, seed=1):
         if name.startswith("rms_"):
             w[name] = torch.ones(shapes[name], dtype=dtype, device=device)
         else:
-            t = torch.empty(shapes[name], dtype=torch.float32, device=device)
-            t.normal_(0.0, 0.02, generator=g)
-            w[name] = t.to(dtype)
-            del t
+            w[name] = torch.empty(shapes[name], dtype=dtype, device=device).normal_(0.0, 0.02, generator=g)
     return w
 
 
@@ -328,6 +325,200 @@ def run_prefill(args, rank, world, local, B, dist):
     return line
 
 
+def vjp_flops(cfg, batch, seq):
+    """Model flops of forward + VJP: 3x the GEMM flops, 3.5x the causal-attention flops."""
+    L, d, h, V = cfg["n_layers"], cfg["dim"], cfg["hidden_dim"], cfg["vocab_size"]
+    W = L * (4 * d * d + 3 * d * h) + V * d
+    T = batch * seq
+    return 3 * 2.0 * T * W + 3.5 * 4.0 * seq * seq * d * L * batch / 2.0
+
+
+def run_vjp(args, rank, world, local, B, dist):
+    """Config 3: forward + reverse mode w.r.t. all weights, global batch 64 x 1024 split over the
+    ranks (data parallel), 8-sequence micro-batches, one fp32 gradient all-reduce per step."""
+    cfg, dname, gbatch, seq, desc = WORKLOADS["c3"]
+    if args.batch > 0:
+        gbatch = args.batch * world
+        desc += f" [global batch overridden to {gbatch}]"
+    dev = torch.device("cuda", local)
+    pk = peaks()
+    per_rank = gbatch // world
+    micro = min(8, per_rank)
+    n_micro = per_rank // micro
+    comm = B.Comm(rank, world) if world > 1 else None
+    plan = B.Plan(cfg, torch.bfloat16)
+    w = synth_weights(cfg, torch.bfloat16, dev)
+    plan.pack_weights(w, with_transposed=True)
+    del w
+    gen = torch.Generator().manual_seed(200 + rank)
+    host_tokens = [torch.randint(0, cfg["vocab_size"], (micro, seq), generator=gen, dtype=torch.int32).pin_memory()
+                   for _ in range(n_micro)]
+    dev_tokens = [t.to(dev) for t in host_tokens]
+    tok_stage = torch.empty(micro, seq, dtype=torch.int32, device=dev)
+    g = torch.Generator(device=dev).manual_seed(300 + rank)
+    dlogits = torch.empty(micro, seq, cfg["vocab_size"], dtype=torch.float32, device=dev)
+    dlogits.normal_(0.0, 1.0, generator=g)
+    logits = torch.empty(micro, seq, cfg["vocab_size"], dtype=torch.float32, device=dev)
+    saved = plan.new_saved(micro, seq)
+    grads = plan.new_grads()
+    norm_host = torch.empty(1, dtype=torch.float32).pin_memory()
+
+    def step(i, e2e=False):
+        for mb in range(n_micro):
+            if e2e:
+                tok_stage.copy_(host_tokens[mb], non_blocking=True)
+                tok = tok_stage
+            else:
+                tok = dev_tokens[mb]
+            plan.forward(tok, saved=saved, logits=logits)
+            plan.backward(tok, dlogits, saved, grads, accumulate=mb > 0)
+        if comm:
+            comm.allreduce_f32(grads)
+        if e2e:
+            norm_host.copy_(grads[:1], non_blocking=True)
+            torch.cuda.current_stream().synchronize()
+
+    for i in range(args.warmup):
+        step(i)
+    torch.cuda.synchronize()
+    if B.device_status() != 0:
+        raise RuntimeError("device status word set during warm-up")
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+        time.sleep(0.3)
+    l0 = B.launch_count()
+    ms = timed(lambda i: step(i), args.steps, world, dist)
+    launches = B.launch_count() - l0
+    ms_e2e = timed(lambda i: step(i, True), args.steps, world, dist)
+    clocks = sampler.stop() if rank == 0 else None
+    B.profile_enable(True)
+    timed(lambda i: step(i), max(1, args.steps // 2), world, dist)
+    prof = B.profile_read()
+    B.profile_enable(False)
+    psteps = max(1, args.steps // 2)
+    tokens = gbatch * seq
+    value = tokens / (ms / args.steps / 1e3)
+    dom_name = max(prof, key=lambda k: prof[k]["ms"])
+    dom = prof[dom_name]
+    ach = dom["work"] / (dom["ms"] / 1e3) / 1e12 if dom["ms"] > 0 else 0.0
+    peak = pk["tflops_sustained"]
+    line = {
+        "metric": "tokens_per_second", "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": desc, "global_batch": gbatch, "seq_len": seq, "micro_batch": micro,
+                   "parallelism": f"dp{world}", "l2_policy": "per-micro-batch working set (2 GB of logits and cotangent, "
+                   "1.8 GB of saved activations) exceeds the 126 MB L2"},
+        "e2e": {"value": tokens / (ms_e2e / args.steps / 1e3), "unit": "tokens/s",
+                "h2d_bytes_per_step": per_rank * seq * 4, "d2h_bytes_per_step": 4, "ms_per_step": ms_e2e / args.steps,
+                "result": "first gradient element after the all-reduce (the gradients stay on the device)"},
+        "gpu_launches": launches,
+        "roofline": {"bound": "tensor", "kernel": dom_name, "achieved": ach, "peak": peak, "unit": "TFLOP/s",
+                     "frac": ach / peak, "traffic": None, "peak_source": pk["source"] + " (sustained bf16 matmul)",
+                     "launches": dom["launches"],
+                     "whole_step_frac": vjp_flops(cfg, per_rank, seq) / (ms / args.steps / 1e3) / 1e12 / peak,
+                     "kernels_ms_per_step": {k: v["ms"] / psteps for k, v in prof.items() if v["launches"]}},
+        "clocks": clocks,
+    }
+    if comm:
+        comm.destroy()
+    return line
+
+
+def run_decode(args, rank, world, local, B, dist):
+    """Config 5: 7B-shape decode, batch 64, 4096 cached tokens per sequence, one token per step."""
+    cfg, dname, batch, ctx0, desc = WORKLOADS["c5"]
+    if args.batch > 0:
+        batch = args.batch
+        desc += f" [batch overridden to {batch}]"
+    dev = torch.device("cuda", local)
+    pk = peaks()
+    tp = world
+    steps_total = 128
+    cfg = dict(cfg, seq_len=ctx0 + steps_total)
+    comm = B.Comm(rank, world) if tp > 1 else None
+    page = 128
+    max_pages = (ctx0 + steps_total + page - 1) // page
+    n_pages = batch * max_pages
+    plan = B.Plan(cfg, torch.bfloat16, tp_rank=rank, tp_size=tp, comm=comm)
+    # weights first (leaves + packed copy live together only here), then the cache:
+    # at tp=1 the cache is 141.7 GB and the packed weights 13.2 GB of the 180 GB
+    w = synth_weights(cfg, torch.bfloat16, dev)
+    plan.pack_weights(w)
+    torch.cuda.synchronize()
+    del w
+    torch.cuda.empty_cache()
+    kv = plan.new_kv_pages(n_pages, page)
+    g = torch.Generator(device=dev).manual_seed(400 + rank)
+    for l in range(cfg["n_layers"]):
+        kv[l].normal_(0.0, 1.0, generator=g)
+    table = torch.arange(n_pages, dtype=torch.int32, device=dev).view(batch, max_pages).contiguous()
+    gen = torch.Generator().manual_seed(500)
+    host_tok = torch.randint(0, cfg["vocab_size"], (batch,), generator=gen, dtype=torch.int32).pin_memory()
+    dev_tok = host_tok.to(dev)
+    tok_stage = torch.empty(batch, dtype=torch.int32, device=dev)
+    logits = torch.empty(batch, plan.vocab_local, dtype=torch.float32, device=dev)
+    host_logits = torch.empty(batch, plan.vocab_local, dtype=torch.float32).pin_memory()
+    steps = min(args.steps, steps_total - args.warmup)
+
+    def step(i, e2e=False, base=0):
+        pos = ctx0 + ((base + i) % steps_total)
+        if e2e:
+            tok_stage.copy_(host_tok, non_blocking=True)
+            plan.decode_step(pos, kv, table, tokens=tok_stage, logits=logits)
+            host_logits.copy_(logits, non_blocking=True)
+            torch.cuda.current_stream().synchronize()
+        else:
+            plan.decode_step(pos, kv, table, tokens=dev_tok, logits=logits)
+
+    for i in range(args.warmup):
+        step(i)
+    torch.cuda.synchronize()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+        time.sleep(0.3)
+    l0 = B.launch_count()
+    ms = timed(lambda i: step(i, base=args.warmup), steps, world, dist)
+    launches = B.launch_count() - l0
+    ms_e2e = timed(lambda i: step(i, True, base=args.warmup), steps, world, dist)
+    clocks = sampler.stop() if rank == 0 else None
+    B.profile_enable(True)
+    timed(lambda i: step(i, base=args.warmup), steps, world, dist)
+    prof = B.profile_read()
+    B.profile_enable(False)
+    if B.device_status() != 0:
+        raise RuntimeError("device status word set during the timed region")
+    L, d, h, V = cfg["n_layers"], cfg["dim"], cfg["hidden_dim"], cfg["vocab_size"]
+    W = L * (4 * d * d + 3 * d * h) + V * d
+    ctx_avg = ctx0 + args.warmup + steps / 2.0
+    bytes_step = (W * 2 + 2 * ctx_avg * d * 2 * L * batch) / tp  # weights once + K and V once, per GPU
+    att = prof["attention_decode"]
+    ach = att["work"] / (att["ms"] / 1e3) / 1e9 if att["ms"] > 0 else 0.0
+    value = batch / (ms / steps / 1e3)
+    line = {
+        "metric": "tokens_per_second", "value": value, "unit": "tokens/s", "n_gpus": world, "steps": steps,
+        "warmup": args.warmup, "ms_per_step": ms / steps, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": desc, "batch": batch, "context": ctx0, "parallelism": f"tp{tp}",
+                   "l2_policy": "each step streams the whole KV cache and all weights (>100 GB), far above L2"},
+        "e2e": {"value": batch / (ms_e2e / steps / 1e3), "unit": "tokens/s", "h2d_bytes_per_step": batch * 4,
+                "d2h_bytes_per_step": batch * plan.vocab_local * 4, "ms_per_step": ms_e2e / steps,
+                "result": "logits of the new token of every sequence"},
+        "gpu_launches": launches,
+        "roofline": {"bound": "hbm", "kernel": "attention_decode", "achieved": ach, "peak": pk["hbm_gbs"],
+                     "unit": "GB/s", "frac": ach / pk["hbm_gbs"], "traffic": None,
+                     "peak_source": pk["source"] + " (copy bandwidth)", "launches": att["launches"],
+                     "whole_step_frac": bytes_step / (ms / steps / 1e3) / 1e9 / pk["hbm_gbs"],
+                     "kernels_ms_per_step": {k: v["ms"] / steps for k, v in prof.items() if v["launches"]}},
+        "clocks": clocks,
+    }
+    if comm:
+        comm.destroy()
+    return line
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -356,8 +547,10 @@ def main():
     try:
         if args.workload in ("c1", "c2", "c4"):
             line = run_prefill(args, rank, world, local, B, dist)
+        elif args.workload == "c3":
+            line = run_vjp(args, rank, world, local, B, dist)
         else:
-            raise SystemExit(f"workload {args.workload} is not wired into bench.py yet")
+            line = run_decode(args, rank, world, local, B, dist)
     finally:
         if world > 1:
             dist.barrier()

@@ -34,17 +34,53 @@ struct EpiParams {
   void* out_up = nullptr;
 };
 
-template <typename TOut>
-__device__ __forceinline__ void store16(TOut* p, const float (&v)[16]) {
+// 16 consecutive outputs of one row: full 32-byte sectors per access where the
+// address allows it (one for bf16, two for fp32).
+__device__ __forceinline__ void store16(float* p, const float (&v)[16]) {
   float lo[8], hi[8];
 #pragma unroll
   for (int i = 0; i < 8; ++i) { lo[i] = v[i]; hi[i] = v[8 + i]; }
-  store8(p, lo);
-  store8(p + 8, hi);
+  store8_wide(p, lo);
+  store8_wide(p + 8, hi);
+}
+__device__ __forceinline__ void store16(bf16* p, const float (&v)[16]) {
+  if (aligned32(p)) {
+    uint32_t r[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+      r[i] = *reinterpret_cast<uint32_t*>(&h);
+    }
+    store32B(p, r);
+  } else {
+    float lo[8], hi[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) { lo[i] = v[i]; hi[i] = v[8 + i]; }
+    store8(p, lo);
+    store8(p + 8, hi);
+  }
+}
+
+// Per-row state computed once per output tile row (not once per 16 columns).
+struct EpiRow {
+  const float* rope_c = nullptr;  // cos/sin rows of this row's position
+  const float* rope_s = nullptr;
+};
+
+template <int KIND>
+__device__ __forceinline__ EpiRow epi_row_begin(const EpiParams& p, int m) {
+  EpiRow r;
+  if constexpr (KIND == EPI_ROPE) {
+    const int pos = p.pos_base + (m % p.seq_len);
+    const size_t off = (size_t)pos * (p.head_size >> 1);
+    r.rope_c = p.rope_cos + off;
+    r.rope_s = p.rope_sin + off;
+  }
+  return r;
 }
 
 template <int KIND, typename TOut>
-__device__ __forceinline__ void epi_apply16(const EpiParams& p, int m, int n, float (&v)[16]) {
+__device__ __forceinline__ void epi_apply16(const EpiParams& p, const EpiRow& row, int m, int n, float (&v)[16]) {
   if constexpr (KIND == EPI_STORE) {
     TOut* o = reinterpret_cast<TOut*>(p.out) + (size_t)m * p.ldo + n;
     if (p.accumulate) {
@@ -59,17 +95,17 @@ __device__ __forceinline__ void epi_apply16(const EpiParams& p, int m, int n, fl
     store16(o, v);
   } else if constexpr (KIND == EPI_ROPE) {
     if (n < p.rope_cols) {
-      const int half = p.head_size >> 1;
-      const int pos = p.pos_base + (m % p.seq_len);
-      const float* c = p.rope_cos + (size_t)pos * half;
-      const float* s = p.rope_sin + (size_t)pos * half;
+      // the 16 columns lie inside one head (head sizes are multiples of 16):
+      // pairs j0 .. j0+7 of that head, read as two 16-byte pieces per table
+      const int j0 = (n % p.head_size) >> 1;
+      float c[8], s[8];
+      load8(row.rope_c + j0, c);
+      load8(row.rope_s + j0, s);
 #pragma unroll
-      for (int i = 0; i < 16; i += 2) {
-        const int j = ((n + i) % p.head_size) >> 1;
-        const float cj = c[j], sj = s[j];
-        const float e = v[i], o = v[i + 1];
-        v[i] = cj * e - sj * o;
-        v[i + 1] = sj * e + cj * o;
+      for (int i = 0; i < 8; ++i) {
+        const float e = v[2 * i], o = v[2 * i + 1];
+        v[2 * i] = c[i] * e - s[i] * o;
+        v[2 * i + 1] = s[i] * e + c[i] * o;
       }
     }
     store16(reinterpret_cast<TOut*>(p.out) + (size_t)m * p.ldo + n, v);
@@ -79,10 +115,10 @@ __device__ __forceinline__ void epi_apply16(const EpiParams& p, int m, int n, fl
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
       float old[8];
-      load8(xi + 8 * h, old);
+      load8_wide(xi + 8 * h, old);
 #pragma unroll
       for (int i = 0; i < 8; ++i) old[i] += v[8 * h + i];
-      store8(x + 8 * h, old);
+      store8_wide(x + 8 * h, old);
     }
   } else {  // EPI_SWIGLU
     const size_t off = (size_t)m * p.ldo + (n >> 1);

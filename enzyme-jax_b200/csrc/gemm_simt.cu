@@ -93,7 +93,10 @@ __global__ void __launch_bounds__(NT) gemm_simt_kernel(const TIn* __restrict__ A
 #pragma unroll
     for (int r = 0; r < 4; ++r) {
       const int m = m0 + ty * 4 + r;
-      if (m < M) epi_apply16<KIND, TOut>(ep, m, n, acc[r]);
+      if (m < M) {
+        const EpiRow row = epi_row_begin<KIND>(ep, m);
+        epi_apply16<KIND, TOut>(ep, row, m, n, acc[r]);
+      }
     }
   }
 }

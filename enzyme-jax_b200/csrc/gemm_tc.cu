@@ -174,12 +174,26 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
       ptx::tc_fence_after_sync();
       const int m = m0 + q * 32 + lane;
       const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN);
-#pragma unroll 2
-      for (int c = 0; c < BN; c += 16) {
-        float v[16];
-        ptx::tmem_ld16(taddr + (uint32_t)c, v);
+      const bool row_ok = m < M;
+      const EpiRow erow = epi_row_begin<KIND>(ep, row_ok ? m : 0);
+      // 32 columns per TMEM round trip; the next pair of loads is in flight
+      // while the current 32 columns go through the epilogue.
+      float cur[2][16], nxt[2][16];
+      ptx::tmem_ld16(taddr, cur[0]);
+      ptx::tmem_ld16(taddr + 16u, cur[1]);
+#pragma unroll 1
+      for (int c = 0; c < BN; c += 32) {
         ptx::tmem_ld_wait();
-        if (m < M && n0 + c < N) epi_apply16<KIND, TOut>(ep, m, n0 + c, v);
+        if (c + 32 < BN) {
+          ptx::tmem_ld16(taddr + (uint32_t)(c + 32), nxt[0]);
+          ptx::tmem_ld16(taddr + (uint32_t)(c + 48), nxt[1]);
+        }
+        if (row_ok) {
+          if (n0 + c < N) epi_apply16<KIND, TOut>(ep, erow, m, n0 + c, cur[0]);
+          if (n0 + c + 16 < N) epi_apply16<KIND, TOut>(ep, erow, m, n0 + c + 16, cur[1]);
+        }
+#pragma unroll
+        for (int i = 0; i < 16; ++i) { cur[0][i] = nxt[0][i]; cur[1][i] = nxt[1][i]; }
       }
       ptx::tc_fence_before_sync();
       __syncwarp();
