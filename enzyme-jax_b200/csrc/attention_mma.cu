@@ -8,10 +8,11 @@
 //   warp 1      one lane issues tcgen05.mma:  S = Q K_j^T  (fp32, TMEM columns
 //               0..127) and, once the probabilities are in shared memory,
 //               O_j = P_j V_j (TMEM columns 128..128+hs)
-//   warps 2..5  softmax, one thread per query row: read S from TMEM, mask the
-//               diagonal block, running max / sum in fp32, write P as bf16 into
-//               shared memory in the swizzled K-major layout the MMA reads, then
-//               fold O_j into the fp32 output row kept in registers
+//   warps 2..9  softmax, two threads per query row (64 keys each): read S from
+//               TMEM once, mask the diagonal block, running max / sum in fp32,
+//               write P as bf16 into shared memory in the swizzled K-major
+//               layout the MMA reads, then fold O_j into the fp32 output
+//               columns kept in registers
 // V is consumed as an MN-major operand straight from its row-major layout.
 // TMEM use is 256 columns so that two CTAs share an SM and one CTA's softmax
 // overlaps the other's MMAs.  All waits are bounded.
@@ -28,7 +29,7 @@ namespace {
 
 constexpr int AQ = 128;   // query rows per CTA
 constexpr int AK = 128;   // keys per block
-constexpr int A_THREADS = 192;
+constexpr int A_THREADS = 320;  // producer warp, MMA warp, 8 softmax warps
 constexpr int SUB = 128 * 128;  // bytes of one [128 rows x 64 columns] bf16 sub-tile
 
 enum : uint32_t { ST_ATTN_TIMEOUT = 1u << 4, ST_ATTN_ALIGN = 1u << 5 };
@@ -42,8 +43,9 @@ template <int HS> struct ACfg {
   static constexpr int kKOff = kTileBytes;
   static constexpr int kVOff = kKOff + kStages * kTileBytes;
   static constexpr int kPOff = kVOff + kStages * kTileBytes;
-  static constexpr int kBarOff = kPOff + kPBytes;
-  static constexpr int kSmemBytes = kBarOff + 256;
+  static constexpr int kXchgOff = kPOff + kPBytes;      // [2][128] bf16 block maxima exchanged between the halves of a row
+  static constexpr int kBarOff = kXchgOff + 2 * 128 * 2;
+  static constexpr int kSmemBytes = kBarOff + 128;      // hs = 64: 115,328 B, two CTAs fit the 228 KB of an SM
   static constexpr int kTmemCols = 256;
   static constexpr int kOCol = 128;
 };
@@ -72,7 +74,7 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
 }
 
 template <int HS>
-__global__ void __launch_bounds__(A_THREADS)
+__global__ void __launch_bounds__(A_THREADS, HS == 64 ? 2 : 1)
     attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                        const __grid_constant__ CUtensorMap tmV, bf16* __restrict__ o, float* __restrict__ lse, int seq,
                        int n_heads, int ldo, float scale, uint32_t* status) {
@@ -87,7 +89,8 @@ __global__ void __launch_bounds__(A_THREADS)
   uint64_t* p_full = bars + 7;      // P_j is in shared memory
   uint64_t* o_full = bars + 8;      // O_j complete in TMEM (P_j and the stage are free)
   uint64_t* o_empty = bars + 9;     // softmax has read O_j
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 10);
+  uint64_t* x_bar = bars + 10;      // the two threads of every row have published their block maximum
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 11);  // 11 barriers + 2 words = 96 bytes
   volatile uint32_t* abort_flag = tmem_slot + 1;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -109,10 +112,11 @@ __global__ void __launch_bounds__(A_THREADS)
       ptx::mbar_init(&kv_empty[i], 1);
     }
     ptx::mbar_init(s_full, 1);
-    ptx::mbar_init(s_empty, 128);
-    ptx::mbar_init(p_full, 128);
+    ptx::mbar_init(s_empty, 256);
+    ptx::mbar_init(p_full, 256);
     ptx::mbar_init(o_full, 1);
-    ptx::mbar_init(o_empty, 128);
+    ptx::mbar_init(o_empty, 256);
+    ptx::mbar_init(x_bar, 256);
     ptx::fence_barrier_init();
     ptx::tma_prefetch_desc(&tmQ);
     ptx::tma_prefetch_desc(&tmK);
@@ -190,16 +194,22 @@ __global__ void __launch_bounds__(A_THREADS)
     }
     __syncwarp();
   } else {
+    // 8 softmax warps: warps 2..5 take keys 0..63 of every block and the first
+    // half of the output columns, warps 6..9 the other halves; the two threads
+    // of a row exchange their block maxima through shared memory.
     const int qd = warp & 3;
+    const int hf = (warp - 2) >> 2;
     const int row = qd * 32 + lane;  // row of the tile == TMEM lane
     const int t = t0 + row;
-    const uint32_t t_s = tmem_base + ((uint32_t)(qd * 32) << 16);
-    const uint32_t t_o = t_s + C::kOCol;
+    constexpr int OH = HS / 2;       // output columns per thread
+    const uint32_t t_s = tmem_base + ((uint32_t)(qd * 32) << 16) + (uint32_t)(hf * 64);
+    const uint32_t t_o = tmem_base + ((uint32_t)(qd * 32) << 16) + (uint32_t)(C::kOCol + hf * OH);
     const float sl2 = scale * 1.4426950408889634f;  // scores are scaled inside the exp2
-    uint8_t* p_row = smem + C::kPOff + row * 128;
-    float acc[HS];
+    uint8_t* p_row = smem + C::kPOff + hf * SUB + row * 128;
+    bf16* xchg = reinterpret_cast<bf16*>(smem + C::kXchgOff);  // [2][128]
+    float acc[OH];
 #pragma unroll
-    for (int i = 0; i < HS; ++i) acc[i] = 0.f;
+    for (int i = 0; i < OH; ++i) acc[i] = 0.f;
     float m = -INFINITY, l = 0.f;
     bool ok = true;
     for (int j = 0; j < n_blocks; ++j) {
@@ -208,61 +218,82 @@ __global__ void __launch_bounds__(A_THREADS)
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       ptx::tc_fence_after_sync();
-      const bool diag = (j == qt);
-      const int u0 = j * AK;
-      // pass 1: row maximum
+      const bool diag = (j == qt);  // diagonal block: keys after the query are masked
+      const int u0 = j * AK + hf * 64;
+      // pass 1: maximum of this thread's 64 scores (32 at a time to bound the registers)
       float bm = -INFINITY;
 #pragma unroll
-      for (int c = 0; c < AK; c += 32) {
-        float v[32];
-        tmem_ld32(t_s + (uint32_t)c, v);
+      for (int c = 0; c < 64; c += 32) {
+        float sv[32];
+        tmem_ld32(t_s + (uint32_t)c, sv);
         ptx::tmem_ld_wait();
+        if (diag) {
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const float s = (diag && (u0 + c + i > t)) ? -INFINITY : v[i];
-          bm = fmaxf(bm, s);
+          for (int i = 0; i < 32; ++i)
+            if (u0 + c + i > t) sv[i] = -INFINITY;
         }
+#pragma unroll
+        for (int i = 0; i < 32; ++i) bm = fmaxf(bm, sv[i]);
       }
-      const float nm = fmaxf(m, bm);
-      const float corr = exp2f((m - nm) * sl2);
+      // Both threads of a row must adopt the same maximum, but it need not be
+      // exact: each rounds its own to bf16 and both take the larger of the two
+      // rounded values.  One slot per half suffices: the partner's next write
+      // comes after o_full of this block, which needs this thread's p_full
+      // arrival, which follows the read below.
+      const bf16 bmh = __float2bfloat16_rn(bm);
+      xchg[hf * 128 + row] = bmh;
+      ptx::mbar_arrive(x_bar);  // release: the store above is visible to whoever sees the phase complete
+      ok = ptx::mbar_wait(x_bar, jp, abort_flag, status, ST_ATTN_TIMEOUT);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      bm = fmaxf(__bfloat162float(bmh), __bfloat162float(xchg[(hf ^ 1) * 128 + row]));
+      const float nm = fmaxf(m, bm);  // finite: key 0 of block 0 is never masked, later maxima only grow
       const float nms = nm * sl2;
-      // pass 2: probabilities -> bf16 -> shared memory (swizzled K-major tile)
+      // pass 2: probabilities -> bf16 -> shared memory
       float rs = 0.f;
 #pragma unroll
-      for (int c = 0; c < AK; c += 32) {
-        float v[32];
-        tmem_ld32(t_s + (uint32_t)c, v);
+      for (int c = 0; c < 64; c += 32) {
+        float sv[32];
+        tmem_ld32(t_s + (uint32_t)c, sv);
         ptx::tmem_ld_wait();
+        if (diag) {
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const float s = (diag && (u0 + c + i > t)) ? -INFINITY : v[i];
-          v[i] = exp2f(fmaf(s, sl2, -nms));
-          rs += v[i];
+          for (int i = 0; i < 32; ++i)
+            if (u0 + c + i > t) sv[i] = -INFINITY;
         }
 #pragma unroll
         for (int g = 0; g < 4; ++g) {  // four 16-byte pieces of 8 keys
-          const int ch = (c >> 3) + g;  // piece index 0..15 within the row of 128 keys
           uint4 raw;
           __nv_bfloat162* hp = reinterpret_cast<__nv_bfloat162*>(&raw);
 #pragma unroll
-          for (int i = 0; i < 4; ++i) hp[i] = __floats2bfloat162_rn(v[g * 8 + 2 * i], v[g * 8 + 2 * i + 1]);
-          *reinterpret_cast<uint4*>(p_row + (ch >> 3) * SUB + (((ch & 7) ^ (row & 7)) << 4)) = raw;
+          for (int i = 0; i < 4; ++i) {
+            const float p0 = exp2f(fmaf(sv[g * 8 + 2 * i], sl2, -nms));
+            const float p1 = exp2f(fmaf(sv[g * 8 + 2 * i + 1], sl2, -nms));
+            rs += p0 + p1;
+            hp[i] = __floats2bfloat162_rn(p0, p1);
+          }
+          const int ch = (c >> 3) + g;  // piece 0..7 of this thread's 64 keys
+          *reinterpret_cast<uint4*>(p_row + ((ch ^ (row & 7)) << 4)) = raw;
         }
       }
       ptx::tc_fence_before_sync();
-      ptx::mbar_arrive(s_empty);
+      ptx::mbar_arrive(s_empty);  // the next block's S may overwrite TMEM
       ptx::fence_proxy_async();  // make the generic-proxy writes of P visible to the MMA's async proxy
       ptx::mbar_arrive(p_full);
-      l = l * corr + rs;
+      if (nm > m) {
+        const float corr = exp2f((m - nm) * sl2);
+        l *= corr;
 #pragma unroll
-      for (int i = 0; i < HS; ++i) acc[i] *= corr;
-      m = nm;
+        for (int i = 0; i < OH; ++i) acc[i] *= corr;
+        m = nm;
+      }
+      l += rs;
       ok = ptx::mbar_wait(o_full, jp, abort_flag, status, ST_ATTN_TIMEOUT);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       ptx::tc_fence_after_sync();
 #pragma unroll
-      for (int c = 0; c < HS; c += 32) {
+      for (int c = 0; c < OH; c += 32) {
         float v[32];
         tmem_ld32(t_o + (uint32_t)c, v);
         ptx::tmem_ld_wait();
@@ -272,17 +303,26 @@ __global__ void __launch_bounds__(A_THREADS)
       ptx::tc_fence_before_sync();
       ptx::mbar_arrive(o_empty);
     }
+    // the two halves of a row hold partial sums under the same running maximum
+    if (ok) {
+      // every MMA that reads Q has completed (the last s_full was consumed): its tile holds the partial sums
+      float* lx = reinterpret_cast<float*>(smem + C::kQOff);
+      lx[hf * 128 + row] = l;
+      ptx::mbar_arrive(x_bar);
+      ok = ptx::mbar_wait(x_bar, (uint32_t)n_blocks & 1u, abort_flag, status, ST_ATTN_TIMEOUT);
+      if (ok) l += lx[(hf ^ 1) * 128 + row];
+    }
     if (ok && t < seq) {
       const float inv = 1.f / l;
-      bf16* dst = o + ((size_t)b * seq + t) * ldo + h * HS;
+      bf16* dst = o + ((size_t)b * seq + t) * ldo + h * HS + hf * OH;
 #pragma unroll
-      for (int c = 0; c < HS; c += 8) {
+      for (int c = 0; c < OH; c += 8) {
         float v[8];
 #pragma unroll
         for (int i = 0; i < 8; ++i) v[i] = acc[c + i] * inv;
         store8(dst + c, v);
       }
-      if (lse) lse[((size_t)b * n_heads + h) * seq + t] = m * scale + __logf(l);
+      if (lse && hf == 0) lse[((size_t)b * n_heads + h) * seq + t] = m * scale + __logf(l);
     }
   }
 

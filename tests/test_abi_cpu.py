@@ -47,3 +47,19 @@ def test_plan_needs_a_device():
         pytest.skip("CUDA present")
     with pytest.raises(RuntimeError):
         B.Plan(dict(dim=64, hidden_dim=128, n_layers=1, n_heads=2, n_kv_heads=2, vocab_size=96, seq_len=8))
+
+
+def test_python_surface_has_the_reference_names():
+    import enzyme_ad.jax as EJ
+    import pytest
+    # src/enzyme_ad/jax/__init__.py:1-12 of the reference
+    for name in ("cpp_call", "ffi_call", "hlo_call", "enzyme_jax_ir", "XLAPipeline", "JaXPipeline", "optimize_module",
+                 "export", "full_optimization_pass_pipeline", "optimization_passes"):
+        assert hasattr(EJ, name), name
+    assert EJ.JaXPipeline("a,enzyme-wrap{x},b,enzyme-wrap{y}").ad_level() == 2
+    assert EJ.XLAPipeline("n").export_llvm() == "n" and EJ.XLAPipeline().mlir_ad() is False
+    for fn in (EJ.cpp_call, EJ.hlo_call, EJ.optimize_module, EJ.export, EJ.optimization_passes):
+        with pytest.raises(NotImplementedError):
+            fn()
+    with pytest.raises(NotImplementedError):
+        EJ.enzyme_jax_ir()(lambda x: x)

@@ -1,0 +1,57 @@
+"""The reference-shaped Python surface (enzyme_ad.jax) on the GPU: the reference's own call
+shape against the golden vector of its forward source, and the jax.vjp-shaped helper."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import llama_ref as O
+
+pytestmark = pytest.mark.gpu
+
+
+def test_reference_call_shape_against_golden():
+    from enzyme_ad.jax import B200Pipeline, enzyme_jax_ir
+    gold = np.load(os.path.join(os.path.dirname(__file__), "golden", "llama_golden.npz"))
+    cfg = O.CONFIGS["c1"]
+    rng = np.random.default_rng(11)
+    w = {}
+    for name, shape in sorted(O.weight_shapes(cfg).items()):
+        w[name] = torch.from_numpy(rng.random(shape).astype(np.float32))
+    x = torch.from_numpy(rng.random(cfg["dim"]).astype(np.float32))
+    w.pop("token_embedding_table")  # the reference's weight dict has no embedding leaf
+    kc = torch.zeros(cfg["n_layers"], 1, cfg["dim"])
+
+    def forward(x, weights, key_cache, value_cache):  # stands for test/llama.py's partial(forward, config)
+        raise AssertionError("the body is never traced here")
+
+    fn = enzyme_jax_ir(pipeline_options=B200Pipeline(cfg, torch.float32))(forward)
+    out = fn(x, {k: v.cuda() for k, v in w.items()}, kc, kc.clone())
+    # uniform[0,1) weights make activations of order 1e2..1e5; the reference's own bar for this test is 1e-3 relative
+    np.testing.assert_allclose(out.cpu().numpy(), gold["A_f32"], rtol=1e-3, atol=1e-3)
+    np.testing.assert_allclose(out.double().cpu().numpy(), gold["A_f64"], rtol=1e-3, atol=1e-3)
+
+
+def test_vjp_helper_and_unsupported_entries():
+    import enzyme_ad.jax as EJ
+    cfg = dict(dim=128, hidden_dim=256, n_layers=2, n_heads=4, n_kv_heads=4, vocab_size=512, seq_len=64)
+    w = O.make_weights(cfg, 7, torch.float32, std=0.1, gains_one=False)
+    tokens = O.make_tokens(cfg, 2, 32, 9)
+    dl = torch.randn(2, 32, cfg["vocab_size"], generator=torch.Generator().manual_seed(1))
+    ref_logits, ref = O.vjp_sequence(tokens, cfg, {k: v.double() for k, v in w.items()}, dl.double())
+
+    @EJ.enzyme_jax_ir(pipeline_options=EJ.B200Pipeline(cfg, torch.float32))
+    def model(tokens, weights):
+        raise AssertionError
+
+    wd = {k: v.cuda() for k, v in w.items()}
+    logits, pull = EJ.vjp(model, tokens, wd)
+    assert torch.allclose(logits.double().cpu(), ref_logits, rtol=1e-4, atol=1e-5)
+    grads = pull(dl)
+    for k, r in ref.items():
+        assert float((grads[k].double().cpu() - r).abs().max() / r.abs().max()) < 1e-4, k
+    with pytest.raises(NotImplementedError):
+        EJ.cpp_call()
+    with pytest.raises(NotImplementedError):
+        EJ.enzyme_jax_ir(pipeline_options=EJ.JaXPipeline("inline"))(lambda x: x)
