@@ -33,6 +33,7 @@ EXPORTS = (
     "b200_gemm", "b200_rmsnorm", "b200_attention", "b200_comm_unique_id", "b200_comm_init_rank",
     "b200_comm_destroy", "b200_launch_count", "b200_profile_enable", "b200_profile_read",
     "b200_attention_decode_scratch_bytes", "b200_attention_decode", "b200_attention_decode_static",
+    "b200_attention_backward",
 )
 
 
@@ -90,6 +91,7 @@ def lib() -> ctypes.CDLL:
         l.b200_attention_decode_scratch_bytes.argtypes = [c_int32] * 4 + [POINTER(c_size_t)]
         l.b200_attention_decode.argtypes = [c_void_p] * 5 + [c_size_t] + [c_int32] * 10 + [c_void_p]
         l.b200_attention_decode_static.argtypes = [c_void_p] * 4 + [c_int32] * 10 + [c_void_p]
+        l.b200_attention_backward.argtypes = [c_void_p] * 10 + [c_int32] * 9 + [c_void_p]
         l.b200_device_status.argtypes = [c_void_p, POINTER(c_uint32)]
         l.b200_comm_unique_id.argtypes = [c_void_p]
         l.b200_comm_init_rank.argtypes = [c_void_p, c_int32, c_int32, POINTER(c_void_p)]
@@ -183,6 +185,22 @@ def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, batch: int, seq
     check(lib().b200_attention(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr(), batch, seq,
                                n_heads, hs, q.stride(0), k.stride(0), o.stride(0), _dt(q.dtype), impl, _stream()))
     return o, lse
+
+
+def attention_backward(qkv: torch.Tensor, o: torch.Tensor, lse: torch.Tensor, d_o: torch.Tensor, batch: int, seq: int,
+                       n_heads: int, impl=0) -> torch.Tensor:
+    """Backward of causal attention for a packed qkv [batch*seq, 3*d]; returns dqkv of the same shape."""
+    T, d3 = qkv.shape
+    d = d3 // 3
+    es = qkv.element_size()
+    dqkv = torch.empty_like(qkv)
+    delta = torch.empty(batch * n_heads * seq, dtype=torch.float32, device=qkv.device)
+    base, dbase = qkv.data_ptr(), dqkv.data_ptr()
+    check(lib().b200_attention_backward(base, base + d * es, base + 2 * d * es, o.data_ptr(), lse.data_ptr(),
+                                        d_o.data_ptr(), dbase, dbase + d * es, dbase + 2 * d * es, delta.data_ptr(),
+                                        batch, seq, n_heads, d // n_heads, d3, d3, o.stride(0), _dt(qkv.dtype), impl,
+                                        _stream()))
+    return dqkv
 
 
 def attention_decode(q: torch.Tensor, kv_layer: torch.Tensor, page_table: torch.Tensor, ctx: int, n_heads: int,

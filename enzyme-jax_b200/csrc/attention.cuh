@@ -36,6 +36,12 @@ struct AttnBwdArgs {
   float* delta = nullptr;  // scratch [batch, n_heads, seq]: rowsum(dO * O)
 };
 int32_t launch_attn_bwd_simt(const AttnBwdArgs& a, cudaStream_t stream);
+int32_t launch_attn_bwd_tc(const AttnBwdArgs& a, cudaStream_t stream);
+bool attn_bwd_tc_supports(const AttnBwdArgs& a);
+// delta[b,h,t] = sum_e dO[t,e] * O[t,e]  (first step of either backward)
+int32_t launch_attn_delta(const AttnBwdArgs& a, cudaStream_t stream);
+// impl: 0 = pick, 1 = tensor-core kernels, 2 = CUDA-core kernels
+int32_t launch_attn_bwd(const AttnBwdArgs& a, int impl, cudaStream_t stream);
 
 // Decode: one query row per (sequence, head) against `ctx` cached rows held in
 // pages.  The context is split into chunks handled by different CTAs; partial

@@ -1,0 +1,360 @@
+// Causal attention backward on the 5th-generation tensor cores (bf16, head
+// size 64).  Given q, k, v, the forward's lse, dO and delta = rowsum(dO * O):
+//   P  = exp(q k^T / sqrt(hs) - lse)          recomputed block by block
+//   dV = P^T dO         dP = dO V^T
+//   dS = P * (dP - delta) / sqrt(hs)
+//   dK = dS^T Q         dQ = dS K
+// which is what the reference's AD rules (exp, divide, reduce-add, dot_general:
+// Implementations/HLODerivatives.td:1133-1182) compose for test/llama.py:177-209.
+//
+// Two passes of one kernel template, both free of atomics (fixed summation order):
+//   MODE_DKV  a CTA owns 128 keys, streams the query blocks at or after them,
+//             accumulates dV and dK in TMEM
+//   MODE_DQ   a CTA owns 128 queries, streams the key blocks at or before
+//             them, accumulates dQ in TMEM
+// Per (query block, key block) pair: S and dP on the tensor cores into TMEM,
+// 8 warps turn them into bf16 P and dS tiles in shared memory (swizzled, so the
+// same bytes serve as a K-major or an MN-major operand), then the accumulating
+// MMAs.  Warp 0 is the TMA producer, warp 1 issues the MMAs.  Waits are bounded.
+#include <cuda.h>
+
+#include "attention.cuh"
+#include "ptx_sm100.cuh"
+#include "tensor_map.cuh"
+
+namespace b200 {
+
+namespace {
+
+constexpr int BQ = 128, BK_ = 128, HSB = 64;
+constexpr int BW_THREADS = 320;
+constexpr int SUBT = 128 * 128;  // bytes of one [128 rows x 64 columns] bf16 tile
+enum { MODE_DKV = 0, MODE_DQ = 1 };
+enum : uint32_t { ST_ATTNB_TIMEOUT = 1u << 6, ST_ATTNB_ALIGN = 1u << 7 };
+
+// shared memory map (bytes)
+constexpr int kFix0 = 0;                 // fixed tile 0 (DKV: K_j, DQ: Q_i)
+constexpr int kFix1 = SUBT;              // fixed tile 1 (DKV: V_j, DQ: dO_i)
+constexpr int kStr = 2 * SUBT;           // 2 stages x {tile 0 (DKV: Q_i, DQ: K_j), tile 1 (DKV: dO_i, DQ: V_j)}
+constexpr int kP = kStr + 4 * SUBT;      // P  [128 q][128 k] as two sub-tiles (keys 0..63, 64..127)
+constexpr int kDS = kP + 2 * SUBT;       // dS, same layout
+constexpr int kBars = kDS + 2 * SUBT;
+constexpr int kBwdSmem = kBars + 256;
+// TMEM columns
+constexpr int cS = 0, cDP = 128, cAcc0 = 256, cAcc1 = 320, kBwdTmem = 512;
+
+struct BwdParams {
+  const float* lse;
+  const float* delta;
+  bf16* out0;  // DKV: dV, DQ: dQ
+  bf16* out1;  // DKV: dK
+  int ld_out;
+  int seq, n_heads;
+  float scale;
+};
+
+template <int MODE>
+__global__ void __launch_bounds__(BW_THREADS, 1)
+    attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                       const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO, BwdParams prm,
+                       uint32_t* status) {
+  extern __shared__ __align__(1024) uint8_t smem[];
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kBars);
+  uint64_t* fix_full = bars;        // fixed tiles landed
+  uint64_t* str_full = bars + 1;    // [2] streamed tiles landed
+  uint64_t* str_empty = bars + 3;   // [2] every MMA reading the stage is done
+  uint64_t* s_full = bars + 5;      // S and dP complete in TMEM
+  uint64_t* s_empty = bars + 6;     // S and dP have been read
+  uint64_t* p_full = bars + 7;      // P / dS tiles written
+  uint64_t* g_done = bars + 8;      // accumulating MMAs of the pair are done (P / dS tiles free)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 9);
+  volatile uint32_t* abort_flag = tmem_slot + 1;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int own = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+  const int nblk = (prm.seq + 127) / 128;
+  // DKV: own key block `own`, query blocks own..nblk-1.  DQ: own query block nblk-1-own (long ones first), key blocks 0..it.
+  const int own_blk = MODE == MODE_DKV ? own : nblk - 1 - own;
+  const int first = MODE == MODE_DKV ? own_blk : 0;
+  const int n_it = MODE == MODE_DKV ? nblk - own_blk : own_blk + 1;
+  const int col = h * HSB;
+
+  if (threadIdx.x == 0) {
+    if (ptx::smem_u32(smem) & 1023u) {
+      atomicOr(status, ST_ATTNB_ALIGN);
+      *abort_flag = 1u;
+    } else {
+      *abort_flag = 0u;
+    }
+    ptx::mbar_init(fix_full, 1);
+    for (int i = 0; i < 2; ++i) {
+      ptx::mbar_init(&str_full[i], 1);
+      ptx::mbar_init(&str_empty[i], 1);
+    }
+    ptx::mbar_init(s_full, 1);
+    ptx::mbar_init(s_empty, 256);
+    ptx::mbar_init(p_full, 256);
+    ptx::mbar_init(g_done, 1);
+    ptx::fence_barrier_init();
+    ptx::tma_prefetch_desc(&tmQ);
+    ptx::tma_prefetch_desc(&tmK);
+    ptx::tma_prefetch_desc(&tmV);
+    ptx::tma_prefetch_desc(&tmDO);
+  }
+  if (warp == 1) {
+    ptx::tmem_alloc(tmem_slot, kBwdTmem);
+    ptx::tmem_relinquish();
+  }
+  ptx::tc_fence_before_sync();
+  __syncthreads();
+  ptx::tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+  const bool aborted = *abort_flag != 0u;
+
+  if (aborted) {
+    // common exit below
+  } else if (warp == 0) {
+    if (lane == 0) {
+      const int own_row = own_blk * 128;
+      ptx::mbar_arrive_expect_tx(fix_full, 2 * SUBT);
+      if (MODE == MODE_DKV) {
+        ptx::tma_load_3d(smem + kFix0, &tmK, col, own_row, b, fix_full);
+        ptx::tma_load_3d(smem + kFix1, &tmV, col, own_row, b, fix_full);
+      } else {
+        ptx::tma_load_3d(smem + kFix0, &tmQ, col, own_row, b, fix_full);
+        ptx::tma_load_3d(smem + kFix1, &tmDO, col, own_row, b, fix_full);
+      }
+      bool ok = true;
+      for (int it = 0; it < n_it && ok; ++it) {
+        const int st = it & 1;
+        const uint32_t ph = (uint32_t)(it >> 1) & 1u;
+        ok = ptx::mbar_wait(&str_empty[st], ph ^ 1u, abort_flag, status, ST_ATTNB_TIMEOUT);
+        if (!ok) break;
+        const int row = (first + it) * 128;
+        uint8_t* dst = smem + kStr + st * 2 * SUBT;
+        ptx::mbar_arrive_expect_tx(&str_full[st], 2 * SUBT);
+        if (MODE == MODE_DKV) {
+          ptx::tma_load_3d(dst, &tmQ, col, row, b, &str_full[st]);
+          ptx::tma_load_3d(dst + SUBT, &tmDO, col, row, b, &str_full[st]);
+        } else {
+          ptx::tma_load_3d(dst, &tmK, col, row, b, &str_full[st]);
+          ptx::tma_load_3d(dst + SUBT, &tmV, col, row, b, &str_full[st]);
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t id_kk = ptx::idesc_bf16_f32(128, 128);                          // A, B K-major
+      constexpr uint32_t id_mm = ptx::idesc_bf16_f32(128, HSB) | (1u << 15) | (1u << 16);  // A, B MN-major
+      constexpr uint32_t id_km = ptx::idesc_bf16_f32(128, HSB) | (1u << 16);               // A K-major, B MN-major
+      const uint32_t p_addr = ptx::smem_u32(smem + kP), ds_addr = ptx::smem_u32(smem + kDS);
+      bool ok = ptx::mbar_wait(fix_full, 0, abort_flag, status, ST_ATTNB_TIMEOUT);
+      for (int it = 0; it < n_it && ok; ++it) {
+        const int st = it & 1;
+        const uint32_t ph = (uint32_t)(it >> 1) & 1u;
+        const uint32_t ip = (uint32_t)it & 1u;
+        ok = ptx::mbar_wait(&str_full[st], ph, abort_flag, status, ST_ATTNB_TIMEOUT) &&
+             ptx::mbar_wait(s_empty, ip ^ 1u, abort_flag, status, ST_ATTNB_TIMEOUT);
+        if (!ok) break;
+        ptx::tc_fence_after_sync();
+        const uint32_t s0 = ptx::smem_u32(smem + kStr + st * 2 * SUBT), s1 = s0 + SUBT;
+        const uint32_t f0 = ptx::smem_u32(smem + kFix0), f1 = f0 + SUBT;
+        const uint32_t q_a = MODE == MODE_DKV ? s0 : f0, do_a = MODE == MODE_DKV ? s1 : f1;
+        const uint32_t k_a = MODE == MODE_DKV ? f0 : s0, v_a = MODE == MODE_DKV ? f1 : s1;
+#pragma unroll
+        for (int k = 0; k < HSB / 16; ++k)  // S = Q K^T
+          ptx::mma_bf16_ss(tmem_base + cS, ptx::smem_desc_sw128(q_a + k * 32), ptx::smem_desc_sw128(k_a + k * 32), id_kk,
+                           k > 0 ? 1u : 0u);
+#pragma unroll
+        for (int k = 0; k < HSB / 16; ++k)  // dP = dO V^T
+          ptx::mma_bf16_ss(tmem_base + cDP, ptx::smem_desc_sw128(do_a + k * 32), ptx::smem_desc_sw128(v_a + k * 32),
+                           id_kk, k > 0 ? 1u : 0u);
+        ptx::mma_commit(s_full);
+        ok = ptx::mbar_wait(p_full, ip, abort_flag, status, ST_ATTNB_TIMEOUT);
+        if (!ok) break;
+        ptx::tc_fence_after_sync();
+        if (MODE == MODE_DKV) {
+#pragma unroll
+          for (int k = 0; k < BQ / 16; ++k) {  // contraction over the 128 queries, 16 rows (2048 B) per step
+            const uint32_t off = (uint32_t)(k * 2048);
+            // dV[key, e] += sum_q P[q, key] dO[q, e]
+            ptx::mma_bf16_ss(tmem_base + cAcc0, ptx::smem_desc_sw128_mn(p_addr + off, SUBT),
+                             ptx::smem_desc_sw128_mn(do_a + off, SUBT), id_mm, (it > 0 || k > 0) ? 1u : 0u);
+          }
+#pragma unroll
+          for (int k = 0; k < BQ / 16; ++k) {
+            const uint32_t off = (uint32_t)(k * 2048);
+            // dK[key, e] += sum_q dS[q, key] Q[q, e]
+            ptx::mma_bf16_ss(tmem_base + cAcc1, ptx::smem_desc_sw128_mn(ds_addr + off, SUBT),
+                             ptx::smem_desc_sw128_mn(q_a + off, SUBT), id_mm, (it > 0 || k > 0) ? 1u : 0u);
+          }
+        } else {
+#pragma unroll
+          for (int k = 0; k < BK_ / 16; ++k) {  // dQ[q, e] += sum_key dS[q, key] K[key, e]
+            const uint32_t aoff = (uint32_t)((k >> 2) * SUBT + (k & 3) * 32);
+            ptx::mma_bf16_ss(tmem_base + cAcc0, ptx::smem_desc_sw128(ds_addr + aoff),
+                             ptx::smem_desc_sw128_mn(k_a + (uint32_t)(k * 2048), SUBT), id_km,
+                             (it > 0 || k > 0) ? 1u : 0u);
+          }
+        }
+        ptx::mma_commit(g_done);
+        ptx::mma_commit(&str_empty[st]);
+      }
+    }
+    __syncwarp();
+  } else {
+    const int qd = warp & 3;
+    const int hf = (warp - 2) >> 2;
+    const int row = qd * 32 + lane;  // TMEM lane: the query row of the pair
+    const uint32_t lane_base = tmem_base + ((uint32_t)(qd * 32) << 16);
+    const float sl2 = prm.scale * 1.4426950408889634f;
+    uint8_t* p_row = smem + kP + hf * SUBT + row * 128;
+    uint8_t* ds_row = smem + kDS + hf * SUBT + row * 128;
+    bool ok = true;
+    for (int it = 0; it < n_it; ++it) {
+      const uint32_t ip = (uint32_t)it & 1u;
+      const int qb = MODE == MODE_DKV ? first + it : own_blk;
+      const int kb = MODE == MODE_DKV ? own_blk : it;
+      const int t = qb * 128 + row;
+      const bool valid = t < prm.seq;
+      const size_t stat = ((size_t)b * prm.n_heads + h) * prm.seq + (valid ? t : 0);
+      const float lse2 = prm.lse[stat] * 1.4426950408889634f;
+      const float dlt = prm.delta[stat];
+      const bool diag = qb == kb;
+      const int u0 = kb * 128 + hf * 64;
+      ok = ptx::mbar_wait(s_full, ip, abort_flag, status, ST_ATTNB_TIMEOUT);
+      // the P / dS tiles of the previous pair must have been consumed
+      if (ok && it > 0) ok = ptx::mbar_wait(g_done, ip ^ 1u, abort_flag, status, ST_ATTNB_TIMEOUT);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      ptx::tc_fence_after_sync();
+#pragma unroll
+      for (int c = 0; c < 64; c += 32) {
+        float sv[32], dp[32];
+        ptx::tmem_ld32(lane_base + (uint32_t)(cS + hf * 64 + c), sv);
+        ptx::tmem_ld32(lane_base + (uint32_t)(cDP + hf * 64 + c), dp);
+        ptx::tmem_ld_wait();
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+          uint4 praw, draw;
+          __nv_bfloat162* pp = reinterpret_cast<__nv_bfloat162*>(&praw);
+          __nv_bfloat162* dd = reinterpret_cast<__nv_bfloat162*>(&draw);
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const int e0 = g * 8 + 2 * i;
+            float p0 = exp2f(fmaf(sv[e0], sl2, -lse2));
+            float p1 = exp2f(fmaf(sv[e0 + 1], sl2, -lse2));
+            if (!valid || (diag && u0 + c + e0 > t)) p0 = 0.f;
+            if (!valid || (diag && u0 + c + e0 + 1 > t)) p1 = 0.f;
+            const float d0 = p0 * (dp[e0] - dlt) * prm.scale;
+            const float d1 = p1 * (dp[e0 + 1] - dlt) * prm.scale;
+            pp[i] = __floats2bfloat162_rn(p0, p1);
+            dd[i] = __floats2bfloat162_rn(d0, d1);
+          }
+          const int ch = (c >> 3) + g;
+          const int off = (ch ^ (row & 7)) << 4;
+          if (MODE == MODE_DKV) *reinterpret_cast<uint4*>(p_row + off) = praw;
+          *reinterpret_cast<uint4*>(ds_row + off) = draw;
+        }
+      }
+      ptx::tc_fence_before_sync();
+      ptx::mbar_arrive(s_empty);
+      ptx::fence_proxy_async();
+      ptx::mbar_arrive(p_full);
+    }
+    // epilogue: the last pair's accumulating MMAs complete the sums
+    if (ok) ok = ptx::mbar_wait(g_done, (uint32_t)(n_it - 1) & 1u, abort_flag, status, ST_ATTNB_TIMEOUT);
+    ok = __all_sync(0xffffffffu, ok);
+    if (ok) {
+      ptx::tc_fence_after_sync();
+      const int r_glob = own_blk * 128 + row;  // DKV: key row, DQ: query row
+      if (MODE == MODE_DKV) {
+        // hf 0 writes dV (columns cAcc0..), hf 1 writes dK (columns cAcc1..)
+        bf16* dst = (hf == 0 ? prm.out0 : prm.out1) + ((size_t)b * prm.seq + r_glob) * prm.ld_out + col;
+        const uint32_t src = lane_base + (uint32_t)(hf == 0 ? cAcc0 : cAcc1);
+#pragma unroll
+        for (int c = 0; c < 64; c += 32) {
+          float v[32];
+          ptx::tmem_ld32(src + (uint32_t)c, v);
+          ptx::tmem_ld_wait();
+          if (r_glob < prm.seq) {
+#pragma unroll
+            for (int g = 0; g < 4; ++g) {
+              float w[8];
+#pragma unroll
+              for (int i = 0; i < 8; ++i) w[i] = v[g * 8 + i];
+              store8(dst + c + g * 8, w);
+            }
+          }
+        }
+      } else {
+        bf16* dst = prm.out0 + ((size_t)b * prm.seq + r_glob) * prm.ld_out + col + hf * 32;
+        float v[32];
+        ptx::tmem_ld32(lane_base + (uint32_t)(cAcc0 + hf * 32), v);
+        ptx::tmem_ld_wait();
+        if (r_glob < prm.seq) {
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            float w[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) w[i] = v[g * 8 + i];
+            store8(dst + g * 8, w);
+          }
+        }
+      }
+    }
+  }
+
+  ptx::tc_fence_before_sync();
+  __syncthreads();
+  if (*abort_flag) {
+    for (int i = 0; i < 1000; ++i) __nanosleep(1000);
+  }
+  if (warp == 1) {
+    ptx::tc_fence_after_sync();
+    ptx::tmem_dealloc(tmem_base, kBwdTmem);
+  }
+}
+
+}  // namespace
+
+bool attn_bwd_tc_supports(const AttnBwdArgs& a) {
+  const AttnArgs& f = a.f;
+  return f.dtype == B200_BF16 && f.head_size == 64 && f.ldq % 8 == 0 && f.ldkv % 8 == 0 && a.lddo % 8 == 0 &&
+         a.lddq % 8 == 0 && a.lddkv % 8 == 0 && a.lddq == a.lddkv && aligned16(f.q) && aligned16(f.k) &&
+         aligned16(f.v) && aligned16(a.d_o) && aligned16(a.dq) && aligned16(a.dk) && aligned16(a.dv) && f.lse &&
+         a.delta && f.batch > 0 && f.seq > 0 && f.n_heads > 0;
+}
+
+int32_t launch_attn_bwd_tc(const AttnBwdArgs& a, cudaStream_t stream) {
+  if (!attn_bwd_tc_supports(a))
+    return fail(B200_ERR_UNSUPPORTED, "tensor-core attention backward needs bf16, head size 64 and 16-byte aligned rows");
+  const AttnArgs& f = a.f;
+  B200_TRY(launch_attn_delta(a, stream));
+  CUtensorMap tq, tk, tv, tdo;
+  const int cols = f.n_heads * 64;
+  B200_TRY(make_map_3d(&tq, f.q, f.batch, f.seq, cols, f.ldq));
+  B200_TRY(make_map_3d(&tk, f.k, f.batch, f.seq, cols, f.ldkv));
+  B200_TRY(make_map_3d(&tv, f.v, f.batch, f.seq, cols, f.ldkv));
+  B200_TRY(make_map_3d(&tdo, a.d_o, f.batch, f.seq, cols, a.lddo));
+  static bool attr_set = false;
+  if (!attr_set) {
+    B200_CUDA_OK(cudaFuncSetAttribute(attn_bwd_tc_kernel<MODE_DKV>, cudaFuncAttributeMaxDynamicSharedMemorySize, kBwdSmem));
+    B200_CUDA_OK(cudaFuncSetAttribute(attn_bwd_tc_kernel<MODE_DQ>, cudaFuncAttributeMaxDynamicSharedMemorySize, kBwdSmem));
+    attr_set = true;
+  }
+  BwdParams prm;
+  prm.lse = f.lse; prm.delta = a.delta; prm.seq = f.seq; prm.n_heads = f.n_heads;
+  prm.scale = 1.f / sqrtf(64.f);
+  dim3 grid(cdiv(f.seq, 128), f.n_heads, f.batch);
+  prm.out0 = (bf16*)a.dv; prm.out1 = (bf16*)a.dk; prm.ld_out = a.lddkv;
+  attn_bwd_tc_kernel<MODE_DKV><<<grid, BW_THREADS, kBwdSmem, stream>>>(tq, tk, tv, tdo, prm, device_status_word());
+  B200_LAUNCH_OK("attn_bwd_tc_kernel<dkv>");
+  prm.out0 = (bf16*)a.dq; prm.out1 = nullptr; prm.ld_out = a.lddq;
+  attn_bwd_tc_kernel<MODE_DQ><<<grid, BW_THREADS, kBwdSmem, stream>>>(tq, tk, tv, tdo, prm, device_status_word());
+  B200_LAUNCH_OK("attn_bwd_tc_kernel<dq>");
+  return B200_OK;
+}
+
+}  // namespace b200

@@ -22,6 +22,7 @@
 
 #include "attention.cuh"
 #include "ptx_sm100.cuh"
+#include "tensor_map.cuh"
 
 namespace b200 {
 
@@ -49,29 +50,6 @@ template <int HS> struct ACfg {
   static constexpr int kTmemCols = 256;
   static constexpr int kOCol = 128;
 };
-
-__device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* map, int x, int y, int z, uint64_t* bar) {
-  asm volatile(
-      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];" ::
-          "r"(ptx::smem_u32(dst)),
-      "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(z), "r"(ptx::smem_u32(bar))
-      : "memory");
-}
-
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
-  uint32_t r[32];
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
-        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
-        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-      : "r"(taddr)
-      : "memory");
-#pragma unroll
-  for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
-}
 
 template <int HS>
 __global__ void __launch_bounds__(A_THREADS, HS == 64 ? 2 : 1)
@@ -138,7 +116,7 @@ __global__ void __launch_bounds__(A_THREADS, HS == 64 ? 2 : 1)
     if (lane == 0) {
       ptx::mbar_arrive_expect_tx(q_full, C::kTileBytes);
 #pragma unroll
-      for (int s = 0; s < C::kSubs; ++s) tma_load_3d(smem + C::kQOff + s * SUB, &tmQ, h * HS + 64 * s, t0, b, q_full);
+      for (int s = 0; s < C::kSubs; ++s) ptx::tma_load_3d(smem + C::kQOff + s * SUB, &tmQ, h * HS + 64 * s, t0, b, q_full);
       bool ok = true;
       for (int j = 0; j < n_blocks && ok; ++j) {
         const int st = j & 1;
@@ -148,8 +126,8 @@ __global__ void __launch_bounds__(A_THREADS, HS == 64 ? 2 : 1)
         ptx::mbar_arrive_expect_tx(&kv_full[st], 2 * C::kTileBytes);
 #pragma unroll
         for (int s = 0; s < C::kSubs; ++s) {
-          tma_load_3d(smem + C::kKOff + st * C::kTileBytes + s * SUB, &tmK, h * HS + 64 * s, j * AK, b, &kv_full[st]);
-          tma_load_3d(smem + C::kVOff + st * C::kTileBytes + s * SUB, &tmV, h * HS + 64 * s, j * AK, b, &kv_full[st]);
+          ptx::tma_load_3d(smem + C::kKOff + st * C::kTileBytes + s * SUB, &tmK, h * HS + 64 * s, j * AK, b, &kv_full[st]);
+          ptx::tma_load_3d(smem + C::kVOff + st * C::kTileBytes + s * SUB, &tmV, h * HS + 64 * s, j * AK, b, &kv_full[st]);
         }
       }
     }
@@ -225,7 +203,7 @@ __global__ void __launch_bounds__(A_THREADS, HS == 64 ? 2 : 1)
 #pragma unroll
       for (int c = 0; c < 64; c += 32) {
         float sv[32];
-        tmem_ld32(t_s + (uint32_t)c, sv);
+        ptx::tmem_ld32(t_s + (uint32_t)c, sv);
         ptx::tmem_ld_wait();
         if (diag) {
 #pragma unroll
@@ -233,7 +211,7 @@ __global__ void __launch_bounds__(A_THREADS, HS == 64 ? 2 : 1)
             if (u0 + c + i > t) sv[i] = -INFINITY;
         }
 #pragma unroll
-        for (int i = 0; i < 32; ++i) bm = fmaxf(bm, sv[i]);
+        for (int i = 0; i < 32; i += 2) bm = ptx::max3(bm, sv[i], sv[i + 1]);
       }
       // Both threads of a row must adopt the same maximum, but it need not be
       // exact: each rounds its own to bf16 and both take the larger of the two
@@ -250,11 +228,12 @@ __global__ void __launch_bounds__(A_THREADS, HS == 64 ? 2 : 1)
       const float nm = fmaxf(m, bm);  // finite: key 0 of block 0 is never masked, later maxima only grow
       const float nms = nm * sl2;
       // pass 2: probabilities -> bf16 -> shared memory
-      float rs = 0.f;
+      float2 rs2 = make_float2(0.f, 0.f);
+      const float2 sl2v = make_float2(sl2, sl2), nmsv = make_float2(-nms, -nms);
 #pragma unroll
       for (int c = 0; c < 64; c += 32) {
         float sv[32];
-        tmem_ld32(t_s + (uint32_t)c, sv);
+        ptx::tmem_ld32(t_s + (uint32_t)c, sv);
         ptx::tmem_ld_wait();
         if (diag) {
 #pragma unroll
@@ -266,11 +245,11 @@ __global__ void __launch_bounds__(A_THREADS, HS == 64 ? 2 : 1)
           uint4 raw;
           __nv_bfloat162* hp = reinterpret_cast<__nv_bfloat162*>(&raw);
 #pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            const float p0 = exp2f(fmaf(sv[g * 8 + 2 * i], sl2, -nms));
-            const float p1 = exp2f(fmaf(sv[g * 8 + 2 * i + 1], sl2, -nms));
-            rs += p0 + p1;
-            hp[i] = __floats2bfloat162_rn(p0, p1);
+          for (int i = 0; i < 4; ++i) {  // packed fp32x2 arithmetic: two keys per instruction
+            const float2 x = __ffma2_rn(make_float2(sv[g * 8 + 2 * i], sv[g * 8 + 2 * i + 1]), sl2v, nmsv);
+            const float2 pr = make_float2(exp2f(x.x), exp2f(x.y));
+            rs2 = __fadd2_rn(rs2, pr);
+            hp[i] = __floats2bfloat162_rn(pr.x, pr.y);
           }
           const int ch = (c >> 3) + g;  // piece 0..7 of this thread's 64 keys
           *reinterpret_cast<uint4*>(p_row + ((ch ^ (row & 7)) << 4)) = raw;
@@ -283,11 +262,16 @@ __global__ void __launch_bounds__(A_THREADS, HS == 64 ? 2 : 1)
       if (nm > m) {
         const float corr = exp2f((m - nm) * sl2);
         l *= corr;
+        const float2 cv = make_float2(corr, corr);
 #pragma unroll
-        for (int i = 0; i < OH; ++i) acc[i] *= corr;
+        for (int i = 0; i < OH; i += 2) {
+          const float2 r = __fmul2_rn(make_float2(acc[i], acc[i + 1]), cv);
+          acc[i] = r.x;
+          acc[i + 1] = r.y;
+        }
         m = nm;
       }
-      l += rs;
+      l += rs2.x + rs2.y;
       ok = ptx::mbar_wait(o_full, jp, abort_flag, status, ST_ATTN_TIMEOUT);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
@@ -295,10 +279,14 @@ __global__ void __launch_bounds__(A_THREADS, HS == 64 ? 2 : 1)
 #pragma unroll
       for (int c = 0; c < OH; c += 32) {
         float v[32];
-        tmem_ld32(t_o + (uint32_t)c, v);
+        ptx::tmem_ld32(t_o + (uint32_t)c, v);
         ptx::tmem_ld_wait();
 #pragma unroll
-        for (int i = 0; i < 32; ++i) acc[c + i] += v[i];
+        for (int i = 0; i < 32; i += 2) {
+          const float2 r = __fadd2_rn(make_float2(acc[c + i], acc[c + i + 1]), make_float2(v[i], v[i + 1]));
+          acc[c + i] = r.x;
+          acc[c + i + 1] = r.y;
+        }
       }
       ptx::tc_fence_before_sync();
       ptx::mbar_arrive(o_empty);
@@ -337,46 +325,14 @@ __global__ void __launch_bounds__(A_THREADS, HS == 64 ? 2 : 1)
   }
 }
 
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn encode_fn() {
-  static EncodeTiledFn fn = nullptr;
-  static std::once_flag once;
-  std::call_once(once, [] {
-    void* p = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
-        q == cudaDriverEntryPointSuccess)
-      fn = reinterpret_cast<EncodeTiledFn>(p);
-  });
-  return fn;
-}
-
-// [batch][seq][cols] bf16 with row pitch ld; box = 64 columns x 128 rows of one sequence.
-int32_t make_map3(CUtensorMap* map, const void* base, int batch, int seq, int cols, int ld) {
-  EncodeTiledFn fn = encode_fn();
-  if (!fn) return fail(B200_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
-  cuuint64_t dims[3] = {(cuuint64_t)cols, (cuuint64_t)seq, (cuuint64_t)batch};
-  cuuint64_t strides[2] = {(cuuint64_t)ld * 2, (cuuint64_t)seq * ld * 2};
-  cuuint32_t box[3] = {64, 128, 1};
-  cuuint32_t estr[3] = {1, 1, 1};
-  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
-                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  if (r != CUDA_SUCCESS) return fail(B200_ERR_CUDA, "cuTensorMapEncodeTiled (attention) failed with %d", (int)r);
-  return B200_OK;
-}
-
 template <int HS>
 int32_t launch_hs(const AttnArgs& a, cudaStream_t stream) {
   using C = ACfg<HS>;
   CUtensorMap tq, tk, tv;
   const int cols = a.n_heads * HS;
-  B200_TRY(make_map3(&tq, a.q, a.batch, a.seq, cols, a.ldq));
-  B200_TRY(make_map3(&tk, a.k, a.batch, a.seq, cols, a.ldkv));
-  B200_TRY(make_map3(&tv, a.v, a.batch, a.seq, cols, a.ldkv));
+  B200_TRY(make_map_3d(&tq, a.q, a.batch, a.seq, cols, a.ldq));
+  B200_TRY(make_map_3d(&tk, a.k, a.batch, a.seq, cols, a.ldkv));
+  B200_TRY(make_map_3d(&tv, a.v, a.batch, a.seq, cols, a.ldkv));
   auto kern = attn_fwd_tc_kernel<HS>;
   static bool attr_set = false;
   if (!attr_set) {

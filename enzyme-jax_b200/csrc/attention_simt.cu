@@ -302,6 +302,34 @@ int32_t launch_attn_fwd_simt(const AttnArgs& a, cudaStream_t stream) {
 }  // namespace b200
 
 namespace b200 {
+namespace {
+template <typename T, int HS>
+int32_t launch_delta_hs(const AttnBwdArgs& a, cudaStream_t stream) {
+  const AttnArgs& f = a.f;
+  dim3 grid(cdiv(f.seq, QB), f.n_heads, f.batch);
+  attn_delta_kernel<T, HS><<<grid, 128, 0, stream>>>((const T*)f.o, (const T*)a.d_o, a.delta, f.seq, f.n_heads, f.ldo,
+                                                     a.lddo);
+  B200_LAUNCH_OK("attn_delta_kernel");
+  return B200_OK;
+}
+}  // namespace
+
+int32_t launch_attn_delta(const AttnBwdArgs& a, cudaStream_t stream) {
+  if (a.f.dtype == B200_BF16 && a.f.head_size == 64) return launch_delta_hs<bf16, 64>(a, stream);
+  if (a.f.dtype == B200_BF16 && a.f.head_size == 128) return launch_delta_hs<bf16, 128>(a, stream);
+  return fail(B200_ERR_UNSUPPORTED, "delta kernel: unsupported dtype/head size");
+}
+
+int32_t launch_attn_bwd(const AttnBwdArgs& a, int impl, cudaStream_t stream) {
+  const AttnArgs& f = a.f;
+  // forward + 2.5x: S and dP twice (two passes), dV, dK, dQ: 7 products of S^2*hs per (batch, head), causal half
+  ProfScope prof(PROF_ATTN_BWD, 7.0 * f.batch * f.n_heads * (double)f.seq * f.seq * f.head_size, stream);
+  if (impl == 2) return launch_attn_bwd_simt(a, stream);
+  if (impl == 1) return launch_attn_bwd_tc(a, stream);
+  if (attn_bwd_tc_supports(a)) return launch_attn_bwd_tc(a, stream);
+  return launch_attn_bwd_simt(a, stream);
+}
+
 int32_t launch_attn_bwd_simt(const AttnBwdArgs& a, cudaStream_t stream) {
   if (!a.delta || !a.f.lse) return fail(B200_ERR_INVALID_ARG, "attention backward needs lse and a delta scratch");
   if (a.f.dtype == B200_F32) return launch_bwd_t<float>(a, stream);

@@ -18,6 +18,7 @@
 
 #include "gemm_epilogue.cuh"
 #include "ptx_sm100.cuh"
+#include "tensor_map.cuh"
 
 namespace b200 {
 
@@ -218,48 +219,16 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
 
 // ---- host side ---------------------------------------------------------------
 
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn encode_fn() {
-  static EncodeTiledFn fn = nullptr;
-  static std::once_flag once;
-  std::call_once(once, [] {
-    void* p = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
-        q == cudaDriverEntryPointSuccess)
-      fn = reinterpret_cast<EncodeTiledFn>(p);
-  });
-  return fn;
-}
-
-// 2-D bf16 row-major [rows, cols] with leading dimension ld; box = 64 x box_rows.
-int32_t make_map(CUtensorMap* map, const void* base, int rows, int cols, int ld, int box_rows) {
-  EncodeTiledFn fn = encode_fn();
-  if (!fn) return fail(B200_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
-  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
-  cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
-  cuuint32_t box[2] = {(cuuint32_t)TBK, (cuuint32_t)box_rows};
-  cuuint32_t estr[2] = {1, 1};
-  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
-                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  if (r != CUDA_SUCCESS) return fail(B200_ERR_CUDA, "cuTensorMapEncodeTiled failed with %d", (int)r);
-  return B200_OK;
-}
-
 template <int BN, int KIND, typename TOut, bool AMN, bool BMN>
 int32_t launch_cfg(const GemmArgs& g, cudaStream_t stream) {
   using Cfg = TcCfg<BN>;
   CUtensorMap tmA, tmB;
   // K-major operand: [rows = M or N, cols = K], box 64 (K) x tile rows.
   // MN-major operand: stored [K, M or N], box 64 (M or N) x TBK rows of K.
-  if (AMN) B200_TRY(make_map(&tmA, g.A, g.K, g.M, g.lda, TBK));
-  else B200_TRY(make_map(&tmA, g.A, g.M, g.K, g.lda, TBM));
-  if (BMN) B200_TRY(make_map(&tmB, g.B, g.K, g.N, g.ldb, TBK));
-  else B200_TRY(make_map(&tmB, g.B, g.N, g.K, g.ldb, BN));
+  if (AMN) B200_TRY(make_map_2d(&tmA, g.A, g.K, g.M, g.lda, TBK));
+  else B200_TRY(make_map_2d(&tmA, g.A, g.M, g.K, g.lda, TBM));
+  if (BMN) B200_TRY(make_map_2d(&tmB, g.B, g.K, g.N, g.ldb, TBK));
+  else B200_TRY(make_map_2d(&tmB, g.B, g.N, g.K, g.ldb, BN));
   auto kern = gemm_tc_kernel<BN, KIND, TOut, AMN, BMN>;
   static bool attr_set = false;  // per instantiation
   if (!attr_set) {

@@ -111,7 +111,7 @@ int32_t backward_impl(B200Plan* p, const int32_t* tokens, int B, int S, const ui
       ab.dq = dbase; ab.dk = dbase + (size_t)d * p->esize; ab.dv = dbase + (size_t)2 * d * p->esize;
       ab.lddq = 3 * d; ab.lddkv = 3 * d;
       ab.delta = b.delta;
-      B200_TRY(launch_attn_bwd_simt(ab, stream));
+      B200_TRY(launch_attn_bwd(ab, p->attn_impl, stream));
     }
     B200_TRY(launch_rope_bwd(b.dqkv, dt, 3 * d, T, 2 * d, p->hs, S, p->rope_cos, p->rope_sin, stream));
     B200_TRY(gemm(*p, b.dqkv, 3 * d, 1, a.xb, d, 1, 3 * d, d, T, gf(go.wqkv), d, B200_F32, accumulate, stream));

@@ -214,4 +214,19 @@ int32_t b200_attention(const void* q, const void* k, const void* v, void* o, flo
   return launch_attn_fwd(a, impl, reinterpret_cast<cudaStream_t>(stream));
 }
 
+int32_t b200_attention_backward(const void* q, const void* k, const void* v, const void* o, const float* lse,
+                                const void* d_o, void* dq, void* dk, void* dv, float* delta_scratch, int32_t batch,
+                                int32_t seq, int32_t n_heads, int32_t head_size, int32_t ldq, int32_t ldkv, int32_t ldo,
+                                int32_t dtype, int32_t impl, b200_stream_t stream) {
+  if (!q || !k || !v || !o || !lse || !d_o || !dq || !dk || !dv || !delta_scratch)
+    return fail(B200_ERR_INVALID_ARG, "null operand");
+  AttnBwdArgs a;
+  a.f.q = q; a.f.k = k; a.f.v = v; a.f.o = const_cast<void*>(o); a.f.lse = const_cast<float*>(lse);
+  a.f.batch = batch; a.f.seq = seq; a.f.n_heads = n_heads; a.f.head_size = head_size;
+  a.f.ldq = ldq; a.f.ldkv = ldkv; a.f.ldo = ldo; a.f.dtype = dtype;
+  a.d_o = d_o; a.lddo = ldo; a.dq = dq; a.dk = dk; a.dv = dv; a.lddq = ldq; a.lddkv = ldkv;
+  a.delta = delta_scratch;
+  return launch_attn_bwd(a, impl, reinterpret_cast<cudaStream_t>(stream));
+}
+
 }  // extern "C"

@@ -214,6 +214,16 @@ B200_API int32_t b200_attention(const void* q, const void* k, const void* v, voi
                                 int32_t seq, int32_t n_heads, int32_t head_size, int32_t ldq, int32_t ldkv,
                                 int32_t ldo, int32_t dtype, int32_t impl, b200_stream_t stream);
 
+/* Reverse mode of b200_attention: given the forward's inputs, output and lse and
+ * the cotangent d_o, writes dq, dk, dv (layouts of q, k, v).  delta_scratch is
+ * batch*n_heads*seq floats.  The rules are those of
+ * Implementations/HLODerivatives.td:1133-1182 (divide, dot_general, exp) composed
+ * over test/llama.py:177-209. */
+B200_API int32_t b200_attention_backward(const void* q, const void* k, const void* v, const void* o, const float* lse,
+                                         const void* d_o, void* dq, void* dk, void* dv, float* delta_scratch,
+                                         int32_t batch, int32_t seq, int32_t n_heads, int32_t head_size, int32_t ldq,
+                                         int32_t ldkv, int32_t ldo, int32_t dtype, int32_t impl, b200_stream_t stream);
+
 /* Decode attention over the paged cache (test/llama.py:177-209 with a cache of
  * ctx rows): one query row per (sequence, head).
  *   q          [batch, ldq] of `dtype`

@@ -1,0 +1,77 @@
+"""Worker for the multi-GPU parity tests; launched with torch.distributed.run, one rank per GPU.
+
+Checks, against the CPU oracle: tensor-parallel forward (vocabulary-sharded logits), tensor-parallel decode steps,
+and the data-parallel gradient all-reduce."""
+import os
+import sys
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+for p in (ROOT, os.path.join(ROOT, "enzyme-jax_b200")):
+    if p not in sys.path:
+        sys.path.insert(0, p)
+
+import torch
+import torch.distributed as dist
+
+import b200_llama as B
+from oracle import llama_ref as O
+
+
+def main():
+    rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
+    torch.cuda.set_device(local)
+    dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    comm = B.Comm(rank, world)
+    cfg = dict(dim=256, hidden_dim=512, n_layers=2, n_heads=4, n_kv_heads=4, vocab_size=1024, seq_len=160)
+    for dtype, tol in ((torch.float32, 1e-4), (torch.bfloat16, 2e-2)):
+        w = {k: v.to(dtype) for k, v in O.make_weights(cfg, 3, torch.float32, std=0.05).items()}
+        tokens = O.make_tokens(cfg, 2, 128, 4)
+        ref = O.forward_sequence(tokens, cfg, {k: v.double() for k, v in w.items()})
+        plan = B.Plan(cfg, dtype, tp_rank=rank, tp_size=world, comm=comm)
+        plan.pack_weights({k: v.cuda().contiguous() for k, v in w.items()})
+        got = plan.forward(tokens.int().cuda())
+        torch.cuda.synchronize()
+        vl = cfg["vocab_size"] // world
+        mine = ref[..., rank * vl:(rank + 1) * vl]
+        err = float((got.double().cpu() - mine).abs().max() / ref.abs().max())
+        assert err < tol, ("tp forward", dtype, err)
+        # decode, tensor parallel: the cache holds this rank's heads only
+        page, seq = 32, 40
+        max_pages = (seq + page - 1) // page
+        kv = plan.new_kv_pages(2 * max_pages, page)
+        table = torch.arange(2 * max_pages, dtype=torch.int32, device="cuda").view(2, max_pages)
+        tok = tokens.int().cuda()
+        for pos in range(seq):
+            _, lg = plan.decode_step(pos, kv, table, tokens=tok[:, pos].contiguous())
+            e = float((lg.double().cpu() - mine[:, pos]).abs().max() / ref.abs().max())
+            assert e < tol, ("tp decode", dtype, pos, e)
+        assert B.device_status() == 0
+        plan.close()
+    # data parallel: each rank differentiates its own sequences, gradients are summed over the ranks
+    dtype = torch.float32
+    w = O.make_weights(cfg, 5, torch.float32, std=0.05, gains_one=False)
+    tokens = O.make_tokens(cfg, 2 * world, 64, 6)
+    g = torch.Generator().manual_seed(7)
+    dl = torch.randn(2 * world, 64, cfg["vocab_size"], generator=g)
+    _, ref = O.vjp_sequence(tokens, cfg, {k: v.double() for k, v in w.items()}, dl.double())
+    plan = B.Plan(cfg, dtype)
+    plan.pack_weights({k: v.cuda().contiguous() for k, v in w.items()}, with_transposed=True)
+    tok = tokens[2 * rank:2 * rank + 2].int().cuda().contiguous()
+    saved = plan.new_saved(2, 64)
+    plan.forward(tok, saved=saved)
+    grads = plan.backward(tok, dl[2 * rank:2 * rank + 2].cuda().contiguous(), saved, plan.new_grads())
+    comm.allreduce_f32(grads)
+    leaves = plan.unpack_grads(grads)
+    for k, r in ref.items():
+        e = float((leaves[k].double().cpu() - r).abs().max() / r.abs().max())
+        assert e < 1e-4, ("dp grads", k, e)
+    torch.cuda.synchronize()
+    dist.barrier()
+    comm.destroy()
+    dist.destroy_process_group()
+    if rank == 0:
+        print("MULTI_GPU_OK", world)
+
+
+if __name__ == "__main__":
+    main()

@@ -168,3 +168,24 @@ def test_gemm_tensor_core_transposed_operands(ta, tb, M, N, K):
     ref = (a.float().T if ta else a.float()) @ (b.float() if tb else b.float().T)
     assert B.device_status() == 0
     assert torch.equal(y, ref)
+
+
+@pytest.mark.parametrize("impl", [0, 2])
+@pytest.mark.parametrize("B_,S,H,hs,dtype", [(2, 256, 3, 64, torch.bfloat16), (1, 200, 2, 64, torch.bfloat16),
+                                             (2, 1024, 2, 64, torch.bfloat16), (1, 96, 2, 48, torch.float32)])
+def test_attention_backward(impl, B_, S, H, hs, dtype):
+    g = torch.Generator().manual_seed(5)
+    d = H * hs
+    qkv = torch.randn(B_ * S, 3 * d, generator=g).to(dtype).to(DEV)
+    d_o = torch.randn(B_ * S, d, generator=g).to(dtype).to(DEV)
+    ref_in = qkv.double().clone().requires_grad_(True)
+    ro, _ = _attn_ref(ref_in[:, :d], ref_in[:, d:2 * d], ref_in[:, 2 * d:], B_, S, H)
+    ro.backward(d_o.double())
+    o, lse = B.attention(qkv[:, :d], qkv[:, d:2 * d], qkv[:, 2 * d:], B_, S, H, impl=impl)
+    dqkv = B.attention_backward(qkv, o, lse, d_o, B_, S, H, impl=impl)
+    assert B.device_status() == 0
+    tol = 1e-4 if dtype == torch.float32 else 2e-2
+    for name, sl in (("dq", slice(0, d)), ("dk", slice(d, 2 * d)), ("dv", slice(2 * d, 3 * d))):
+        r = ref_in.grad[:, sl]
+        err = float((dqkv[:, sl].double() - r).abs().max() / r.abs().max())
+        assert err < tol, (name, err)
