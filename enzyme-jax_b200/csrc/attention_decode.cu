@@ -108,6 +108,139 @@ __global__ void __launch_bounds__(DW * 32)
   }
 }
 
+// bf16 fast path.  A key or value row of one head is HS*2 bytes; LPK = HS/8
+// lanes each fetch 16 bytes of it, so one warp-wide load brings in 32/LPK whole
+// rows, fully coalesced.  Every lane keeps G such loads of K and of V in flight.
+// The dot product is finished with log2(LPK) shuffles; each group of LPK lanes
+// runs its own online softmax over the keys it sees and the groups, warps and
+// (when the context is split) CTAs are merged at the end.
+constexpr int VW = 8;  // warps per CTA
+constexpr int VG = 4;  // loads in flight per lane and operand
+
+__device__ __forceinline__ void unpack8(const uint4& raw, float (&v)[8]) {
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 f = __bfloat1622float2(h[i]);
+    v[2 * i] = f.x;
+    v[2 * i + 1] = f.y;
+  }
+}
+
+template <int HS>
+__global__ void __launch_bounds__(VW * 32)
+    attn_decode_vec_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kpages, const bf16* __restrict__ vpages,
+                           const int32_t* __restrict__ page_table, float* __restrict__ scratch, bf16* __restrict__ o,
+                           int ctx, int n_heads, int ldq, int ldo, int page_size, int max_pages, int d_local,
+                           int n_splits, float scale) {
+  constexpr int LPK = HS / 8;
+  constexpr int KPW = 32 / LPK;
+  __shared__ float s_acc[VW][HS];
+  __shared__ float s_m[VW], s_l[VW];
+  const int split = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int sub = lane / LPK, li = lane % LPK;
+  const int32_t* table = page_table + (size_t)b * max_pages;
+  float qf[8];
+  load8(q + (size_t)b * ldq + h * HS + li * 8, qf);
+#pragma unroll
+  for (int i = 0; i < 8; ++i) qf[i] *= scale;
+
+  const int per = (ctx + n_splits - 1) / n_splits;
+  const int c0 = split * per, c1 = min(ctx, c0 + per);
+  float m = -INFINITY, l = 0.f, acc[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+
+  for (int u0 = c0 + warp * (VG * KPW); u0 < c1; u0 += VW * VG * KPW) {
+    uint4 kr[VG], vr[VG];
+    bool live[VG];
+#pragma unroll
+    for (int g = 0; g < VG; ++g) {
+      const int u = u0 + g * KPW + sub;
+      live[g] = u < c1;
+      kr[g] = make_uint4(0u, 0u, 0u, 0u);
+      vr[g] = make_uint4(0u, 0u, 0u, 0u);
+      if (live[g]) {
+        const int page = table[u / page_size];
+        const size_t off = ((size_t)page * page_size + (u % page_size)) * d_local + h * HS + li * 8;
+        kr[g] = *reinterpret_cast<const uint4*>(kpages + off);
+        vr[g] = *reinterpret_cast<const uint4*>(vpages + off);
+      }
+    }
+    float s[VG];
+    float bm = -INFINITY;
+#pragma unroll
+    for (int g = 0; g < VG; ++g) {
+      float kf[8];
+      unpack8(kr[g], kf);
+      float d = 0.f;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) d = fmaf(qf[i], kf[i], d);
+#pragma unroll
+      for (int off = LPK / 2; off > 0; off >>= 1) d += __shfl_xor_sync(0xffffffffu, d, off);
+      s[g] = live[g] ? d : -INFINITY;
+      bm = fmaxf(bm, s[g]);
+    }
+    if (bm > -INFINITY) {  // uniform within a group of LPK lanes
+      const float nm = fmaxf(m, bm);
+      const float corr = __expf(m - nm);
+      l *= corr;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) acc[i] *= corr;
+#pragma unroll
+      for (int g = 0; g < VG; ++g) {
+        const float p = __expf(s[g] - nm);  // exp(-inf) = 0 for keys past the end
+        l += p;
+        float vf[8];
+        unpack8(vr[g], vf);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc[i] = fmaf(p, vf[i], acc[i]);
+      }
+      m = nm;
+    }
+  }
+  // merge the key groups of the warp (they hold the same head dimensions)
+#pragma unroll
+  for (int off = LPK; off < 32; off <<= 1) {
+    const float mo = __shfl_xor_sync(0xffffffffu, m, off);
+    const float lo = __shfl_xor_sync(0xffffffffu, l, off);
+    const float nm = fmaxf(m, mo);
+    const float a = m > -INFINITY ? __expf(m - nm) : 0.f;
+    const float c = mo > -INFINITY ? __expf(mo - nm) : 0.f;
+    l = l * a + lo * c;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const float ao = __shfl_xor_sync(0xffffffffu, acc[i], off);
+      acc[i] = acc[i] * a + ao * c;
+    }
+    m = nm;
+  }
+  if (sub == 0) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) s_acc[warp][li * 8 + i] = acc[i];
+  }
+  if (lane == 0) { s_m[warp] = m; s_l[warp] = l; }
+  __syncthreads();
+  float gm = -INFINITY;
+#pragma unroll
+  for (int w = 0; w < VW; ++w) gm = fmaxf(gm, s_m[w]);
+  float gl = 0.f;
+#pragma unroll
+  for (int w = 0; w < VW; ++w)
+    if (s_m[w] > -INFINITY) gl += s_l[w] * __expf(s_m[w] - gm);
+  float* part = scratch + (((size_t)b * n_heads + h) * n_splits + split) * (HS + 2);
+  for (int e = threadIdx.x; e < HS; e += blockDim.x) {
+    float a = 0.f;
+#pragma unroll
+    for (int w = 0; w < VW; ++w)
+      if (s_m[w] > -INFINITY) a += s_acc[w][e] * __expf(s_m[w] - gm);
+    if (n_splits == 1) o[(size_t)b * ldo + h * HS + e] = __float2bfloat16_rn(a / gl);
+    else part[e] = a;
+  }
+  if (n_splits > 1 && threadIdx.x == 0) { part[HS] = gm; part[HS + 1] = gl; }
+}
+
 template <typename T, int HS>
 __global__ void attn_decode_combine_kernel(const float* __restrict__ scratch, T* __restrict__ o, int n_heads, int ldo,
                                            int n_splits) {
@@ -136,6 +269,18 @@ int32_t launch_hs(const AttnDecodeArgs& a, cudaStream_t stream) {
   const T* kp = reinterpret_cast<const T*>(a.kv_pages);
   const T* vp = kp + page_elems;
   dim3 grid(a.n_splits, a.n_heads, a.batch);
+  if constexpr (sizeof(T) == 2 && (HS == 64 || HS == 128)) {
+    attn_decode_vec_kernel<HS><<<grid, VW * 32, 0, stream>>>((const bf16*)a.q, (const bf16*)kp, (const bf16*)vp,
+                                                            a.page_table, a.scratch, (bf16*)a.o, a.ctx, a.n_heads,
+                                                            a.ldq, a.ldo, a.page_size, a.max_pages, a.d_local,
+                                                            a.n_splits, 1.f / sqrtf((float)HS));
+    B200_LAUNCH_OK("attn_decode_vec_kernel");
+    if (a.n_splits == 1) return B200_OK;  // the kernel wrote the output itself
+    dim3 grid2v(a.n_heads, a.batch);
+    attn_decode_combine_kernel<T, HS><<<grid2v, HS, 0, stream>>>(a.scratch, (T*)a.o, a.n_heads, a.ldo, a.n_splits);
+    B200_LAUNCH_OK("attn_decode_combine_kernel");
+    return B200_OK;
+  }
   attn_decode_kernel<T, HS><<<grid, DW * 32, 0, stream>>>((const T*)a.q, kp, vp, a.page_table, a.scratch, a.ctx,
                                                           a.n_heads, a.ldq, a.page_size, a.max_pages, a.d_local,
                                                           a.n_splits, 1.f / sqrtf((float)HS));

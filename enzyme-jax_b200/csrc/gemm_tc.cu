@@ -31,7 +31,7 @@ constexpr int TC_THREADS = 192;
 constexpr int kMnBoxBytes = 64 * TBK * 2;  // one TMA box of an MN-major operand: TBK rows of 64 elements
 
 template <int BN> struct TcCfg {
-  static constexpr int kStages = (BN >= 256) ? 4 : 6;
+  static constexpr int kStages = (BN >= 256) ? 4 : (BN >= 128 ? 6 : 8);
   static constexpr int kABytes = TBM * TBK * 2;
   static constexpr int kBBytes = BN * TBK * 2;
   static constexpr int kStageBytes = kABytes + kBBytes;
@@ -244,11 +244,21 @@ int32_t launch_cfg(const GemmArgs& g, cudaStream_t stream) {
 
 template <int KIND, typename TOut, bool AMN, bool BMN>
 int32_t launch_bn(const GemmArgs& g, cudaStream_t stream) {
-  // Wide tiles when they still fill the machine, narrower ones otherwise.
   const int sms = sm_count();
-  const long t256 = (long)cdiv(g.M, TBM) * cdiv(g.N, 256);
+  const long mt = cdiv(g.M, TBM);
+  if (mt == 1) {
+    // One row of tiles (decode: the batch is the M dimension).  The kernel then
+    // only streams the weights, so what matters is how many SMs pull on HBM:
+    // take the widest tile that still gives every SM a tile.
+    if (g.N % 256 == 0 && g.N / 256 >= sms) return launch_cfg<256, KIND, TOut, AMN, BMN>(g, stream);
+    if (cdiv(g.N, 128) >= sms) return launch_cfg<128, KIND, TOut, AMN, BMN>(g, stream);
+    if (BMN || cdiv(g.N, 64) >= sms) return launch_cfg<64, KIND, TOut, AMN, BMN>(g, stream);  // MN-major boxes are 64 wide
+    return launch_cfg<32, KIND, TOut, AMN, false>(g, stream);
+  }
+  // Wide tiles when they still fill the machine, narrower ones otherwise.
+  const long t256 = mt * cdiv(g.N, 256);
   if (g.N % 256 == 0 && t256 >= 2L * sms) return launch_cfg<256, KIND, TOut, AMN, BMN>(g, stream);
-  const long t128 = (long)cdiv(g.M, TBM) * cdiv(g.N, 128);
+  const long t128 = mt * cdiv(g.N, 128);
   if (t128 >= sms || g.N >= 128) return launch_cfg<128, KIND, TOut, AMN, BMN>(g, stream);
   return launch_cfg<64, KIND, TOut, AMN, BMN>(g, stream);
 }
