@@ -169,20 +169,50 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
     bool ok = true;
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
       const int m0 = (tile % m_tiles) * TBM, n0 = (tile / m_tiles) * BN;
-      ok = ptx::mbar_wait(&acc_full[acc], acc_phase, abort_flag, status, ST_EPILOGUE_TIMEOUT);
-      ok = __all_sync(0xffffffffu, ok);
-      if (!ok) break;
-      ptx::tc_fence_after_sync();
       const int m = m0 + q * 32 + lane;
       const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN);
       const bool row_ok = m < M;
       const EpiRow erow = epi_row_begin<KIND>(ep, row_ok ? m : 0);
+      // Operands the epilogue reads from global memory are fetched BEFORE the
+      // wait for the accumulator, so that their latency overlaps the main loop:
+      // the residual row (first 128 columns of the tile) and, for head size 64,
+      // the 32 cos/sin pairs of the row's position.
+      constexpr int PRE = (KIND == EPI_RESID) ? (BN < 128 ? BN : 128) : 8;
+      float rpre[PRE];
+      float rc[32], rs[32];
+      const bool rope64 = KIND == EPI_ROPE && ep.head_size == 64 && (BN % 64 == 0);
+      if constexpr (KIND == EPI_RESID) {
+        const float* xi = ep.resid_in + (size_t)(row_ok ? m : 0) * ep.ldo + n0;
+#pragma unroll
+        for (int c = 0; c < PRE; c += 8) {
+          float t8[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+          if (row_ok && n0 + c < N) load8_wide(xi + c, t8);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) rpre[c + i] = t8[i];
+        }
+      }
+      if constexpr (KIND == EPI_ROPE) {
+        if (rope64) {
+#pragma unroll
+          for (int c = 0; c < 32; c += 8) {
+            float t8[8], u8[8];
+            load8_wide(erow.rope_c + c, t8);
+            load8_wide(erow.rope_s + c, u8);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) { rc[c + i] = t8[i]; rs[c + i] = u8[i]; }
+          }
+        }
+      }
+      ok = ptx::mbar_wait(&acc_full[acc], acc_phase, abort_flag, status, ST_EPILOGUE_TIMEOUT);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      ptx::tc_fence_after_sync();
       // 32 columns per TMEM round trip; the next pair of loads is in flight
       // while the current 32 columns go through the epilogue.
       float cur[2][16], nxt[2][16];
       ptx::tmem_ld16(taddr, cur[0]);
       ptx::tmem_ld16(taddr + 16u, cur[1]);
-#pragma unroll 1
+#pragma unroll
       for (int c = 0; c < BN; c += 32) {
         ptx::tmem_ld_wait();
         if (c + 32 < BN) {
@@ -190,8 +220,38 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
           ptx::tmem_ld16(taddr + (uint32_t)(c + 48), nxt[1]);
         }
         if (row_ok) {
-          if (n0 + c < N) epi_apply16<KIND, TOut>(ep, erow, m, n0 + c, cur[0]);
-          if (n0 + c + 16 < N) epi_apply16<KIND, TOut>(ep, erow, m, n0 + c + 16, cur[1]);
+#pragma unroll
+          for (int hlf = 0; hlf < 2; ++hlf) {
+            const int cc = c + 16 * hlf;
+            if (n0 + cc < N) {
+              if (KIND == EPI_RESID && cc < PRE) {
+                float* xo = reinterpret_cast<float*>(ep.out) + (size_t)m * ep.ldo + n0 + cc;
+                float lo[8], hi[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                  lo[i] = rpre[(cc % PRE) + i] + cur[hlf][i];
+                  hi[i] = rpre[(cc % PRE) + 8 + i] + cur[hlf][8 + i];
+                }
+                store8_wide(xo, lo);
+                store8_wide(xo + 8, hi);
+              } else if (KIND == EPI_ROPE && rope64) {
+                if (n0 + cc < ep.rope_cols) {
+                  constexpr int dummy = 0;
+                  (void)dummy;
+                  const int j0 = (cc % 64) >> 1;  // compile-time after unrolling: tiles start on head boundaries
+#pragma unroll
+                  for (int i = 0; i < 8; ++i) {
+                    const float e = cur[hlf][2 * i], o = cur[hlf][2 * i + 1];
+                    cur[hlf][2 * i] = rc[j0 + i] * e - rs[j0 + i] * o;
+                    cur[hlf][2 * i + 1] = rs[j0 + i] * e + rc[j0 + i] * o;
+                  }
+                }
+                store16(reinterpret_cast<TOut*>(ep.out) + (size_t)m * ep.ldo + n0 + cc, cur[hlf]);
+              } else {
+                epi_apply16<KIND, TOut>(ep, erow, m, n0 + cc, cur[hlf]);
+              }
+            }
+          }
         }
 #pragma unroll
         for (int i = 0; i < 16; ++i) { cur[0][i] = nxt[0][i]; cur[1][i] = nxt[1][i]; }
