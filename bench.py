@@ -60,34 +60,83 @@ def peaks():
 
 
 class ClockSampler:
-    """Samples SM clock and throttle reasons of one GPU with nvidia-smi during the timed region."""
+    """Samples SM clock and throttle reasons of one GPU during the timed region: NVML in a background thread
+    (read-only queries), or an `nvidia-smi -lms` child process when the NVML binding is missing."""
 
     FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
               "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
               "clocks_event_reasons.sw_power_cap")
+    REASONS = {0x4: "sw_power_cap", 0x8: "hw_slowdown", 0x20: "sw_thermal_slowdown", 0x40: "hw_thermal_slowdown"}
 
-    def __init__(self, gpu_index: int):
+    def __init__(self, gpu_index: int, period_s: float = 0.1):
         self.gpu = gpu_index
+        self.period = period_s
         self.lines = []
+        self.samples = []
         self.proc = None
+        self.thread = None
+        self.stop_flag = threading.Event()
+        self.max_mhz = None
+
+    def _physical_index(self):
+        vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+        if vis:
+            ids = [x.strip() for x in vis.split(",") if x.strip()]
+            if self.gpu < len(ids) and ids[self.gpu].isdigit():
+                return int(ids[self.gpu])
+        return self.gpu
 
     def start(self):
         try:
-            self.proc = subprocess.Popen(
-                ["nvidia-smi", "-i", str(self.gpu), f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
-                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
-            self.thread = threading.Thread(target=self._read, daemon=True)
+            import pynvml
+            pynvml.nvmlInit()
+            self.nvml = pynvml
+            self.handle = pynvml.nvmlDeviceGetHandleByIndex(self._physical_index())
+            self.max_mhz = float(pynvml.nvmlDeviceGetMaxClockInfo(self.handle, pynvml.NVML_CLOCK_SM))
+            self.thread = threading.Thread(target=self._poll, daemon=True)
             self.thread.start()
+            return
+        except Exception:
+            self.thread = None
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self._physical_index()), f"--query-gpu={self.FIELDS}",
+                 "--format=csv,noheader,nounits", "-lms", "200"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL,
+                text=True)
+            self.reader = threading.Thread(target=self._read, daemon=True)
+            self.reader.start()
         except Exception:
             self.proc = None
+
+    def _poll(self):
+        n = self.nvml
+        while not self.stop_flag.is_set():
+            try:
+                mhz = float(n.nvmlDeviceGetClockInfo(self.handle, n.NVML_CLOCK_SM))
+                mask = int(n.nvmlDeviceGetCurrentClocksThrottleReasons(self.handle))
+                self.samples.append((mhz, mask))
+            except Exception:
+                pass
+            self.stop_flag.wait(self.period)
 
     def _read(self):
         for line in self.proc.stdout:
             self.lines.append(line.strip())
 
     def stop(self):
+        if self.thread is not None:
+            self.stop_flag.set()
+            self.thread.join(timeout=2)
+            sm = sorted(x[0] for x in self.samples)
+            reasons = set()
+            for _, mask in self.samples:
+                for bit, name in self.REASONS.items():
+                    if mask & bit:
+                        reasons.add(name)
+            return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": self.max_mhz,
+                    "reasons": sorted(reasons), "samples": len(sm), "source": "nvml"}
         if not self.proc:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["clock sampling unavailable"]}
         self.proc.terminate()
         try:
             self.proc.wait(timeout=5)
@@ -109,7 +158,7 @@ class ClockSampler:
                     reasons.add(name)
         sm.sort()
         return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": mx, "reasons": sorted(reasons),
-                "samples": len(sm)}
+                "samples": len(sm), "source": "nvidia-smi"}
 
 
 def cpu_oracle_rate(cfg, seq, sample_batch, reps, vjp=False):
@@ -245,13 +294,30 @@ def run_prefill(args, rank, world, local, B, dist):
     last_host = torch.empty(batch, plan.vocab_local, dtype=torch.float32).pin_memory()
     tok_stage = torch.empty(batch, seq, dtype=torch.int32, device=dev)
 
+    # The plan's kernel sequence is static: replay it as a CUDA graph (one graph per token buffer).
+    use_graph = not args.no_graph and tp == 1
+    launches_per_forward = None
+    if use_graph:
+        l_before = B.launch_count()
+        graphs = [plan.capture_forward(t, logits) for t in dev_tokens]
+        graph_stage = plan.capture_forward(tok_stage, logits)
+        launches_per_forward = (B.launch_count() - l_before) // (2 * (n_bufs + 1))
+    last_dev = torch.empty(batch, plan.vocab_local, dtype=torch.float32, device=dev)
+
     def step_resident(i):
-        plan.forward(dev_tokens[i % n_bufs], logits=logits)
+        if use_graph:
+            graphs[i % n_bufs].replay()
+        else:
+            plan.forward(dev_tokens[i % n_bufs], logits=logits)
 
     def step_e2e(i):
         tok_stage.copy_(host_tokens[i % n_bufs], non_blocking=True)
-        plan.forward(tok_stage, logits=logits)
-        last_host.copy_(logits[:, -1, :], non_blocking=True)
+        if use_graph:
+            graph_stage.replay()
+        else:
+            plan.forward(tok_stage, logits=logits)
+        last_dev.copy_(logits[:, -1, :])
+        last_host.copy_(last_dev, non_blocking=True)
         torch.cuda.current_stream().synchronize()
 
     for i in range(args.warmup):
@@ -266,14 +332,14 @@ def run_prefill(args, rank, world, local, B, dist):
         time.sleep(0.3)
     l0 = B.launch_count()
     ms = timed(step_resident, args.steps, world, dist)
-    launches = B.launch_count() - l0
+    launches = (B.launch_count() - l0) if not use_graph else launches_per_forward * args.steps
     ms_e2e = timed(step_e2e, args.steps, world, dist)
     clocks = sampler.stop() if rank == 0 else None
 
-    # per-kernel event timing over the same K steps (a second pass: the event
+    # per-kernel event timing over the same K steps (a second pass, eager launches: the event
     # pairs cost a little, so they are kept out of the headline timing)
     B.profile_enable(True)
-    timed(step_resident, args.steps, world, dist)
+    timed(lambda i: plan.forward(dev_tokens[i % n_bufs], logits=logits), args.steps, world, dist)
     prof = B.profile_read()
     B.profile_enable(False)
     if B.device_status() != 0:
@@ -305,7 +371,8 @@ def run_prefill(args, rank, world, local, B, dist):
         "config": {"workload": desc, "batch_per_rank": batch, "seq_len": seq,
                    "parallelism": f"tp{tp}" if tp > 1 else (f"replicas{world}" if world > 1 else "single"),
                    "l2_policy": "working set per step (weights + 1.05 GB of logits) exceeds the 126 MB L2; "
-                                "token buffers rotate"},
+                                "token buffers rotate",
+                   "launch": "cuda graph replay" if use_graph else "eager launches"},
         "e2e": {"value": e2e, "unit": "tokens/s", "h2d_bytes_per_step": batch * seq * 4,
                 "d2h_bytes_per_step": batch * plan.vocab_local * 4, "ms_per_step": ms_e2e / args.steps,
                 "result": "last-position logits of every sequence"},
@@ -528,6 +595,7 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--batch", type=int, default=0, help="override the batch per rank (profiling on a small case)")
+    ap.add_argument("--no-graph", action="store_true", help="launch every kernel eagerly instead of replaying a CUDA graph")
     args = ap.parse_args()
 
     rank = int(os.environ.get("RANK", "0"))

@@ -352,6 +352,17 @@ class Plan:
                                  _ptr(saved), _ptr(kv_out), ws.data_ptr(), ws.numel(), _stream()))
         return logits
 
+    def capture_forward(self, tokens: torch.Tensor, logits: torch.Tensor) -> "torch.cuda.CUDAGraph":
+        """Captures one forward over fixed token / logits buffers into a CUDA graph (the kernel sequence of a
+        plan is static, so a replay costs one launch instead of 1 + 7L + 2).  Run one eager forward first so that
+        the workspace exists and every kernel attribute is set outside the capture."""
+        self.forward(tokens, logits=logits)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            self.forward(tokens, logits=logits)
+        return graph
+
     def new_saved(self, batch: int, seq: int) -> torch.Tensor:
         return torch.empty(self.saved_bytes(batch, seq), dtype=torch.uint8, device=self.device)
 

@@ -148,7 +148,12 @@ struct GemmArgs {
   int out_dtype = B200_BF16;
   int kind = EPI_STORE;
   EpiParams epi;
+  // optional scratch for K-split partial sums (fp32); null disables splitting
+  void* splitk_scratch = nullptr;
+  size_t splitk_bytes = 0;
 };
+// Scratch that lets the tensor-core kernel split K whenever it wants to for an M x N output.
+inline size_t gemm_splitk_scratch_bytes(int M, int N) { return (size_t)32 * M * N * sizeof(float); }
 
 int32_t launch_gemm_simt(const GemmArgs& g, cudaStream_t stream);
 int32_t launch_gemm_tc(const GemmArgs& g, cudaStream_t stream);

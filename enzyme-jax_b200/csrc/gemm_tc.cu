@@ -48,7 +48,7 @@ enum : uint32_t {
 template <int BN, int KIND, typename TOut, bool AMN, bool BMN>
 __global__ void __launch_bounds__(TC_THREADS, 1)
     gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, int M, int N,
-                   int K, EpiParams ep, uint32_t* status) {
+                   int K, EpiParams ep, int splits, float* __restrict__ partial, uint32_t* status) {
   using Cfg = TcCfg<BN>;
   constexpr int S = Cfg::kStages;
   extern __shared__ uint8_t smem_raw[];
@@ -67,6 +67,9 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
   const int n_tiles = (N + BN - 1) / BN;
   const int num_tiles = m_tiles * n_tiles;
   const int num_kb = (K + TBK - 1) / TBK;
+  // Work item w = (tile, K-split): tile = w % num_tiles, split = w / num_tiles; the
+  // split covers k-blocks [split*num_kb/splits, (split+1)*num_kb/splits).
+  const int num_items = num_tiles * splits;
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < S; ++i) {
@@ -96,9 +99,11 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+      for (int item = blockIdx.x; item < num_items && ok; item += gridDim.x) {
+        const int tile = item % num_tiles, split = item / num_tiles;
         const int m0 = (tile % m_tiles) * TBM, n0 = (tile / m_tiles) * BN;
-        for (int kb = 0; kb < num_kb; ++kb) {
+        const int kb0 = (int)((long)split * num_kb / splits), kb1 = (int)((long)(split + 1) * num_kb / splits);
+        for (int kb = kb0; kb < kb1; ++kb) {
           ok = ptx::mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag, status, ST_PRODUCER_TIMEOUT);
           if (!ok) break;
           uint8_t* sa = smem + stage * Cfg::kStageBytes;
@@ -133,12 +138,14 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
       int acc = 0;
       uint32_t acc_phase = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+      for (int item = blockIdx.x; item < num_items && ok; item += gridDim.x) {
+        const int split = item / num_tiles;
+        const int kb0 = (int)((long)split * num_kb / splits), kb1 = (int)((long)(split + 1) * num_kb / splits);
         ok = ptx::mbar_wait(&acc_empty[acc], acc_phase ^ 1u, abort_flag, status, ST_MMA_TIMEOUT);
         if (!ok) break;
         ptx::tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
-        for (int kb = 0; kb < num_kb; ++kb) {
+        for (int kb = kb0; kb < kb1; ++kb) {
           ok = ptx::mbar_wait(&full_bar[stage], phase, abort_flag, status, ST_MMA_TIMEOUT);
           if (!ok) break;
           ptx::tc_fence_after_sync();
@@ -150,7 +157,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
           for (int k = 0; k < TBK / UMMA_K; ++k) {
             // K-major: 16 elements further along a 128-byte row = 32 bytes;
             // MN-major: 16 rows of 128 bytes further down.
-            ptx::mma_bf16_ss(d_tmem, adesc + a_step * k, bdesc + b_step * k, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+            ptx::mma_bf16_ss(d_tmem, adesc + a_step * k, bdesc + b_step * k, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
           }
           ptx::mma_commit(&empty_bar[stage]);
           if (++stage == S) { stage = 0; phase ^= 1u; }
@@ -167,7 +174,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
     int acc = 0;
     uint32_t acc_phase = 0;
     bool ok = true;
-    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+    for (int item = blockIdx.x; item < num_items && ok; item += gridDim.x) {
+      const int tile = item % num_tiles, split = item / num_tiles;
       const int m0 = (tile % m_tiles) * TBM, n0 = (tile / m_tiles) * BN;
       const int m = m0 + q * 32 + lane;
       const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN);
@@ -181,7 +189,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
       float rpre[PRE];
       float rc[32], rs[32];
       const bool rope64 = KIND == EPI_ROPE && ep.head_size == 64 && (BN % 64 == 0);
-      if constexpr (KIND == EPI_RESID) {
+      if (KIND == EPI_RESID && splits == 1) {
         const float* xi = ep.resid_in + (size_t)(row_ok ? m : 0) * ep.ldo + n0;
 #pragma unroll
         for (int c = 0; c < PRE; c += 8) {
@@ -191,7 +199,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
           for (int i = 0; i < 8; ++i) rpre[c + i] = t8[i];
         }
       }
-      if constexpr (KIND == EPI_ROPE) {
+      if (KIND == EPI_ROPE && splits == 1) {
         if (rope64) {
 #pragma unroll
           for (int c = 0; c < 32; c += 8) {
@@ -224,7 +232,9 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
           for (int hlf = 0; hlf < 2; ++hlf) {
             const int cc = c + 16 * hlf;
             if (n0 + cc < N) {
-              if (KIND == EPI_RESID && cc < PRE) {
+              if (splits > 1) {  // K-split: raw fp32 partial sums, the fused epilogue runs in the reduction kernel
+                store16(partial + ((size_t)split * M + m) * N + n0 + cc, cur[hlf]);
+              } else if (KIND == EPI_RESID && cc < PRE) {
                 float* xo = reinterpret_cast<float*>(ep.out) + (size_t)m * ep.ldo + n0 + cc;
                 float lo[8], hi[8];
 #pragma unroll
@@ -279,6 +289,48 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
 
 // ---- host side ---------------------------------------------------------------
 
+// Sums the K-split partials in split order and applies the fused epilogue.
+template <int KIND, typename TOut>
+__global__ void __launch_bounds__(256) splitk_reduce_kernel(const float* __restrict__ partial, int splits, int M, int N,
+                                                            EpiParams ep) {
+  const int per_row = N / 16;
+  const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= M * per_row) return;
+  const int m = idx / per_row, n = (idx % per_row) * 16;
+  float v[16];
+#pragma unroll
+  for (int i = 0; i < 16; ++i) v[i] = 0.f;
+  for (int s = 0; s < splits; ++s) {
+    const float* p = partial + ((size_t)s * M + m) * N + n;
+    float a[8], b[8];
+    load8_wide(p, a);
+    load8_wide(p + 8, b);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) { v[i] += a[i]; v[8 + i] += b[i]; }
+  }
+  const EpiRow row = epi_row_begin<KIND>(ep, m);
+  epi_apply16<KIND, TOut>(ep, row, m, n, v);
+}
+
+// K-splits for problems with too few output tiles to fill the machine (weight
+// gradients: small M x N, K = tokens; decode projections: one row of tiles).
+// Needs caller scratch for splits * M * N floats.
+int pick_splits(const GemmArgs& g, int tiles) {
+  if (!g.splitk_scratch) return 1;
+  const int sms = sm_count();
+  const int num_kb = cdiv(g.K, TBK);
+  if (tiles >= 2 * sms || num_kb < 16) return 1;
+  // cost of s splits in units of one full-K tile: rounds of the persistent grid, each 1/s long
+  int best = 1;
+  double best_cost = (double)cdiv(tiles, sms);
+  for (int s = 2; s <= 32 && num_kb / s >= 8; ++s) {
+    if ((size_t)s * g.M * g.N * sizeof(float) > g.splitk_bytes) break;
+    const double cost = (double)cdiv(tiles * s, sms) / s + 0.02 * s;  // small charge for the extra partial traffic
+    if (cost < best_cost * 0.95) { best = s; best_cost = cost; }
+  }
+  return best;
+}
+
 template <int BN, int KIND, typename TOut, bool AMN, bool BMN>
 int32_t launch_cfg(const GemmArgs& g, cudaStream_t stream) {
   using Cfg = TcCfg<BN>;
@@ -296,9 +348,18 @@ int32_t launch_cfg(const GemmArgs& g, cudaStream_t stream) {
     attr_set = true;
   }
   const int tiles = cdiv(g.M, TBM) * cdiv(g.N, BN);
-  const int grid = tiles < sm_count() ? tiles : sm_count();
-  kern<<<grid, TC_THREADS, Cfg::kSmemBytes, stream>>>(tmA, tmB, g.M, g.N, g.K, g.epi, device_status_word());
+  const int splits = pick_splits(g, tiles);
+  const int items = tiles * splits;
+  const int grid = items < sm_count() ? items : sm_count();
+  kern<<<grid, TC_THREADS, Cfg::kSmemBytes, stream>>>(tmA, tmB, g.M, g.N, g.K, g.epi, splits,
+                                                      reinterpret_cast<float*>(g.splitk_scratch), device_status_word());
   B200_LAUNCH_OK("gemm_tc_kernel");
+  if (splits > 1) {
+    const int chunks = g.M * (g.N / 16);
+    splitk_reduce_kernel<KIND, TOut><<<cdiv(chunks, 256), 256, 0, stream>>>(
+        reinterpret_cast<const float*>(g.splitk_scratch), splits, g.M, g.N, g.epi);
+    B200_LAUNCH_OK("splitk_reduce_kernel");
+  }
   return B200_OK;
 }
 
@@ -306,6 +367,11 @@ template <int KIND, typename TOut, bool AMN, bool BMN>
 int32_t launch_bn(const GemmArgs& g, cudaStream_t stream) {
   const int sms = sm_count();
   const long mt = cdiv(g.M, TBM);
+  if (g.splitk_scratch && mt * cdiv(g.N, 128) < 2 * sms) {
+    // few output tiles and scratch for K-splitting: keep the tile wide (more bytes in flight per CTA) and split K
+    if (g.N % 256 == 0 && mt * (g.N / 256) >= sms / 2) return launch_cfg<256, KIND, TOut, AMN, BMN>(g, stream);
+    return launch_cfg<128, KIND, TOut, AMN, BMN>(g, stream);
+  }
   if (mt == 1) {
     // One row of tiles (decode: the batch is the M dimension).  The kernel then
     // only streams the weights, so what matters is how many SMs pull on HBM:

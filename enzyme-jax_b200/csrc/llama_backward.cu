@@ -15,6 +15,7 @@ namespace b200 {
 
 struct BwdWs {
   float* dx; void* dxb; void* dlog; void* dhg; void* dgu; void* d_o; void* dqkv; float* delta; float* dg_part;
+  void* splitk; size_t splitk_bytes;
   int n_parts;
 };
 
@@ -30,6 +31,8 @@ static void carve_backward(const B200Plan& p, Arena& a, int B, int S, BwdWs* w) 
   w->delta = a.take<float>((size_t)B * p.H * S * 4);
   w->n_parts = rmsnorm_bwd_parts((int)T);
   w->dg_part = a.take<float>((size_t)w->n_parts * p.d * 4);
+  w->splitk_bytes = (size_t)64 << 20;  // K-split partials of the weight-gradient GEMMs
+  w->splitk = a.take(w->splitk_bytes);
 }
 
 size_t backward_workspace_bytes(const B200Plan& p, int B, int S) {
@@ -40,9 +43,10 @@ size_t backward_workspace_bytes(const B200Plan& p, int B, int S) {
 }
 
 // Y[M,N] (+)= op(A) op(B)^T into `out` of dtype out_dtype.
-static int32_t gemm(const B200Plan& p, const void* A, int lda, int ta, const void* Bm, int ldb, int tb, int M, int N,
-                    int K, void* out, int ldo, int out_dtype, int accumulate, cudaStream_t stream) {
+static int32_t gemm(const B200Plan& p, const BwdWs& ws, const void* A, int lda, int ta, const void* Bm, int ldb, int tb,
+                    int M, int N, int K, void* out, int ldo, int out_dtype, int accumulate, cudaStream_t stream) {
   GemmArgs g;
+  g.splitk_scratch = ws.splitk; g.splitk_bytes = ws.splitk_bytes;
   g.A = A; g.B = Bm; g.M = M; g.N = N; g.K = K; g.lda = lda; g.ldb = ldb; g.ta = ta; g.tb = tb;
   g.in_dtype = p.dtype; g.out_dtype = out_dtype; g.kind = EPI_STORE;
   g.epi.out = out; g.epi.ldo = ldo; g.epi.accumulate = accumulate;
@@ -75,8 +79,8 @@ int32_t backward_impl(B200Plan* p, const int32_t* tokens, int B, int S, const ui
     B200_TRY(launch_convert(dlogits, B200_F32, b.dlog, dt, (size_t)T * V, stream));
     dlog = b.dlog;
   }
-  B200_TRY(gemm(*p, dlog, V, 1, acts.fin.xf, d, 1, V, d, T, gf(gl.wcls), d, B200_F32, accumulate, stream));
-  B200_TRY(gemm(*p, dlog, V, 0, w + wl.wcls_t, V, 0, T, d, V, b.dxb, d, dt, 0, stream));
+  B200_TRY(gemm(*p, b, dlog, V, 1, acts.fin.xf, d, 1, V, d, T, gf(gl.wcls), d, B200_F32, accumulate, stream));
+  B200_TRY(gemm(*p, b, dlog, V, 0, w + wl.wcls_t, V, 0, T, d, V, b.dxb, d, dt, 0, stream));
   B200_TRY(launch_rmsnorm_bwd(acts.fin.x_last, g_fin, acts.fin.rinv_f, b.dxb, dt, b.dx, 0, b.dg_part, b.n_parts, T, d,
                               stream));
   B200_TRY(launch_colsum_parts(b.dg_part, b.n_parts, d, gf(gl.g_final), accumulate, stream));
@@ -87,18 +91,18 @@ int32_t backward_impl(B200Plan* p, const int32_t* tokens, int B, int S, const ui
     const LayerOffsets& go = gl.layer[l];
     // ---- feed-forward block: x_out = x_mid + hg W2^T
     B200_TRY(launch_convert(b.dx, B200_F32, b.dxb, dt, (size_t)T * d, stream));
-    B200_TRY(gemm(*p, b.dxb, d, 1, a.hg, h, 1, d, h, T, gf(go.w2), h, B200_F32, accumulate, stream));
-    B200_TRY(gemm(*p, b.dxb, d, 0, w + o.w2_t, d, 0, T, h, d, b.dhg, h, dt, 0, stream));
+    B200_TRY(gemm(*p, b, b.dxb, d, 1, a.hg, h, 1, d, h, T, gf(go.w2), h, B200_F32, accumulate, stream));
+    B200_TRY(gemm(*p, b, b.dxb, d, 0, w + o.w2_t, d, 0, T, h, d, b.dhg, h, dt, 0, stream));
     B200_TRY(launch_swiglu_bwd(a.gate, a.up, b.dhg, b.dgu, dt, T, h, stream));
-    B200_TRY(gemm(*p, b.dgu, 2 * h, 1, a.xb2, d, 1, 2 * h, d, T, gf(go.w13), d, B200_F32, accumulate, stream));
-    B200_TRY(gemm(*p, b.dgu, 2 * h, 0, w + o.w13_t, 2 * h, 0, T, d, 2 * h, b.dxb, d, dt, 0, stream));
+    B200_TRY(gemm(*p, b, b.dgu, 2 * h, 1, a.xb2, d, 1, 2 * h, d, T, gf(go.w13), d, B200_F32, accumulate, stream));
+    B200_TRY(gemm(*p, b, b.dgu, 2 * h, 0, w + o.w13_t, 2 * h, 0, T, d, 2 * h, b.dxb, d, dt, 0, stream));
     B200_TRY(launch_rmsnorm_bwd(a.x_mid, g_ffn + (size_t)l * d, a.rinv2, b.dxb, dt, b.dx, 1, b.dg_part, b.n_parts, T, d,
                                 stream));
     B200_TRY(launch_colsum_parts(b.dg_part, b.n_parts, d, gf(gl.g_ffn) + (size_t)l * d, accumulate, stream));
     // ---- attention block: x_mid = x_in + o Wo^T
     B200_TRY(launch_convert(b.dx, B200_F32, b.dxb, dt, (size_t)T * d, stream));
-    B200_TRY(gemm(*p, b.dxb, d, 1, a.o, d, 1, d, d, T, gf(go.wo), d, B200_F32, accumulate, stream));
-    B200_TRY(gemm(*p, b.dxb, d, 0, w + o.wo_t, d, 0, T, d, d, b.d_o, d, dt, 0, stream));
+    B200_TRY(gemm(*p, b, b.dxb, d, 1, a.o, d, 1, d, d, T, gf(go.wo), d, B200_F32, accumulate, stream));
+    B200_TRY(gemm(*p, b, b.dxb, d, 0, w + o.wo_t, d, 0, T, d, d, b.d_o, d, dt, 0, stream));
     {
       AttnBwdArgs ab;
       const uint8_t* base = reinterpret_cast<const uint8_t*>(a.qkv);
@@ -114,8 +118,8 @@ int32_t backward_impl(B200Plan* p, const int32_t* tokens, int B, int S, const ui
       B200_TRY(launch_attn_bwd(ab, p->attn_impl, stream));
     }
     B200_TRY(launch_rope_bwd(b.dqkv, dt, 3 * d, T, 2 * d, p->hs, S, p->rope_cos, p->rope_sin, stream));
-    B200_TRY(gemm(*p, b.dqkv, 3 * d, 1, a.xb, d, 1, 3 * d, d, T, gf(go.wqkv), d, B200_F32, accumulate, stream));
-    B200_TRY(gemm(*p, b.dqkv, 3 * d, 0, w + o.wqkv_t, 3 * d, 0, T, d, 3 * d, b.dxb, d, dt, 0, stream));
+    B200_TRY(gemm(*p, b, b.dqkv, 3 * d, 1, a.xb, d, 1, 3 * d, d, T, gf(go.wqkv), d, B200_F32, accumulate, stream));
+    B200_TRY(gemm(*p, b, b.dqkv, 3 * d, 0, w + o.wqkv_t, 3 * d, 0, T, d, 3 * d, b.dxb, d, dt, 0, stream));
     B200_TRY(launch_rmsnorm_bwd(a.x_in, g_att + (size_t)l * d, a.rinv1, b.dxb, dt, b.dx, 1, b.dg_part, b.n_parts, T, d,
                                 stream));
     B200_TRY(launch_colsum_parts(b.dg_part, b.n_parts, d, gf(gl.g_att) + (size_t)l * d, accumulate, stream));

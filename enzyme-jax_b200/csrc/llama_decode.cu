@@ -37,6 +37,7 @@ __global__ void kv_append_kernel(const T* __restrict__ qkv, T* __restrict__ kpag
 
 struct DecodeWs {
   float* x; void* xb; void* qkv; void* o; void* hg; void* tp_tmp; float* scratch;
+  void* splitk; size_t splitk_bytes;
   int n_splits;
 };
 
@@ -50,25 +51,29 @@ void carve_decode(const B200Plan& p, Arena& a, int B, int ctx, DecodeWs* w) {
   w->tp_tmp = p.tp_size > 1 ? a.take((size_t)B * p.d * es) : nullptr;
   w->n_splits = decode_pick_splits(B, p.H_loc, ctx);
   w->scratch = a.take<float>(decode_scratch_floats(B, p.H_loc, p.hs, w->n_splits) * 4);
+  // K-split partials of the projections: up to 8 splits of the widest one (W1|W3)
+  w->splitk_bytes = (size_t)8 * B * 2 * p.h_loc * 4;
+  w->splitk = a.take(w->splitk_bytes);
 }
 
-int32_t gemm(const B200Plan& p, const void* A, int lda, const void* Bm, int ldb, int M, int N, int K, int kind,
-             int out_dtype, const EpiParams& epi, cudaStream_t stream) {
+int32_t gemm(const B200Plan& p, const DecodeWs& ws, const void* A, int lda, const void* Bm, int ldb, int M, int N, int K,
+             int kind, int out_dtype, const EpiParams& epi, cudaStream_t stream) {
   GemmArgs g;
+  g.splitk_scratch = ws.splitk; g.splitk_bytes = ws.splitk_bytes;
   g.A = A; g.B = Bm; g.M = M; g.N = N; g.K = K; g.lda = lda; g.ldb = ldb;
   g.in_dtype = p.dtype; g.out_dtype = out_dtype; g.kind = kind; g.epi = epi;
   return launch_gemm(g, p.gemm_impl, stream);
 }
 
-int32_t proj_residual(const B200Plan& p, const void* A, int lda, const void* W, int ldw, int M, int K, float* x,
-                      void* tp_tmp, cudaStream_t stream) {
+int32_t proj_residual(const B200Plan& p, const DecodeWs& ws, const void* A, int lda, const void* W, int ldw, int M, int K,
+                      float* x, void* tp_tmp, cudaStream_t stream) {
   EpiParams e;
   if (p.tp_size == 1) {
     e.out = x; e.ldo = p.d; e.resid_in = x;
-    return gemm(p, A, lda, W, ldw, M, p.d, K, EPI_RESID, B200_F32, e, stream);
+    return gemm(p, ws, A, lda, W, ldw, M, p.d, K, EPI_RESID, B200_F32, e, stream);
   }
   e.out = tp_tmp; e.ldo = p.d;
-  B200_TRY(gemm(p, A, lda, W, ldw, M, p.d, K, EPI_STORE, p.dtype, e, stream));
+  B200_TRY(gemm(p, ws, A, lda, W, ldw, M, p.d, K, EPI_STORE, p.dtype, e, stream));
   B200_TRY(comm_allreduce(p.comm, tp_tmp, (size_t)M * p.d, p.dtype, stream));
   return launch_add_to_f32(x, tp_tmp, p.dtype, (size_t)M * p.d, stream);
 }
@@ -149,7 +154,7 @@ int32_t b200_decode_step(B200Plan* p, const int32_t* tokens, const float* x_in, 
       e.out = w.qkv; e.ldo = 3 * dl;
       e.rope_cos = p->rope_cos; e.rope_sin = p->rope_sin;
       e.seq_len = 1; e.pos_base = pos; e.head_size = p->hs; e.rope_cols = 2 * dl;
-      B200_TRY(gemm(*p, w.xb, d, wt + o.wqkv, d, B, 3 * dl, d, EPI_ROPE, p->dtype, e, stream));
+      B200_TRY(gemm(*p, w, w.xb, d, wt + o.wqkv, d, B, 3 * dl, d, EPI_ROPE, p->dtype, e, stream));
     }
     if (p->dtype == B200_BF16)
       kv_append_kernel<bf16><<<B, 128, 0, stream>>>((const bf16*)w.qkv, (bf16*)kv, (bf16*)(kv + layer_bytes / 2),
@@ -166,21 +171,21 @@ int32_t b200_decode_step(B200Plan* p, const int32_t* tokens, const float* x_in, 
       a.d_local = dl; a.dtype = p->dtype; a.n_splits = w.n_splits;
       B200_TRY(launch_attn_decode(a, stream));
     }
-    B200_TRY(proj_residual(*p, w.o, dl, wt + o.wo, dl, B, dl, w.x, w.tp_tmp, stream));
+    B200_TRY(proj_residual(*p, w, w.o, dl, wt + o.wo, dl, B, dl, w.x, w.tp_tmp, stream));
     B200_TRY(launch_rmsnorm(w.x, g_ffn + (size_t)l * d, w.xb, nullptr, B, d, eps, p->dtype, stream));
     {
       EpiParams e;
       e.out = w.hg; e.ldo = hl;
-      B200_TRY(gemm(*p, w.xb, d, wt + o.w13, d, B, 2 * hl, d, EPI_SWIGLU, p->dtype, e, stream));
+      B200_TRY(gemm(*p, w, w.xb, d, wt + o.w13, d, B, 2 * hl, d, EPI_SWIGLU, p->dtype, e, stream));
     }
-    B200_TRY(proj_residual(*p, w.hg, hl, wt + o.w2, hl, B, hl, w.x, w.tp_tmp, stream));
+    B200_TRY(proj_residual(*p, w, w.hg, hl, wt + o.w2, hl, B, hl, w.x, w.tp_tmp, stream));
   }
   if (hidden_out) B200_TRY(launch_rmsnorm(w.x, g_fin, hidden_out, nullptr, B, d, eps, B200_F32, stream));
   if (logits) {
     B200_TRY(launch_rmsnorm(w.x, g_fin, w.xb, nullptr, B, d, eps, p->dtype, stream));
     EpiParams e;
     e.out = logits; e.ldo = p->V_loc;
-    B200_TRY(gemm(*p, w.xb, d, wt + wl.wcls, d, B, p->V_loc, d, EPI_STORE, B200_F32, e, stream));
+    B200_TRY(gemm(*p, w, w.xb, d, wt + wl.wcls, d, B, p->V_loc, d, EPI_STORE, B200_F32, e, stream));
   }
   return B200_OK;
 }
