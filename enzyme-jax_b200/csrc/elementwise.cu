@@ -172,13 +172,101 @@ __global__ void __launch_bounds__(RB_THREADS)
   }
 }
 
-__global__ void colsum_parts_kernel(const float* __restrict__ part, int n_parts, int dim, float* __restrict__ out,
-                                    int accumulate) {
-  const int c = blockIdx.x * blockDim.x + threadIdx.x;
-  if (c >= dim) return;
+// Warp-per-row variant for dim <= 1536: no block-wide barrier per row.  Lane l
+// owns columns {l*8 + 256*i}; the 8 warps of a CTA walk the CTA's rows round
+// robin and their gain partials are summed through shared memory at the end in
+// warp order (fixed order, no atomics).
+constexpr int RW_WARPS = 8;
+constexpr int RW_MAXCH = 6;  // 8-wide chunks per lane: dim <= 32*8*6 = 1536
+
+template <typename TDy, int NCH>
+__global__ void __launch_bounds__(RW_WARPS * 32)
+    rmsnorm_bwd_warp_kernel(const float* __restrict__ x, const float* __restrict__ gain, const float* __restrict__ rinv,
+                            const TDy* __restrict__ dy, float* __restrict__ dx, int accumulate_dx,
+                            float* __restrict__ dg_part, int rows, int dim, int rows_per_part) {
+  extern __shared__ float s_dg[];  // [RW_WARPS][dim]
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  float dg[NCH][8];
+  float g[NCH][8];
+#pragma unroll
+  for (int ch = 0; ch < NCH; ++ch) {
+    const int c = (ch * 32 + lane) * 8;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) { dg[ch][i] = 0.f; g[ch][i] = 0.f; }
+    if (c < dim) load8(gain + c, g[ch]);
+  }
+  const int r_begin = blockIdx.x * rows_per_part;
+  const int r_end = min(rows, r_begin + rows_per_part);
+  for (int row = r_begin + warp; row < r_end; row += RW_WARPS) {
+    const float r = rinv[row];
+    const float* xr = x + (size_t)row * dim;
+    const TDy* dyr = dy + (size_t)row * dim;
+    float xv[NCH][8], dv[NCH][8];
+    float dot = 0.f;
+#pragma unroll
+    for (int ch = 0; ch < NCH; ++ch) {
+      const int c = (ch * 32 + lane) * 8;
+      if (c < dim) {
+        load8(xr + c, xv[ch]);
+        load8(dyr + c, dv[ch]);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          dot = fmaf(g[ch][i] * dv[ch][i], xv[ch][i], dot);
+          dg[ch][i] = fmaf(dv[ch][i] * xv[ch][i], r, dg[ch][i]);
+        }
+      }
+    }
+    dot = warp_sum(dot);
+    const float coef = r * r * r / (float)dim * dot;
+    float* dxr = dx + (size_t)row * dim;
+#pragma unroll
+    for (int ch = 0; ch < NCH; ++ch) {
+      const int c = (ch * 32 + lane) * 8;
+      if (c < dim) {
+        float out[8];
+        if (accumulate_dx) load8(dxr + c, out);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const float val = r * g[ch][i] * dv[ch][i] - xv[ch][i] * coef;
+          out[i] = accumulate_dx ? out[i] + val : val;
+        }
+        store8(dxr + c, out);
+      }
+    }
+  }
+#pragma unroll
+  for (int ch = 0; ch < NCH; ++ch) {
+    const int c = (ch * 32 + lane) * 8;
+    if (c < dim) store8(s_dg + (size_t)warp * dim + c, dg[ch]);
+  }
+  __syncthreads();
+  float* part = dg_part + (size_t)blockIdx.x * dim;
+  for (int c = threadIdx.x; c < dim; c += blockDim.x) {
+    float sum = 0.f;
+#pragma unroll
+    for (int w = 0; w < RW_WARPS; ++w) sum += s_dg[(size_t)w * dim + c];
+    part[c] = sum;
+  }
+}
+
+// out[c] (+)= sum_p part[p, c].  A CTA of 32 x 8 threads owns 32 columns; thread
+// (c, g) adds parts g, g+8, ... and the 8 group sums are added in group order.
+__global__ void __launch_bounds__(256) colsum_parts_kernel(const float* __restrict__ part, int n_parts, int dim,
+                                                           float* __restrict__ out, int accumulate) {
+  __shared__ float red[8][33];
+  const int cx = threadIdx.x & 31, g = threadIdx.x >> 5;
+  const int c = blockIdx.x * 32 + cx;
   float s = 0.f;
-  for (int p = 0; p < n_parts; ++p) s += part[(size_t)p * dim + c];
-  out[c] = accumulate ? out[c] + s : s;
+  if (c < dim)
+    for (int p = g; p < n_parts; p += 8) s += part[(size_t)p * dim + c];
+  red[g][cx] = s;
+  __syncthreads();
+  if (g == 0 && c < dim) {
+    float t = 0.f;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) t += red[k][cx];
+    out[c] = accumulate ? out[c] + t : t;
+  }
 }
 
 template <typename T>
@@ -228,31 +316,41 @@ __global__ void swiglu_bwd_kernel(const T* __restrict__ gate, const T* __restric
   }
 }
 
-// Each CTA owns the table rows [v0, v1) and walks the whole token list in
-// order, so that every table row receives its contributions in sequence order.
-constexpr int EB_CHUNK = 1024;
+// Each CTA owns the table rows [v0, v1).  It scans the token list 256 tokens at
+// a time (one token per thread, matches recorded as warp ballots) and then
+// applies the matching rows in token order, so that every table row receives its
+// contributions in sequence order: deterministic, no atomics.
 __global__ void __launch_bounds__(256) embed_bwd_kernel(const int32_t* __restrict__ tokens,
                                                         const float* __restrict__ dx, float* __restrict__ dtable,
                                                         int n_tokens, int dim, int vocab, int rows_per_cta) {
-  __shared__ int32_t toks[EB_CHUNK];
+  __shared__ uint32_t hit[8];
+  __shared__ int32_t toks[256];
   const int v0 = blockIdx.x * rows_per_cta;
   const int v1 = min(vocab, v0 + rows_per_cta);
-  for (int base = 0; base < n_tokens; base += EB_CHUNK) {
-    const int n = min(EB_CHUNK, n_tokens - base);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int base = 0; base < n_tokens; base += 256) {
+    const int i = base + threadIdx.x;
+    const int tok = i < n_tokens ? tokens[i] : -1;
+    const uint32_t b = __ballot_sync(0xffffffffu, tok >= v0 && tok < v1);
+    __syncthreads();  // the previous chunk's lists are no longer read
+    toks[threadIdx.x] = tok;
+    if (lane == 0) hit[warp] = b;
     __syncthreads();
-    for (int i = threadIdx.x; i < n; i += blockDim.x) toks[i] = tokens[base + i];
-    __syncthreads();
-    for (int i = 0; i < n; ++i) {
-      const int tok = toks[i];
-      if (tok >= v0 && tok < v1) {
-        const float* s = dx + (size_t)(base + i) * dim;
-        float* d = dtable + (size_t)tok * dim;
+    for (int w = 0; w < 8; ++w) {
+      uint32_t bits = hit[w];
+      while (bits) {
+        const int k = __ffs(bits) - 1;
+        bits &= bits - 1;
+        const int t = w * 32 + k;
+        const float* src = dx + (size_t)(base + t) * dim;
+        float* dst = dtable + (size_t)toks[t] * dim;
         for (int c = threadIdx.x * 4; c < dim; c += blockDim.x * 4) {
-          float4 a = *reinterpret_cast<const float4*>(s + c);
-          float4 b = *reinterpret_cast<float4*>(d + c);
-          b.x += a.x; b.y += a.y; b.z += a.z; b.w += a.w;
-          *reinterpret_cast<float4*>(d + c) = b;
+          float4 a = *reinterpret_cast<const float4*>(src + c);
+          float4 d = *reinterpret_cast<float4*>(dst + c);
+          d.x += a.x; d.y += a.y; d.z += a.z; d.w += a.w;
+          *reinterpret_cast<float4*>(dst + c) = d;
         }
+        __syncthreads();  // two hits of one chunk may target the same table row
       }
     }
   }
@@ -368,6 +466,25 @@ int32_t launch_rmsnorm_bwd(const float* x, const float* gain, const float* rinv,
                 RB_THREADS * 8 * RB_MAXCH);
   const int rpp = cdiv(rows, n_parts);
   if (cdiv(rows, rpp) > n_parts) return fail(B200_ERR_INVALID_ARG, "rmsnorm backward: bad partition");
+  if (dim <= 1536) {  // 8 warps x dim floats of shared memory stay within the default 48 KB
+    const int nch = cdiv(dim, 256);
+    const size_t smem = (size_t)RW_WARPS * dim * sizeof(float);
+#define B200_RW_CASE(N)                                                                                              \
+  case N:                                                                                                            \
+    if (dy_dtype == B200_F32)                                                                                        \
+      rmsnorm_bwd_warp_kernel<float, N><<<n_parts, RW_WARPS * 32, smem, stream>>>(                                   \
+          x, gain, rinv, (const float*)dy, dx, accumulate_dx, dg_part, rows, dim, rpp);                              \
+    else                                                                                                             \
+      rmsnorm_bwd_warp_kernel<bf16, N><<<n_parts, RW_WARPS * 32, smem, stream>>>(                                    \
+          x, gain, rinv, (const bf16*)dy, dx, accumulate_dx, dg_part, rows, dim, rpp);                               \
+    break;
+    switch (nch) {
+      B200_RW_CASE(1) B200_RW_CASE(2) B200_RW_CASE(3) B200_RW_CASE(4) B200_RW_CASE(5) B200_RW_CASE(6)
+    }
+#undef B200_RW_CASE
+    B200_LAUNCH_OK("rmsnorm_bwd_warp_kernel");
+    return B200_OK;
+  }
   // Parts beyond the last row still write zeros so that the column sum may read all of them.
   if (dy_dtype == B200_F32)
     rmsnorm_bwd_kernel<float><<<n_parts, RB_THREADS, 0, stream>>>(x, gain, rinv, (const float*)dy, dx, accumulate_dx,
@@ -381,7 +498,7 @@ int32_t launch_rmsnorm_bwd(const float* x, const float* gain, const float* rinv,
 
 int32_t launch_colsum_parts(const float* part, int n_parts, int dim, float* out, int accumulate,
                             cudaStream_t stream) {
-  colsum_parts_kernel<<<cdiv(dim, 128), 128, 0, stream>>>(part, n_parts, dim, out, accumulate);
+  colsum_parts_kernel<<<cdiv(dim, 32), 256, 0, stream>>>(part, n_parts, dim, out, accumulate);
   B200_LAUNCH_OK("colsum_parts_kernel");
   return B200_OK;
 }
