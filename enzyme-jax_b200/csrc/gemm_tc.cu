@@ -18,6 +18,7 @@
 
 #include "gemm_epilogue.cuh"
 #include "ptx_sm100.cuh"
+#include "plan.cuh"
 #include "tensor_map.cuh"
 
 namespace b200 {
@@ -429,7 +430,11 @@ int32_t launch_gemm_tc(const GemmArgs& g, cudaStream_t stream) {
 int32_t launch_gemm(const GemmArgs& g, int impl, cudaStream_t stream) {
   const bool tc = impl == 1 || (impl != 2 && gemm_tc_supports(g));
   ProfScope prof(tc ? PROF_GEMM_TC : PROF_GEMM_SIMT, 2.0 * g.M * (double)g.N * g.K, stream);
-  return tc ? launch_gemm_tc(g, stream) : launch_gemm_simt(g, stream);
+  if (!tc) return launch_gemm_simt(g, stream);
+  // B200_GEMM_PAIR=0 keeps every problem on the single-CTA kernel
+  static const int use_pair = env_int("B200_GEMM_PAIR", 1);
+  if (use_pair && gemm_tc2_supports(g)) return launch_gemm_tc2(g, stream);
+  return launch_gemm_tc(g, stream);
 }
 
 }  // namespace b200

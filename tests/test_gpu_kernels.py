@@ -21,7 +21,9 @@ def _ints(shape, seed, lo=-2, hi=3, dtype=torch.bfloat16):
 
 @pytest.mark.parametrize("impl", [1, 2])
 @pytest.mark.parametrize("M,N,K", [(128, 128, 64), (128, 256, 128), (256, 512, 768), (384, 768, 2048),
-                                   (100, 96, 72), (8192, 2304, 768), (64, 4096, 1024), (1, 32, 8)])
+                                   (100, 96, 72), (8192, 2304, 768), (64, 4096, 1024), (1, 32, 8),
+                                   # large enough for the CTA-pair kernel (256-row tiles), with M and K tails
+                                   (4096, 768, 2048), (8192, 1024, 256), (5000, 1536, 704), (8192, 32000, 64)])
 def test_gemm_bf16_exact_on_small_integers(impl, M, N, K):
     # integer operands in [-2,2]: every product and partial sum is exact in fp32
     a, b = _ints((M, K), 1), _ints((N, K), 2)
