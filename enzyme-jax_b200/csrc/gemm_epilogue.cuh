@@ -137,6 +137,19 @@ __device__ __forceinline__ void epi_apply16(const EpiParams& p, const EpiRow& ro
   }
 }
 
+// Tile order of the persistent tensor-core kernels: bands of GM row-tiles are
+// walked column-tile by column-tile, so that the tiles in flight at any time
+// share a few row-tiles of A and a few column-tiles of B (both stay in L2 even
+// when a whole operand does not fit).
+__device__ __forceinline__ void tile_coords(int tile, int m_tiles, int n_tiles, int gm, int& mt, int& nt) {
+  const int per_band = gm * n_tiles;
+  const int band = tile / per_band;
+  const int r = tile - band * per_band;
+  const int rows = min(gm, m_tiles - band * gm);  // the last band may be short
+  nt = r / rows;
+  mt = band * gm + r % rows;
+}
+
 // Host-side launchers (definitions in gemm_simt.cu / gemm_tc.cu).
 struct GemmArgs {
   const void* A = nullptr;  // [M,K] (or [K,M] when ta)

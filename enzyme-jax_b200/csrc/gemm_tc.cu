@@ -102,7 +102,9 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
       bool ok = true;
       for (int item = blockIdx.x; item < num_items && ok; item += gridDim.x) {
         const int tile = item % num_tiles, split = item / num_tiles;
-        const int m0 = (tile % m_tiles) * TBM, n0 = (tile / m_tiles) * BN;
+        int mt, nt;
+        tile_coords(tile, m_tiles, n_tiles, 16, mt, nt);
+        const int m0 = mt * TBM, n0 = nt * BN;
         const int kb0 = (int)((long)split * num_kb / splits), kb1 = (int)((long)(split + 1) * num_kb / splits);
         for (int kb = kb0; kb < kb1; ++kb) {
           ok = ptx::mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag, status, ST_PRODUCER_TIMEOUT);
@@ -177,7 +179,9 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
     bool ok = true;
     for (int item = blockIdx.x; item < num_items && ok; item += gridDim.x) {
       const int tile = item % num_tiles, split = item / num_tiles;
-      const int m0 = (tile % m_tiles) * TBM, n0 = (tile / m_tiles) * BN;
+      int mt, nt;
+        tile_coords(tile, m_tiles, n_tiles, 16, mt, nt);
+        const int m0 = mt * TBM, n0 = nt * BN;
       const int m = m0 + q * 32 + lane;
       const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN);
       const bool row_ok = m < M;

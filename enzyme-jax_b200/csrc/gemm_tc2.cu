@@ -139,8 +139,10 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(P_THREADS, 1)
       uint32_t phase = 0;
       bool ok = true;
       for (int tile = pair; tile < num_tiles && ok; tile += n_pairs) {
-        const int m0 = (tile % m_tiles) * (2 * PM) + (int)rank * PM;
-        const int n0 = (tile / m_tiles) * BN + (int)rank * (BN / 2);
+        int mt, nt;
+        tile_coords(tile, m_tiles, n_tiles, 8, mt, nt);
+        const int m0 = mt * (2 * PM) + (int)rank * PM;
+        const int n0 = nt * BN + (int)rank * (BN / 2);
         for (int kb = 0; kb < num_kb; ++kb) {
           ok = ptx::mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag, status, ST_PAIR_PRODUCER);
           if (!ok) break;
@@ -194,8 +196,10 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(P_THREADS, 1)
     uint32_t acc_phase = 0;
     bool ok = true;
     for (int tile = pair; tile < num_tiles && ok; tile += n_pairs) {
-      const int m0 = (tile % m_tiles) * (2 * PM) + (int)rank * PM;
-      const int n0 = (tile / m_tiles) * BN;
+      int mt, nt;
+      tile_coords(tile, m_tiles, n_tiles, 8, mt, nt);
+      const int m0 = mt * (2 * PM) + (int)rank * PM;
+      const int n0 = nt * BN;
       const int m = m0 + q * 32 + lane;
       const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN);
       const bool row_ok = m < M;
@@ -337,7 +341,12 @@ int32_t launch_pair_cfg(const GemmArgs& g, cudaStream_t stream) {
 
 template <int KIND, typename TOut>
 int32_t launch_pair_bn(const GemmArgs& g, cudaStream_t stream) {
-  if (g.N % 256 == 0) return launch_pair_cfg<256, KIND, TOut>(g, stream);
+  // rounds of the persistent grid times the tile width: prefer the wide tile unless it wastes a round
+  const int pairs = sm_count() / 2;
+  const long mt = cdiv(g.M, 2 * PM);
+  const long cost256 = g.N % 256 == 0 ? (long)cdiv((int)(mt * (g.N / 256)), pairs) * 256 : -1;
+  const long cost128 = (long)cdiv((int)(mt * cdiv(g.N, 128)), pairs) * 128;
+  if (cost256 >= 0 && cost256 <= cost128) return launch_pair_cfg<256, KIND, TOut>(g, stream);
   return launch_pair_cfg<128, KIND, TOut>(g, stream);
 }
 
