@@ -11,7 +11,7 @@ namespace b200 {
 
 namespace {
 
-constexpr int BM = 128, BN = 64, BK = 16, NT = 128;
+constexpr int BN = 64, BK = 16, NT = 128;  // rows per CTA: 32 * RPT (RPT rows per thread)
 
 template <typename TIn, bool VEC>
 __device__ __forceinline__ void fetch8(const TIn* base, int ld, int r, int c, int R, int C, float (&v)[8]) {
@@ -24,18 +24,19 @@ __device__ __forceinline__ void fetch8(const TIn* base, int ld, int r, int c, in
   }
 }
 
-template <typename TIn, typename TOut, int KIND, bool TA, bool TB, bool VEC>
+template <typename TIn, typename TOut, int KIND, bool TA, bool TB, bool VEC, int RPT>
 __global__ void __launch_bounds__(NT) gemm_simt_kernel(const TIn* __restrict__ A, const TIn* __restrict__ B, int M,
                                                        int N, int K, int lda, int ldb, EpiParams ep) {
+  constexpr int BM = 32 * RPT;
   __shared__ __align__(16) float As[BK][BM + 4];
   __shared__ __align__(16) float Bs[BK][BN + 4];
   const int tid = threadIdx.x;
   const int ty = tid >> 2, tx = tid & 3;
   const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
 
-  float acc[4][16];
+  float acc[RPT][16];
 #pragma unroll
-  for (int r = 0; r < 4; ++r)
+  for (int r = 0; r < RPT; ++r)
 #pragma unroll
     for (int c = 0; c < 16; ++c) acc[r][c] = 0.f;
 
@@ -43,16 +44,16 @@ __global__ void __launch_bounds__(NT) gemm_simt_kernel(const TIn* __restrict__ A
     float v[8];
     if constexpr (!TA) {
 #pragma unroll
-      for (int i = 0; i < 2; ++i) {
-        const int row = i * 64 + (tid >> 1), k8 = (tid & 1) * 8;
+      for (int idx = tid; idx < 2 * BM; idx += NT) {
+        const int row = idx >> 1, k8 = (idx & 1) * 8;
         fetch8<TIn, VEC>(A, lda, m0 + row, k0 + k8, M, K, v);
 #pragma unroll
         for (int j = 0; j < 8; ++j) As[k8 + j][row] = v[j];
       }
     } else {
 #pragma unroll
-      for (int i = 0; i < 2; ++i) {
-        const int k = i * 8 + (tid >> 4), m8 = (tid & 15) * 8;
+      for (int idx = tid; idx < 2 * BM; idx += NT) {
+        const int k = idx / (BM / 8), m8 = (idx % (BM / 8)) * 8;
         fetch8<TIn, VEC>(A, lda, k0 + k, m0 + m8, K, M, v);
 #pragma unroll
         for (int j = 0; j < 8; ++j) As[k][m8 + j] = v[j];
@@ -72,8 +73,9 @@ __global__ void __launch_bounds__(NT) gemm_simt_kernel(const TIn* __restrict__ A
     __syncthreads();
 #pragma unroll
     for (int k = 0; k < BK; ++k) {
-      const float4 a4 = *reinterpret_cast<const float4*>(&As[k][ty * 4]);
-      const float a[4] = {a4.x, a4.y, a4.z, a4.w};
+      float a[RPT];
+#pragma unroll
+      for (int r = 0; r < RPT; ++r) a[r] = As[k][ty * RPT + r];
       float b[16];
 #pragma unroll
       for (int q = 0; q < 4; ++q) {
@@ -81,7 +83,7 @@ __global__ void __launch_bounds__(NT) gemm_simt_kernel(const TIn* __restrict__ A
         b[q * 4 + 0] = b4.x; b[q * 4 + 1] = b4.y; b[q * 4 + 2] = b4.z; b[q * 4 + 3] = b4.w;
       }
 #pragma unroll
-      for (int r = 0; r < 4; ++r)
+      for (int r = 0; r < RPT; ++r)
 #pragma unroll
         for (int c = 0; c < 16; ++c) acc[r][c] = fmaf(a[r], b[c], acc[r][c]);
     }
@@ -91,8 +93,8 @@ __global__ void __launch_bounds__(NT) gemm_simt_kernel(const TIn* __restrict__ A
   const int n = n0 + tx * 16;
   if (n < N) {
 #pragma unroll
-    for (int r = 0; r < 4; ++r) {
-      const int m = m0 + ty * 4 + r;
+    for (int r = 0; r < RPT; ++r) {
+      const int m = m0 + ty * RPT + r;
       if (m < M) {
         const EpiRow row = epi_row_begin<KIND>(ep, m);
         epi_apply16<KIND, TOut>(ep, row, m, n, acc[r]);
@@ -103,14 +105,19 @@ __global__ void __launch_bounds__(NT) gemm_simt_kernel(const TIn* __restrict__ A
 
 template <typename TIn, typename TOut, int KIND, bool TA, bool TB>
 int32_t launch_t(const GemmArgs& g, cudaStream_t stream) {
-  dim3 grid(cdiv(g.N, BN), cdiv(g.M, BM));
   const bool vec = aligned16(g.A) && aligned16(g.B) && (g.lda % 8 == 0) && (g.ldb % 8 == 0);
-  if (vec)
-    gemm_simt_kernel<TIn, TOut, KIND, TA, TB, true><<<grid, NT, 0, stream>>>(
-        (const TIn*)g.A, (const TIn*)g.B, g.M, g.N, g.K, g.lda, g.ldb, g.epi);
-  else
-    gemm_simt_kernel<TIn, TOut, KIND, TA, TB, false><<<grid, NT, 0, stream>>>(
-        (const TIn*)g.A, (const TIn*)g.B, g.M, g.N, g.K, g.lda, g.ldb, g.epi);
+  // 128-row tiles when they fill the machine, 32-row tiles (4x the CTAs) for small problems
+  const bool small = (long)cdiv(g.M, 128) * cdiv(g.N, BN) < 2L * sm_count();
+  const int bm = small ? 32 : 128;
+  dim3 grid(cdiv(g.N, BN), cdiv(g.M, bm));
+#define B200_SIMT_LAUNCH(V, R)                                                           \
+  gemm_simt_kernel<TIn, TOut, KIND, TA, TB, V, R><<<grid, NT, 0, stream>>>(              \
+      (const TIn*)g.A, (const TIn*)g.B, g.M, g.N, g.K, g.lda, g.ldb, g.epi)
+  if (vec && small) B200_SIMT_LAUNCH(true, 1);
+  else if (vec) B200_SIMT_LAUNCH(true, 4);
+  else if (small) B200_SIMT_LAUNCH(false, 1);
+  else B200_SIMT_LAUNCH(false, 4);
+#undef B200_SIMT_LAUNCH
   B200_LAUNCH_OK("gemm_simt_kernel");
   return B200_OK;
 }
