@@ -311,7 +311,7 @@ size_t decode_scratch_floats(int batch, int n_heads, int head_size, int n_splits
 }
 
 int decode_pick_splits(int batch, int n_heads, int ctx) {
-  const int want = 2 * sm_count();
+  const int want = 8 * sm_count();  // the bf16 kernel wants several 8-warp CTAs per SM to cover HBM latency
   int s = cdiv(want, batch * n_heads);
   const int max_s = ctx / 128 > 0 ? ctx / 128 : 1;
   if (s > max_s) s = max_s;

@@ -164,6 +164,8 @@ struct GemmArgs {
   // optional scratch for K-split partial sums (fp32); null disables splitting
   void* splitk_scratch = nullptr;
   size_t splitk_bytes = 0;
+  // upper bound on the persistent grid (0 = every SM); lets a collective on another stream keep some SMs
+  int max_ctas = 0;
 };
 // Scratch that lets the tensor-core kernel split K whenever it wants to for an M x N output.
 inline size_t gemm_splitk_scratch_bytes(int M, int N) { return (size_t)32 * M * N * sizeof(float); }

@@ -355,7 +355,9 @@ int32_t launch_cfg(const GemmArgs& g, cudaStream_t stream) {
   const int tiles = cdiv(g.M, TBM) * cdiv(g.N, BN);
   const int splits = pick_splits(g, tiles);
   const int items = tiles * splits;
-  const int grid = items < sm_count() ? items : sm_count();
+  int limit = sm_count();
+  if (g.max_ctas > 0 && g.max_ctas < limit) limit = g.max_ctas;
+  const int grid = items < limit ? items : limit;
   kern<<<grid, TC_THREADS, Cfg::kSmemBytes, stream>>>(tmA, tmB, g.M, g.N, g.K, g.epi, splits,
                                                       reinterpret_cast<float*>(g.splitk_scratch), device_status_word());
   B200_LAUNCH_OK("gemm_tc_kernel");

@@ -333,6 +333,7 @@ int32_t launch_pair_cfg(const GemmArgs& g, cudaStream_t stream) {
   }
   const int tiles = cdiv(g.M, 2 * PM) * cdiv(g.N, BN);
   int pairs = max_pairs;
+  if (g.max_ctas > 0 && g.max_ctas / 2 < pairs) pairs = g.max_ctas / 2;
   if (pairs > tiles) pairs = tiles;
   kern<<<2 * pairs, P_THREADS, Cfg::kSmemBytes, stream>>>(tmA, tmB, g.M, g.N, g.K, g.epi, device_status_word());
   B200_LAUNCH_OK("gemm_tc2_kernel");

@@ -76,6 +76,12 @@ struct B200Plan {
   int dtype = B200_BF16;
   int device = 0;
   int gemm_impl = 0, attn_impl = 0;
+  // tensor parallelism: the all-reduces run on a stream of their own, chunk by chunk, while the
+  // projection of the next chunk computes; `reserve_sms` SMs are left to the collective's kernels
+  cudaStream_t comm_stream = nullptr;
+  cudaEvent_t ev_fork[8] = {}, ev_join[8] = {};
+  int reserve_sms = 0;
+  int tp_chunks = 1;
   float* rope_cos = nullptr;  // [seq_len, hs/2], owned by the plan
   float* rope_sin = nullptr;
   b200::PackedLayout wl;   // weights

@@ -47,6 +47,21 @@ def main():
             assert e < tol, ("tp decode", dtype, pos, e)
         assert B.device_status() == 0
         plan.close()
+    # long enough for the chunked projection + overlapped all-reduce path (4 chunks of 512 tokens)
+    cfg_long = dict(cfg, seq_len=1024)
+    w = {k: v.bfloat16() for k, v in O.make_weights(cfg_long, 8, torch.float32, std=0.05).items()}
+    tokens = O.make_tokens(cfg_long, 2, 1024, 9)
+    ref = O.forward_sequence(tokens, cfg_long, {k: v.float() for k, v in w.items()})
+    plan = B.Plan(cfg_long, torch.bfloat16, tp_rank=rank, tp_size=world, comm=comm)
+    plan.pack_weights({k: v.cuda().contiguous() for k, v in w.items()})
+    for _ in range(3):  # repeated calls reuse the fork/join events
+        got = plan.forward(tokens.int().cuda())
+    torch.cuda.synchronize()
+    vl = cfg_long["vocab_size"] // world
+    err = float((got.cpu() - ref[..., rank * vl:(rank + 1) * vl]).abs().max() / ref.abs().max())
+    assert err < 2e-2, ("tp forward, chunked", err)
+    assert B.device_status() == 0
+    plan.close()
     # data parallel: each rank differentiates its own sequences, gradients are summed over the ranks
     dtype = torch.float32
     w = O.make_weights(cfg, 5, torch.float32, std=0.05, gains_one=False)
