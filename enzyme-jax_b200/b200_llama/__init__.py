@@ -33,7 +33,7 @@ EXPORTS = (
     "b200_gemm", "b200_rmsnorm", "b200_attention", "b200_comm_unique_id", "b200_comm_init_rank",
     "b200_comm_destroy", "b200_launch_count", "b200_profile_enable", "b200_profile_read",
     "b200_attention_decode_scratch_bytes", "b200_attention_decode", "b200_attention_decode_static",
-    "b200_attention_backward",
+    "b200_attention_backward", "b200_comm_peer_memory",
 )
 
 
@@ -96,6 +96,7 @@ def lib() -> ctypes.CDLL:
         l.b200_comm_unique_id.argtypes = [c_void_p]
         l.b200_comm_init_rank.argtypes = [c_void_p, c_int32, c_int32, POINTER(c_void_p)]
         l.b200_comm_destroy.argtypes = [c_void_p]
+        l.b200_comm_peer_memory.argtypes = [c_void_p, POINTER(c_int32)]
         _lib = l
     return _lib
 
@@ -132,7 +133,7 @@ def launch_count() -> int:
     return int(lib().b200_launch_count())
 
 
-PROFILE_CLASSES = ("gemm_tcgen05", "gemm_ffma", "attention_fwd", "attention_bwd", "attention_decode")
+PROFILE_CLASSES = ("gemm_tcgen05", "gemm_ffma", "attention_fwd", "attention_bwd", "attention_decode", "allreduce")
 
 
 def profile_enable(on: bool) -> None:
@@ -254,6 +255,12 @@ class Comm:
         handle = c_void_p()
         check(lib().b200_comm_init_rank(ident, rank, world, byref(handle)))
         self.handle, self.rank, self.world = handle, rank, world
+
+    def peer_memory(self) -> bool:
+        """True when tensor-parallel partial sums travel through peer-mapped memory instead of NCCL."""
+        on = c_int32(0)
+        check(lib().b200_comm_peer_memory(self.handle, byref(on)))
+        return bool(on.value)
 
     def allreduce_f32(self, t: torch.Tensor) -> None:
         check(lib().b200_allreduce_f32(self.handle, t.data_ptr(), t.numel(), _stream()))

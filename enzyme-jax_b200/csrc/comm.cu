@@ -1,7 +1,18 @@
-// NCCL glue.  The library does not link NCCL: the symbols are resolved at first
-// use from the libnccl already loaded into the process (the one PyTorch ships)
-// or from the system library, so single-GPU users need no NCCL at all.
+// Communication between the ranks of one node.
+//
+// (1) NCCL glue.  The library does not link NCCL: the symbols are resolved at
+//     first use from the libnccl already loaded into the process (the one
+//     PyTorch ships) or from the system library, so single-GPU users need no
+//     NCCL at all.
+// (2) A peer-memory all-reduce fused with the residual add for the tensor
+//     parallel projections: every rank keeps its partial product in a buffer the
+//     other ranks map through CUDA IPC; one kernel reduces this rank's slice by
+//     plain loads over NVLink and stores the sum into every rank's buffer, a
+//     second kernel adds the complete sum to the residual stream.  No NVLink
+//     multicast object, no TMA: plain ld/st with system-scope flags.  Every wait
+//     on a peer is bounded.
 #include <dlfcn.h>
+#include <string.h>
 
 #include <mutex>
 
@@ -17,6 +28,7 @@ typedef int (*GetUniqueIdFn)(NcclUniqueId*);
 typedef int (*CommInitRankFn)(NcclComm*, int, NcclUniqueId, int);
 typedef int (*CommDestroyFn)(NcclComm);
 typedef int (*AllReduceFn)(const void*, void*, size_t, int, int, NcclComm, cudaStream_t);
+typedef int (*AllGatherFn)(const void*, void*, size_t, int, NcclComm, cudaStream_t);
 typedef const char* (*GetErrorStringFn)(int);
 
 struct NcclApi {
@@ -24,12 +36,13 @@ struct NcclApi {
   CommInitRankFn comm_init_rank = nullptr;
   CommDestroyFn comm_destroy = nullptr;
   AllReduceFn all_reduce = nullptr;
+  AllGatherFn all_gather = nullptr;
   GetErrorStringFn error_string = nullptr;
   bool ok = false;
 };
 
 // ncclDataType_t / ncclRedOp_t values of the public nccl.h
-constexpr int kNcclFloat32 = 7, kNcclBfloat16 = 9, kNcclSum = 0;
+constexpr int kNcclChar = 0, kNcclFloat32 = 7, kNcclBfloat16 = 9, kNcclSum = 0;
 
 NcclApi& api() {
   static NcclApi a;
@@ -48,8 +61,9 @@ NcclApi& api() {
     a.comm_init_rank = (CommInitRankFn)dlsym(h, "ncclCommInitRank");
     a.comm_destroy = (CommDestroyFn)dlsym(h, "ncclCommDestroy");
     a.all_reduce = (AllReduceFn)dlsym(h, "ncclAllReduce");
+    a.all_gather = (AllGatherFn)dlsym(h, "ncclAllGather");
     a.error_string = (GetErrorStringFn)dlsym(h, "ncclGetErrorString");
-    a.ok = a.get_unique_id && a.comm_init_rank && a.comm_destroy && a.all_reduce && a.error_string;
+    a.ok = a.get_unique_id && a.comm_init_rank && a.comm_destroy && a.all_reduce && a.all_gather && a.error_string;
   });
   return a;
 }
@@ -58,15 +72,363 @@ int32_t nccl_fail(const char* what, int rc) {
   return fail(B200_ERR_NCCL, "%s failed: %s", what, api().error_string ? api().error_string(rc) : "?");
 }
 
+constexpr int kMaxPeers = 8;
+constexpr int kFlagWords = 64;  // [0..7] "partial ready" per source rank, [8..15] "slice written" per source rank, [32] CTA counter
+
+struct PeerMem {
+  bool on = false;
+  size_t bytes = 0;
+  void* buf[kMaxPeers] = {};       // buf[r]: rank r's exchange buffer as seen from this process
+  uint32_t* flags[kMaxPeers] = {}; // flags[r]: rank r's flag words
+  uint32_t epoch = 0;
+};
+
+}  // namespace
+
+// What the opaque communicator handle of the C ABI points to.
+struct Comm {
+  NcclComm nccl = nullptr;
+  int rank = 0, world = 1;
+  PeerMem pm;
+};
+
+namespace {
+
+struct IpcBlob {
+  cudaIpcMemHandle_t buf, flags;
+  int valid;
+};
+
+// Allocates this rank's exchange buffer and flag words and maps every peer's
+// through CUDA IPC.  The handles travel by an NCCL all-gather and the ranks
+// agree on the outcome with an NCCL all-reduce, so that either all of them use
+// the peer path or none does.  Every rank takes part in both collectives
+// whatever happened locally.  Failure only disables the peer path.
+void setup_peer_memory(Comm* c) {
+  if (c->world < 2 || c->world > kMaxPeers || env_int("B200_P2P", 1) == 0) return;
+  NcclApi& a = api();
+  PeerMem& pm = c->pm;
+  pm.bytes = (size_t)env_int("B200_P2P_MB", 72) << 20;
+  void* lbuf = nullptr;
+  uint32_t* lflags = nullptr;
+  uint8_t* dscratch = nullptr;  // [world + 1] blobs, then one float for the agreement
+  IpcBlob mine, all[kMaxPeers];
+  memset(&mine, 0, sizeof(mine));
+  const size_t blob_bytes = sizeof(IpcBlob) * (kMaxPeers + 1);
+  if (cudaMalloc(&dscratch, blob_bytes + 256) != cudaSuccess) {  // without it this rank cannot even take part
+    cudaGetLastError();
+    return;
+  }
+  bool ok = cudaMalloc(&lbuf, pm.bytes) == cudaSuccess && cudaMalloc(&lflags, kFlagWords * 4) == cudaSuccess &&
+            cudaMemset(lflags, 0, kFlagWords * 4) == cudaSuccess &&
+            cudaIpcGetMemHandle(&mine.buf, lbuf) == cudaSuccess &&
+            cudaIpcGetMemHandle(&mine.flags, lflags) == cudaSuccess;
+  mine.valid = ok ? 1 : 0;
+  IpcBlob* dblobs = reinterpret_cast<IpcBlob*>(dscratch);
+  bool gathered = cudaMemcpy(dblobs + kMaxPeers, &mine, sizeof(mine), cudaMemcpyHostToDevice) == cudaSuccess &&
+                  a.all_gather(dblobs + kMaxPeers, dblobs, sizeof(IpcBlob), kNcclChar, c->nccl, 0) == 0 &&
+                  cudaStreamSynchronize(0) == cudaSuccess &&
+                  cudaMemcpy(all, dblobs, sizeof(IpcBlob) * c->world, cudaMemcpyDeviceToHost) == cudaSuccess;
+  ok = ok && gathered;
+  for (int r = 0; ok && r < c->world; ++r) ok = all[r].valid == 1;
+  for (int r = 0; ok && r < c->world; ++r) {
+    if (r == c->rank) {
+      pm.buf[r] = lbuf;
+      pm.flags[r] = lflags;
+    } else {
+      void* pb = nullptr;
+      void* pf = nullptr;
+      ok = cudaIpcOpenMemHandle(&pb, all[r].buf, cudaIpcMemLazyEnablePeerAccess) == cudaSuccess &&
+           cudaIpcOpenMemHandle(&pf, all[r].flags, cudaIpcMemLazyEnablePeerAccess) == cudaSuccess;
+      pm.buf[r] = pb;
+      pm.flags[r] = reinterpret_cast<uint32_t*>(pf);
+    }
+  }
+  // agreement: the sum of the ranks' verdicts must equal the world size
+  float verdict = ok ? 1.f : 0.f, total = 0.f;
+  float* dv = reinterpret_cast<float*>(dscratch + blob_bytes);
+  const bool agreed = cudaMemcpy(dv, &verdict, 4, cudaMemcpyHostToDevice) == cudaSuccess &&
+                      a.all_reduce(dv, dv, 1, kNcclFloat32, kNcclSum, c->nccl, 0) == 0 &&
+                      cudaStreamSynchronize(0) == cudaSuccess &&
+                      cudaMemcpy(&total, dv, 4, cudaMemcpyDeviceToHost) == cudaSuccess;
+  ok = ok && agreed && total == (float)c->world;
+  cudaFree(dscratch);
+  if (!ok) {
+    cudaGetLastError();
+    for (int r = 0; r < c->world; ++r) {
+      if (r == c->rank) continue;
+      if (pm.buf[r]) cudaIpcCloseMemHandle(pm.buf[r]);
+      if (pm.flags[r]) cudaIpcCloseMemHandle(pm.flags[r]);
+    }
+    if (lbuf) cudaFree(lbuf);
+    if (lflags) cudaFree(lflags);
+    pm = PeerMem();
+    return;
+  }
+  pm.on = true;
+}
+
+void free_peer_memory(Comm* c) {
+  PeerMem& pm = c->pm;
+  if (!pm.on) return;
+  for (int r = 0; r < c->world; ++r) {
+    if (r == c->rank) continue;
+    cudaIpcCloseMemHandle(pm.buf[r]);
+    cudaIpcCloseMemHandle(pm.flags[r]);
+  }
+  cudaFree(pm.buf[c->rank]);
+  cudaFree(pm.flags[c->rank]);
+  pm = PeerMem();
+}
+
 }  // namespace
 
 int32_t comm_allreduce(void* comm, void* data, size_t count, int dtype, cudaStream_t stream) {
   if (!comm) return fail(B200_ERR_INVALID_ARG, "communicator is null");
+  Comm* c = reinterpret_cast<Comm*>(comm);
   NcclApi& a = api();
   if (!a.ok) return fail(B200_ERR_NCCL, "NCCL is not available in this process");
   const int nt = dtype == B200_BF16 ? kNcclBfloat16 : kNcclFloat32;
-  const int rc = a.all_reduce(data, data, count, nt, kNcclSum, comm, stream);
+  ProfScope prof(PROF_COMM, (double)count * (dtype == B200_BF16 ? 2 : 4), stream);
+  const int rc = a.all_reduce(data, data, count, nt, kNcclSum, c->nccl, stream);
   if (rc != 0) return nccl_fail("ncclAllReduce", rc);
+  return B200_OK;
+}
+
+}  // namespace b200
+
+// ---- peer-memory all-reduce + residual add --------------------------------------
+namespace b200 {
+
+namespace {
+
+enum : uint32_t { ST_PEER_TIMEOUT = 1u << 12 };
+constexpr int kReadyBase = 0, kDoneBase = 8, kCounter = 32;
+
+__device__ __forceinline__ void flag_store_sys(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t flag_load_sys(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+// 16 bytes from memory that another GPU owns or may have written: skip the L1, which is not coherent with peers
+// (ordering comes from the acquire on the flag that precedes these loads)
+__device__ __forceinline__ uint4 load16_sys(const void* p) {
+  uint4 v;
+  asm volatile("ld.global.cg.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+  return v;
+}
+
+struct PeerPtrs {
+  void* buf[kMaxPeers];
+  uint32_t* flags[kMaxPeers];
+};
+
+// Thread 0 of the CTA waits until every rank's flag word `base + r` in this
+// rank's flag array has reached `epoch`; about two seconds at most.  Returns
+// false (for the whole CTA) when the wait ran out.
+__device__ __forceinline__ bool wait_all_peers(const uint32_t* my_flags, int base, int world, uint32_t epoch,
+                                               uint32_t* status) {
+  __shared__ int s_ok;
+  if (threadIdx.x == 0) {
+    int ok = 1;
+    const long long t0 = clock64();
+    for (int r = 0; r < world && ok; ++r) {
+      while ((int32_t)(flag_load_sys(my_flags + base + r) - epoch) < 0) {
+        if (clock64() - t0 > 4000000000LL) {
+          ok = 0;
+          atomicOr(status, ST_PEER_TIMEOUT);
+          break;
+        }
+      }
+    }
+    s_ok = ok;
+  }
+  __syncthreads();
+  return s_ok != 0;
+}
+
+__device__ __forceinline__ void accum8(const uint4& raw, float (&acc)[8], bf16) {
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 f = __bfloat1622float2(h[i]);
+    acc[2 * i] += f.x;
+    acc[2 * i + 1] += f.y;
+  }
+}
+__device__ __forceinline__ void accum8(const uint4& raw, float (&acc)[8], float) {
+  acc[0] += __uint_as_float(raw.x); acc[1] += __uint_as_float(raw.y);
+  acc[2] += __uint_as_float(raw.z); acc[3] += __uint_as_float(raw.w);
+}
+
+// Pass 1: tell the peers this rank's partial is complete, wait for theirs, then
+// sum this rank's slice over all ranks (rank order, fp32) and store the result
+// into every rank's buffer.  The last CTA to finish tells the peers.
+template <typename T>
+__global__ void __launch_bounds__(512) peer_reduce_kernel(PeerPtrs pp, int rank, int world, size_t n_vec16,
+                                                          uint32_t epoch, uint32_t* status) {
+  uint32_t* my_flags = pp.flags[rank];
+  if (blockIdx.x == 0 && threadIdx.x < world) {
+    __threadfence_system();
+    flag_store_sys(pp.flags[threadIdx.x] + kReadyBase + rank, epoch);
+  }
+  const bool ok = wait_all_peers(my_flags, kReadyBase, world, epoch, status);
+  if (ok) {
+    const size_t per = (n_vec16 + world - 1) / world;
+    const size_t v0 = (size_t)rank * per, v1 = min(n_vec16, v0 + per);
+    for (size_t i = v0 + blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < v1; i += (size_t)gridDim.x * blockDim.x) {
+      uint4 raw[kMaxPeers];
+#pragma unroll
+      for (int r = 0; r < kMaxPeers; ++r)
+        if (r < world) raw[r] = load16_sys(reinterpret_cast<const uint4*>(pp.buf[r]) + i);
+      float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int r = 0; r < kMaxPeers; ++r)
+        if (r < world) accum8(raw[r], acc, T());
+      uint4 out;
+      if (sizeof(T) == 2) {
+        __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&out);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) h[k] = __floats2bfloat162_rn(acc[2 * k], acc[2 * k + 1]);
+      } else {
+        out = make_uint4(__float_as_uint(acc[0]), __float_as_uint(acc[1]), __float_as_uint(acc[2]), __float_as_uint(acc[3]));
+      }
+#pragma unroll
+      for (int r = 0; r < kMaxPeers; ++r)
+        if (r < world) reinterpret_cast<uint4*>(pp.buf[r])[i] = out;
+    }
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const uint32_t done = atomicAdd(my_flags + kCounter, 1u);
+    if (done == gridDim.x - 1) {
+      my_flags[kCounter] = 0u;
+      __threadfence_system();
+      for (int r = 0; r < world; ++r) flag_store_sys(pp.flags[r] + kDoneBase + rank, epoch);
+    }
+  }
+}
+
+// Pass 2: once every rank has written its slice, out = resid + sum.
+template <typename T>
+__global__ void __launch_bounds__(512) peer_add_kernel(PeerPtrs pp, int rank, int world, size_t n_vec16,
+                                                       uint32_t epoch, const float* __restrict__ resid,
+                                                       float* __restrict__ out, uint32_t* status) {
+  if (!wait_all_peers(pp.flags[rank], kDoneBase, world, epoch, status)) return;
+  constexpr int E = 16 / sizeof(T);  // elements per 16 bytes
+  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n_vec16; i += (size_t)gridDim.x * blockDim.x) {
+    const uint4 raw = load16_sys(reinterpret_cast<const uint4*>(pp.buf[rank]) + i);
+    float s[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    accum8(raw, s, T());
+    const float4 a = *reinterpret_cast<const float4*>(resid + i * E);
+    *reinterpret_cast<float4*>(out + i * E) = make_float4(a.x + s[0], a.y + s[1], a.z + s[2], a.w + s[3]);
+    if (E == 8) {
+      const float4 b = *reinterpret_cast<const float4*>(resid + i * E + 4);
+      *reinterpret_cast<float4*>(out + i * E + 4) = make_float4(b.x + s[4], b.y + s[5], b.z + s[6], b.w + s[7]);
+    }
+  }
+}
+
+// Small messages (decode): one pass.  Every rank reads all ranks' partials and
+// adds the sum to its residual rows itself; one flag round instead of two.  The
+// exchange buffer is used in halves that alternate from call to call, so a
+// peer may still be reading the previous half while this rank fills the next.
+template <typename T>
+__global__ void __launch_bounds__(512) peer_oneshot_kernel(PeerPtrs pp, int rank, int world, size_t n_vec16,
+                                                           size_t half_off, uint32_t epoch,
+                                                           const float* __restrict__ resid, float* __restrict__ out,
+                                                           uint32_t* status) {
+  if (blockIdx.x == 0 && threadIdx.x < world) {
+    __threadfence_system();
+    flag_store_sys(pp.flags[threadIdx.x] + kReadyBase + rank, epoch);
+  }
+  if (!wait_all_peers(pp.flags[rank], kReadyBase, world, epoch, status)) return;
+  constexpr int E = 16 / sizeof(T);
+  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n_vec16; i += (size_t)gridDim.x * blockDim.x) {
+    uint4 raw[kMaxPeers];
+#pragma unroll
+    for (int r = 0; r < kMaxPeers; ++r)
+      if (r < world) raw[r] = load16_sys(reinterpret_cast<const uint8_t*>(pp.buf[r]) + half_off + i * 16);
+    float s[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int r = 0; r < kMaxPeers; ++r)
+      if (r < world) accum8(raw[r], s, T());
+    const float4 a = *reinterpret_cast<const float4*>(resid + i * E);
+    *reinterpret_cast<float4*>(out + i * E) = make_float4(a.x + s[0], a.y + s[1], a.z + s[2], a.w + s[3]);
+    if (E == 8) {
+      const float4 b = *reinterpret_cast<const float4*>(resid + i * E + 4);
+      *reinterpret_cast<float4*>(out + i * E + 4) = make_float4(b.x + s[4], b.y + s[5], b.z + s[6], b.w + s[7]);
+    }
+  }
+}
+
+constexpr size_t kOneShotMaxBytes = (size_t)2 << 20;
+
+}  // namespace
+
+// The caller writes its partial into the returned buffer and then calls
+// comm_peer_allreduce_add with the same size; the two calls must alternate.
+void* comm_peer_buffer(void* comm, size_t bytes) {
+  if (!comm) return nullptr;
+  Comm* c = reinterpret_cast<Comm*>(comm);
+  if (!c->pm.on || c->pm.bytes < 2 * kOneShotMaxBytes) return nullptr;
+  uint8_t* base = reinterpret_cast<uint8_t*>(c->pm.buf[c->rank]);
+  // layout: two alternating halves for the one-pass path, then the region of the two-pass path
+  // (separate regions: a peer may still read a half when this rank already fills the large region)
+  if (bytes <= kOneShotMaxBytes) return base + ((c->pm.epoch + 1) & 1u) * kOneShotMaxBytes;
+  if (bytes > c->pm.bytes - 2 * kOneShotMaxBytes) return nullptr;
+  return base + 2 * kOneShotMaxBytes;
+}
+
+int32_t comm_peer_allreduce_add(void* comm, size_t count, int dtype, const float* resid, float* out,
+                                cudaStream_t stream) {
+  Comm* c = reinterpret_cast<Comm*>(comm);
+  if (!c || !c->pm.on) return fail(B200_ERR_INVALID_ARG, "peer memory is not set up for this communicator");
+  const size_t es = dtype == B200_BF16 ? 2 : 4;
+  if ((count * es) % 16 || count * es > c->pm.bytes - 2 * kOneShotMaxBytes)
+    return fail(B200_ERR_BAD_SHAPE, "peer all-reduce: bad size");
+  ProfScope prof(PROF_COMM, (double)count * es, stream);
+  const bool small = count * es <= kOneShotMaxBytes;
+  PeerPtrs pp;
+  for (int r = 0; r < kMaxPeers; ++r) {
+    // the two-pass kernels index from the start of the large region
+    pp.buf[r] = c->pm.buf[r] ? reinterpret_cast<uint8_t*>(c->pm.buf[r]) + (small ? 0 : 2 * kOneShotMaxBytes) : nullptr;
+    pp.flags[r] = c->pm.flags[r];
+  }
+  const uint32_t epoch = ++c->pm.epoch;
+  const size_t n_vec = count * es / 16;
+  uint32_t* status = device_status_word();
+  if (small) {
+    const size_t half_off = (size_t)(epoch & 1u) * kOneShotMaxBytes;
+    int g1 = (int)((n_vec + 511) / 512);
+    if (g1 > sm_count()) g1 = sm_count();
+    if (dtype == B200_BF16)
+      peer_oneshot_kernel<bf16><<<g1, 512, 0, stream>>>(pp, c->rank, c->world, n_vec, half_off, epoch, resid, out, status);
+    else
+      peer_oneshot_kernel<float><<<g1, 512, 0, stream>>>(pp, c->rank, c->world, n_vec, half_off, epoch, resid, out, status);
+    B200_LAUNCH_OK("peer_oneshot_kernel");
+    return B200_OK;
+  }
+  int grid = sm_count();
+  const size_t want = (n_vec / c->world + 511) / 512;
+  if ((size_t)grid > want) grid = want < 1 ? 1 : (int)want;
+  if (dtype == B200_BF16)
+    peer_reduce_kernel<bf16><<<grid, 512, 0, stream>>>(pp, c->rank, c->world, n_vec, epoch, status);
+  else
+    peer_reduce_kernel<float><<<grid, 512, 0, stream>>>(pp, c->rank, c->world, n_vec, epoch, status);
+  B200_LAUNCH_OK("peer_reduce_kernel");
+  int grid2 = sm_count() * 2;
+  const size_t want2 = (n_vec + 511) / 512;
+  if ((size_t)grid2 > want2) grid2 = want2 < 1 ? 1 : (int)want2;
+  if (dtype == B200_BF16)
+    peer_add_kernel<bf16><<<grid2, 512, 0, stream>>>(pp, c->rank, c->world, n_vec, epoch, resid, out, status);
+  else
+    peer_add_kernel<float><<<grid2, 512, 0, stream>>>(pp, c->rank, c->world, n_vec, epoch, resid, out, status);
+  B200_LAUNCH_OK("peer_add_kernel");
   return B200_OK;
 }
 
@@ -92,24 +454,39 @@ int32_t b200_comm_init_rank(const void* id128, int32_t rank, int32_t world, void
   if (!a.ok) return fail(B200_ERR_NCCL, "NCCL is not available in this process");
   NcclUniqueId id;
   memcpy(&id, id128, sizeof(id));
-  NcclComm c = nullptr;
-  const int rc = a.comm_init_rank(&c, world, id, rank);
+  NcclComm nc = nullptr;
+  const int rc = a.comm_init_rank(&nc, world, id, rank);
   if (rc != 0) return nccl_fail("ncclCommInitRank", rc);
+  Comm* c = new Comm();
+  c->nccl = nc;
+  c->rank = rank;
+  c->world = world;
+  setup_peer_memory(c);
   *comm = c;
   return B200_OK;
 }
 
 int32_t b200_comm_destroy(void* comm) {
   if (!comm) return B200_OK;
+  Comm* c = reinterpret_cast<Comm*>(comm);
   NcclApi& a = api();
   if (!a.ok) return fail(B200_ERR_NCCL, "NCCL is not available in this process");
-  const int rc = a.comm_destroy(comm);
+  cudaDeviceSynchronize();
+  free_peer_memory(c);
+  const int rc = a.comm_destroy(c->nccl);
+  delete c;
   if (rc != 0) return nccl_fail("ncclCommDestroy", rc);
   return B200_OK;
 }
 
 int32_t b200_allreduce_f32(void* comm, float* data, size_t count, b200_stream_t stream) {
   return comm_allreduce(comm, data, count, B200_F32, reinterpret_cast<cudaStream_t>(stream));
+}
+
+int32_t b200_comm_peer_memory(void* comm, int32_t* enabled) {
+  if (!comm || !enabled) return fail(B200_ERR_INVALID_ARG, "null argument");
+  *enabled = reinterpret_cast<Comm*>(comm)->pm.on ? 1 : 0;
+  return B200_OK;
 }
 
 }  // extern "C"

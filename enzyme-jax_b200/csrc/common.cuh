@@ -41,7 +41,7 @@ int32_t fail(int32_t code, const char* fmt, ...);
 void count_launch();
 
 // Event-pair profiling of kernel classes (off unless enabled through the ABI).
-enum ProfClass : int { PROF_GEMM_TC = 0, PROF_GEMM_SIMT = 1, PROF_ATTN_FWD = 2, PROF_ATTN_BWD = 3, PROF_ATTN_DECODE = 4, PROF_NUM = 5 };
+enum ProfClass : int { PROF_GEMM_TC = 0, PROF_GEMM_SIMT = 1, PROF_ATTN_FWD = 2, PROF_ATTN_BWD = 3, PROF_ATTN_DECODE = 4, PROF_COMM = 5, PROF_NUM = 6 };
 struct ProfScope {
   int slot = -1;
   cudaStream_t stream;

@@ -72,6 +72,11 @@ int32_t proj_residual(const B200Plan& p, const DecodeWs& ws, const void* A, int 
     e.out = x; e.ldo = p.d; e.resid_in = x;
     return gemm(p, ws, A, lda, W, ldw, M, p.d, K, EPI_RESID, B200_F32, e, stream);
   }
+  if (void* pbuf = comm_peer_buffer(p.comm, (size_t)M * p.d * p.esize)) {
+    e.out = pbuf; e.ldo = p.d;
+    B200_TRY(gemm(p, ws, A, lda, W, ldw, M, p.d, K, EPI_STORE, p.dtype, e, stream));
+    return comm_peer_allreduce_add(p.comm, (size_t)M * p.d, p.dtype, x, x, stream);
+  }
   e.out = tp_tmp; e.ldo = p.d;
   B200_TRY(gemm(p, ws, A, lda, W, ldw, M, p.d, K, EPI_STORE, p.dtype, e, stream));
   B200_TRY(comm_allreduce(p.comm, tp_tmp, (size_t)M * p.d, p.dtype, stream));

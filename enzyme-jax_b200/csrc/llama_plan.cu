@@ -187,6 +187,13 @@ static int32_t proj_residual(const B200Plan& p, const void* A, int lda, const vo
     e.out = x_out; e.ldo = p.d; e.resid_in = x_in;
     return gemm(p, A, lda, W, ldw, T, p.d, K, EPI_RESID, B200_F32, e, stream);
   }
+  // Peer-memory path: the partial product goes straight into the buffer the other ranks map; two kernels
+  // reduce it over NVLink and add the sum to the residual stream.
+  if (void* pbuf = comm_peer_buffer(p.comm, (size_t)T * p.d * p.esize)) {
+    e.out = pbuf; e.ldo = p.d;
+    B200_TRY(gemm(p, A, lda, W, ldw, T, p.d, K, EPI_STORE, p.dtype, e, stream));
+    return comm_peer_allreduce_add(p.comm, (size_t)T * p.d, p.dtype, x_in, x_out, stream);
+  }
   // Token chunks: the projection of chunk c+1 computes while chunk c is summed over the ranks on the
   // communication stream (NCCL over NVLink); the compute stream joins all chunks before the add.
   int chunks = (T >= 512 * p.tp_chunks && T % (128 * p.tp_chunks) == 0) ? p.tp_chunks : 1;

@@ -97,6 +97,11 @@ void build_layout(const B200Plan& p, size_t mat_esize, bool with_t, PackedLayout
 void carve_forward(const B200Plan& p, Arena& a, int B, int S, bool keep, FwdActs* out);
 
 int32_t comm_allreduce(void* comm, void* data, size_t count, int dtype, cudaStream_t stream);
+// This rank's peer-mapped exchange buffer when the peer path is up and `bytes` fit, else null.
+void* comm_peer_buffer(void* comm, size_t bytes);
+// out = resid + sum over ranks of the `count` elements each rank left in its exchange buffer
+int32_t comm_peer_allreduce_add(void* comm, size_t count, int dtype, const float* resid, float* out,
+                                cudaStream_t stream);
 
 // Environment knobs (read once at plan creation): B200_GEMM_IMPL and
 // B200_ATTN_IMPL select 0 = pick, 1 = tensor-core kernels, 2 = CUDA-core kernels.

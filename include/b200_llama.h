@@ -111,8 +111,8 @@ B200_API int64_t b200_launch_count(void);
  * b200_profile_enable(1) clears earlier samples and brackets every GEMM and
  * attention launch with an event pair; b200_profile_read synchronises those
  * events and returns, for one kernel class (0 tcgen05 GEMM, 1 FFMA GEMM,
- * 2 attention forward, 3 attention backward, 4 decode attention), the summed
- * milliseconds, the summed algorithmic work (flops; bytes for class 4) and
+ * 2 attention forward, 3 attention backward, 4 decode attention, 5 all-reduce), the summed
+ * milliseconds, the summed algorithmic work (flops; bytes for classes 4 and 5) and
  * the launch count.  Off by default; costs two event records per launch. */
 B200_API int32_t b200_profile_enable(int32_t on);
 B200_API int32_t b200_profile_read(int32_t kernel_class, double* total_ms, double* total_work, int64_t* launches);
@@ -268,6 +268,9 @@ B200_API int32_t b200_attention_decode_static(const void* q, const void* kv_page
 B200_API int32_t b200_comm_unique_id(void* id128 /* 128 bytes out */);
 B200_API int32_t b200_comm_init_rank(const void* id128, int32_t rank, int32_t world, void** comm);
 B200_API int32_t b200_comm_destroy(void* comm);
+/* *enabled = 1 when the ranks of the communicator exchange the tensor-parallel partial sums through
+ * peer-mapped memory (CUDA IPC over NVLink) instead of NCCL. */
+B200_API int32_t b200_comm_peer_memory(void* comm, int32_t* enabled);
 
 #ifdef __cplusplus
 }

@@ -22,6 +22,8 @@ def main():
     torch.cuda.set_device(local)
     dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     comm = B.Comm(rank, world)
+    if rank == 0:
+        print("PEER_MEMORY", comm.peer_memory())
     cfg = dict(dim=256, hidden_dim=512, n_layers=2, n_heads=4, n_kv_heads=4, vocab_size=1024, seq_len=160)
     for dtype, tol in ((torch.float32, 1e-4), (torch.bfloat16, 2e-2)):
         w = {k: v.to(dtype) for k, v in O.make_weights(cfg, 3, torch.float32, std=0.05).items()}
