@@ -347,7 +347,7 @@ int32_t launch_pair_bn(const GemmArgs& g, cudaStream_t stream) {
   const long mt = cdiv(g.M, 2 * PM);
   const long cost256 = g.N % 256 == 0 ? (long)cdiv((int)(mt * (g.N / 256)), pairs) * 256 : -1;
   const long cost128 = (long)cdiv((int)(mt * cdiv(g.N, 128)), pairs) * 128;
-  if (cost256 >= 0 && cost256 * 10 <= cost128 * 12) return  // the wide tile moves fewer bytes per flop: keep it unless it wastes > 20 %
+  if (cost256 >= 0 && cost256 * 10 <= cost128 * 12) return  // the wide tile moves fewer bytes per flop: keep it unless it wastes > 20 % (a 40 % margin measured slower in the 110M step)
     launch_pair_cfg<256, KIND, TOut>(g, stream);
   return launch_pair_cfg<128, KIND, TOut>(g, stream);
 }
