@@ -52,6 +52,44 @@ __global__ void __launch_bounds__(256) rmsnorm_kernel(const float* __restrict__ 
   }
 }
 
+// Warp-per-row variant (dim <= 2048): the row is read once and stays in
+// registers between the reduction and the scaling; no block barrier.
+template <typename TOut, int NCH>
+__global__ void __launch_bounds__(256) rmsnorm_warp_kernel(const float* __restrict__ x, const float* __restrict__ gain,
+                                                           TOut* __restrict__ y, float* __restrict__ rinv, int rows,
+                                                           int dim, float eps) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int row = blockIdx.x * 8 + warp;
+  if (row >= rows) return;
+  const float* xr = x + (size_t)row * dim;
+  float v[NCH][8];
+  float ss = 0.f;
+#pragma unroll
+  for (int ch = 0; ch < NCH; ++ch) {
+    const int c = (ch * 32 + lane) * 8;
+    if (c < dim) {
+      load8_wide(xr + c, v[ch]);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) ss = fmaf(v[ch][i], v[ch][i], ss);
+    }
+  }
+  ss = warp_sum(ss);
+  const float r = rsqrtf(ss / (float)dim + eps);
+  if (rinv && lane == 0) rinv[row] = r;
+  TOut* yr = y + (size_t)row * dim;
+#pragma unroll
+  for (int ch = 0; ch < NCH; ++ch) {
+    const int c = (ch * 32 + lane) * 8;
+    if (c < dim) {
+      float g[8];
+      load8(gain + c, g);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) v[ch][i] = g[i] * v[ch][i] * r;
+      store8(yr + c, v[ch]);
+    }
+  }
+}
+
 template <typename T>
 __global__ void add_to_f32_kernel(float* __restrict__ x, const T* __restrict__ d, size_t n8) {
   for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n8; i += (size_t)gridDim.x * blockDim.x) {
@@ -405,6 +443,24 @@ int32_t launch_rmsnorm(const float* x, const float* gain, void* y, float* rinv, 
                        int out_dtype, cudaStream_t stream) {
   if (dim % 8) return fail(B200_ERR_BAD_SHAPE, "rmsnorm: dim=%d must be a multiple of 8", dim);
   if (rows <= 0) return fail(B200_ERR_BAD_SHAPE, "rmsnorm: no rows");
+  if (dim <= 2048 && (out_dtype == B200_F32 || out_dtype == B200_BF16)) {
+    const int nch = cdiv(dim, 256);
+    const int grid = cdiv(rows, 8);
+#define B200_RN_CASE(N)                                                                                          \
+  case N:                                                                                                        \
+    if (out_dtype == B200_F32)                                                                                   \
+      rmsnorm_warp_kernel<float, N><<<grid, 256, 0, stream>>>(x, gain, (float*)y, rinv, rows, dim, eps);         \
+    else                                                                                                         \
+      rmsnorm_warp_kernel<bf16, N><<<grid, 256, 0, stream>>>(x, gain, (bf16*)y, rinv, rows, dim, eps);           \
+    break;
+    switch (nch) {
+      B200_RN_CASE(1) B200_RN_CASE(2) B200_RN_CASE(3) B200_RN_CASE(4)
+      B200_RN_CASE(5) B200_RN_CASE(6) B200_RN_CASE(7) B200_RN_CASE(8)
+    }
+#undef B200_RN_CASE
+    B200_LAUNCH_OK("rmsnorm_warp_kernel");
+    return B200_OK;
+  }
   int threads = ((dim / 8 + 31) / 32) * 32;
   if (threads > 256) threads = 256;
   if (out_dtype == B200_F32)

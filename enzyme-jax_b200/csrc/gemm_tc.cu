@@ -216,8 +216,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
           }
         }
       }
-      ok = ptx::mbar_wait(&acc_full[acc], acc_phase, abort_flag, status, ST_EPILOGUE_TIMEOUT);
-      ok = __all_sync(0xffffffffu, ok);
+      ok = ptx::mbar_wait_warp(&acc_full[acc], acc_phase, abort_flag, status, ST_EPILOGUE_TIMEOUT);
       if (!ok) break;
       ptx::tc_fence_after_sync();
       // 32 columns per TMEM round trip; the next pair of loads is in flight

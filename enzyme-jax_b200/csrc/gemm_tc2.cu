@@ -229,8 +229,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(P_THREADS, 1)
           for (int i = 0; i < 8; ++i) { rc[c + i] = t8[i]; rs[c + i] = u8[i]; }
         }
       }
-      ok = ptx::mbar_wait(&acc_full[acc], acc_phase, abort_flag, status, ST_PAIR_EPILOGUE);
-      ok = __all_sync(0xffffffffu, ok);
+      ok = ptx::mbar_wait_warp(&acc_full[acc], acc_phase, abort_flag, status, ST_PAIR_EPILOGUE);
       if (!ok) break;
       ptx::tc_fence_after_sync();
       float cur[2][16], nxt[2][16];

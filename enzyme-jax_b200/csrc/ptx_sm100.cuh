@@ -67,6 +67,17 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
   }
 }
 
+// Warp-collective wait: one lane polls (256 threads hammering try_wait saturate the shared-memory
+// pipe the barrier lives in and slow the co-resident CTA down), the verdict is broadcast, and
+// __shfl_sync orders the other lanes' later accesses after lane 0's acquire.
+__device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag,
+                                               uint32_t* status, uint32_t code) {
+  int ok = 1;
+  if ((threadIdx.x & 31) == 0) ok = mbar_wait(bar, parity, abort_flag, status, code) ? 1 : 0;
+  ok = __shfl_sync(0xffffffffu, ok, 0);
+  return ok != 0;
+}
+
 // ---- TMA --------------------------------------------------------------------
 __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
   asm volatile(
