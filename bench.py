@@ -274,6 +274,9 @@ def run_prefill(args, rank, world, local, B, dist):
     if args.batch > 0:
         batch = args.batch
         desc += f" [batch overridden to {batch}]"
+    if args.layers > 0:
+        cfg = dict(cfg, n_layers=args.layers)
+        desc += f" [layers overridden to {args.layers}]"
     dtype = torch.bfloat16 if dname == "bf16" else torch.float32
     dev = torch.device("cuda", local)
     pk = peaks()
@@ -504,6 +507,9 @@ def run_decode(args, rank, world, local, B, dist):
     tp = world
     steps_total = 128
     cfg = dict(cfg, seq_len=ctx0 + steps_total)
+    if args.layers > 0:
+        cfg = dict(cfg, n_layers=args.layers)
+        desc += f" [layers overridden to {args.layers}]"
     comm = B.Comm(rank, world) if tp > 1 else None
     page = 128
     max_pages = (ctx0 + steps_total + page - 1) // page
@@ -595,6 +601,7 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--batch", type=int, default=0, help="override the batch per rank (profiling on a small case)")
+    ap.add_argument("--layers", type=int, default=0, help="override the layer count (profiling on a small case)")
     ap.add_argument("--no-graph", action="store_true", help="launch every kernel eagerly instead of replaying a CUDA graph")
     args = ap.parse_args()
 
@@ -609,6 +616,7 @@ def main():
     import torch.distributed as dist
     import b200_llama as B
 
+    os.environ["NCCL_DEBUG"] = os.environ.get("B200_NCCL_DEBUG", "WARN")  # keep NCCL's banner off stdout: one JSON line
     torch.cuda.set_device(local)
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
