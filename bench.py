@@ -357,9 +357,12 @@ def run_prefill(args, rank, world, local, B, dist):
     tensor_bound = dname == "bf16"
     ach = dom["work"] / (dom["ms"] / 1e3) / 1e12 if dom["ms"] > 0 else 0.0
     peak = pk["tflops_sustained"]
+    # DRAM bytes per launch of the GEMM class from the ncu capture of one full-size step
+    # (dram__bytes_read.sum + dram__bytes_write.sum over the 49 GEMM launches of config 2: 2841 MB)
+    traffic = 58.0e6 if (args.workload == "c2" and args.batch == 0 and args.layers == 0 and dom_name == "gemm_tcgen05") else None
     roofline = {
         "bound": "tensor", "kernel": dom_name, "achieved": ach, "peak": peak, "unit": "TFLOP/s",
-        "frac": ach / peak, "traffic": None, "peak_source": pk["source"] + " (sustained bf16 matmul)",
+        "frac": ach / peak, "traffic": traffic, "traffic_unit": "bytes per launch (ncu, mean over the GEMM launches of a step)", "peak_source": pk["source"] + " (sustained bf16 matmul)",
         "launches": dom["launches"], "kernel_ms_per_step": dom["ms"] / args.steps,
         "share_of_step": dom["ms"] / max(1e-9, sum(v["ms"] for v in prof.values())),
         "whole_step_frac": fwd_flops(cfg, batch, seq) / tp / (ms / args.steps / 1e3) / 1e12 / peak,

@@ -174,9 +174,11 @@ __global__ void __launch_bounds__(VW * 32)
     for (int g = 0; g < VG; ++g) {
       float kf[8];
       unpack8(kr[g], kf);
-      float d = 0.f;
+      float2 d2 = make_float2(0.f, 0.f);  // packed fp32x2 FMAs: two head dimensions per instruction
 #pragma unroll
-      for (int i = 0; i < 8; ++i) d = fmaf(qf[i], kf[i], d);
+      for (int i = 0; i < 8; i += 2)
+        d2 = __ffma2_rn(make_float2(qf[i], qf[i + 1]), make_float2(kf[i], kf[i + 1]), d2);
+      float d = d2.x + d2.y;
 #pragma unroll
       for (int off = LPK / 2; off > 0; off >>= 1) d += __shfl_xor_sync(0xffffffffu, d, off);
       s[g] = live[g] ? d : -INFINITY;
@@ -194,8 +196,13 @@ __global__ void __launch_bounds__(VW * 32)
         l += p;
         float vf[8];
         unpack8(vr[g], vf);
+        const float2 p2 = make_float2(p, p);
 #pragma unroll
-        for (int i = 0; i < 8; ++i) acc[i] = fmaf(p, vf[i], acc[i]);
+        for (int i = 0; i < 8; i += 2) {
+          const float2 r = __ffma2_rn(p2, make_float2(vf[i], vf[i + 1]), make_float2(acc[i], acc[i + 1]));
+          acc[i] = r.x;
+          acc[i + 1] = r.y;
+        }
       }
       m = nm;
     }
