@@ -206,10 +206,10 @@ def attention_backward(qkv: torch.Tensor, o: torch.Tensor, lse: torch.Tensor, d_
 
 def attention_decode(q: torch.Tensor, kv_layer: torch.Tensor, page_table: torch.Tensor, ctx: int, n_heads: int,
                      scratch: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """Decode attention of q [batch, n_heads*hs] over one layer of a paged cache [2, n_pages, page_size, d]."""
+    """Decode attention of q [batch, n_heads*hs] over one layer of a paged cache [2, n_pages, n_heads, page_size, hs]."""
     batch, d = q.shape
     hs = d // n_heads
-    n_pages, page_size = kv_layer.shape[1], kv_layer.shape[2]
+    n_pages, page_size = kv_layer.shape[1], kv_layer.shape[3]
     o = torch.empty(batch, d, dtype=q.dtype, device=q.device)
     if scratch is None:
         n = c_size_t(0)
@@ -231,7 +231,7 @@ def attention_decode_static(q: torch.Tensor, kv_layer: torch.Tensor, page_table:
     hs = d // n_heads
     check(lib().b200_attention_decode_static(q.data_ptr(), kv_layer.data_ptr(), page_table.data_ptr(),
                                              out.data_ptr(), batch, ctx, n_heads, hs, q.stride(0), out.stride(0),
-                                             kv_layer.shape[1], kv_layer.shape[2], page_table.shape[1],
+                                             kv_layer.shape[1], kv_layer.shape[3], page_table.shape[1],
                                              _dt(q.dtype), _stream()))
     return out
 
@@ -403,14 +403,15 @@ class Plan:
     # ---- decode ----------------------------------------------------------
     def new_kv_pages(self, n_pages: int, page_size: int) -> torch.Tensor:
         L = self.config["n_layers"]
-        return torch.zeros(L, 2, n_pages, page_size, self.d_local, dtype=self.dtype, device=self.device)
+        hs = self.config["dim"] // self.config["n_heads"]
+        return torch.zeros(L, 2, n_pages, self.d_local // hs, page_size, hs, dtype=self.dtype, device=self.device)
 
     def decode_step(self, pos: int, kv_pages: torch.Tensor, page_table: torch.Tensor, *,
                     tokens: Optional[torch.Tensor] = None, x: Optional[torch.Tensor] = None,
                     want_hidden: bool = False, want_logits: bool = True,
                     logits: Optional[torch.Tensor] = None):
         B = (tokens if tokens is not None else x).shape[0]
-        n_pages, page_size = kv_pages.shape[2], kv_pages.shape[3]
+        n_pages, page_size = kv_pages.shape[2], kv_pages.shape[4]
         hidden = torch.empty(B, self.config["dim"], dtype=torch.float32, device=self.device) if want_hidden else None
         if want_logits and logits is None:
             logits = torch.empty(B, self.vocab_local, dtype=torch.float32, device=self.device)

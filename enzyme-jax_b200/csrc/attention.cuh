@@ -48,7 +48,7 @@ int32_t launch_attn_bwd(const AttnBwdArgs& a, int impl, cudaStream_t stream);
 // (max, sum, acc) go to scratch and a second kernel combines them.
 struct AttnDecodeArgs {
   const void* q = nullptr;        // [batch, ldq]
-  const void* kv_pages = nullptr; // layer base: K pages at [0], V pages at [1]: [2, n_pages, page_size, d]
+  const void* kv_pages = nullptr; // layer base: K pages at [0], V pages at [1]: [2, n_pages, n_heads, page_size, head_size]
   const int32_t* page_table = nullptr;  // [batch, max_pages]
   void* o = nullptr;              // [batch, ldo]
   float* scratch = nullptr;       // decode_scratch_floats() floats

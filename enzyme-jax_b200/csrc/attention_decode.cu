@@ -19,9 +19,12 @@ namespace {
 constexpr int DW = 4;  // warps per CTA
 
 template <typename T>
-__device__ __forceinline__ const T* page_row(const T* base, const int32_t* table, int u, int page_size, int d_local) {
+// Pages are head-major: [page][head][row][head_size], so the rows of one (sequence, head) are contiguous
+// within a page (page_size * head_size elements) instead of head_size elements out of every d-wide row.
+__device__ __forceinline__ const T* page_row(const T* base, const int32_t* table, int u, int page_size, int n_heads,
+                                             int h, int hs) {
   const int page = table[u / page_size];
-  return base + ((size_t)page * page_size + (u % page_size)) * d_local;
+  return base + (((size_t)page * n_heads + h) * page_size + (u % page_size)) * hs;
 }
 
 template <typename T, int HS>
@@ -49,7 +52,7 @@ __global__ void __launch_bounds__(DW * 32)
     const int u = u0 + lane;
     float s = -INFINITY;
     if (u < c1) {
-      const T* kr = page_row(kpages, table, u, page_size, d_local) + h * HS;
+      const T* kr = page_row(kpages, table, u, page_size, n_heads, h, HS);
       float d = 0.f;
 #pragma unroll
       for (int e = 0; e < HS; e += 8) {
@@ -70,7 +73,7 @@ __global__ void __launch_bounds__(DW * 32)
     const int n = min(32, c1 - u0);
     for (int j = 0; j < n; ++j) {
       const float pj = __shfl_sync(0xffffffffu, p, j);
-      const T* vr = page_row(vpages, table, u0 + j, page_size, d_local) + h * HS;
+      const T* vr = page_row(vpages, table, u0 + j, page_size, n_heads, h, HS);
 #pragma unroll
       for (int i = 0; i < DPL; ++i) {
         const int e = lane + 32 * i;
@@ -163,7 +166,7 @@ __global__ void __launch_bounds__(VW * 32)
       vr[g] = make_uint4(0u, 0u, 0u, 0u);
       if (live[g]) {
         const int page = table[u / page_size];
-        const size_t off = ((size_t)page * page_size + (u % page_size)) * d_local + h * HS + li * 8;
+        const size_t off = (((size_t)page * n_heads + h) * page_size + (u % page_size)) * HS + li * 8;
         kr[g] = *reinterpret_cast<const uint4*>(kpages + off);
         vr[g] = *reinterpret_cast<const uint4*>(vpages + off);
       }

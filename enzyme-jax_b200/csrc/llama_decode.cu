@@ -12,26 +12,22 @@ size_t backward_workspace_bytes(const B200Plan& p, int B, int S);
 namespace {
 
 // Writes row `pos` of every sequence: the rotated key and the value just
-// produced by the QKV projection (test/llama.py:170-175, append-last).
+// produced by the QKV projection (test/llama.py:170-175, append-last).  Pages
+// are head-major: [page][head][row][head_size].
 template <typename T>
 __global__ void kv_append_kernel(const T* __restrict__ qkv, T* __restrict__ kpages, T* __restrict__ vpages,
                                  const int32_t* __restrict__ page_table, int pos, int page_size, int max_pages,
-                                 int d_local) {
+                                 int d_local, int hs) {
+  constexpr int E = 16 / sizeof(T);  // elements per 16-byte piece
   const int b = blockIdx.x;
   const int page = page_table[(size_t)b * max_pages + pos / page_size];
-  const size_t dst = ((size_t)page * page_size + pos % page_size) * d_local;
+  const int n_heads = d_local / hs;
   const T* src = qkv + (size_t)b * 3 * d_local;
-  for (int c = threadIdx.x * 8; c < d_local; c += blockDim.x * 8) {
-    *reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(kpages + dst + c)) =
-        *reinterpret_cast<const uint4*>(reinterpret_cast<const uint8_t*>(src + d_local + c));
-    *reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(vpages + dst + c)) =
-        *reinterpret_cast<const uint4*>(reinterpret_cast<const uint8_t*>(src + 2 * d_local + c));
-    if (sizeof(T) == 4) {  // 8 floats are two 16-byte pieces
-      *reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(kpages + dst + c + 4)) =
-          *reinterpret_cast<const uint4*>(reinterpret_cast<const uint8_t*>(src + d_local + c + 4));
-      *reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(vpages + dst + c + 4)) =
-          *reinterpret_cast<const uint4*>(reinterpret_cast<const uint8_t*>(src + 2 * d_local + c + 4));
-    }
+  for (int c = threadIdx.x * E; c < d_local; c += blockDim.x * E) {
+    const int h = c / hs, e = c % hs;
+    const size_t dst = (((size_t)page * n_heads + h) * page_size + pos % page_size) * hs + e;
+    *reinterpret_cast<uint4*>(kpages + dst) = *reinterpret_cast<const uint4*>(src + d_local + c);
+    *reinterpret_cast<uint4*>(vpages + dst) = *reinterpret_cast<const uint4*>(src + 2 * d_local + c);
   }
 }
 
@@ -163,10 +159,10 @@ int32_t b200_decode_step(B200Plan* p, const int32_t* tokens, const float* x_in, 
     }
     if (p->dtype == B200_BF16)
       kv_append_kernel<bf16><<<B, 128, 0, stream>>>((const bf16*)w.qkv, (bf16*)kv, (bf16*)(kv + layer_bytes / 2),
-                                                    page_table, pos, page_size, max_pages, dl);
+                                                    page_table, pos, page_size, max_pages, dl, p->hs);
     else
       kv_append_kernel<float><<<B, 128, 0, stream>>>((const float*)w.qkv, (float*)kv, (float*)(kv + layer_bytes / 2),
-                                                     page_table, pos, page_size, max_pages, dl);
+                                                     page_table, pos, page_size, max_pages, dl, p->hs);
     B200_LAUNCH_OK("kv_append_kernel");
     {
       AttnDecodeArgs a;

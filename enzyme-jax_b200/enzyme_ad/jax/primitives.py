@@ -163,8 +163,11 @@ class _LlamaRoute:
         page = max(16, 1 << (pos).bit_length())
         kv = plan.new_kv_pages(1, page)
         if pos:
-            kv[:, 0, 0, :pos] = key_cache.to(plan.device, self.pipe.dtype)
-            kv[:, 1, 0, :pos] = value_cache.to(plan.device, self.pipe.dtype)
+            H = cfg["n_heads"]
+            hs = cfg["dim"] // H
+            # [L, pos, kv_dim] -> head-major page [L, H, pos, hs]
+            kv[:, 0, 0, :, :pos] = key_cache.to(plan.device, self.pipe.dtype).view(L, pos, H, hs).permute(0, 2, 1, 3)
+            kv[:, 1, 0, :, :pos] = value_cache.to(plan.device, self.pipe.dtype).view(L, pos, H, hs).permute(0, 2, 1, 3)
         table = torch.zeros(1, 1, dtype=torch.int32, device=plan.device)
         xin = x.to(plan.device, torch.float32).reshape(1, cfg["dim"]).contiguous()
         hidden, _ = plan.decode_step(pos, kv, table, x=xin, want_hidden=True, want_logits=False)

@@ -184,8 +184,9 @@ B200_API int32_t b200_allreduce_f32(void* comm, float* data, size_t count, b200_
  * pos = key_cache.shape[1]).
  *   tokens     int32 [batch], or NULL when x_in is given
  *   x_in       NULL, or fp32 [batch, d] residual vectors (the reference's `x`)
- *   kv_pages   the paged cache: [L, 2, n_pages, page_size, d/tp] of the config
- *              dtype; the step appends row `pos` of every sequence
+ *   kv_pages   the paged cache: [L, 2, n_pages, H/tp, page_size, head_size] of the
+ *              config dtype (head-major pages: the rows of one head are contiguous);
+ *              the step appends row `pos` of every sequence
  *   page_table int32 [batch, max_pages]: page index of each sequence's pages
  *   hidden_out NULL, or fp32 [batch, d]: final-normed hidden state (what the
  *              reference returns, test/llama.py:235-238)
@@ -227,7 +228,7 @@ B200_API int32_t b200_attention_backward(const void* q, const void* k, const voi
 /* Decode attention over the paged cache (test/llama.py:177-209 with a cache of
  * ctx rows): one query row per (sequence, head).
  *   q          [batch, ldq] of `dtype`
- *   kv_pages   one layer of the cache: [2, n_pages, page_size, n_heads*head_size]
+ *   kv_pages   one layer of the cache: [2, n_pages, n_heads, page_size, head_size]
  *   page_table int32 [batch, max_pages]
  *   o          [batch, ldo]
  *   scratch    caller-owned, b200_attention_decode_scratch_bytes() bytes: the

@@ -130,7 +130,7 @@ def _decode_case(batch, ctx, H, hs, dtype, page, seed=0):
     d = H * hs
     max_pages = (ctx + page - 1) // page
     n_pages = batch * max_pages + 3
-    kv = torch.randn(2, n_pages, page, d, generator=g).to(dtype).to(DEV)
+    kv = torch.randn(2, n_pages, H, page, hs, generator=g).to(dtype).to(DEV)  # head-major pages
     q = torch.randn(batch, d, generator=g).to(dtype).to(DEV)
     table = torch.randperm(n_pages, generator=g)[: batch * max_pages].view(batch, max_pages).int().to(DEV)
     return q, kv, table
@@ -139,12 +139,12 @@ def _decode_case(batch, ctx, H, hs, dtype, page, seed=0):
 def _decode_ref(q, kv, table, ctx, H):
     batch, d = q.shape
     hs = d // H
-    page = kv.shape[2]
+    page = kv.shape[3]
     out = torch.empty(batch, d, dtype=torch.float64)
     for b in range(batch):
         rows = [(int(table[b, u // page]), u % page) for u in range(ctx)]
-        k = torch.stack([kv[0, p, r] for p, r in rows]).double().cpu().view(ctx, H, hs)
-        v = torch.stack([kv[1, p, r] for p, r in rows]).double().cpu().view(ctx, H, hs)
+        k = torch.stack([kv[0, p, :, r] for p, r in rows]).double().cpu()  # [ctx, H, hs]
+        v = torch.stack([kv[1, p, :, r] for p, r in rows]).double().cpu()
         qq = q[b].double().cpu().view(H, hs)
         att = torch.softmax(torch.einsum("he,uhe->hu", qq, k) / math.sqrt(hs), -1)
         out[b] = torch.einsum("hu,uhe->he", att, v).reshape(d)

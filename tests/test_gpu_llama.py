@@ -164,8 +164,11 @@ def test_decode_reference_signature_hidden_state():
     ref = O.forward_token(x, cfg, wn, kc, vc)
     p = _plan(cfg, w, torch.float32)
     kv = p.new_kv_pages(1, 16)
-    kv[:, 0, 0, :pos] = torch.from_numpy(kc).float().to(DEV)
-    kv[:, 1, 0, :pos] = torch.from_numpy(vc).float().to(DEV)
+    L, H = cfg["n_layers"], cfg["n_heads"]
+    hs = cfg["dim"] // H
+    # the reference's [L, pos, kv_dim] cache into head-major pages [L, 2, page, H, row, hs]
+    kv[:, 0, 0, :, :pos] = torch.from_numpy(kc).float().view(L, pos, H, hs).permute(0, 2, 1, 3).to(DEV)
+    kv[:, 1, 0, :, :pos] = torch.from_numpy(vc).float().view(L, pos, H, hs).permute(0, 2, 1, 3).to(DEV)
     table = torch.zeros(1, 1, dtype=torch.int32, device=DEV)
     hidden, _ = p.decode_step(pos, kv, table, x=torch.from_numpy(x).float().to(DEV).view(1, -1), want_hidden=True,
                               want_logits=False)

@@ -27,7 +27,7 @@ def _case(batch, ctx, H, hs, dtype, page, seed):
     d = H * hs
     max_pages = (ctx + page - 1) // page
     n_pages = batch * max_pages + 2
-    kv = torch.randn(2, n_pages, page, d, generator=g).to(dtype).to(DEV)
+    kv = torch.randn(2, n_pages, H, page, hs, generator=g).to(dtype).to(DEV)  # head-major pages
     q = torch.randn(batch, d, generator=g).to(dtype).to(DEV)
     table = torch.randperm(n_pages, generator=g)[: batch * max_pages].view(batch, max_pages).int().to(DEV)
     return q, kv, table
