@@ -33,7 +33,7 @@ EXPORTS = (
     "b200_gemm", "b200_rmsnorm", "b200_attention", "b200_comm_unique_id", "b200_comm_init_rank",
     "b200_comm_destroy", "b200_launch_count", "b200_profile_enable", "b200_profile_read",
     "b200_attention_decode_scratch_bytes", "b200_attention_decode", "b200_attention_decode_static",
-    "b200_attention_backward", "b200_comm_peer_memory",
+    "b200_attention_backward", "b200_comm_peer_memory", "b200_selftest_bounded_wait",
 )
 
 
@@ -92,6 +92,7 @@ def lib() -> ctypes.CDLL:
         l.b200_attention_decode.argtypes = [c_void_p] * 5 + [c_size_t] + [c_int32] * 10 + [c_void_p]
         l.b200_attention_decode_static.argtypes = [c_void_p] * 4 + [c_int32] * 10 + [c_void_p]
         l.b200_attention_backward.argtypes = [c_void_p] * 10 + [c_int32] * 9 + [c_void_p]
+        l.b200_selftest_bounded_wait.argtypes = [ctypes.c_int64, c_void_p, c_void_p]
         l.b200_device_status.argtypes = [c_void_p, POINTER(c_uint32)]
         l.b200_comm_unique_id.argtypes = [c_void_p]
         l.b200_comm_init_rank.argtypes = [c_void_p, c_int32, c_int32, POINTER(c_void_p)]

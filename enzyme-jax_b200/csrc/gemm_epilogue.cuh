@@ -175,6 +175,7 @@ int32_t launch_gemm_tc(const GemmArgs& g, cudaStream_t stream);
 // Picks the tensor-core kernel when it covers the problem, else FFMA.
 int32_t launch_gemm(const GemmArgs& g, int impl, cudaStream_t stream);
 bool gemm_tc_supports(const GemmArgs& g);
+int32_t launch_bounded_wait_selftest(long long budget_cycles, uint32_t* reached_end, cudaStream_t stream);
 // CTA-pair (cta_group::2) variant for large K-major problems
 int32_t launch_gemm_tc2(const GemmArgs& g, cudaStream_t stream);
 bool gemm_tc2_supports(const GemmArgs& g);

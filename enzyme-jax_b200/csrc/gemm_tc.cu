@@ -414,6 +414,33 @@ int32_t launch_kind(const GemmArgs& g, cudaStream_t stream) {
 
 }  // namespace
 
+// Self-test of the bounded-wait path: one CTA waits on an mbarrier that nothing
+// ever arrives on, with a budget of `budget_cycles`; the wait must give up,
+// record ST_SELFTEST_TIMEOUT in the status word and let the kernel return.
+namespace {
+enum : uint32_t { ST_SELFTEST_TIMEOUT = 1u << 15 };
+__global__ void bounded_wait_selftest_kernel(long long budget_cycles, uint32_t* status, uint32_t* reached_end) {
+  __shared__ uint64_t bar;
+  __shared__ uint32_t abort_flag;
+  if (threadIdx.x == 0) {
+    ptx::mbar_init(&bar, 1);
+    abort_flag = 0u;
+    ptx::fence_barrier_init();
+  }
+  __syncthreads();
+  // every thread waits; the first to run out raises the CTA-wide abort flag, which releases the others
+  const bool ok = ptx::mbar_wait(&bar, 0, &abort_flag, status, ST_SELFTEST_TIMEOUT, budget_cycles);
+  __syncthreads();
+  if (threadIdx.x == 0) *reached_end = ok ? 2u : 1u;
+}
+}  // namespace
+
+int32_t launch_bounded_wait_selftest(long long budget_cycles, uint32_t* reached_end, cudaStream_t stream) {
+  bounded_wait_selftest_kernel<<<1, 64, 0, stream>>>(budget_cycles, device_status_word(), reached_end);
+  B200_LAUNCH_OK("bounded_wait_selftest_kernel");
+  return B200_OK;
+}
+
 bool gemm_tc_supports(const GemmArgs& g) {
   if ((g.ta || g.tb) && g.kind != EPI_STORE) return false;
   // TMA needs 16-byte aligned bases and row pitches; the extent of the

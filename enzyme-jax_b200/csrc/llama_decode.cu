@@ -235,4 +235,10 @@ int32_t b200_attention_backward(const void* q, const void* k, const void* v, con
   return launch_attn_bwd(a, impl, reinterpret_cast<cudaStream_t>(stream));
 }
 
+int32_t b200_selftest_bounded_wait(int64_t budget_cycles, uint32_t* reached_end_device, b200_stream_t stream) {
+  if (!reached_end_device) return fail(B200_ERR_INVALID_ARG, "null argument");
+  if (budget_cycles <= 0 || budget_cycles > 4000000000LL) return fail(B200_ERR_INVALID_ARG, "budget out of range");
+  return launch_bounded_wait_selftest(budget_cycles, reached_end_device, reinterpret_cast<cudaStream_t>(stream));
+}
+
 }  // extern "C"

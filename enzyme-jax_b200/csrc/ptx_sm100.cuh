@@ -52,14 +52,14 @@ constexpr long long kWaitBudgetCycles = 4000000000LL;
 // polled so that one failed wait releases every other waiter of the CTA.
 // Returns false when the wait ran out or the CTA is aborting.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag,
-                                          uint32_t* status, uint32_t code) {
+                                          uint32_t* status, uint32_t code, long long budget = kWaitBudgetCycles) {
   if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
   for (;;) {
     for (int i = 0; i < 64; ++i)
       if (mbar_try_wait(bar, parity)) return true;
     if (*abort_flag) return false;
-    if (clock64() - t0 > kWaitBudgetCycles) {
+    if (clock64() - t0 > budget) {
       *abort_flag = 1u;
       if (status) atomicOr(status, code);
       return false;

@@ -103,6 +103,14 @@ B200_API const char* b200_version(void);
  * B200_OK or B200_ERR_TIMEOUT; *code receives the raw word. */
 B200_API int32_t b200_device_status(b200_stream_t stream, uint32_t* code);
 
+/* Failure-detection self-test: launches one CTA that waits, with a budget of budget_cycles SM
+ * clocks, on an mbarrier nothing ever signals.  The wait gives up, the kernel writes 1 to
+ * *reached_end_device and returns, and the next b200_device_status call answers
+ * B200_ERR_TIMEOUT; the context stays usable.  This is the host-visible form of the bounded
+ * waits every tcgen05 kernel of the library uses (the reference has no counterpart: its
+ * failures surface as XLA errors, xla_ffi/cuda/throw_error.cc:20-35). */
+B200_API int32_t b200_selftest_bounded_wait(int64_t budget_cycles, uint32_t* reached_end_device, b200_stream_t stream);
+
 /* Number of kernels this library has launched in this process. */
 B200_API int64_t b200_launch_count(void);
 

@@ -63,3 +63,18 @@ def test_python_surface_has_the_reference_names():
             fn()
     with pytest.raises(NotImplementedError):
         EJ.enzyme_jax_ir()(lambda x: x)
+
+
+def test_harness_csv_format_matches_reference(tmp_path, monkeypatch):
+    """Header and row layout of test/test_utils.py:589-614, without a GPU."""
+    import csv
+    from enzyme_ad.jax.harness import CSV_HEADER, Llama
+    h = Llama()
+    assert h.repeat == 50
+    h.pretty_print_table("llama", "B200", "gpu", "Primal", 0.00125)
+    monkeypatch.setenv("TEST_UNDECLARED_OUTPUTS_DIR", str(tmp_path))
+    path = h.write_results_csv()
+    rows = list(csv.reader(open(path)))
+    assert path.endswith("results_Llama.csv")
+    assert rows[0] == ["Benchmark Name", "Pass Pipeline", "Backend", "Key", "Time"] == CSV_HEADER
+    assert rows[1] == ["llama", "B200", "gpu", "Primal", "0.00125"]

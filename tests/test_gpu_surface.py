@@ -55,3 +55,31 @@ def test_vjp_helper_and_unsupported_entries():
         EJ.cpp_call()
     with pytest.raises(NotImplementedError):
         EJ.enzyme_jax_ir(pipeline_options=EJ.JaXPipeline("inline"))(lambda x: x)
+
+
+def test_harness_rows_and_csv(tmp_path, monkeypatch):
+    """The reference-format timing harness: Primal and the three reverse keys, 5-column CSV named after the class."""
+    import csv
+    import enzyme_ad.jax as EJ
+    from enzyme_ad.jax.harness import CSV_HEADER, Llama
+    cfg = dict(dim=128, hidden_dim=256, n_layers=2, n_heads=4, n_kv_heads=4, vocab_size=512, seq_len=64)
+    w = {k: v.cuda() for k, v in O.make_weights(cfg, 7, torch.bfloat16, std=0.1, gains_one=False).items()}
+    tokens = O.make_tokens(cfg, 2, 32, 9)
+    dl = torch.randn(2, 32, cfg["vocab_size"], generator=torch.Generator().manual_seed(1))
+
+    @EJ.enzyme_jax_ir(pipeline_options=EJ.B200Pipeline(cfg, torch.bfloat16))
+    def model(tokens, weights):
+        raise AssertionError
+
+    h = Llama(repeat=5, warmup=1)
+    times = h.harness("llama", model, (tokens, w), dl)
+    assert list(times) == ["Primal", "PreRev", "PostRev", "BothRev"]
+    assert all(0 < t < 1 for t in times.values())
+    assert times["BothRev"] > times["Primal"]  # reverse rows include the primal (revprimal)
+    monkeypatch.setenv("TEST_UNDECLARED_OUTPUTS_DIR", str(tmp_path))
+    path = h.write_results_csv()
+    assert os.path.basename(path) == "results_Llama.csv"
+    rows = list(csv.reader(open(path)))
+    assert rows[0] == CSV_HEADER and len(rows) == 5
+    assert [r[3] for r in rows[1:]] == ["Primal", "PreRev", "PostRev", "BothRev"]
+    assert all(r[:3] == ["llama", "B200", "gpu"] and float(r[4]) > 0 for r in rows[1:])
