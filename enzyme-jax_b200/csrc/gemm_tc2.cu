@@ -17,6 +17,7 @@
 
 #include "gemm_epilogue.cuh"
 #include "ptx_sm100.cuh"
+#include "plan.cuh"
 #include "tensor_map.cuh"
 
 namespace b200 {
@@ -27,13 +28,20 @@ constexpr int PM = 128;   // rows per CTA (256 per pair)
 constexpr int PK = 64;    // K elements per stage
 constexpr int P_THREADS = 192;
 
-template <int BN> struct PairCfg {
+template <int BN, int KIND> struct PairCfg {
   static constexpr int kABytes = PM * PK * 2;
   static constexpr int kBBytes = (BN / 2) * PK * 2;
   static constexpr int kStageBytes = kABytes + kBBytes;
-  static constexpr int kStages = (200 * 1024) / kStageBytes > 8 ? 8 : (200 * 1024) / kStageBytes;
-  static constexpr int kTmemCols = 2 * BN;
-  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 + 256;
+  // staging buffers of the four epilogue warps: 32 rows x 128 bytes (x 64 bytes for SwiGLU, which has up to
+  // three output matrices); two in flight per output, four for the residual add (they also receive its read side)
+  static constexpr int kBufBytes = KIND == EPI_SWIGLU ? 2048 : 4096;
+  static constexpr int kBufs = KIND == EPI_SWIGLU ? 6 : (KIND == EPI_RESID ? 4 : 2);
+  static constexpr int kStagingBytes = 4 * kBufs * kBufBytes;
+  static constexpr int kBudget = 227 * 1024 - 2048 - kStagingBytes;  // 1 KB alignment slack, 1 KB barriers
+  static constexpr int kStages = kBudget / kStageBytes > 8 ? 8 : kBudget / kStageBytes;
+  static constexpr int kAccStride = BN == 192 ? 256 : BN;  // TMEM columns between the two accumulators
+  static constexpr int kTmemCols = 2 * kAccStride;         // a power of two, as the allocator wants
+  static constexpr int kSmemBytes = kStages * kStageBytes + kStagingBytes + 2048;
 };
 
 enum : uint32_t { ST_PAIR_PRODUCER = 1u << 8, ST_PAIR_MMA = 1u << 9, ST_PAIR_EPILOGUE = 1u << 10 };
@@ -85,18 +93,21 @@ __device__ __forceinline__ void mma_pair_commit(uint64_t* bar) {
 
 template <int BN, int KIND, typename TOut>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(P_THREADS, 1)
-    gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, int M, int N,
+    gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                    const __grid_constant__ CUtensorMap tmO, const __grid_constant__ CUtensorMap tmR,
+                    const __grid_constant__ CUtensorMap tmG, const __grid_constant__ CUtensorMap tmU, int M, int N,
                     int K, EpiParams ep, uint32_t* status) {
-  using Cfg = PairCfg<BN>;
+  using Cfg = PairCfg<BN, KIND>;
   constexpr int S = Cfg::kStages;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + S * Cfg::kStageBytes);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + S * Cfg::kStageBytes + Cfg::kStagingBytes);
   uint64_t* full_bar = bars;               // [S]  leader's: bytes of both CTAs landed
   uint64_t* empty_bar = bars + S;          // [S]  own: the pair's MMAs are done with the stage
   uint64_t* acc_full = bars + 2 * S;       // [2]  own: accumulator complete
   uint64_t* acc_empty = bars + 2 * S + 2;  // [2]  leader's: both CTAs' epilogues drained the accumulator
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * S + 4);
+  uint64_t* resid_bar = bars + 2 * S + 4;  // [4 warps][4]  own: a residual chunk has landed in its staging buffer
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * S + 4 + 16);
   volatile uint32_t* abort_flag = tmem_slot + 1;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -116,10 +127,12 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(P_THREADS, 1)
       ptx::mbar_init(&acc_full[i], 1);
       ptx::mbar_init(&acc_empty[i], 8);  // 4 epilogue warps of each CTA
     }
+    for (int i = 0; i < 16; ++i) ptx::mbar_init(&resid_bar[i], 1);
     *abort_flag = 0u;
     ptx::fence_barrier_init();
     ptx::tma_prefetch_desc(&tmA);
     ptx::tma_prefetch_desc(&tmB);
+    ptx::tma_prefetch_desc(&tmO);
   }
   if (warp == 1) {
     asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(ptx::smem_u32(tmem_slot)),
@@ -168,7 +181,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(P_THREADS, 1)
         ok = ptx::mbar_wait(&acc_empty[acc], acc_phase ^ 1u, abort_flag, status, ST_PAIR_MMA);
         if (!ok) break;
         ptx::tc_fence_after_sync();
-        const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
+        const uint32_t d_tmem = tmem_base + (uint32_t)(acc * Cfg::kAccStride);
         for (int kb = 0; kb < num_kb; ++kb) {
           ok = ptx::mbar_wait(&full_bar[stage], phase, abort_flag, status, ST_PAIR_MMA);
           if (!ok) break;
@@ -191,7 +204,19 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(P_THREADS, 1)
     }
     __syncwarp();
   } else {
+    // ---- epilogue warps: TMEM -> registers -> swizzled shared-memory tile -> TMA store ----
+    // A warp owns 32 rows (its TMEM lane quarter) of the CTA's accumulator; lane = row.  Writing whole
+    // rows from registers would put every lane of a store on a different cache line, which the
+    // load/store unit serialises; the bulk store writes full lines and runs beside the next chunk.
     const int q = warp & 3;
+    constexpr int NBUF = Cfg::kBufs, BUFB = Cfg::kBufBytes;
+    uint8_t* stg_ptr = smem + S * Cfg::kStageBytes + (warp - 2) * NBUF * BUFB;  // this warp's staging buffers
+    const uint32_t stg = ptx::smem_u32(stg_ptr);
+    uint64_t* rbar = resid_bar + (warp - 2) * 4;  // EPI_RESID: one barrier per staging buffer
+    uint32_t rphase = 0;                          // bit b: parity the next wait on rbar[b] uses
+    int ring = 0;                                 // staging buffers are used round-robin
+    const uint32_t sw128 = (uint32_t)(lane & 7) << 4;
+    const uint32_t row128 = stg + (uint32_t)lane * 128u;
     int acc = 0;
     uint32_t acc_phase = 0;
     bool ok = true;
@@ -200,25 +225,12 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(P_THREADS, 1)
       tile_coords(tile, m_tiles, n_tiles, 8, mt, nt);
       const int m0 = mt * (2 * PM) + (int)rank * PM;
       const int n0 = nt * BN;
-      const int m = m0 + q * 32 + lane;
-      const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN);
-      const bool row_ok = m < M;
-      const EpiRow erow = epi_row_begin<KIND>(ep, row_ok ? m : 0);
-      // operands of the epilogue are fetched before the accumulator wait (see the single-CTA kernel)
-      constexpr int PRE = (KIND == EPI_RESID) ? (BN < 128 ? BN : 128) : 8;
-      float rpre[PRE];
+      const int mrow0 = m0 + q * 32;  // first row of this warp's boxes; rows past M are clipped by the store
+      const int m = mrow0 + lane;
+      const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * Cfg::kAccStride);
+      const EpiRow erow = epi_row_begin<KIND>(ep, m < M ? m : 0);
       float rc[32], rs[32];
-      const bool rope64 = KIND == EPI_ROPE && ep.head_size == 64 && (BN % 64 == 0);
-      if (KIND == EPI_RESID) {
-        const float* xi = ep.resid_in + (size_t)(row_ok ? m : 0) * ep.ldo + n0;
-#pragma unroll
-        for (int c = 0; c < PRE; c += 8) {
-          float t8[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-          if (row_ok && n0 + c < N) load8_wide(xi + c, t8);
-#pragma unroll
-          for (int i = 0; i < 8; ++i) rpre[c + i] = t8[i];
-        }
-      }
+      const bool rope64 = KIND == EPI_ROPE && ep.head_size == 64;
       if (KIND == EPI_ROPE && rope64) {
 #pragma unroll
         for (int c = 0; c < 32; c += 8) {
@@ -227,6 +239,19 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(P_THREADS, 1)
           load8_wide(erow.rope_s + c, u8);
 #pragma unroll
           for (int i = 0; i < 8; ++i) { rc[c + i] = t8[i]; rs[c + i] = u8[i]; }
+        }
+      }
+      if (KIND == EPI_RESID) {
+        // the residual tile comes in by TMA too, into the buffers its sum leaves from; the first four
+        // 32-column chunks are requested before the accumulator is waited for
+        if (lane == 0) {
+          ptx::tma_store_wait_read<0>();
+#pragma unroll
+          for (int i = 0; i < (BN / 32 < 4 ? BN / 32 : 4); ++i)
+            if (n0 + 32 * i < N) {
+              ptx::mbar_arrive_expect_tx(&rbar[i], 4096u);
+              ptx::tma_load_2d(stg_ptr + i * BUFB, &tmR, n0 + 32 * i, mrow0, &rbar[i]);
+            }
         }
       }
       ok = ptx::mbar_wait_warp(&acc_full[acc], acc_phase, abort_flag, status, ST_PAIR_EPILOGUE);
@@ -241,48 +266,172 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(P_THREADS, 1)
         if (c + 32 < BN) {
           ptx::tmem_ld16(taddr + (uint32_t)(c + 32), nxt[0]);
           ptx::tmem_ld16(taddr + (uint32_t)(c + 48), nxt[1]);
+        } else {
+          // the accumulator is in registers: hand it back to the MMA warp before the last chunk is stored
+          ptx::tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) mbar_arrive_remote(map_to_cta(ptx::smem_u32(&acc_empty[acc]), 0));
         }
-        if (row_ok) {
+        if (n0 + c < N) {
+          if constexpr (KIND == EPI_STORE || KIND == EPI_ROPE) {
+            if constexpr (KIND == EPI_ROPE) {
 #pragma unroll
-          for (int hlf = 0; hlf < 2; ++hlf) {
-            const int cc = c + 16 * hlf;
-            if (n0 + cc < N) {
-              if (KIND == EPI_RESID && cc < PRE) {
-                float* xo = reinterpret_cast<float*>(ep.out) + (size_t)m * ep.ldo + n0 + cc;
-                float lo[8], hi[8];
-#pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                  lo[i] = rpre[(cc % PRE) + i] + cur[hlf][i];
-                  hi[i] = rpre[(cc % PRE) + 8 + i] + cur[hlf][8 + i];
-                }
-                store8_wide(xo, lo);
-                store8_wide(xo + 8, hi);
-              } else if (KIND == EPI_ROPE && rope64) {
+              for (int hlf = 0; hlf < 2; ++hlf) {
+                const int cc = c + 16 * hlf;
                 if (n0 + cc < ep.rope_cols) {
-                  const int j0 = (cc % 64) >> 1;
+                  const int j0 = ((n0 + cc) % ep.head_size) >> 1;
+                  if (rope64) {
+                    const int jj = (cc % 64) >> 1;  // n0 is a multiple of 64
 #pragma unroll
-                  for (int i = 0; i < 8; ++i) {
-                    const float e = cur[hlf][2 * i], o = cur[hlf][2 * i + 1];
-                    cur[hlf][2 * i] = rc[j0 + i] * e - rs[j0 + i] * o;
-                    cur[hlf][2 * i + 1] = rs[j0 + i] * e + rc[j0 + i] * o;
+                    for (int i = 0; i < 8; ++i) {
+                      const float e = cur[hlf][2 * i], o = cur[hlf][2 * i + 1];
+                      cur[hlf][2 * i] = rc[jj + i] * e - rs[jj + i] * o;
+                      cur[hlf][2 * i + 1] = rs[jj + i] * e + rc[jj + i] * o;
+                    }
+                  } else {
+                    float cs[8], sn[8];
+                    load8(erow.rope_c + j0, cs);
+                    load8(erow.rope_s + j0, sn);
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                      const float e = cur[hlf][2 * i], o = cur[hlf][2 * i + 1];
+                      cur[hlf][2 * i] = cs[i] * e - sn[i] * o;
+                      cur[hlf][2 * i + 1] = sn[i] * e + cs[i] * o;
+                    }
                   }
                 }
-                store16(reinterpret_cast<TOut*>(ep.out) + (size_t)m * ep.ldo + n0 + cc, cur[hlf]);
-              } else {
-                epi_apply16<KIND, TOut>(ep, erow, m, n0 + cc, cur[hlf]);
               }
+            }
+            if constexpr (sizeof(TOut) == 4) {
+              // one 32-column fp32 box per chunk
+              const uint32_t buf = row128 + (uint32_t)((ring % NBUF) * BUFB);
+              if (lane == 0) ptx::tma_store_wait_read<NBUF - 1>();
+              __syncwarp();
+#pragma unroll
+              for (int j = 0; j < 8; ++j)
+                ptx::st_shared_v4(buf + (((uint32_t)j << 4) ^ sw128), __float_as_uint(cur[j >> 2][(j & 3) * 4 + 0]),
+                                  __float_as_uint(cur[j >> 2][(j & 3) * 4 + 1]),
+                                  __float_as_uint(cur[j >> 2][(j & 3) * 4 + 2]),
+                                  __float_as_uint(cur[j >> 2][(j & 3) * 4 + 3]));
+              ptx::fence_proxy_async();
+              __syncwarp();
+              if (lane == 0) {
+                ptx::tma_store_2d(&tmO, stg + (uint32_t)((ring % NBUF) * BUFB), n0 + c, mrow0);
+                ptx::tma_store_commit();
+              }
+              ++ring;
+            } else {
+              // one 64-column bf16 box per two chunks
+              const int half = (c >> 5) & 1;
+              const uint32_t buf = row128 + (uint32_t)((ring % NBUF) * BUFB);
+              if (half == 0) {
+                if (lane == 0) ptx::tma_store_wait_read<NBUF - 1>();
+                __syncwarp();
+              }
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                uint32_t r[4];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                  __nv_bfloat162 h2 = __floats2bfloat162_rn(cur[j >> 1][(j & 1) * 8 + 2 * i], cur[j >> 1][(j & 1) * 8 + 2 * i + 1]);
+                  r[i] = *reinterpret_cast<uint32_t*>(&h2);
+                }
+                ptx::st_shared_v4(buf + (((uint32_t)(half * 4 + j) << 4) ^ sw128), r[0], r[1], r[2], r[3]);
+              }
+              if (half == 1) {
+                ptx::fence_proxy_async();
+                __syncwarp();
+                if (lane == 0) {
+                  ptx::tma_store_2d(&tmO, stg + (uint32_t)((ring % NBUF) * BUFB), n0 + c - 32, mrow0);
+                  ptx::tma_store_commit();
+                }
+                ++ring;
+              }
+            }
+          } else if constexpr (KIND == EPI_RESID) {
+            const int i = c >> 5, b = i & 3;
+            ok = ptx::mbar_wait_warp(&rbar[b], (rphase >> b) & 1u, abort_flag, status, ST_PAIR_EPILOGUE);
+            if (!ok) break;
+            rphase ^= 1u << b;
+            const uint32_t buf = row128 + (uint32_t)(b * BUFB);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              const uint32_t a = buf + (((uint32_t)j << 4) ^ sw128);
+              uint32_t x0, x1, x2, x3;
+              ptx::ld_shared_v4(a, x0, x1, x2, x3);
+              ptx::st_shared_v4(a, __float_as_uint(__uint_as_float(x0) + cur[j >> 2][(j & 3) * 4 + 0]),
+                                __float_as_uint(__uint_as_float(x1) + cur[j >> 2][(j & 3) * 4 + 1]),
+                                __float_as_uint(__uint_as_float(x2) + cur[j >> 2][(j & 3) * 4 + 2]),
+                                __float_as_uint(__uint_as_float(x3) + cur[j >> 2][(j & 3) * 4 + 3]));
+            }
+            ptx::fence_proxy_async();
+            __syncwarp();
+            if (lane == 0) {
+              ptx::tma_store_2d(&tmO, stg + (uint32_t)(b * BUFB), n0 + c, mrow0);
+              ptx::tma_store_commit();
+              // chunk i+3 goes where chunk i-1 left from, once that store has read its tile
+              if (i >= 1 && i + 3 < BN / 32 && n0 + 32 * (i + 3) < N) {
+                ptx::tma_store_wait_read<1>();
+                const int nb = (i + 3) & 3;
+                ptx::mbar_arrive_expect_tx(&rbar[nb], 4096u);
+                ptx::tma_load_2d(stg_ptr + nb * BUFB, &tmR, n0 + 32 * (i + 3), mrow0, &rbar[nb]);
+              }
+            }
+          } else {  // EPI_SWIGLU: 64 accumulator columns = 32 outputs = one 64-byte-wide box per output matrix
+            const int half = (c >> 5) & 1;
+            const bool has_gu = ep.out_gate != nullptr;
+            const int set = ring & 1;
+            const uint32_t base = stg + (uint32_t)(set * 3 * BUFB);
+            const uint32_t row64 = base + (uint32_t)lane * 64u;
+            const uint32_t sw64 = (uint32_t)((lane >> 1) & 3) << 4;
+            if (half == 0) {
+              if (lane == 0) ptx::tma_store_wait_read<1>();
+              __syncwarp();
+            }
+#pragma unroll
+            for (int grp = 0; grp < 2; ++grp) {
+              uint32_t hr[4], gr[4], ur[4];
+#pragma unroll
+              for (int i2 = 0; i2 < 4; ++i2) {
+                const float g0 = cur[grp][2 * i2], g1 = cur[grp][2 * i2 + 1];
+                const float u0 = cur[grp][8 + 2 * i2], u1 = cur[grp][8 + 2 * i2 + 1];
+                __nv_bfloat162 hh = __floats2bfloat162_rn(g0 / (1.f + __expf(-g0)) * u0, g1 / (1.f + __expf(-g1)) * u1);
+                __nv_bfloat162 gg = __floats2bfloat162_rn(g0, g1);
+                __nv_bfloat162 uu = __floats2bfloat162_rn(u0, u1);
+                hr[i2] = *reinterpret_cast<uint32_t*>(&hh);
+                gr[i2] = *reinterpret_cast<uint32_t*>(&gg);
+                ur[i2] = *reinterpret_cast<uint32_t*>(&uu);
+              }
+              const uint32_t off = ((uint32_t)(half * 2 + grp) << 4) ^ sw64;
+              ptx::st_shared_v4(row64 + off, hr[0], hr[1], hr[2], hr[3]);
+              if (has_gu) {
+                ptx::st_shared_v4(row64 + (uint32_t)BUFB + off, gr[0], gr[1], gr[2], gr[3]);
+                ptx::st_shared_v4(row64 + (uint32_t)(2 * BUFB) + off, ur[0], ur[1], ur[2], ur[3]);
+              }
+            }
+            if (half == 1) {
+              ptx::fence_proxy_async();
+              __syncwarp();
+              if (lane == 0) {
+                const int x = (n0 + c - 32) >> 1;
+                ptx::tma_store_2d(&tmO, base, x, mrow0);
+                if (has_gu) {
+                  ptx::tma_store_2d(&tmG, base + (uint32_t)BUFB, x, mrow0);
+                  ptx::tma_store_2d(&tmU, base + (uint32_t)(2 * BUFB), x, mrow0);
+                }
+                ptx::tma_store_commit();
+              }
+              ++ring;
             }
           }
         }
 #pragma unroll
         for (int i = 0; i < 16; ++i) { cur[0][i] = nxt[0][i]; cur[1][i] = nxt[1][i]; }
       }
-      ptx::tc_fence_before_sync();
-      __syncwarp();
-      if (lane == 0) mbar_arrive_remote(map_to_cta(ptx::smem_u32(&acc_empty[acc]), 0));
       acc ^= 1;
       if (acc == 0) acc_phase ^= 1u;
     }
+    if (lane == 0) ptx::tma_store_wait<0>();
   }
 
   ptx::tc_fence_before_sync();
@@ -298,12 +447,43 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(P_THREADS, 1)
   }
 }
 
+// Tile width by modelled time: rounds of the persistent grid x columns per tile.  The 128-wide tile
+// reads A and B from shared memory at the full 128 B/clk of an SM and measures about 1.5x slower per
+// column than the wider ones, so it is charged that.
+int pair_tile_width(int M, int N) {
+  const int pairs = sm_count() / 2;
+  const long mt = cdiv(M, 2 * PM);
+  long best = -1;
+  int bn = 128;
+  const int widths[3] = {256, 192, 128};
+  for (int w : widths) {
+    if (N % w) continue;
+    long cost = (long)cdiv((int)(mt * (N / w)), pairs) * w * 2;
+    if (w == 128) cost = cost * 3 / 2;
+    if (best < 0 || cost < best) { best = cost; bn = w; }
+  }
+  return bn;
+}
+
 template <int BN, int KIND, typename TOut>
 int32_t launch_pair_cfg(const GemmArgs& g, cudaStream_t stream) {
-  using Cfg = PairCfg<BN>;
-  CUtensorMap tmA, tmB;
+  using Cfg = PairCfg<BN, KIND>;
+  CUtensorMap tmA, tmB, tmO, tmR, tmG, tmU;
   B200_TRY(make_map_2d(&tmA, g.A, g.M, g.K, g.lda, PM));
   B200_TRY(make_map_2d(&tmB, g.B, g.N, g.K, g.ldb, BN / 2));
+  if (KIND == EPI_SWIGLU) {
+    B200_TRY(make_map_out(&tmO, g.epi.out, g.M, g.N / 2, g.epi.ldo, 2, 64));
+    tmG = tmU = tmO;
+    if (g.epi.out_gate) {
+      B200_TRY(make_map_out(&tmG, g.epi.out_gate, g.M, g.N / 2, g.epi.ldo, 2, 64));
+      B200_TRY(make_map_out(&tmU, g.epi.out_up, g.M, g.N / 2, g.epi.ldo, 2, 64));
+    }
+    tmR = tmO;
+  } else {
+    B200_TRY(make_map_out(&tmO, g.epi.out, g.M, g.N, g.epi.ldo, (int)sizeof(TOut), 128));
+    tmR = tmG = tmU = tmO;
+    if (KIND == EPI_RESID) B200_TRY(make_map_out(&tmR, g.epi.resid_in, g.M, g.N, g.epi.ldo, 4, 128));
+  }
   auto kern = gemm_tc2_kernel<BN, KIND, TOut>;
   static bool attr_set = false;
   if (!attr_set) {
@@ -334,20 +514,19 @@ int32_t launch_pair_cfg(const GemmArgs& g, cudaStream_t stream) {
   int pairs = max_pairs;
   if (g.max_ctas > 0 && g.max_ctas / 2 < pairs) pairs = g.max_ctas / 2;
   if (pairs > tiles) pairs = tiles;
-  kern<<<2 * pairs, P_THREADS, Cfg::kSmemBytes, stream>>>(tmA, tmB, g.M, g.N, g.K, g.epi, device_status_word());
+  kern<<<2 * pairs, P_THREADS, Cfg::kSmemBytes, stream>>>(tmA, tmB, tmO, tmR, tmG, tmU, g.M, g.N, g.K, g.epi,
+                                                          device_status_word());
   B200_LAUNCH_OK("gemm_tc2_kernel");
   return B200_OK;
 }
 
 template <int KIND, typename TOut>
 int32_t launch_pair_bn(const GemmArgs& g, cudaStream_t stream) {
-  // rounds of the persistent grid times the tile width: prefer the wide tile unless it wastes a round
-  const int pairs = sm_count() / 2;
-  const long mt = cdiv(g.M, 2 * PM);
-  const long cost256 = g.N % 256 == 0 ? (long)cdiv((int)(mt * (g.N / 256)), pairs) * 256 : -1;
-  const long cost128 = (long)cdiv((int)(mt * cdiv(g.N, 128)), pairs) * 128;
-  if (cost256 >= 0 && cost256 * 10 <= cost128 * 12) return  // the wide tile moves fewer bytes per flop: keep it unless it wastes > 20 % (a 40 % margin measured slower in the 110M step)
-    launch_pair_cfg<256, KIND, TOut>(g, stream);
+  static const int forced = env_int("B200_PAIR_BN", 0);  // tuning knob: 128, 192 or 256 overrides the choice below
+  int bn = pair_tile_width(g.M, g.N);
+  if (forced == 128 || (forced == 192 && g.N % 192 == 0) || (forced == 256 && g.N % 256 == 0)) bn = forced;
+  if (bn == 256) return launch_pair_cfg<256, KIND, TOut>(g, stream);
+  if (bn == 192) return launch_pair_cfg<192, KIND, TOut>(g, stream);
   return launch_pair_cfg<128, KIND, TOut>(g, stream);
 }
 
@@ -368,7 +547,14 @@ int32_t launch_pair_kind(const GemmArgs& g, cudaStream_t stream) {
 bool gemm_tc2_supports(const GemmArgs& g) {
   if (!gemm_tc_supports(g) || g.ta || g.tb) return false;
   if (g.N % 128) return false;
-  const long tiles = (long)cdiv(g.M, 2 * PM) * cdiv(g.N, g.N % 256 == 0 ? 256 : 128);
+  // the staged epilogue writes whole tiles through TMA: no read-modify-write, 16-byte aligned rows
+  if (g.kind == EPI_STORE && g.epi.accumulate) return false;
+  if (g.kind == EPI_RESID && (g.out_dtype != B200_F32 || !g.epi.resid_in || !aligned16(g.epi.resid_in))) return false;
+  if (g.kind == EPI_SWIGLU && g.out_dtype != B200_BF16) return false;
+  const int oes = g.out_dtype == B200_F32 ? 4 : 2;
+  if (!aligned16(g.epi.out) || ((size_t)g.epi.ldo * oes) % 16) return false;
+  if (g.kind == EPI_SWIGLU && g.epi.out_gate && (!aligned16(g.epi.out_gate) || !aligned16(g.epi.out_up))) return false;
+  const long tiles = (long)cdiv(g.M, 2 * PM) * (g.N / pair_tile_width(g.M, g.N));
   return g.M >= 2 * PM && tiles >= sm_count() / 2;
 }
 

@@ -42,6 +42,23 @@ inline int32_t make_map_2d(CUtensorMap* map, const void* base, int rows, int col
   return B200_OK;
 }
 
+// Output tile map of the staged GEMM epilogues: row-major [rows, cols] of 2- or 4-byte elements with row pitch ld
+// elements; box = box_bytes (128 or 64) of one row x 32 rows, swizzled by the box width.
+inline int32_t make_map_out(CUtensorMap* map, const void* base, int rows, int cols, int ld, int esize, int box_bytes) {
+  EncodeTiledFn fn = tensor_map_encoder();
+  if (!fn) return fail(B200_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)ld * (cuuint64_t)esize};
+  cuuint32_t box[2] = {(cuuint32_t)(box_bytes / esize), 32u};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, esize == 4 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
+                  const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  box_bytes == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B,
+                  CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(B200_ERR_CUDA, "cuTensorMapEncodeTiled (output tile) failed with %d", (int)r);
+  return B200_OK;
+}
+
 // 3-D bf16 [batch][seq][cols] with row pitch ld; box = 64 columns x 128 rows of one sequence, so that rows past
 // the end of a sequence read as zero.
 inline int32_t make_map_3d(CUtensorMap* map, const void* base, int batch, int seq, int cols, int ld) {

@@ -23,7 +23,9 @@ def _ints(shape, seed, lo=-2, hi=3, dtype=torch.bfloat16):
 @pytest.mark.parametrize("M,N,K", [(128, 128, 64), (128, 256, 128), (256, 512, 768), (384, 768, 2048),
                                    (100, 96, 72), (8192, 2304, 768), (64, 4096, 1024), (1, 32, 8),
                                    # large enough for the CTA-pair kernel (256-row tiles), with M and K tails
-                                   (4096, 768, 2048), (8192, 1024, 256), (5000, 1536, 704), (8192, 32000, 64)])
+                                   (4096, 768, 2048), (8192, 1024, 256), (5000, 1536, 704), (8192, 32000, 64),
+                                   # 192-column pair tiles (N = 768, 1152), with an M tail
+                                   (8192, 768, 512), (8000, 1152, 192)])
 def test_gemm_bf16_exact_on_small_integers(impl, M, N, K):
     # integer operands in [-2,2]: every product and partial sum is exact in fp32
     a, b = _ints((M, K), 1), _ints((N, K), 2)
@@ -31,6 +33,15 @@ def test_gemm_bf16_exact_on_small_integers(impl, M, N, K):
     ref = a.float() @ b.float().T
     assert B.device_status() == 0
     assert torch.equal(y, ref)
+
+
+@pytest.mark.parametrize("M,N", [(8192, 768), (8192, 1024), (8000, 1152), (8192, 640)])
+def test_pair_gemm_bf16_output_exact(M, N):
+    # K = 64 and operands in [-2,2]: |sums| <= 256, exact in bf16, so the staged bf16 store path is checked bit for bit
+    a, b = _ints((M, 64), 3), _ints((N, 64), 4)
+    y = B.gemm(a, b, out_dtype=torch.bfloat16, impl=1)
+    assert B.device_status() == 0
+    assert torch.equal(y.float(), a.float() @ b.float().T)
 
 
 @pytest.mark.parametrize("impl", [1, 2])
