@@ -371,6 +371,24 @@ class Plan:
             self.forward(tokens, logits=logits)
         return graph
 
+    def capture_prefill_step(self, host_tokens: torch.Tensor, tokens: torch.Tensor, logits: torch.Tensor,
+                             last_logits: torch.Tensor, host_last_logits: torch.Tensor) -> "torch.cuda.CUDAGraph":
+        """One serving step as a single CUDA graph: upload `host_tokens` (pinned) into `tokens`, run the forward,
+        gather the last-position logits of every sequence into `last_logits` and copy them to
+        `host_last_logits` (pinned).  Copies inside the graph keep consecutive replays back to back; separate
+        copy calls between replays cost more than the copies themselves."""
+        if not (host_tokens.is_pinned() and host_last_logits.is_pinned()):
+            raise B200Error(1, "host buffers of a captured step must be pinned")
+        self.forward(tokens, logits=logits)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            tokens.copy_(host_tokens, non_blocking=True)
+            self.forward(tokens, logits=logits)
+            last_logits.copy_(logits[:, -1, :])
+            host_last_logits.copy_(last_logits, non_blocking=True)
+        return graph
+
     def new_saved(self, batch: int, seq: int) -> torch.Tensor:
         return torch.empty(self.saved_bytes(batch, seq), dtype=torch.uint8, device=self.device)
 

@@ -194,3 +194,34 @@ def test_bad_calls_return_status_codes():
     st = B.lib().b200_forward(p._h, tok.data_ptr(), 1, 8, p.packed.data_ptr(), logits.data_ptr(), None, None,
                               ws.data_ptr(), ws.numel(), None)
     assert st == 5  # workspace too small, nothing launched
+
+
+def test_captured_graphs_replay_the_eager_forward():
+    """capture_forward / capture_prefill_step: a replay gives the eager result bit for bit, and the captured
+    step moves its tokens up from and its last-position logits down to pinned host memory."""
+    cfg = SMALL
+    w = O.make_weights(cfg, 5, torch.float32, std=0.1, gains_one=False)
+    p = _plan(cfg, w, torch.bfloat16)
+    t1, t2 = O.make_tokens(cfg, 4, 64, 1).int(), O.make_tokens(cfg, 4, 64, 2).int()
+    eager1, eager2 = p.forward(t1.to(DEV)).clone(), p.forward(t2.to(DEV)).clone()
+    tok = t1.to(DEV)
+    logits = torch.empty_like(eager1)
+    g = p.capture_forward(tok, logits)
+    logits.zero_()
+    g.replay()
+    assert torch.equal(logits, eager1)
+    host_tok = t2.clone().pin_memory()
+    last, host_last = torch.empty(4, cfg["vocab_size"], device=DEV), torch.empty(4, cfg["vocab_size"]).pin_memory()
+    gs = p.capture_prefill_step(host_tok, tok, logits, last, host_last)
+    host_last.zero_()
+    gs.replay()
+    torch.cuda.synchronize()
+    assert torch.equal(logits, eager2)
+    assert torch.equal(host_last, eager2[:, -1, :].cpu())
+    host_tok.copy_(t1)  # the graph reads the pinned buffer at replay time
+    gs.replay()
+    torch.cuda.synchronize()
+    assert torch.equal(host_last, eager1[:, -1, :].cpu())
+    with pytest.raises(B.B200Error):
+        p.capture_prefill_step(t2, tok, logits, last, host_last)  # pageable host tokens
+    assert B.device_status() == 0
