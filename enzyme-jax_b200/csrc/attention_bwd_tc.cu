@@ -71,7 +71,9 @@ __global__ void __launch_bounds__(BW_THREADS, 1)
   volatile uint32_t* abort_flag = tmem_slot + 1;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int own = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+  // (head, batch) in x/y, the block index in z: blocks are dispatched x-fastest, so the longest loops of the
+  // whole launch start first
+  const int own = blockIdx.z, h = blockIdx.x, b = blockIdx.y;
   const int nblk = (prm.seq + 127) / 128;
   // DKV: own key block `own`, query blocks own..nblk-1.  DQ: own query block nblk-1-own (long ones first), key blocks 0..it.
   const int own_blk = MODE == MODE_DKV ? own : nblk - 1 - own;
@@ -347,7 +349,7 @@ int32_t launch_attn_bwd_tc(const AttnBwdArgs& a, cudaStream_t stream) {
   BwdParams prm;
   prm.lse = f.lse; prm.delta = a.delta; prm.seq = f.seq; prm.n_heads = f.n_heads;
   prm.scale = 1.f / sqrtf(64.f);
-  dim3 grid(cdiv(f.seq, 128), f.n_heads, f.batch);
+  dim3 grid(f.n_heads, f.batch, cdiv(f.seq, 128));
   prm.out0 = (bf16*)a.dv; prm.out1 = (bf16*)a.dk; prm.ld_out = a.lddkv;
   attn_bwd_tc_kernel<MODE_DKV><<<grid, BW_THREADS, kBwdSmem, stream>>>(tq, tk, tv, tdo, prm, device_status_word());
   B200_LAUNCH_OK("attn_bwd_tc_kernel<dkv>");

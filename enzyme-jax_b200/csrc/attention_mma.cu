@@ -72,8 +72,12 @@ __global__ void __launch_bounds__(A_THREADS, HS == 64 ? 2 : 1)
   volatile uint32_t* abort_flag = tmem_slot + 1;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int qt = (int)gridDim.x - 1 - (int)blockIdx.x;  // long tiles first
-  const int h = blockIdx.y, b = blockIdx.z;
+  pdl_launch_dependents();
+  // Blocks are dispatched x-fastest: with (head, batch) in x/y and the query tile in z, every long tile (many
+  // key blocks) of the whole launch starts before any short one, so the launch does not end on a long tile
+  // that started late.
+  const int qt = (int)gridDim.z - 1 - (int)blockIdx.z;
+  const int h = blockIdx.x, b = blockIdx.y;
   const int t0 = qt * AQ;
   const int n_blocks = qt + 1;  // key blocks 0..qt
 
@@ -109,6 +113,7 @@ __global__ void __launch_bounds__(A_THREADS, HS == 64 ? 2 : 1)
   ptx::tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
   const bool aborted = *abort_flag != 0u;
+  pdl_wait();  // q, k and v come from the previous kernel
 
   if (aborted) {
     // fall through to the common exit
@@ -339,9 +344,9 @@ int32_t launch_hs(const AttnArgs& a, cudaStream_t stream) {
     B200_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes));
     attr_set = true;
   }
-  dim3 grid(cdiv(a.seq, AQ), a.n_heads, a.batch);
-  kern<<<grid, A_THREADS, C::kSmemBytes, stream>>>(tq, tk, tv, (bf16*)a.o, a.lse, a.seq, a.n_heads, a.ldo,
-                                                   1.f / sqrtf((float)HS), device_status_word());
+  dim3 grid(a.n_heads, a.batch, cdiv(a.seq, AQ));
+  B200_CUDA_OK(launch_pdl(kern, grid, dim3(A_THREADS), C::kSmemBytes, stream, tq, tk, tv, (bf16*)a.o, a.lse, a.seq,
+                          a.n_heads, a.ldo, 1.f / sqrtf((float)HS), device_status_word()));
   B200_LAUNCH_OK("attn_fwd_tc_kernel");
   return B200_OK;
 }

@@ -52,6 +52,32 @@ struct ProfScope {
 // Device word that kernels with bounded waits OR their failure code into.
 uint32_t* device_status_word();  // lazily allocated per device, never on a hot path
 
+// ---- programmatic dependent launch -------------------------------------------
+// Kernels of the forward chain are launched so that the next kernel's CTAs may start (set up barriers,
+// allocate tensor memory, prefetch descriptors) while the last CTAs of the previous kernel drain.  Such a
+// kernel calls pdl_launch_dependents() at its start and pdl_wait() before it first touches global memory
+// that an earlier kernel wrote or still reads; pdl_wait returns once every earlier kernel has completed.
+// Both are no-ops in a kernel launched the ordinary way.  B200_PDL=0 turns the launch attribute off.
+bool pdl_enabled();
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                              Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
+}
+
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 inline int cdiv(int a, int b) { return (a + b - 1) / b; }

@@ -12,6 +12,8 @@ template <typename T>
 __global__ void embed_kernel(const int32_t* __restrict__ tokens, const T* __restrict__ table, float* __restrict__ x,
                              int dim, int vocab) {
   const int t = blockIdx.x;
+  pdl_launch_dependents();
+  pdl_wait();
   int tok = tokens[t];
   tok = tok < 0 ? 0 : (tok >= vocab ? vocab - 1 : tok);
   const T* src = table + (size_t)tok * dim;
@@ -60,6 +62,8 @@ __global__ void __launch_bounds__(256) rmsnorm_warp_kernel(const float* __restri
                                                            int dim, float eps) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int row = blockIdx.x * 8 + warp;
+  pdl_launch_dependents();
+  pdl_wait();
   if (row >= rows) return;
   const float* xr = x + (size_t)row * dim;
   float v[NCH][8];
@@ -430,9 +434,11 @@ int32_t launch_embed(const int32_t* tokens, const void* table, int table_dtype, 
   if (dim % 8) return fail(B200_ERR_BAD_SHAPE, "embedding: dim=%d must be a multiple of 8", dim);
   const int threads = dim / 8 < 128 ? ((dim / 8 + 31) / 32) * 32 : 128;
   if (table_dtype == B200_F32)
-    embed_kernel<float><<<n_tokens, threads, 0, stream>>>(tokens, (const float*)table, x, dim, vocab);
+    B200_CUDA_OK(launch_pdl(embed_kernel<float>, dim3(n_tokens), dim3(threads), 0, stream, tokens, (const float*)table,
+                            x, dim, vocab));
   else if (table_dtype == B200_BF16)
-    embed_kernel<bf16><<<n_tokens, threads, 0, stream>>>(tokens, (const bf16*)table, x, dim, vocab);
+    B200_CUDA_OK(launch_pdl(embed_kernel<bf16>, dim3(n_tokens), dim3(threads), 0, stream, tokens, (const bf16*)table,
+                            x, dim, vocab));
   else
     return fail(B200_ERR_BAD_DTYPE, "embedding: unsupported dtype %d", table_dtype);
   B200_LAUNCH_OK("embed_kernel");
@@ -449,9 +455,11 @@ int32_t launch_rmsnorm(const float* x, const float* gain, void* y, float* rinv, 
 #define B200_RN_CASE(N)                                                                                          \
   case N:                                                                                                        \
     if (out_dtype == B200_F32)                                                                                   \
-      rmsnorm_warp_kernel<float, N><<<grid, 256, 0, stream>>>(x, gain, (float*)y, rinv, rows, dim, eps);         \
+      B200_CUDA_OK(launch_pdl(rmsnorm_warp_kernel<float, N>, dim3(grid), dim3(256), 0, stream, x, gain, (float*)y, \
+                              rinv, rows, dim, eps));                                                            \
     else                                                                                                         \
-      rmsnorm_warp_kernel<bf16, N><<<grid, 256, 0, stream>>>(x, gain, (bf16*)y, rinv, rows, dim, eps);           \
+      B200_CUDA_OK(launch_pdl(rmsnorm_warp_kernel<bf16, N>, dim3(grid), dim3(256), 0, stream, x, gain, (bf16*)y,  \
+                              rinv, rows, dim, eps));                                                            \
     break;
     switch (nch) {
       B200_RN_CASE(1) B200_RN_CASE(2) B200_RN_CASE(3) B200_RN_CASE(4)

@@ -94,6 +94,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
   __syncthreads();
   ptx::tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
+  pdl_wait();  // set-up above may overlap the previous kernel's tail; operands are touched from here on
 
   if (warp == 0) {
     if (lane == 0) {
@@ -357,8 +358,8 @@ int32_t launch_cfg(const GemmArgs& g, cudaStream_t stream) {
   int limit = sm_count();
   if (g.max_ctas > 0 && g.max_ctas < limit) limit = g.max_ctas;
   const int grid = items < limit ? items : limit;
-  kern<<<grid, TC_THREADS, Cfg::kSmemBytes, stream>>>(tmA, tmB, g.M, g.N, g.K, g.epi, splits,
-                                                      reinterpret_cast<float*>(g.splitk_scratch), device_status_word());
+  B200_CUDA_OK(launch_pdl(kern, dim3(grid), dim3(TC_THREADS), Cfg::kSmemBytes, stream, tmA, tmB, g.M, g.N, g.K, g.epi,
+                          splits, reinterpret_cast<float*>(g.splitk_scratch), device_status_word()));
   B200_LAUNCH_OK("gemm_tc_kernel");
   if (splits > 1) {
     const int chunks = g.M * (g.N / 16);

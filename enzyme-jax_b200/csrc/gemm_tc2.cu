@@ -111,6 +111,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(P_THREADS, 1)
   volatile uint32_t* abort_flag = tmem_slot + 1;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  pdl_launch_dependents();
   const uint32_t rank = cluster_ctarank();
   const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
   const int m_tiles = (M + 2 * PM - 1) / (2 * PM);
@@ -145,6 +146,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(P_THREADS, 1)
   cluster_sync_all();  // both CTAs' barriers exist before anything is signalled across the pair
   ptx::tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
+  pdl_wait();  // everything above overlapped the previous kernel's tail; operands are touched from here on
 
   if (warp == 0) {
     if (lane == 0) {
@@ -514,8 +516,8 @@ int32_t launch_pair_cfg(const GemmArgs& g, cudaStream_t stream) {
   int pairs = max_pairs;
   if (g.max_ctas > 0 && g.max_ctas / 2 < pairs) pairs = g.max_ctas / 2;
   if (pairs > tiles) pairs = tiles;
-  kern<<<2 * pairs, P_THREADS, Cfg::kSmemBytes, stream>>>(tmA, tmB, tmO, tmR, tmG, tmU, g.M, g.N, g.K, g.epi,
-                                                          device_status_word());
+  B200_CUDA_OK(launch_pdl(kern, dim3(2 * pairs), dim3(P_THREADS), Cfg::kSmemBytes, stream, tmA, tmB, tmO, tmR, tmG,
+                          tmU, g.M, g.N, g.K, g.epi, device_status_word()));
   B200_LAUNCH_OK("gemm_tc2_kernel");
   return B200_OK;
 }

@@ -39,6 +39,11 @@ int env_int(const char* name, int dflt) {
   return (v && *v) ? atoi(v) : dflt;
 }
 
+bool pdl_enabled() {
+  static const bool on = env_int("B200_PDL", 1) != 0;
+  return on;
+}
+
 // ---- launch counter and event profiler -----------------------------------------
 static std::atomic<long long> g_launches{0};
 void count_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
