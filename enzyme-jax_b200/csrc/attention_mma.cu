@@ -7,12 +7,18 @@
 //   warp 0      TMA producer: Q once, then K_j / V_j into a 2-stage ring
 //   warp 1      one lane issues tcgen05.mma:  S = Q K_j^T  (fp32, TMEM columns
 //               0..127) and, once the probabilities are in shared memory,
-//               O_j = P_j V_j (TMEM columns 128..128+hs)
+//               O += P_j V_j (TMEM columns 128..128+hs, accumulated over all
+//               key blocks).  S of block j+1 is issued as soon as the softmax
+//               threads hold S of block j in registers, so it is computed
+//               beside block j's exponentials.
 //   warps 2..9  softmax, two threads per query row (64 keys each): read S from
-//               TMEM once, mask the diagonal block, running max / sum in fp32,
-//               write P as bf16 into shared memory in the swizzled K-major
-//               layout the MMA reads, then fold O_j into the fp32 output
-//               columns kept in registers
+//               TMEM once, mask the diagonal block, running reference maximum
+//               and row sum in fp32, write P as bf16 into shared memory in the
+//               swizzled K-major layout the MMA reads.  The reference maximum of
+//               a row is only raised -- and O in TMEM and the row sum rescaled --
+//               when a block's maximum exceeds it by more than 2^8; until then
+//               probabilities are taken against the older reference (they stay
+//               below 2^8; O / l at the end is exact either way).
 // V is consumed as an MN-major operand straight from its row-major layout.
 // TMEM use is 256 columns so that two CTAs share an SM and one CTA's softmax
 // overlaps the other's MMAs.  All waits are bounded.
@@ -143,34 +149,47 @@ __global__ void __launch_bounds__(A_THREADS, HS == 64 ? 2 : 1)
       constexpr uint32_t idesc_o = ptx::idesc_bf16_f32(AQ, HS) | (1u << 16);  // V is MN-major
       const uint32_t q_addr = ptx::smem_u32(smem + C::kQOff);
       const uint32_t p_addr = ptx::smem_u32(smem + C::kPOff);
-      bool ok = ptx::mbar_wait(q_full, 0, abort_flag, status, ST_ATTN_TIMEOUT);
-      for (int j = 0; j < n_blocks && ok; ++j) {
-        const int st = j & 1;
-        const uint32_t ph = (uint32_t)(j >> 1) & 1u;
-        const uint32_t jp = (uint32_t)j & 1u;
-        ok = ptx::mbar_wait(&kv_full[st], ph, abort_flag, status, ST_ATTN_TIMEOUT) &&
-             ptx::mbar_wait(s_empty, jp ^ 1u, abort_flag, status, ST_ATTN_TIMEOUT);
-        if (!ok) break;
-        ptx::tc_fence_after_sync();
-        const uint32_t k_addr = ptx::smem_u32(smem + C::kKOff + st * C::kTileBytes);
-        const uint32_t v_addr = ptx::smem_u32(smem + C::kVOff + st * C::kTileBytes);
+      // Descriptors are built once; a stage or k-step adds its byte offset >> 4 to the address field (shared
+      // memory addresses stay below 2^18, so the 14-bit field never carries): the issuing thread is a single
+      // instruction stream and two descriptor builds per MMA are most of its work otherwise.
+      const uint64_t q_desc = ptx::smem_desc_sw128(q_addr);
+      const uint64_t k_desc = ptx::smem_desc_sw128(ptx::smem_u32(smem + C::kKOff));
+      const uint64_t p_desc = ptx::smem_desc_sw128(p_addr);
+      const uint64_t v_desc = ptx::smem_desc_sw128_mn(ptx::smem_u32(smem + C::kVOff), SUB);
+      auto issue_s = [&](int st) {
+        const uint64_t ka = k_desc + (uint64_t)st * (C::kTileBytes >> 4);
 #pragma unroll
         for (int k = 0; k < HS / 16; ++k) {  // S = Q K^T, contraction over the head dimension
-          const uint32_t off = (uint32_t)((k >> 2) * SUB + (k & 3) * 32);
-          ptx::mma_bf16_ss(tmem_base, ptx::smem_desc_sw128(q_addr + off), ptx::smem_desc_sw128(k_addr + off), idesc_s,
-                           k > 0 ? 1u : 0u);
+          const uint64_t off = (uint64_t)(((k >> 2) * SUB + (k & 3) * 32) >> 4);
+          ptx::mma_bf16_ss(tmem_base, q_desc + off, ka + off, idesc_s, k > 0 ? 1u : 0u);
         }
         ptx::mma_commit(s_full);
-        ok = ptx::mbar_wait(p_full, jp, abort_flag, status, ST_ATTN_TIMEOUT) &&
-             ptx::mbar_wait(o_empty, jp ^ 1u, abort_flag, status, ST_ATTN_TIMEOUT);
+      };
+      bool ok = ptx::mbar_wait(q_full, 0, abort_flag, status, ST_ATTN_TIMEOUT) &&
+                ptx::mbar_wait(&kv_full[0], 0, abort_flag, status, ST_ATTN_TIMEOUT);
+      if (ok) {
+        ptx::tc_fence_after_sync();
+        issue_s(0);
+      }
+      for (int j = 0; j < n_blocks && ok; ++j) {
+        const int st = j & 1;
+        const uint32_t jp = (uint32_t)j & 1u;
+        if (j + 1 < n_blocks) {
+          // scores of the next block, once this block's are in the softmax threads' registers
+          ok = ptx::mbar_wait(&kv_full[st ^ 1], (uint32_t)((j + 1) >> 1) & 1u, abort_flag, status, ST_ATTN_TIMEOUT) &&
+               ptx::mbar_wait(s_empty, jp, abort_flag, status, ST_ATTN_TIMEOUT);
+          if (!ok) break;
+          ptx::tc_fence_after_sync();
+          issue_s(st ^ 1);
+        }
+        ok = ptx::mbar_wait(p_full, jp, abort_flag, status, ST_ATTN_TIMEOUT);
         if (!ok) break;
         ptx::tc_fence_after_sync();
+        const uint64_t va = v_desc + (uint64_t)st * (C::kTileBytes >> 4);
 #pragma unroll
-        for (int k = 0; k < AK / 16; ++k) {  // O_j = P V, contraction over the 128 keys of the block
-          const uint32_t poff = (uint32_t)((k >> 2) * SUB + (k & 3) * 32);
-          ptx::mma_bf16_ss(tmem_base + C::kOCol, ptx::smem_desc_sw128(p_addr + poff),
-                           ptx::smem_desc_sw128_mn(v_addr + (uint32_t)(k * 16 * 128), SUB), idesc_o, k > 0 ? 1u : 0u);
-        }
+        for (int k = 0; k < AK / 16; ++k)  // O += P V, contraction over the 128 keys of the block, 16 rows of V per step
+          ptx::mma_bf16_ss(tmem_base + C::kOCol, p_desc + (uint64_t)(((k >> 2) * SUB + (k & 3) * 32) >> 4),
+                           va + (uint64_t)(k * (2048 >> 4)), idesc_o, (j > 0 || k > 0) ? 1u : 0u);
         ptx::mma_commit(o_full);
         ptx::mma_commit(&kv_empty[st]);
       }
@@ -190,10 +209,8 @@ __global__ void __launch_bounds__(A_THREADS, HS == 64 ? 2 : 1)
     const float sl2 = scale * 1.4426950408889634f;  // scores are scaled inside the exp2
     uint8_t* p_row = smem + C::kPOff + hf * SUB + row * 128;
     bf16* xchg = reinterpret_cast<bf16*>(smem + C::kXchgOff);  // [2][128]
-    float acc[OH];
-#pragma unroll
-    for (int i = 0; i < OH; ++i) acc[i] = 0.f;
-    float m = -INFINITY, l = 0.f;
+    float ms = -INFINITY;  // reference maximum of the row, in exp2 units (score * sl2)
+    float l = 0.f;
     bool ok = true;
     for (int j = 0; j < n_blocks; ++j) {
       const uint32_t jp = (uint32_t)j & 1u;
@@ -203,26 +220,25 @@ __global__ void __launch_bounds__(A_THREADS, HS == 64 ? 2 : 1)
       ptx::tc_fence_after_sync();
       const bool diag = (j == qt);  // diagonal block: keys after the query are masked
       const int u0 = j * AK + hf * 64;
-      // pass 1: maximum of this thread's 64 scores (32 at a time to bound the registers)
+      // pass 1: maximum of this thread's 64 scores, 32 at a time (the 64 live values of pass 2 and the
+      // 32 of a rescale would not fit the register budget of two CTAs per SM together)
       float bm = -INFINITY;
 #pragma unroll
       for (int c = 0; c < 64; c += 32) {
-        float sv[32];
-        ptx::tmem_ld32(t_s + (uint32_t)c, sv);
+        float s32[32];
+        ptx::tmem_ld32(t_s + (uint32_t)c, s32);
         ptx::tmem_ld_wait();
         if (diag) {
 #pragma unroll
           for (int i = 0; i < 32; ++i)
-            if (u0 + c + i > t) sv[i] = -INFINITY;
+            if (u0 + c + i > t) s32[i] = -INFINITY;
         }
 #pragma unroll
-        for (int i = 0; i < 32; i += 2) bm = ptx::max3(bm, sv[i], sv[i + 1]);
+        for (int i = 0; i < 32; i += 2) bm = ptx::max3(bm, s32[i], s32[i + 1]);
       }
       // Both threads of a row must adopt the same maximum, but it need not be
       // exact: each rounds its own to bf16 and both take the larger of the two
-      // rounded values.  One slot per half suffices: the partner's next write
-      // comes after o_full of this block, which needs this thread's p_full
-      // arrival, which follows the read below.
+      // rounded values.
       const bf16 bmh = __float2bfloat16_rn(bm);
       xchg[hf * 128 + row] = bmh;
       ptx::mbar_arrive(x_bar);  // release: the store above is visible to whoever sees the phase complete
@@ -230,71 +246,77 @@ __global__ void __launch_bounds__(A_THREADS, HS == 64 ? 2 : 1)
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       bm = fmaxf(__bfloat162float(bmh), __bfloat162float(xchg[(hf ^ 1) * 128 + row]));
-      const float nm = fmaxf(m, bm);  // finite: key 0 of block 0 is never masked, later maxima only grow
-      const float nms = nm * sl2;
-      // pass 2: probabilities -> bf16 -> shared memory
-      float2 rs2 = make_float2(0.f, 0.f);
-      const float2 sl2v = make_float2(sl2, sl2), nmsv = make_float2(-nms, -nms);
-#pragma unroll
-      for (int c = 0; c < 64; c += 32) {
-        float sv[32];
-        ptx::tmem_ld32(t_s + (uint32_t)c, sv);
-        ptx::tmem_ld_wait();
-        if (diag) {
-#pragma unroll
-          for (int i = 0; i < 32; ++i)
-            if (u0 + c + i > t) sv[i] = -INFINITY;
-        }
-#pragma unroll
-        for (int g = 0; g < 4; ++g) {  // four 16-byte pieces of 8 keys
-          uint4 raw;
-          __nv_bfloat162* hp = reinterpret_cast<__nv_bfloat162*>(&raw);
-#pragma unroll
-          for (int i = 0; i < 4; ++i) {  // packed fp32x2 arithmetic: two keys per instruction
-            const float2 x = __ffma2_rn(make_float2(sv[g * 8 + 2 * i], sv[g * 8 + 2 * i + 1]), sl2v, nmsv);
-            const float2 pr = make_float2(exp2f(x.x), exp2f(x.y));
-            rs2 = __fadd2_rn(rs2, pr);
-            hp[i] = __floats2bfloat162_rn(pr.x, pr.y);
-          }
-          const int ch = (c >> 3) + g;  // piece 0..7 of this thread's 64 keys
-          *reinterpret_cast<uint4*>(p_row + ((ch ^ (row & 7)) << 4)) = raw;
-        }
-      }
-      ptx::tc_fence_before_sync();
-      ptx::mbar_arrive(s_empty);  // the next block's S may overwrite TMEM
-      ptx::fence_proxy_async();  // make the generic-proxy writes of P visible to the MMA's async proxy
-      ptx::mbar_arrive(p_full);
-      if (nm > m) {
-        const float corr = exp2f((m - nm) * sl2);
+      const float bms = bm * sl2;  // finite or -inf only for a fully masked half, which the partner's value covers
+      bool o_waited = false;
+      if (j == 0) {
+        ms = bms;
+      } else if (__any_sync(0xffffffffu, bms > ms + 8.f)) {
+        // raise the reference of every row of the warp (tcgen05.ld/st are warp-wide); the partner warp sees the same
+        // maxima and decides the same.  O must be at rest: O += P_{j-1} V_{j-1} has completed.
+        const float nm = fmaxf(ms, bms);
+        const float corr = exp2f(ms - nm);
+        ms = nm;
         l *= corr;
-        const float2 cv = make_float2(corr, corr);
+        ok = ptx::mbar_wait(o_full, jp ^ 1u, abort_flag, status, ST_ATTN_TIMEOUT);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        ptx::tc_fence_after_sync();
+        o_waited = true;
 #pragma unroll
-        for (int i = 0; i < OH; i += 2) {
-          const float2 r = __fmul2_rn(make_float2(acc[i], acc[i + 1]), cv);
-          acc[i] = r.x;
-          acc[i + 1] = r.y;
+        for (int c = 0; c < OH; c += 32) {
+          float v[32];
+          ptx::tmem_ld32(t_o + (uint32_t)c, v);
+          ptx::tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] *= corr;
+          ptx::tmem_st32(t_o + (uint32_t)c, v);
         }
-        m = nm;
+        ptx::tmem_st_wait();
+        ptx::tc_fence_before_sync();
+      }
+      if (j > 0 && !o_waited) {
+        // P_{j-1} is being read until O += P_{j-1} V_{j-1} completes
+        ok = ptx::mbar_wait(o_full, jp ^ 1u, abort_flag, status, ST_ATTN_TIMEOUT);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+      }
+      // pass 2: the 64 scores into registers; the MMA warp may then overwrite S with the next block's scores
+      // (the partner's maximum was read above, so the partner, which waits for those scores, cannot have
+      // reused the exchange slot before)
+      float sv[64];
+      ptx::tmem_ld32_at<0>(t_s, sv);
+      ptx::tmem_ld32_at<32>(t_s + 32u, sv);
+      ptx::tmem_ld_wait();
+      ptx::tc_fence_before_sync();
+      ptx::mbar_arrive(s_empty);
+      if (diag) {
+#pragma unroll
+        for (int i = 0; i < 64; ++i)
+          if (u0 + i > t) sv[i] = -INFINITY;
+      }
+      // probabilities against the reference -> bf16 -> shared memory
+      float2 rs2 = make_float2(0.f, 0.f);
+      const float2 sl2v = make_float2(sl2, sl2), nmsv = make_float2(-ms, -ms);
+#pragma unroll
+      for (int c = 0; c < 64; c += 8) {  // 16-byte pieces of 8 keys
+        uint4 raw;
+        __nv_bfloat162* hp = reinterpret_cast<__nv_bfloat162*>(&raw);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {  // packed fp32x2 arithmetic: two keys per instruction
+          const float2 x = __ffma2_rn(make_float2(sv[c + 2 * i], sv[c + 2 * i + 1]), sl2v, nmsv);
+          const float2 pr = make_float2(exp2f(x.x), exp2f(x.y));
+          rs2 = __fadd2_rn(rs2, pr);
+          hp[i] = __floats2bfloat162_rn(pr.x, pr.y);
+        }
+        *reinterpret_cast<uint4*>(p_row + (((c >> 3) ^ (row & 7)) << 4)) = raw;
       }
       l += rs2.x + rs2.y;
-      ok = ptx::mbar_wait(o_full, jp, abort_flag, status, ST_ATTN_TIMEOUT);
+      ptx::fence_proxy_async();  // make the generic-proxy writes of P visible to the MMA's async proxy
+      ptx::mbar_arrive(p_full);
+    }
+    if (ok) {
+      ok = ptx::mbar_wait(o_full, (uint32_t)(n_blocks - 1) & 1u, abort_flag, status, ST_ATTN_TIMEOUT);
       ok = __all_sync(0xffffffffu, ok);
-      if (!ok) break;
-      ptx::tc_fence_after_sync();
-#pragma unroll
-      for (int c = 0; c < OH; c += 32) {
-        float v[32];
-        ptx::tmem_ld32(t_o + (uint32_t)c, v);
-        ptx::tmem_ld_wait();
-#pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          const float2 r = __fadd2_rn(make_float2(acc[c + i], acc[c + i + 1]), make_float2(v[i], v[i + 1]));
-          acc[c + i] = r.x;
-          acc[c + i + 1] = r.y;
-        }
-      }
-      ptx::tc_fence_before_sync();
-      ptx::mbar_arrive(o_empty);
     }
     // the two halves of a row hold partial sums under the same running maximum
     if (ok) {
@@ -305,17 +327,27 @@ __global__ void __launch_bounds__(A_THREADS, HS == 64 ? 2 : 1)
       ok = ptx::mbar_wait(x_bar, (uint32_t)n_blocks & 1u, abort_flag, status, ST_ATTN_TIMEOUT);
       if (ok) l += lx[(hf ^ 1) * 128 + row];
     }
-    if (ok && t < seq) {
+    ok = __all_sync(0xffffffffu, ok);
+    if (ok) {
+      ptx::tc_fence_after_sync();
       const float inv = 1.f / l;
       bf16* dst = o + ((size_t)b * seq + t) * ldo + h * HS + hf * OH;
 #pragma unroll
-      for (int c = 0; c < OH; c += 8) {
-        float v[8];
+      for (int c = 0; c < OH; c += 32) {
+        float v[32];
+        ptx::tmem_ld32(t_o + (uint32_t)c, v);
+        ptx::tmem_ld_wait();
+        if (t < seq) {
 #pragma unroll
-        for (int i = 0; i < 8; ++i) v[i] = acc[c + i] * inv;
-        store8(dst + c, v);
+          for (int g = 0; g < 32; g += 8) {
+            float w8[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) w8[i] = v[g + i] * inv;
+            store8(dst + c + g, w8);
+          }
+        }
       }
-      if (lse && hf == 0) lse[((size_t)b * n_heads + h) * seq + t] = m * scale + __logf(l);
+      if (lse && hf == 0 && t < seq) lse[((size_t)b * n_heads + h) * seq + t] = ms * 0.6931471805599453f + __logf(l);
     }
   }
 

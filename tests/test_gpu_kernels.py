@@ -136,6 +136,22 @@ def test_attention_forward(impl, B_, S, H, hs, dtype):
     assert torch.allclose(lse.double(), rl, rtol=1e-4, atol=1e-4 if dtype == torch.float32 else 2e-2)
 
 
+@pytest.mark.parametrize("B_,S,H,gain", [(2, 384, 2, 1.0), (1, 640, 3, 3.0), (2, 1024, 2, 3.0), (3, 130, 2, 2.0)])
+def test_attention_forward_tensor_core_edges(B_, S, H, gain):
+    """Tensor-core kernel, output accumulated in tensor memory: an odd number of tiles, a ragged tail, and scores
+    spread widely enough (gain > 1) that block maxima exceed the running reference by more than 2^8, so that the
+    in-place rescale of the accumulator runs."""
+    g = torch.Generator().manual_seed(7)
+    d = H * 64
+    qkv = (torch.randn(B_ * S, 3 * d, generator=g) * gain).bfloat16().to(DEV)
+    q, k, v = qkv[:, :d], qkv[:, d:2 * d], qkv[:, 2 * d:]
+    o, lse = B.attention(q, k, v, B_, S, H, impl=1)
+    assert B.device_status() == 0
+    ro, rl = _attn_ref(q, k, v, B_, S, H)
+    assert torch.allclose(o.double(), ro, rtol=1e-2, atol=1e-2 * gain)
+    assert torch.allclose(lse.double(), rl, rtol=1e-4, atol=2e-2)
+
+
 def _decode_case(batch, ctx, H, hs, dtype, page, seed=0):
     g = torch.Generator().manual_seed(seed)
     d = H * hs
