@@ -144,6 +144,8 @@ __global__ void __launch_bounds__(VW * 32)
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int sub = lane / LPK, li = lane % LPK;
   const int32_t* table = page_table + (size_t)b * max_pages;
+  pdl_launch_dependents();
+  pdl_wait();  // q and this step's K/V row come from the kernels before
   float qf[8];
   load8(q + (size_t)b * ldq + h * HS + li * 8, qf);
 #pragma unroll
@@ -256,6 +258,8 @@ __global__ void attn_decode_combine_kernel(const float* __restrict__ scratch, T*
                                            int n_splits) {
   const int h = blockIdx.x, b = blockIdx.y;
   const float* base = scratch + ((size_t)b * n_heads + h) * n_splits * (HS + 2);
+  pdl_launch_dependents();
+  pdl_wait();
   float gm = -INFINITY;
   for (int s = 0; s < n_splits; ++s) gm = fmaxf(gm, base[(size_t)s * (HS + 2) + HS]);
   float gl = 0.f;
@@ -280,14 +284,14 @@ int32_t launch_hs(const AttnDecodeArgs& a, cudaStream_t stream) {
   const T* vp = kp + page_elems;
   dim3 grid(a.n_splits, a.n_heads, a.batch);
   if constexpr (sizeof(T) == 2 && (HS == 64 || HS == 128)) {
-    attn_decode_vec_kernel<HS><<<grid, VW * 32, 0, stream>>>((const bf16*)a.q, (const bf16*)kp, (const bf16*)vp,
-                                                            a.page_table, a.scratch, (bf16*)a.o, a.ctx, a.n_heads,
-                                                            a.ldq, a.ldo, a.page_size, a.max_pages, a.d_local,
-                                                            a.n_splits, 1.f / sqrtf((float)HS));
+    B200_CUDA_OK(launch_pdl(attn_decode_vec_kernel<HS>, grid, dim3(VW * 32), 0, stream, (const bf16*)a.q, (const bf16*)kp,
+                            (const bf16*)vp, a.page_table, a.scratch, (bf16*)a.o, a.ctx, a.n_heads, a.ldq, a.ldo,
+                            a.page_size, a.max_pages, a.d_local, a.n_splits, 1.f / sqrtf((float)HS)));
     B200_LAUNCH_OK("attn_decode_vec_kernel");
     if (a.n_splits == 1) return B200_OK;  // the kernel wrote the output itself
     dim3 grid2v(a.n_heads, a.batch);
-    attn_decode_combine_kernel<T, HS><<<grid2v, HS, 0, stream>>>(a.scratch, (T*)a.o, a.n_heads, a.ldo, a.n_splits);
+    B200_CUDA_OK(launch_pdl(attn_decode_combine_kernel<T, HS>, grid2v, dim3(HS), 0, stream, (const float*)a.scratch, (T*)a.o,
+                            a.n_heads, a.ldo, a.n_splits));
     B200_LAUNCH_OK("attn_decode_combine_kernel");
     return B200_OK;
   }

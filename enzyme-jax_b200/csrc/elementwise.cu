@@ -155,7 +155,7 @@ constexpr int RB_MAXCH = 4;  // 8-wide chunks per thread: dim <= 256*8*4 = 8192
 template <typename TDy>
 __global__ void __launch_bounds__(RB_THREADS)
     rmsnorm_bwd_kernel(const float* __restrict__ x, const float* __restrict__ gain, const float* __restrict__ rinv,
-                       const TDy* __restrict__ dy, float* __restrict__ dx, int accumulate_dx,
+                       const TDy* dy, float* __restrict__ dx, int accumulate_dx, TDy* dx_copy,
                        float* __restrict__ dg_part, int rows, int dim, int rows_per_part) {
   __shared__ float red[32];
   float dg[RB_MAXCH][8];
@@ -203,6 +203,7 @@ __global__ void __launch_bounds__(RB_THREADS)
           out[i] = accumulate_dx ? out[i] + val : val;
         }
         store8(dxr + c, out);
+        if (dx_copy) store8(dx_copy + (size_t)row * dim + c, out);  // may be dy itself: this thread has read its piece
       }
     }
   }
@@ -224,7 +225,7 @@ constexpr int RW_MAXCH = 6;  // 8-wide chunks per lane: dim <= 32*8*6 = 1536
 template <typename TDy, int NCH>
 __global__ void __launch_bounds__(RW_WARPS * 32)
     rmsnorm_bwd_warp_kernel(const float* __restrict__ x, const float* __restrict__ gain, const float* __restrict__ rinv,
-                            const TDy* __restrict__ dy, float* __restrict__ dx, int accumulate_dx,
+                            const TDy* dy, float* __restrict__ dx, int accumulate_dx, TDy* dx_copy,
                             float* __restrict__ dg_part, int rows, int dim, int rows_per_part) {
   extern __shared__ float s_dg[];  // [RW_WARPS][dim]
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -273,6 +274,7 @@ __global__ void __launch_bounds__(RW_WARPS * 32)
           out[i] = accumulate_dx ? out[i] + val : val;
         }
         store8(dxr + c, out);
+        if (dx_copy) store8(dx_copy + (size_t)row * dim + c, out);  // may be dy itself: the row is in registers
       }
     }
   }
@@ -523,7 +525,7 @@ int rmsnorm_bwd_parts(int rows) {
 }
 
 int32_t launch_rmsnorm_bwd(const float* x, const float* gain, const float* rinv, const void* dy, int dy_dtype,
-                           float* dx, int accumulate_dx, float* dg_part, int n_parts, int rows, int dim,
+                           float* dx, int accumulate_dx, void* dx_copy, float* dg_part, int n_parts, int rows, int dim,
                            cudaStream_t stream) {
   if (dim % 8 || dim > RB_THREADS * 8 * RB_MAXCH)
     return fail(B200_ERR_BAD_SHAPE, "rmsnorm backward: dim=%d must be a multiple of 8 and at most %d", dim,
@@ -537,10 +539,10 @@ int32_t launch_rmsnorm_bwd(const float* x, const float* gain, const float* rinv,
   case N:                                                                                                            \
     if (dy_dtype == B200_F32)                                                                                        \
       rmsnorm_bwd_warp_kernel<float, N><<<n_parts, RW_WARPS * 32, smem, stream>>>(                                   \
-          x, gain, rinv, (const float*)dy, dx, accumulate_dx, dg_part, rows, dim, rpp);                              \
+          x, gain, rinv, (const float*)dy, dx, accumulate_dx, (float*)dx_copy, dg_part, rows, dim, rpp);                              \
     else                                                                                                             \
       rmsnorm_bwd_warp_kernel<bf16, N><<<n_parts, RW_WARPS * 32, smem, stream>>>(                                    \
-          x, gain, rinv, (const bf16*)dy, dx, accumulate_dx, dg_part, rows, dim, rpp);                               \
+          x, gain, rinv, (const bf16*)dy, dx, accumulate_dx, (bf16*)dx_copy, dg_part, rows, dim, rpp);                               \
     break;
     switch (nch) {
       B200_RW_CASE(1) B200_RW_CASE(2) B200_RW_CASE(3) B200_RW_CASE(4) B200_RW_CASE(5) B200_RW_CASE(6)
@@ -552,10 +554,10 @@ int32_t launch_rmsnorm_bwd(const float* x, const float* gain, const float* rinv,
   // Parts beyond the last row still write zeros so that the column sum may read all of them.
   if (dy_dtype == B200_F32)
     rmsnorm_bwd_kernel<float><<<n_parts, RB_THREADS, 0, stream>>>(x, gain, rinv, (const float*)dy, dx, accumulate_dx,
-                                                                  dg_part, rows, dim, rpp);
+                                                                  (float*)dx_copy, dg_part, rows, dim, rpp);
   else
     rmsnorm_bwd_kernel<bf16><<<n_parts, RB_THREADS, 0, stream>>>(x, gain, rinv, (const bf16*)dy, dx, accumulate_dx,
-                                                                 dg_part, rows, dim, rpp);
+                                                                 (bf16*)dx_copy, dg_part, rows, dim, rpp);
   B200_LAUNCH_OK("rmsnorm_bwd_kernel");
   return B200_OK;
 }

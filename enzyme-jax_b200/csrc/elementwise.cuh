@@ -35,9 +35,10 @@ int32_t launch_rope_table(float* cos_t, float* sin_t, int n_pos, int head_size, 
 
 // RMSNorm backward for y = g * x * r: dx (+)= r*u - x * r^3/d * sum(u*x), u = g*dy;
 // dgain partials are written per CTA to `dg_part` [n_parts, dim] and reduced by
-// launch_colsum_parts (fixed order, no atomics).  dy has dtype `dy_dtype`.
+// launch_colsum_parts (fixed order, no atomics).  dy has dtype `dy_dtype`.  dx_copy (optional, dtype of dy, may be dy
+// itself) receives the updated dx as well: the next GEMMs take it as their low-precision operand.
 int32_t launch_rmsnorm_bwd(const float* x, const float* gain, const float* rinv, const void* dy, int dy_dtype,
-                           float* dx, int accumulate_dx, float* dg_part, int n_parts, int rows, int dim,
+                           float* dx, int accumulate_dx, void* dx_copy, float* dg_part, int n_parts, int rows, int dim,
                            cudaStream_t stream);
 int rmsnorm_bwd_parts(int rows);
 // out[c] (+)= sum_p part[p, c]

@@ -300,6 +300,8 @@ __global__ void __launch_bounds__(256) splitk_reduce_kernel(const float* __restr
                                                             EpiParams ep) {
   const int per_row = N / 16;
   const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+  pdl_launch_dependents();
+  pdl_wait();  // the partial sums come from the GEMM kernel before
   if (idx >= M * per_row) return;
   const int m = idx / per_row, n = (idx % per_row) * 16;
   float v[16];
@@ -363,8 +365,8 @@ int32_t launch_cfg(const GemmArgs& g, cudaStream_t stream) {
   B200_LAUNCH_OK("gemm_tc_kernel");
   if (splits > 1) {
     const int chunks = g.M * (g.N / 16);
-    splitk_reduce_kernel<KIND, TOut><<<cdiv(chunks, 256), 256, 0, stream>>>(
-        reinterpret_cast<const float*>(g.splitk_scratch), splits, g.M, g.N, g.epi);
+    B200_CUDA_OK(launch_pdl(splitk_reduce_kernel<KIND, TOut>, dim3(cdiv(chunks, 256)), dim3(256), 0, stream,
+                            reinterpret_cast<const float*>(g.splitk_scratch), splits, g.M, g.N, g.epi));
     B200_LAUNCH_OK("splitk_reduce_kernel");
   }
   return B200_OK;

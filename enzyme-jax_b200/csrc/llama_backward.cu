@@ -81,7 +81,7 @@ int32_t backward_impl(B200Plan* p, const int32_t* tokens, int B, int S, const ui
   }
   B200_TRY(gemm(*p, b, dlog, V, 1, acts.fin.xf, d, 1, V, d, T, gf(gl.wcls), d, B200_F32, accumulate, stream));
   B200_TRY(gemm(*p, b, dlog, V, 0, w + wl.wcls_t, V, 0, T, d, V, b.dxb, d, dt, 0, stream));
-  B200_TRY(launch_rmsnorm_bwd(acts.fin.x_last, g_fin, acts.fin.rinv_f, b.dxb, dt, b.dx, 0, b.dg_part, b.n_parts, T, d,
+  B200_TRY(launch_rmsnorm_bwd(acts.fin.x_last, g_fin, acts.fin.rinv_f, b.dxb, dt, b.dx, 0, b.dxb, b.dg_part, b.n_parts, T, d,
                               stream));
   B200_TRY(launch_colsum_parts(b.dg_part, b.n_parts, d, gf(gl.g_final), accumulate, stream));
 
@@ -89,18 +89,17 @@ int32_t backward_impl(B200Plan* p, const int32_t* tokens, int B, int S, const ui
     const LayerActs& a = acts.layer[l];
     const LayerOffsets& o = wl.layer[l];
     const LayerOffsets& go = gl.layer[l];
-    // ---- feed-forward block: x_out = x_mid + hg W2^T
-    B200_TRY(launch_convert(b.dx, B200_F32, b.dxb, dt, (size_t)T * d, stream));
+    // ---- feed-forward block: x_out = x_mid + hg W2^T  (b.dxb holds dx in the config dtype: written by the
+    //      RMSNorm backward that produced dx)
     B200_TRY(gemm(*p, b, b.dxb, d, 1, a.hg, h, 1, d, h, T, gf(go.w2), h, B200_F32, accumulate, stream));
     B200_TRY(gemm(*p, b, b.dxb, d, 0, w + o.w2_t, d, 0, T, h, d, b.dhg, h, dt, 0, stream));
     B200_TRY(launch_swiglu_bwd(a.gate, a.up, b.dhg, b.dgu, dt, T, h, stream));
     B200_TRY(gemm(*p, b, b.dgu, 2 * h, 1, a.xb2, d, 1, 2 * h, d, T, gf(go.w13), d, B200_F32, accumulate, stream));
     B200_TRY(gemm(*p, b, b.dgu, 2 * h, 0, w + o.w13_t, 2 * h, 0, T, d, 2 * h, b.dxb, d, dt, 0, stream));
-    B200_TRY(launch_rmsnorm_bwd(a.x_mid, g_ffn + (size_t)l * d, a.rinv2, b.dxb, dt, b.dx, 1, b.dg_part, b.n_parts, T, d,
+    B200_TRY(launch_rmsnorm_bwd(a.x_mid, g_ffn + (size_t)l * d, a.rinv2, b.dxb, dt, b.dx, 1, b.dxb, b.dg_part, b.n_parts, T, d,
                                 stream));
     B200_TRY(launch_colsum_parts(b.dg_part, b.n_parts, d, gf(gl.g_ffn) + (size_t)l * d, accumulate, stream));
     // ---- attention block: x_mid = x_in + o Wo^T
-    B200_TRY(launch_convert(b.dx, B200_F32, b.dxb, dt, (size_t)T * d, stream));
     B200_TRY(gemm(*p, b, b.dxb, d, 1, a.o, d, 1, d, d, T, gf(go.wo), d, B200_F32, accumulate, stream));
     B200_TRY(gemm(*p, b, b.dxb, d, 0, w + o.wo_t, d, 0, T, d, d, b.d_o, d, dt, 0, stream));
     {
@@ -120,7 +119,7 @@ int32_t backward_impl(B200Plan* p, const int32_t* tokens, int B, int S, const ui
     B200_TRY(launch_rope_bwd(b.dqkv, dt, 3 * d, T, 2 * d, p->hs, S, p->rope_cos, p->rope_sin, stream));
     B200_TRY(gemm(*p, b, b.dqkv, 3 * d, 1, a.xb, d, 1, 3 * d, d, T, gf(go.wqkv), d, B200_F32, accumulate, stream));
     B200_TRY(gemm(*p, b, b.dqkv, 3 * d, 0, w + o.wqkv_t, 3 * d, 0, T, d, 3 * d, b.dxb, d, dt, 0, stream));
-    B200_TRY(launch_rmsnorm_bwd(a.x_in, g_att + (size_t)l * d, a.rinv1, b.dxb, dt, b.dx, 1, b.dg_part, b.n_parts, T, d,
+    B200_TRY(launch_rmsnorm_bwd(a.x_in, g_att + (size_t)l * d, a.rinv1, b.dxb, dt, b.dx, 1, b.dxb, b.dg_part, b.n_parts, T, d,
                                 stream));
     B200_TRY(launch_colsum_parts(b.dg_part, b.n_parts, d, gf(gl.g_att) + (size_t)l * d, accumulate, stream));
   }

@@ -20,6 +20,8 @@ __global__ void kv_append_kernel(const T* __restrict__ qkv, T* __restrict__ kpag
                                  int d_local, int hs) {
   constexpr int E = 16 / sizeof(T);  // elements per 16-byte piece
   const int b = blockIdx.x;
+  pdl_launch_dependents();
+  pdl_wait();  // qkv comes from the projection before
   const int page = page_table[(size_t)b * max_pages + pos / page_size];
   const int n_heads = d_local / hs;
   const T* src = qkv + (size_t)b * 3 * d_local;
@@ -158,11 +160,11 @@ int32_t b200_decode_step(B200Plan* p, const int32_t* tokens, const float* x_in, 
       B200_TRY(gemm(*p, w, w.xb, d, wt + o.wqkv, d, B, 3 * dl, d, EPI_ROPE, p->dtype, e, stream));
     }
     if (p->dtype == B200_BF16)
-      kv_append_kernel<bf16><<<B, 128, 0, stream>>>((const bf16*)w.qkv, (bf16*)kv, (bf16*)(kv + layer_bytes / 2),
-                                                    page_table, pos, page_size, max_pages, dl, p->hs);
+      B200_CUDA_OK(launch_pdl(kv_append_kernel<bf16>, dim3(B), dim3(128), 0, stream, (const bf16*)w.qkv, (bf16*)kv,
+                              (bf16*)(kv + layer_bytes / 2), page_table, pos, page_size, max_pages, dl, p->hs));
     else
-      kv_append_kernel<float><<<B, 128, 0, stream>>>((const float*)w.qkv, (float*)kv, (float*)(kv + layer_bytes / 2),
-                                                     page_table, pos, page_size, max_pages, dl, p->hs);
+      B200_CUDA_OK(launch_pdl(kv_append_kernel<float>, dim3(B), dim3(128), 0, stream, (const float*)w.qkv, (float*)kv,
+                              (float*)(kv + layer_bytes / 2), page_table, pos, page_size, max_pages, dl, p->hs));
     B200_LAUNCH_OK("kv_append_kernel");
     {
       AttnDecodeArgs a;

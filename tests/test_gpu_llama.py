@@ -225,3 +225,21 @@ def test_captured_graphs_replay_the_eager_forward():
     with pytest.raises(B.B200Error):
         p.capture_prefill_step(t2, tok, logits, last, host_last)  # pageable host tokens
     assert B.device_status() == 0
+
+
+RAGGED = dict(dim=768, hidden_dim=2048, n_layers=2, n_heads=12, n_kv_heads=12, vocab_size=2048, seq_len=256)
+
+
+def test_forward_and_vjp_bf16_on_ragged_shapes():
+    """Sequence length 200 (not a multiple of the 128-row tiles of the tensor-core GEMM and attention kernels) and an odd
+    batch: 600 rows leave ragged last tiles in every GEMM (M and K tails), in the attention forward and in both backward
+    attention passes.  Head size 64, so the tcgen05 kernels run."""
+    batch, seq = 3, 200
+    p, tok, dlogits, saved, leaves = _grad_check(RAGGED, torch.bfloat16, batch, seq, 3e-2, 0.05)
+    w = O.make_weights(RAGGED, 7, torch.float32, std=0.05, gains_one=False)
+    wq = {k: v.bfloat16() for k, v in w.items()}
+    ref = O.forward_sequence(O.make_tokens(RAGGED, batch, seq, 9), RAGGED, {k: v.float() for k, v in wq.items()})
+    got = p.forward(tok)
+    torch.cuda.synchronize()
+    assert B.device_status() == 0
+    assert _norm_rel(got, ref) < 2e-2
