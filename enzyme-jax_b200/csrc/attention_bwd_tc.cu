@@ -71,6 +71,7 @@ __global__ void __launch_bounds__(BW_THREADS, 1)
   volatile uint32_t* abort_flag = tmem_slot + 1;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  pdl_launch_dependents();
   // (head, batch) in x/y, the block index in z: blocks are dispatched x-fastest, so the longest loops of the
   // whole launch start first
   const int own = blockIdx.z, h = blockIdx.x, b = blockIdx.y;
@@ -112,6 +113,7 @@ __global__ void __launch_bounds__(BW_THREADS, 1)
   ptx::tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
   const bool aborted = *abort_flag != 0u;
+  pdl_wait();  // the operands come from the kernels before; everything above overlapped their tail
 
   if (aborted) {
     // common exit below
@@ -351,10 +353,12 @@ int32_t launch_attn_bwd_tc(const AttnBwdArgs& a, cudaStream_t stream) {
   prm.scale = 1.f / sqrtf(64.f);
   dim3 grid(f.n_heads, f.batch, cdiv(f.seq, 128));
   prm.out0 = (bf16*)a.dv; prm.out1 = (bf16*)a.dk; prm.ld_out = a.lddkv;
-  attn_bwd_tc_kernel<MODE_DKV><<<grid, BW_THREADS, kBwdSmem, stream>>>(tq, tk, tv, tdo, prm, device_status_word());
+  B200_CUDA_OK(launch_pdl(attn_bwd_tc_kernel<MODE_DKV>, grid, dim3(BW_THREADS), kBwdSmem, stream, tq, tk, tv, tdo, prm,
+                          device_status_word()));
   B200_LAUNCH_OK("attn_bwd_tc_kernel<dkv>");
   prm.out0 = (bf16*)a.dq; prm.out1 = nullptr; prm.ld_out = a.lddq;
-  attn_bwd_tc_kernel<MODE_DQ><<<grid, BW_THREADS, kBwdSmem, stream>>>(tq, tk, tv, tdo, prm, device_status_word());
+  B200_CUDA_OK(launch_pdl(attn_bwd_tc_kernel<MODE_DQ>, grid, dim3(BW_THREADS), kBwdSmem, stream, tq, tk, tv, tdo, prm,
+                          device_status_word()));
   B200_LAUNCH_OK("attn_bwd_tc_kernel<dq>");
   return B200_OK;
 }

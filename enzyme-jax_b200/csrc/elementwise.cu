@@ -229,6 +229,8 @@ __global__ void __launch_bounds__(RW_WARPS * 32)
                             float* __restrict__ dg_part, int rows, int dim, int rows_per_part) {
   extern __shared__ float s_dg[];  // [RW_WARPS][dim]
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  pdl_launch_dependents();
+  pdl_wait();
   float dg[NCH][8];
   float g[NCH][8];
 #pragma unroll
@@ -319,6 +321,8 @@ __global__ void rope_bwd_kernel(T* __restrict__ d, int ld, int rows, int rope_co
   const int c8n = rope_cols / 8;
   const size_t total = (size_t)rows * c8n;
   const int half = head_size >> 1;
+  pdl_launch_dependents();
+  pdl_wait();
   for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
     const int r = (int)(i / c8n), c = (int)(i % c8n) * 8;
     const int pos = r % seq_len;
@@ -342,6 +346,8 @@ __global__ void swiglu_bwd_kernel(const T* __restrict__ gate, const T* __restric
                                   T* __restrict__ dgu, int rows, int hidden) {
   const int c8n = hidden / 8;
   const size_t total = (size_t)rows * c8n;
+  pdl_launch_dependents();
+  pdl_wait();
   for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
     const int r = (int)(i / c8n), c = (int)(i % c8n) * 8;
     float a[8], b[8], d[8], da[8], db[8];
@@ -538,11 +544,11 @@ int32_t launch_rmsnorm_bwd(const float* x, const float* gain, const float* rinv,
 #define B200_RW_CASE(N)                                                                                              \
   case N:                                                                                                            \
     if (dy_dtype == B200_F32)                                                                                        \
-      rmsnorm_bwd_warp_kernel<float, N><<<n_parts, RW_WARPS * 32, smem, stream>>>(                                   \
-          x, gain, rinv, (const float*)dy, dx, accumulate_dx, (float*)dx_copy, dg_part, rows, dim, rpp);                              \
+      B200_CUDA_OK(launch_pdl(rmsnorm_bwd_warp_kernel<float, N>, dim3(n_parts), dim3(RW_WARPS * 32), smem, stream,   \
+          x, gain, rinv, (const float*)dy, dx, accumulate_dx, (float*)dx_copy, dg_part, rows, dim, rpp));                              \
     else                                                                                                             \
-      rmsnorm_bwd_warp_kernel<bf16, N><<<n_parts, RW_WARPS * 32, smem, stream>>>(                                    \
-          x, gain, rinv, (const bf16*)dy, dx, accumulate_dx, (bf16*)dx_copy, dg_part, rows, dim, rpp);                               \
+      B200_CUDA_OK(launch_pdl(rmsnorm_bwd_warp_kernel<bf16, N>, dim3(n_parts), dim3(RW_WARPS * 32), smem, stream,    \
+          x, gain, rinv, (const bf16*)dy, dx, accumulate_dx, (bf16*)dx_copy, dg_part, rows, dim, rpp));                               \
     break;
     switch (nch) {
       B200_RW_CASE(1) B200_RW_CASE(2) B200_RW_CASE(3) B200_RW_CASE(4) B200_RW_CASE(5) B200_RW_CASE(6)
@@ -574,9 +580,11 @@ int32_t launch_rope_bwd(void* dqkv, int dtype, int ld, int rows, int rope_cols, 
   if (rope_cols % 8) return fail(B200_ERR_BAD_SHAPE, "rope backward: width must be a multiple of 8");
   const int g = grid_for((size_t)rows * (rope_cols / 8), 256);
   if (dtype == B200_F32)
-    rope_bwd_kernel<float><<<g, 256, 0, stream>>>((float*)dqkv, ld, rows, rope_cols, head_size, seq_len, cos_t, sin_t);
+    B200_CUDA_OK(launch_pdl(rope_bwd_kernel<float>, dim3(g), dim3(256), 0, stream, (float*)dqkv, ld, rows, rope_cols,
+                            head_size, seq_len, cos_t, sin_t));
   else
-    rope_bwd_kernel<bf16><<<g, 256, 0, stream>>>((bf16*)dqkv, ld, rows, rope_cols, head_size, seq_len, cos_t, sin_t);
+    B200_CUDA_OK(launch_pdl(rope_bwd_kernel<bf16>, dim3(g), dim3(256), 0, stream, (bf16*)dqkv, ld, rows, rope_cols,
+                            head_size, seq_len, cos_t, sin_t));
   B200_LAUNCH_OK("rope_bwd_kernel");
   return B200_OK;
 }
@@ -586,11 +594,11 @@ int32_t launch_swiglu_bwd(const void* gate, const void* up, const void* dh, void
   if (hidden % 8) return fail(B200_ERR_BAD_SHAPE, "swiglu backward: hidden must be a multiple of 8");
   const int g = grid_for((size_t)rows * (hidden / 8), 256);
   if (dtype == B200_F32)
-    swiglu_bwd_kernel<float><<<g, 256, 0, stream>>>((const float*)gate, (const float*)up, (const float*)dh,
-                                                    (float*)dgu, rows, hidden);
+    B200_CUDA_OK(launch_pdl(swiglu_bwd_kernel<float>, dim3(g), dim3(256), 0, stream, (const float*)gate, (const float*)up,
+                            (const float*)dh, (float*)dgu, rows, hidden));
   else
-    swiglu_bwd_kernel<bf16><<<g, 256, 0, stream>>>((const bf16*)gate, (const bf16*)up, (const bf16*)dh, (bf16*)dgu,
-                                                   rows, hidden);
+    B200_CUDA_OK(launch_pdl(swiglu_bwd_kernel<bf16>, dim3(g), dim3(256), 0, stream, (const bf16*)gate, (const bf16*)up,
+                            (const bf16*)dh, (bf16*)dgu, rows, hidden));
   B200_LAUNCH_OK("swiglu_bwd_kernel");
   return B200_OK;
 }
