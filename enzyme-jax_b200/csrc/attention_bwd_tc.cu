@@ -152,7 +152,16 @@ __global__ void __launch_bounds__(BW_THREADS, 1)
       constexpr uint32_t id_kk = ptx::idesc_bf16_f32(128, 128);                          // A, B K-major
       constexpr uint32_t id_mm = ptx::idesc_bf16_f32(128, HSB) | (1u << 15) | (1u << 16);  // A, B MN-major
       constexpr uint32_t id_km = ptx::idesc_bf16_f32(128, HSB) | (1u << 16);               // A K-major, B MN-major
-      const uint32_t p_addr = ptx::smem_u32(smem + kP), ds_addr = ptx::smem_u32(smem + kDS);
+      // Descriptors are built once; a stage or a k-step adds its byte offset >> 4 to the address field (shared-memory
+      // addresses stay below 2^18, so the 14-bit field never carries).  One thread issues the 16 to 24 MMAs of an
+      // iteration: two descriptor builds per MMA were most of its instruction stream.
+      const uint32_t str_addr = ptx::smem_u32(smem + kStr), fix_addr = ptx::smem_u32(smem + kFix0);
+      const uint64_t str_k = ptx::smem_desc_sw128(str_addr), str_m = ptx::smem_desc_sw128_mn(str_addr, SUBT);
+      const uint64_t fix_k = ptx::smem_desc_sw128(fix_addr), fix_m = ptx::smem_desc_sw128_mn(fix_addr, SUBT);
+      const uint64_t p_m = ptx::smem_desc_sw128_mn(ptx::smem_u32(smem + kP), SUBT);
+      const uint64_t ds_m = ptx::smem_desc_sw128_mn(ptx::smem_u32(smem + kDS), SUBT);
+      const uint64_t ds_k = ptx::smem_desc_sw128(ptx::smem_u32(smem + kDS));
+      constexpr uint64_t kSub = SUBT >> 4;
       bool ok = ptx::mbar_wait(fix_full, 0, abort_flag, status, ST_ATTNB_TIMEOUT);
       for (int it = 0; it < n_it && ok; ++it) {
         const int st = it & 1;
@@ -162,18 +171,21 @@ __global__ void __launch_bounds__(BW_THREADS, 1)
              ptx::mbar_wait(s_empty, ip ^ 1u, abort_flag, status, ST_ATTNB_TIMEOUT);
         if (!ok) break;
         ptx::tc_fence_after_sync();
-        const uint32_t s0 = ptx::smem_u32(smem + kStr + st * 2 * SUBT), s1 = s0 + SUBT;
-        const uint32_t f0 = ptx::smem_u32(smem + kFix0), f1 = f0 + SUBT;
-        const uint32_t q_a = MODE == MODE_DKV ? s0 : f0, do_a = MODE == MODE_DKV ? s1 : f1;
-        const uint32_t k_a = MODE == MODE_DKV ? f0 : s0, v_a = MODE == MODE_DKV ? f1 : s1;
+        // streamed pair (stage st): sub-tile 0 and 1; fixed pair: sub-tile 0 and 1
+        const uint64_t s0k = str_k + (uint64_t)(2 * st) * kSub, s1k = s0k + kSub;
+        const uint64_t s0m = str_m + (uint64_t)(2 * st) * kSub, s1m = s0m + kSub;
+        const uint64_t f0k = fix_k, f1k = fix_k + kSub;
+        const uint64_t f0m = fix_m;
+        const uint64_t q_k = MODE == MODE_DKV ? s0k : f0k, do_k = MODE == MODE_DKV ? s1k : f1k;
+        const uint64_t k_k = MODE == MODE_DKV ? f0k : s0k, v_k = MODE == MODE_DKV ? f1k : s1k;
+        const uint64_t q_m = MODE == MODE_DKV ? s0m : f0m, do_m = s1m;  // MN-major views (do_m: dKV pass only)
+        const uint64_t k_m = s0m;                                       // dQ pass only
 #pragma unroll
         for (int k = 0; k < HSB / 16; ++k)  // S = Q K^T
-          ptx::mma_bf16_ss(tmem_base + cS, ptx::smem_desc_sw128(q_a + k * 32), ptx::smem_desc_sw128(k_a + k * 32), id_kk,
-                           k > 0 ? 1u : 0u);
+          ptx::mma_bf16_ss(tmem_base + cS, q_k + (uint64_t)(2 * k), k_k + (uint64_t)(2 * k), id_kk, k > 0 ? 1u : 0u);
 #pragma unroll
         for (int k = 0; k < HSB / 16; ++k)  // dP = dO V^T
-          ptx::mma_bf16_ss(tmem_base + cDP, ptx::smem_desc_sw128(do_a + k * 32), ptx::smem_desc_sw128(v_a + k * 32),
-                           id_kk, k > 0 ? 1u : 0u);
+          ptx::mma_bf16_ss(tmem_base + cDP, do_k + (uint64_t)(2 * k), v_k + (uint64_t)(2 * k), id_kk, k > 0 ? 1u : 0u);
         ptx::mma_commit(s_full);
         ok = ptx::mbar_wait(p_full, ip, abort_flag, status, ST_ATTNB_TIMEOUT);
         if (!ok) break;
@@ -181,24 +193,21 @@ __global__ void __launch_bounds__(BW_THREADS, 1)
         if (MODE == MODE_DKV) {
 #pragma unroll
           for (int k = 0; k < BQ / 16; ++k) {  // contraction over the 128 queries, 16 rows (2048 B) per step
-            const uint32_t off = (uint32_t)(k * 2048);
+            const uint64_t off = (uint64_t)(k * (2048 >> 4));
             // dV[key, e] += sum_q P[q, key] dO[q, e]
-            ptx::mma_bf16_ss(tmem_base + cAcc0, ptx::smem_desc_sw128_mn(p_addr + off, SUBT),
-                             ptx::smem_desc_sw128_mn(do_a + off, SUBT), id_mm, (it > 0 || k > 0) ? 1u : 0u);
+            ptx::mma_bf16_ss(tmem_base + cAcc0, p_m + off, do_m + off, id_mm, (it > 0 || k > 0) ? 1u : 0u);
           }
 #pragma unroll
           for (int k = 0; k < BQ / 16; ++k) {
-            const uint32_t off = (uint32_t)(k * 2048);
+            const uint64_t off = (uint64_t)(k * (2048 >> 4));
             // dK[key, e] += sum_q dS[q, key] Q[q, e]
-            ptx::mma_bf16_ss(tmem_base + cAcc1, ptx::smem_desc_sw128_mn(ds_addr + off, SUBT),
-                             ptx::smem_desc_sw128_mn(q_a + off, SUBT), id_mm, (it > 0 || k > 0) ? 1u : 0u);
+            ptx::mma_bf16_ss(tmem_base + cAcc1, ds_m + off, q_m + off, id_mm, (it > 0 || k > 0) ? 1u : 0u);
           }
         } else {
 #pragma unroll
           for (int k = 0; k < BK_ / 16; ++k) {  // dQ[q, e] += sum_key dS[q, key] K[key, e]
-            const uint32_t aoff = (uint32_t)((k >> 2) * SUBT + (k & 3) * 32);
-            ptx::mma_bf16_ss(tmem_base + cAcc0, ptx::smem_desc_sw128(ds_addr + aoff),
-                             ptx::smem_desc_sw128_mn(k_a + (uint32_t)(k * 2048), SUBT), id_km,
+            const uint64_t aoff = (uint64_t)(((k >> 2) * SUBT + (k & 3) * 32) >> 4);
+            ptx::mma_bf16_ss(tmem_base + cAcc0, ds_k + aoff, k_m + (uint64_t)(k * (2048 >> 4)), id_km,
                              (it > 0 || k > 0) ? 1u : 0u);
           }
         }
