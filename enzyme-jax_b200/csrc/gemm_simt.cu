@@ -40,37 +40,64 @@ __global__ void __launch_bounds__(NT) gemm_simt_kernel(const TIn* __restrict__ A
 #pragma unroll
     for (int c = 0; c < 16; ++c) acc[r][c] = 0.f;
 
-  for (int k0 = 0; k0 < K; k0 += BK) {
-    float v[8];
-    if constexpr (!TA) {
+  // Global loads of k-tile i+1 are issued before the FMAs of k-tile i and land in registers meanwhile; small
+  // problems (one or two CTAs of four warps per SM) would otherwise pay a full memory round trip per 16 k-steps.
+  constexpr int A_ITEMS = (2 * BM + NT - 1) / NT;  // 8-element pieces of the A tile per thread
+  float va[A_ITEMS][8], vb[8];
+  auto fetch_tile = [&](int k0) {
 #pragma unroll
-      for (int idx = tid; idx < 2 * BM; idx += NT) {
-        const int row = idx >> 1, k8 = (idx & 1) * 8;
-        fetch8<TIn, VEC>(A, lda, m0 + row, k0 + k8, M, K, v);
-#pragma unroll
-        for (int j = 0; j < 8; ++j) As[k8 + j][row] = v[j];
-      }
-    } else {
-#pragma unroll
-      for (int idx = tid; idx < 2 * BM; idx += NT) {
-        const int k = idx / (BM / 8), m8 = (idx % (BM / 8)) * 8;
-        fetch8<TIn, VEC>(A, lda, k0 + k, m0 + m8, K, M, v);
-#pragma unroll
-        for (int j = 0; j < 8; ++j) As[k][m8 + j] = v[j];
+    for (int it = 0; it < A_ITEMS; ++it) {
+      const int idx = tid + it * NT;
+      if (idx < 2 * BM) {
+        if constexpr (!TA) {
+          const int row = idx >> 1, k8 = (idx & 1) * 8;
+          fetch8<TIn, VEC>(A, lda, m0 + row, k0 + k8, M, K, va[it]);
+        } else {
+          const int k = idx / (BM / 8), m8 = (idx % (BM / 8)) * 8;
+          fetch8<TIn, VEC>(A, lda, k0 + k, m0 + m8, K, M, va[it]);
+        }
       }
     }
     if constexpr (!TB) {
       const int row = tid >> 1, k8 = (tid & 1) * 8;
-      fetch8<TIn, VEC>(B, ldb, n0 + row, k0 + k8, N, K, v);
-#pragma unroll
-      for (int j = 0; j < 8; ++j) Bs[k8 + j][row] = v[j];
+      fetch8<TIn, VEC>(B, ldb, n0 + row, k0 + k8, N, K, vb);
     } else {
       const int k = tid >> 3, n8 = (tid & 7) * 8;
-      fetch8<TIn, VEC>(B, ldb, k0 + k, n0 + n8, K, N, v);
-#pragma unroll
-      for (int j = 0; j < 8; ++j) Bs[k][n8 + j] = v[j];
+      fetch8<TIn, VEC>(B, ldb, k0 + k, n0 + n8, K, N, vb);
     }
+  };
+  auto store_tile = [&]() {
+#pragma unroll
+    for (int it = 0; it < A_ITEMS; ++it) {
+      const int idx = tid + it * NT;
+      if (idx < 2 * BM) {
+        if constexpr (!TA) {
+          const int row = idx >> 1, k8 = (idx & 1) * 8;
+#pragma unroll
+          for (int j = 0; j < 8; ++j) As[k8 + j][row] = va[it][j];
+        } else {
+          const int k = idx / (BM / 8), m8 = (idx % (BM / 8)) * 8;
+#pragma unroll
+          for (int j = 0; j < 8; ++j) As[k][m8 + j] = va[it][j];
+        }
+      }
+    }
+    if constexpr (!TB) {
+      const int row = tid >> 1, k8 = (tid & 1) * 8;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) Bs[k8 + j][row] = vb[j];
+    } else {
+      const int k = tid >> 3, n8 = (tid & 7) * 8;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) Bs[k][n8 + j] = vb[j];
+    }
+  };
+
+  fetch_tile(0);
+  for (int k0 = 0; k0 < K; k0 += BK) {
+    store_tile();
     __syncthreads();
+    if (k0 + BK < K) fetch_tile(k0 + BK);
 #pragma unroll
     for (int k = 0; k < BK; ++k) {
       float a[RPT];

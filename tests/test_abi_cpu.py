@@ -78,3 +78,21 @@ def test_harness_csv_format_matches_reference(tmp_path, monkeypatch):
     assert path.endswith("results_Llama.csv")
     assert rows[0] == ["Benchmark Name", "Pass Pipeline", "Backend", "Key", "Time"] == CSV_HEADER
     assert rows[1] == ["llama", "B200", "gpu", "Primal", "0.00125"]
+
+
+def test_bench_reference_arm_prints_the_contract_line():
+    """`bench.py --impl reference` times the CPU restatement of the path and prints one JSON line with the keys the
+    measurement contract names; it needs no GPU."""
+    import json
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    out = subprocess.run([sys.executable, os.path.join(root, "bench.py"), "--impl", "reference", "--steps", "1",
+                          "--warmup", "0"], capture_output=True, text=True, timeout=600, cwd=root)
+    assert out.returncode == 0, out.stderr[-2000:]
+    line = json.loads(out.stdout.strip().splitlines()[-1])
+    assert line["impl"] == "reference" and line["metric"] == "tokens_per_second" and line["unit"] == "tokens/s"
+    assert line["higher_is_better"] is True and line["value"] > 0 and line["n_gpus"] == 1
+    assert line["cpu_baseline"]["kind"] == "port" and line["cpu_baseline"]["cores"] >= 1
+    assert line["e2e"] == {"value": line["value"], "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}
+    assert "workload" in line["config"]
