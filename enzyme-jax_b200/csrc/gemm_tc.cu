@@ -181,8 +181,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
     for (int item = blockIdx.x; item < num_items && ok; item += gridDim.x) {
       const int tile = item % num_tiles, split = item / num_tiles;
       int mt, nt;
-        tile_coords(tile, m_tiles, n_tiles, 16, mt, nt);
-        const int m0 = mt * TBM, n0 = nt * BN;
+      tile_coords(tile, m_tiles, n_tiles, 16, mt, nt);
+      const int m0 = mt * TBM, n0 = nt * BN;
       const int m = m0 + q * 32 + lane;
       const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN);
       const bool row_ok = m < M;
@@ -251,8 +251,6 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
                 store8_wide(xo + 8, hi);
               } else if (KIND == EPI_ROPE && rope64) {
                 if (n0 + cc < ep.rope_cols) {
-                  constexpr int dummy = 0;
-                  (void)dummy;
                   const int j0 = (cc % 64) >> 1;  // compile-time after unrolling: tiles start on head boundaries
 #pragma unroll
                   for (int i = 0; i < 8; ++i) {
