@@ -515,6 +515,8 @@ int32_t launch_pair_cfg(const GemmArgs& g, cudaStream_t stream) {
   const int tiles = cdiv(g.M, 2 * PM) * cdiv(g.N, BN);
   int pairs = max_pairs;
   if (g.max_ctas > 0 && g.max_ctas / 2 < pairs) pairs = g.max_ctas / 2;
+  static const int dbg_pairs = env_int("B200_DBG_PAIRS", 0);
+  if (dbg_pairs > 0 && dbg_pairs < pairs) pairs = dbg_pairs;
   if (pairs > tiles) pairs = tiles;
   B200_CUDA_OK(launch_pdl(kern, dim3(2 * pairs), dim3(P_THREADS), Cfg::kSmemBytes, stream, tmA, tmB, tmO, tmR, tmG,
                           tmU, g.M, g.N, g.K, g.epi, device_status_word()));
