@@ -54,11 +54,12 @@ def lib() -> ctypes.CDLL:
     """Loads the CUDA library; raises if it has not been built."""
     global _lib
     if _lib is None:
-        if not os.path.exists(LIB_PATH):
+        path = os.environ.get("B200_LLAMA_LIB", LIB_PATH)  # another build of the same ABI, e.g. to compare two kernels
+        if not os.path.exists(path):
             raise RuntimeError(
-                f"{LIB_PATH} is missing: build it with `python enzyme-jax_b200/build.py` "
+                f"{path} is missing: build it with `python enzyme-jax_b200/build.py` "
                 "(there is no fallback implementation)")
-        l = ctypes.CDLL(LIB_PATH)
+        l = ctypes.CDLL(path)
         l.b200_last_error.restype = c_char_p
         l.b200_version.restype = c_char_p
         for name in EXPORTS:

@@ -137,6 +137,13 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
       // encoded (16-byte units) start-address step per 16 K-elements
       constexpr uint64_t a_step = AMN ? (16 * 128) / 16 : 2;
       constexpr uint64_t b_step = BMN ? (16 * 128) / 16 : 2;
+      // descriptors of stage 0, built once: a stage adds its byte offset >> 4 to the 14-bit address field (shared-memory
+      // addresses stay below 2^18, so it never carries); this thread's instruction stream is what bounds narrow tiles
+      const uint32_t s0 = ptx::smem_u32(smem);
+      const uint64_t a_base = AMN ? ptx::smem_desc_sw128_mn(s0, kMnBoxBytes) : ptx::smem_desc_sw128(s0);
+      const uint64_t b_base = BMN ? ptx::smem_desc_sw128_mn(s0 + Cfg::kABytes, kMnBoxBytes)
+                                  : ptx::smem_desc_sw128(s0 + Cfg::kABytes);
+      constexpr uint64_t stage_step = Cfg::kStageBytes >> 4;
       int stage = 0;
       uint32_t phase = 0;
       int acc = 0;
@@ -153,10 +160,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
           ok = ptx::mbar_wait(&full_bar[stage], phase, abort_flag, status, ST_MMA_TIMEOUT);
           if (!ok) break;
           ptx::tc_fence_after_sync();
-          const uint32_t sa = ptx::smem_u32(smem + stage * Cfg::kStageBytes);
-          const uint64_t adesc = AMN ? ptx::smem_desc_sw128_mn(sa, kMnBoxBytes) : ptx::smem_desc_sw128(sa);
-          const uint64_t bdesc = BMN ? ptx::smem_desc_sw128_mn(sa + Cfg::kABytes, kMnBoxBytes)
-                                     : ptx::smem_desc_sw128(sa + Cfg::kABytes);
+          const uint64_t adesc = a_base + (uint64_t)stage * stage_step;
+          const uint64_t bdesc = b_base + (uint64_t)stage * stage_step;
 #pragma unroll
           for (int k = 0; k < TBK / UMMA_K; ++k) {
             // K-major: 16 elements further along a 128-byte row = 32 bytes;

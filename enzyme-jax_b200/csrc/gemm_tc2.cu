@@ -174,6 +174,11 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(P_THREADS, 1)
   } else if (warp == 1) {
     if (lane == 0 && rank == 0) {
       constexpr uint32_t idesc = ptx::idesc_bf16_f32(2 * PM, BN);
+      // descriptors of stage 0, built once: a stage adds its byte offset >> 4 to the 14-bit address field (shared-memory
+      // addresses stay below 2^18, so it never carries); this thread's instruction stream is what bounds narrow tiles
+      const uint32_t s0 = ptx::smem_u32(smem);
+      const uint64_t a_base = ptx::smem_desc_sw128(s0), b_base = ptx::smem_desc_sw128(s0 + Cfg::kABytes);
+      constexpr uint64_t stage_step = Cfg::kStageBytes >> 4;
       int stage = 0;
       uint32_t phase = 0;
       int acc = 0;
@@ -188,9 +193,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(P_THREADS, 1)
           ok = ptx::mbar_wait(&full_bar[stage], phase, abort_flag, status, ST_PAIR_MMA);
           if (!ok) break;
           ptx::tc_fence_after_sync();
-          const uint32_t sa = ptx::smem_u32(smem + stage * Cfg::kStageBytes);
-          const uint64_t adesc = ptx::smem_desc_sw128(sa);
-          const uint64_t bdesc = ptx::smem_desc_sw128(sa + Cfg::kABytes);
+          const uint64_t adesc = a_base + (uint64_t)stage * stage_step;
+          const uint64_t bdesc = b_base + (uint64_t)stage * stage_step;
 #pragma unroll
           for (int k = 0; k < PK / 16; ++k)
             mma_pair_bf16_ss(d_tmem, adesc + (uint64_t)(2 * k), bdesc + (uint64_t)(2 * k), idesc,
@@ -515,8 +519,6 @@ int32_t launch_pair_cfg(const GemmArgs& g, cudaStream_t stream) {
   const int tiles = cdiv(g.M, 2 * PM) * cdiv(g.N, BN);
   int pairs = max_pairs;
   if (g.max_ctas > 0 && g.max_ctas / 2 < pairs) pairs = g.max_ctas / 2;
-  static const int dbg_pairs = env_int("B200_DBG_PAIRS", 0);
-  if (dbg_pairs > 0 && dbg_pairs < pairs) pairs = dbg_pairs;
   if (pairs > tiles) pairs = tiles;
   B200_CUDA_OK(launch_pdl(kern, dim3(2 * pairs), dim3(P_THREADS), Cfg::kSmemBytes, stream, tmA, tmB, tmO, tmR, tmG,
                           tmU, g.M, g.N, g.K, g.epi, device_status_word()));
