@@ -35,7 +35,9 @@ template <int BN, int KIND> struct PairCfg {
   // staging buffers of the four epilogue warps: 32 rows x 128 bytes (x 64 bytes for SwiGLU, which has up to
   // three output matrices); two in flight per output, four for the residual add (they also receive its read side)
   static constexpr int kBufBytes = KIND == EPI_SWIGLU ? 2048 : 4096;
-  static constexpr int kBufs = KIND == EPI_SWIGLU ? 6 : (KIND == EPI_RESID ? 4 : 2);
+  // The residual add keeps as many residual chunks in flight as it has boxes; fewer boxes leave room for one more
+  // pipeline stage, which the short mainloops (K = 768, 192-column tiles) need more than a deep epilogue.
+  static constexpr int kBufs = KIND == EPI_SWIGLU ? 6 : (KIND == EPI_RESID ? (BN == 192 ? 3 : 2) : 2);
   static constexpr int kStagingBytes = 4 * kBufs * kBufBytes;
   static constexpr int kBudget = 227 * 1024 - 2048 - kStagingBytes;  // 1 KB alignment slack, 1 KB barriers
   static constexpr int kStages = kBudget / kStageBytes > 8 ? 8 : kBudget / kStageBytes;
@@ -248,12 +250,12 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(P_THREADS, 1)
         }
       }
       if (KIND == EPI_RESID) {
-        // the residual tile comes in by TMA too, into the buffers its sum leaves from; the first four
+        // the residual tile comes in by TMA too, into the buffers its sum leaves from; the first
         // 32-column chunks are requested before the accumulator is waited for
         if (lane == 0) {
           ptx::tma_store_wait_read<0>();
 #pragma unroll
-          for (int i = 0; i < (BN / 32 < 4 ? BN / 32 : 4); ++i)
+          for (int i = 0; i < (BN / 32 < NBUF ? BN / 32 : NBUF); ++i)
             if (n0 + 32 * i < N) {
               ptx::mbar_arrive_expect_tx(&rbar[i], 4096u);
               ptx::tma_load_2d(stg_ptr + i * BUFB, &tmR, n0 + 32 * i, mrow0, &rbar[i]);
@@ -355,7 +357,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(P_THREADS, 1)
               }
             }
           } else if constexpr (KIND == EPI_RESID) {
-            const int i = c >> 5, b = i & 3;
+            const int i = c >> 5, b = i % NBUF;
             ok = ptx::mbar_wait_warp(&rbar[b], (rphase >> b) & 1u, abort_flag, status, ST_PAIR_EPILOGUE);
             if (!ok) break;
             rphase ^= 1u << b;
@@ -375,12 +377,12 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(P_THREADS, 1)
             if (lane == 0) {
               ptx::tma_store_2d(&tmO, stg + (uint32_t)(b * BUFB), n0 + c, mrow0);
               ptx::tma_store_commit();
-              // chunk i+3 goes where chunk i-1 left from, once that store has read its tile
-              if (i >= 1 && i + 3 < BN / 32 && n0 + 32 * (i + 3) < N) {
+              // the next chunk without a box goes where chunk i-1 left from, once that store has read its tile
+              if (i >= 1 && i - 1 + NBUF < BN / 32 && n0 + 32 * (i - 1 + NBUF) < N) {
                 ptx::tma_store_wait_read<1>();
-                const int nb = (i + 3) & 3;
+                const int nb = (i - 1) % NBUF;
                 ptx::mbar_arrive_expect_tx(&rbar[nb], 4096u);
-                ptx::tma_load_2d(stg_ptr + nb * BUFB, &tmR, n0 + 32 * (i + 3), mrow0, &rbar[nb]);
+                ptx::tma_load_2d(stg_ptr + nb * BUFB, &tmR, n0 + 32 * (i - 1 + NBUF), mrow0, &rbar[nb]);
               }
             }
           } else {  // EPI_SWIGLU: 64 accumulator columns = 32 outputs = one 64-byte-wide box per output matrix
