@@ -162,31 +162,41 @@ __global__ void __launch_bounds__(BW_THREADS, 1)
       const uint64_t ds_m = ptx::smem_desc_sw128_mn(ptx::smem_u32(smem + kDS), SUBT);
       const uint64_t ds_k = ptx::smem_desc_sw128(ptx::smem_u32(smem + kDS));
       constexpr uint64_t kSub = SUBT >> 4;
-      bool ok = ptx::mbar_wait(fix_full, 0, abort_flag, status, ST_ATTNB_TIMEOUT);
-      for (int it = 0; it < n_it && ok; ++it) {
-        const int st = it & 1;
-        const uint32_t ph = (uint32_t)(it >> 1) & 1u;
-        const uint32_t ip = (uint32_t)it & 1u;
-        ok = ptx::mbar_wait(&str_full[st], ph, abort_flag, status, ST_ATTNB_TIMEOUT) &&
-             ptx::mbar_wait(s_empty, ip ^ 1u, abort_flag, status, ST_ATTNB_TIMEOUT);
-        if (!ok) break;
-        ptx::tc_fence_after_sync();
-        // streamed pair (stage st): sub-tile 0 and 1; fixed pair: sub-tile 0 and 1
+      // S = Q K^T and dP = dO V^T of one streamed pair (stage st)
+      auto issue_scores = [&](int st) {
         const uint64_t s0k = str_k + (uint64_t)(2 * st) * kSub, s1k = s0k + kSub;
-        const uint64_t s0m = str_m + (uint64_t)(2 * st) * kSub, s1m = s0m + kSub;
         const uint64_t f0k = fix_k, f1k = fix_k + kSub;
-        const uint64_t f0m = fix_m;
         const uint64_t q_k = MODE == MODE_DKV ? s0k : f0k, do_k = MODE == MODE_DKV ? s1k : f1k;
         const uint64_t k_k = MODE == MODE_DKV ? f0k : s0k, v_k = MODE == MODE_DKV ? f1k : s1k;
-        const uint64_t q_m = MODE == MODE_DKV ? s0m : f0m, do_m = s1m;  // MN-major views (do_m: dKV pass only)
-        const uint64_t k_m = s0m;                                       // dQ pass only
 #pragma unroll
-        for (int k = 0; k < HSB / 16; ++k)  // S = Q K^T
+        for (int k = 0; k < HSB / 16; ++k)
           ptx::mma_bf16_ss(tmem_base + cS, q_k + (uint64_t)(2 * k), k_k + (uint64_t)(2 * k), id_kk, k > 0 ? 1u : 0u);
 #pragma unroll
-        for (int k = 0; k < HSB / 16; ++k)  // dP = dO V^T
+        for (int k = 0; k < HSB / 16; ++k)
           ptx::mma_bf16_ss(tmem_base + cDP, do_k + (uint64_t)(2 * k), v_k + (uint64_t)(2 * k), id_kk, k > 0 ? 1u : 0u);
         ptx::mma_commit(s_full);
+      };
+      bool ok = ptx::mbar_wait(fix_full, 0, abort_flag, status, ST_ATTNB_TIMEOUT) &&
+                ptx::mbar_wait(&str_full[0], 0, abort_flag, status, ST_ATTNB_TIMEOUT);
+      if (ok) {
+        ptx::tc_fence_after_sync();
+        issue_scores(0);
+      }
+      for (int it = 0; it < n_it && ok; ++it) {
+        const int st = it & 1;
+        const uint32_t ip = (uint32_t)it & 1u;
+        if (it + 1 < n_it) {
+          // the next pair's scores as soon as the softmax threads hold this pair's S and dP in registers: they are
+          // computed beside this pair's exponentials
+          ok = ptx::mbar_wait(&str_full[st ^ 1], (uint32_t)((it + 1) >> 1) & 1u, abort_flag, status, ST_ATTNB_TIMEOUT) &&
+               ptx::mbar_wait(s_empty, ip, abort_flag, status, ST_ATTNB_TIMEOUT);
+          if (!ok) break;
+          ptx::tc_fence_after_sync();
+          issue_scores(st ^ 1);
+        }
+        const uint64_t s0m = str_m + (uint64_t)(2 * st) * kSub, s1m = s0m + kSub;
+        const uint64_t q_m = MODE == MODE_DKV ? s0m : fix_m, do_m = s1m;  // MN-major views (do_m: dKV pass only)
+        const uint64_t k_m = s0m;                                        // dQ pass only
         ok = ptx::mbar_wait(p_full, ip, abort_flag, status, ST_ATTNB_TIMEOUT);
         if (!ok) break;
         ptx::tc_fence_after_sync();
@@ -237,8 +247,6 @@ __global__ void __launch_bounds__(BW_THREADS, 1)
       const bool diag = qb == kb;
       const int u0 = kb * 128 + hf * 64;
       ok = ptx::mbar_wait(s_full, ip, abort_flag, status, ST_ATTNB_TIMEOUT);
-      // the P / dS tiles of the previous pair must have been consumed
-      if (ok && it > 0) ok = ptx::mbar_wait(g_done, ip ^ 1u, abort_flag, status, ST_ATTNB_TIMEOUT);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       ptx::tc_fence_after_sync();
@@ -248,6 +256,17 @@ __global__ void __launch_bounds__(BW_THREADS, 1)
         ptx::tmem_ld32(lane_base + (uint32_t)(cS + hf * 64 + c), sv);
         ptx::tmem_ld32(lane_base + (uint32_t)(cDP + hf * 64 + c), dp);
         ptx::tmem_ld_wait();
+        if (c == 32) {
+          // S and dP of this pair are in registers: the MMA warp may compute the next pair's
+          ptx::tc_fence_before_sync();
+          ptx::mbar_arrive(s_empty);
+        }
+        if (c == 0 && it > 0) {
+          // the P / dS tiles of the previous pair must have been consumed before they are overwritten
+          ok = ptx::mbar_wait(g_done, ip ^ 1u, abort_flag, status, ST_ATTNB_TIMEOUT);
+          ok = __all_sync(0xffffffffu, ok);
+          if (!ok) break;
+        }
 #pragma unroll
         for (int g = 0; g < 4; ++g) {
           uint4 praw, draw;
@@ -271,8 +290,7 @@ __global__ void __launch_bounds__(BW_THREADS, 1)
           *reinterpret_cast<uint4*>(ds_row + off) = draw;
         }
       }
-      ptx::tc_fence_before_sync();
-      ptx::mbar_arrive(s_empty);
+      if (!ok) break;
       ptx::fence_proxy_async();
       ptx::mbar_arrive(p_full);
     }
