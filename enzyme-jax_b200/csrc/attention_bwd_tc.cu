@@ -36,9 +36,9 @@ enum : uint32_t { ST_ATTNB_TIMEOUT = 1u << 6, ST_ATTNB_ALIGN = 1u << 7 };
 constexpr int kFix0 = 0;                 // fixed tile 0 (DKV: K_j, DQ: Q_i)
 constexpr int kFix1 = SUBT;              // fixed tile 1 (DKV: V_j, DQ: dO_i)
 constexpr int kStr = 2 * SUBT;           // 2 stages x {tile 0 (DKV: Q_i, DQ: K_j), tile 1 (DKV: dO_i, DQ: V_j)}
-constexpr int kP = kStr + 4 * SUBT;      // P  [128 q][128 k] as two sub-tiles (keys 0..63, 64..127)
-constexpr int kDS = kP + 2 * SUBT;       // dS, same layout
-constexpr int kBars = kDS + 2 * SUBT;
+constexpr int kP = kStr + 4 * SUBT;      // 2 x P  [128 q][128 k] as two sub-tiles (keys 0..63, 64..127); pairs alternate
+constexpr int kDS = kP + 4 * SUBT;       // 2 x dS, same layout
+constexpr int kBars = kDS + 4 * SUBT;    // 14 sub-tiles = 224 KB
 constexpr int kBwdSmem = kBars + 256;
 // TMEM columns
 constexpr int cS = 0, cDP = 128, cAcc0 = 256, cAcc1 = 320, kBwdTmem = 512;
@@ -66,8 +66,8 @@ __global__ void __launch_bounds__(BW_THREADS, 1)
   uint64_t* s_full = bars + 5;      // S and dP complete in TMEM
   uint64_t* s_empty = bars + 6;     // S and dP have been read
   uint64_t* p_full = bars + 7;      // P / dS tiles written
-  uint64_t* g_done = bars + 8;      // accumulating MMAs of the pair are done (P / dS tiles free)
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 9);
+  uint64_t* g_done = bars + 8;      // [2] accumulating MMAs of a pair are done (its P / dS buffer is free); pairs alternate
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 10);
   volatile uint32_t* abort_flag = tmem_slot + 1;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -97,7 +97,8 @@ __global__ void __launch_bounds__(BW_THREADS, 1)
     ptx::mbar_init(s_full, 1);
     ptx::mbar_init(s_empty, 256);
     ptx::mbar_init(p_full, 256);
-    ptx::mbar_init(g_done, 1);
+    ptx::mbar_init(&g_done[0], 1);
+    ptx::mbar_init(&g_done[1], 1);
     ptx::fence_barrier_init();
     ptx::tma_prefetch_desc(&tmQ);
     ptx::tma_prefetch_desc(&tmK);
@@ -197,6 +198,7 @@ __global__ void __launch_bounds__(BW_THREADS, 1)
         const uint64_t s0m = str_m + (uint64_t)(2 * st) * kSub, s1m = s0m + kSub;
         const uint64_t q_m = MODE == MODE_DKV ? s0m : fix_m, do_m = s1m;  // MN-major views (do_m: dKV pass only)
         const uint64_t k_m = s0m;                                        // dQ pass only
+        const uint64_t pb = (uint64_t)(2 * st) * kSub;                   // this pair's P / dS buffer
         ok = ptx::mbar_wait(p_full, ip, abort_flag, status, ST_ATTNB_TIMEOUT);
         if (!ok) break;
         ptx::tc_fence_after_sync();
@@ -205,23 +207,23 @@ __global__ void __launch_bounds__(BW_THREADS, 1)
           for (int k = 0; k < BQ / 16; ++k) {  // contraction over the 128 queries, 16 rows (2048 B) per step
             const uint64_t off = (uint64_t)(k * (2048 >> 4));
             // dV[key, e] += sum_q P[q, key] dO[q, e]
-            ptx::mma_bf16_ss(tmem_base + cAcc0, p_m + off, do_m + off, id_mm, (it > 0 || k > 0) ? 1u : 0u);
+            ptx::mma_bf16_ss(tmem_base + cAcc0, p_m + pb + off, do_m + off, id_mm, (it > 0 || k > 0) ? 1u : 0u);
           }
 #pragma unroll
           for (int k = 0; k < BQ / 16; ++k) {
             const uint64_t off = (uint64_t)(k * (2048 >> 4));
             // dK[key, e] += sum_q dS[q, key] Q[q, e]
-            ptx::mma_bf16_ss(tmem_base + cAcc1, ds_m + off, q_m + off, id_mm, (it > 0 || k > 0) ? 1u : 0u);
+            ptx::mma_bf16_ss(tmem_base + cAcc1, ds_m + pb + off, q_m + off, id_mm, (it > 0 || k > 0) ? 1u : 0u);
           }
         } else {
 #pragma unroll
           for (int k = 0; k < BK_ / 16; ++k) {  // dQ[q, e] += sum_key dS[q, key] K[key, e]
             const uint64_t aoff = (uint64_t)(((k >> 2) * SUBT + (k & 3) * 32) >> 4);
-            ptx::mma_bf16_ss(tmem_base + cAcc0, ds_k + aoff, k_m + (uint64_t)(k * (2048 >> 4)), id_km,
+            ptx::mma_bf16_ss(tmem_base + cAcc0, ds_k + pb + aoff, k_m + (uint64_t)(k * (2048 >> 4)), id_km,
                              (it > 0 || k > 0) ? 1u : 0u);
           }
         }
-        ptx::mma_commit(g_done);
+        ptx::mma_commit(&g_done[st]);
         ptx::mma_commit(&str_empty[st]);
       }
     }
@@ -232,8 +234,8 @@ __global__ void __launch_bounds__(BW_THREADS, 1)
     const int row = qd * 32 + lane;  // TMEM lane: the query row of the pair
     const uint32_t lane_base = tmem_base + ((uint32_t)(qd * 32) << 16);
     const float sl2 = prm.scale * 1.4426950408889634f;
-    uint8_t* p_row = smem + kP + hf * SUBT + row * 128;
-    uint8_t* ds_row = smem + kDS + hf * SUBT + row * 128;
+    uint8_t* p_row0 = smem + kP + hf * SUBT + row * 128;
+    uint8_t* ds_row0 = smem + kDS + hf * SUBT + row * 128;
     bool ok = true;
     for (int it = 0; it < n_it; ++it) {
       const uint32_t ip = (uint32_t)it & 1u;
@@ -246,6 +248,8 @@ __global__ void __launch_bounds__(BW_THREADS, 1)
       const float dlt = prm.delta[stat];
       const bool diag = qb == kb;
       const int u0 = kb * 128 + hf * 64;
+      uint8_t* p_row = p_row0 + (it & 1) * 2 * SUBT;  // pairs alternate between two P / dS buffers
+      uint8_t* ds_row = ds_row0 + (it & 1) * 2 * SUBT;
       ok = ptx::mbar_wait(s_full, ip, abort_flag, status, ST_ATTNB_TIMEOUT);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
@@ -261,9 +265,9 @@ __global__ void __launch_bounds__(BW_THREADS, 1)
           ptx::tc_fence_before_sync();
           ptx::mbar_arrive(s_empty);
         }
-        if (c == 0 && it > 0) {
-          // the P / dS tiles of the previous pair must have been consumed before they are overwritten
-          ok = ptx::mbar_wait(g_done, ip ^ 1u, abort_flag, status, ST_ATTNB_TIMEOUT);
+        if (c == 0 && it > 1) {
+          // this buffer's P / dS of two pairs ago must have been consumed before they are overwritten
+          ok = ptx::mbar_wait(&g_done[it & 1], (uint32_t)((it - 2) >> 1) & 1u, abort_flag, status, ST_ATTNB_TIMEOUT);
           ok = __all_sync(0xffffffffu, ok);
           if (!ok) break;
         }
@@ -295,7 +299,8 @@ __global__ void __launch_bounds__(BW_THREADS, 1)
       ptx::mbar_arrive(p_full);
     }
     // epilogue: the last pair's accumulating MMAs complete the sums
-    if (ok) ok = ptx::mbar_wait(g_done, (uint32_t)(n_it - 1) & 1u, abort_flag, status, ST_ATTNB_TIMEOUT);
+    if (ok) ok = ptx::mbar_wait(&g_done[(n_it - 1) & 1], (uint32_t)((n_it - 1) >> 1) & 1u, abort_flag, status,
+                                ST_ATTNB_TIMEOUT);
     ok = __all_sync(0xffffffffu, ok);
     if (ok) {
       ptx::tc_fence_after_sync();
