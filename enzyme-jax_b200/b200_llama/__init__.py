@@ -33,7 +33,7 @@ EXPORTS = (
     "b200_gemm", "b200_rmsnorm", "b200_attention", "b200_comm_unique_id", "b200_comm_init_rank",
     "b200_comm_destroy", "b200_launch_count", "b200_profile_enable", "b200_profile_read",
     "b200_attention_decode_scratch_bytes", "b200_attention_decode", "b200_attention_decode_static",
-    "b200_attention_backward", "b200_comm_peer_memory", "b200_selftest_bounded_wait",
+    "b200_attention_backward", "b200_comm_peer_memory", "b200_selftest_bounded_wait", "b200_argmax",
 )
 
 
@@ -94,6 +94,7 @@ def lib() -> ctypes.CDLL:
         l.b200_attention_decode_static.argtypes = [c_void_p] * 4 + [c_int32] * 10 + [c_void_p]
         l.b200_attention_backward.argtypes = [c_void_p] * 10 + [c_int32] * 9 + [c_void_p]
         l.b200_selftest_bounded_wait.argtypes = [ctypes.c_int64, c_void_p, c_void_p]
+        l.b200_argmax.argtypes = [c_void_p, c_int32, c_int32, c_int32, c_void_p, c_void_p]
         l.b200_device_status.argtypes = [c_void_p, POINTER(c_uint32)]
         l.b200_comm_unique_id.argtypes = [c_void_p]
         l.b200_comm_init_rank.argtypes = [c_void_p, c_int32, c_int32, POINTER(c_void_p)]
@@ -241,6 +242,41 @@ def attention_decode_static(q: torch.Tensor, kv_layer: torch.Tensor, page_table:
 # --------------------------------------------------------------------------
 # communicator
 # --------------------------------------------------------------------------
+
+def argmax(logits: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Row-wise argmax of fp32 logits [rows, cols] on the device (lowest index among equal maxima) -> int32 [rows]."""
+    if logits.dtype != torch.float32 or logits.dim() != 2 or logits.stride(1) != 1:
+        raise B200Error(3, "argmax takes fp32 [rows, cols] logits with unit column stride")
+    if out is None:
+        out = torch.empty(logits.shape[0], dtype=torch.int32, device=logits.device)
+    check(lib().b200_argmax(logits.data_ptr(), logits.shape[0], logits.shape[1], logits.stride(0), out.data_ptr(),
+                            _stream()))
+    return out
+
+
+class PageAllocator:
+    """Free list over the pages of one KV pool (host side).  Sequences take whole pages; a page table row lists a
+    sequence's pages in position order, as ``b200_decode_step`` reads it."""
+
+    def __init__(self, n_pages: int):
+        self.n_pages = int(n_pages)
+        self._free = list(range(self.n_pages - 1, -1, -1))
+
+    @property
+    def free_pages(self) -> int:
+        return len(self._free)
+
+    def alloc(self, n: int):
+        if n > len(self._free):
+            raise B200Error(5, f"KV pool exhausted: {n} pages wanted, {len(self._free)} free")
+        return [self._free.pop() for _ in range(n)]
+
+    def free(self, pages) -> None:
+        for p in pages:
+            if not 0 <= p < self.n_pages or p in self._free:
+                raise B200Error(1, f"page {p} is not an allocated page of this pool")
+        self._free.extend(reversed(list(pages)))
+
 
 class Comm:
     """NCCL communicator created from a unique id that rank 0 shares through
@@ -441,3 +477,50 @@ class Plan:
                                      page_table.shape[1], _ptr(hidden), _ptr(logits) if want_logits else None,
                                      ws.data_ptr(), ws.numel(), _stream()))
         return hidden, (logits if want_logits else None)
+
+    def generate(self, prompt: torch.Tensor, n_new: int, *, page_size: int = 64,
+                 kv_pages: Optional[torch.Tensor] = None, allocator: Optional["PageAllocator"] = None) -> torch.Tensor:
+        """Greedy decoding: prefill the int32 prompts [B, S0], then ``n_new`` decode steps whose next token is the
+        on-device argmax of the step's logits (no logits leave the GPU).  KV rows live in pages taken from
+        ``allocator`` (a pool of ``kv_pages``; both are created when absent) and are returned to it at the end.
+        Returns int32 [B, S0 + n_new].  One GPU (the vocabulary is not sharded)."""
+        if self.tp_size != 1:
+            raise B200Error(10, "generate needs the whole vocabulary on one GPU")
+        B, S0 = prompt.shape
+        total = S0 + n_new
+        if total > self.config["seq_len"]:
+            raise B200Error(2, f"{total} positions exceed the plan's seq_len={self.config['seq_len']}")
+        per_seq = (total + page_size - 1) // page_size
+        if kv_pages is None:
+            kv_pages = self.new_kv_pages(B * per_seq, page_size)
+        if allocator is None:
+            allocator = PageAllocator(kv_pages.shape[2])
+        owned = []
+        try:
+            for _ in range(B):
+                owned.append(allocator.alloc(per_seq))
+            table = torch.tensor(owned, dtype=torch.int32, device=self.device)
+            # prefill: logits of every prompt position and the rotated K / V rows, scattered into the pages
+            L, H = self.config["n_layers"], self.config["n_heads"]
+            hs = self.config["dim"] // H
+            kv_flat = torch.empty(L, 2, B, S0, H * hs, dtype=self.dtype, device=self.device)
+            logits = self.forward(prompt, kv_out=kv_flat)
+            pos = torch.arange(S0, device=self.device)
+            pg = table.long()[:, pos // page_size].reshape(-1)            # [B*S0] page of every (sequence, position)
+            off = (pos % page_size).repeat(B)
+            # advanced indices on the page and row dimensions come first in the indexed view: [B*S0, L, 2, H, hs]
+            kv_pages[:, :, pg, :, off, :] = kv_flat.view(L, 2, B * S0, H, hs).permute(2, 0, 1, 3, 4)
+            out = torch.empty(B, total, dtype=torch.int32, device=self.device)
+            out[:, :S0] = prompt
+            cur = argmax(logits[:, -1, :])
+            step_logits = torch.empty(B, self.vocab_local, dtype=torch.float32, device=self.device)
+            for i in range(n_new):
+                out[:, S0 + i] = cur
+                if i + 1 == n_new:
+                    break
+                self.decode_step(S0 + i, kv_pages, table, tokens=cur, logits=step_logits)
+                cur = argmax(step_logits)
+            return out
+        finally:
+            for pages in owned:
+                allocator.free(pages)

@@ -435,6 +435,38 @@ inline int grid_for(size_t work_items, int threads) {
   else if (sd == B200_BF16 && dd == B200_BF16) { using TS = bf16; using TD = bf16; CALL; } \
   else return fail(B200_ERR_BAD_DTYPE, "unsupported dtype pair %d -> %d", sd, dd);
 
+// ---- greedy sampling ---------------------------------------------------------
+// out[r] = index of the largest of row r's `cols` values, the lowest index among equals (numpy / torch argmax).
+__global__ void __launch_bounds__(256) argmax_rows_kernel(const float* __restrict__ x, int cols, int ld,
+                                                          int32_t* __restrict__ out) {
+  __shared__ float s_v[8];
+  __shared__ int s_i[8];
+  const int row = blockIdx.x;
+  const float* xr = x + (size_t)row * ld;
+  pdl_launch_dependents();
+  pdl_wait();
+  float bv = -INFINITY;
+  int bi = 0x7fffffff;
+  for (int c = threadIdx.x; c < cols; c += blockDim.x) {
+    const float v = xr[c];
+    if (v > bv || (v == bv && c < bi)) { bv = v; bi = c; }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+    if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+  }
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (lane == 0) { s_v[warp] = bv; s_i[warp] = bi; }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int w = 1; w < 8; ++w)
+      if (s_v[w] > bv || (s_v[w] == bv && s_i[w] < bi)) { bv = s_v[w]; bi = s_i[w]; }
+    out[row] = bi == 0x7fffffff ? 0 : bi;  // a row of NaNs compares false everywhere: report index 0
+  }
+}
+
 }  // namespace
 
 int32_t launch_embed(const int32_t* tokens, const void* table, int table_dtype, float* x, int n_tokens, int dim,
@@ -626,6 +658,13 @@ int32_t launch_zero_f32(float* x, size_t n, cudaStream_t stream) {
   if (n % 4) return fail(B200_ERR_BAD_SHAPE, "zero: count must be a multiple of 4");
   zero_kernel<<<grid_for(n / 4, 256), 256, 0, stream>>>(reinterpret_cast<float4*>(x), n / 4);
   B200_LAUNCH_OK("zero_kernel");
+  return B200_OK;
+}
+
+int32_t launch_argmax_rows(const float* x, int rows, int cols, int ld, int32_t* out, cudaStream_t stream) {
+  if (rows <= 0 || cols <= 0 || ld < cols) return fail(B200_ERR_BAD_SHAPE, "argmax: rows=%d cols=%d ld=%d", rows, cols, ld);
+  B200_CUDA_OK(launch_pdl(argmax_rows_kernel, dim3(rows), dim3(256), 0, stream, x, cols, ld, out));
+  B200_LAUNCH_OK("argmax_rows_kernel");
   return B200_OK;
 }
 

@@ -67,4 +67,7 @@ int32_t launch_convert(const void* src, int src_dtype, void* dst, int dst_dtype,
 // x[i] = 0
 int32_t launch_zero_f32(float* x, size_t n, cudaStream_t stream);
 
+// out[r] = argmax of row r (lowest index among equal maxima): greedy sampling from fp32 logits
+int32_t launch_argmax_rows(const float* x, int rows, int cols, int ld, int32_t* out, cudaStream_t stream);
+
 }  // namespace b200

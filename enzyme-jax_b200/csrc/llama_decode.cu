@@ -237,6 +237,12 @@ int32_t b200_attention_backward(const void* q, const void* k, const void* v, con
   return launch_attn_bwd(a, impl, reinterpret_cast<cudaStream_t>(stream));
 }
 
+int32_t b200_argmax(const float* logits, int32_t rows, int32_t cols, int32_t ld, int32_t* out_tokens,
+                    b200_stream_t stream) {
+  if (!logits || !out_tokens) return fail(B200_ERR_INVALID_ARG, "null argument");
+  return launch_argmax_rows(logits, rows, cols, ld, out_tokens, reinterpret_cast<cudaStream_t>(stream));
+}
+
 int32_t b200_selftest_bounded_wait(int64_t budget_cycles, uint32_t* reached_end_device, b200_stream_t stream) {
   if (!reached_end_device) return fail(B200_ERR_INVALID_ARG, "null argument");
   if (budget_cycles <= 0 || budget_cycles > 4000000000LL) return fail(B200_ERR_INVALID_ARG, "budget out of range");

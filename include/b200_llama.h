@@ -103,6 +103,13 @@ B200_API const char* b200_version(void);
  * B200_OK or B200_ERR_TIMEOUT; *code receives the raw word. */
 B200_API int32_t b200_device_status(b200_stream_t stream, uint32_t* code);
 
+/* Greedy sampling on the device: out_tokens[r] = argmax of the r-th row of fp32 logits [rows, ld] (first `cols`
+ * columns; the lowest index among equal maxima).  The decode loop feeds out_tokens straight back into
+ * b200_decode_step, so no logits leave the GPU.  The reference leaves sampling to its caller (test/llama.py returns the
+ * hidden state); this is the device-side half of the decode loop the serving configuration needs. */
+B200_API int32_t b200_argmax(const float* logits, int32_t rows, int32_t cols, int32_t ld, int32_t* out_tokens,
+                             b200_stream_t stream);
+
 /* Failure-detection self-test: launches one CTA that waits, with a budget of budget_cycles SM
  * clocks, on an mbarrier nothing ever signals.  The wait gives up, the kernel writes 1 to
  * *reached_end_device and returns, and the next b200_device_status call answers

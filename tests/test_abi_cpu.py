@@ -4,6 +4,8 @@ import ctypes
 import os
 import re
 
+import pytest
+
 import b200_llama as B
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
@@ -96,3 +98,16 @@ def test_bench_reference_arm_prints_the_contract_line():
     assert line["cpu_baseline"]["kind"] == "port" and line["cpu_baseline"]["cores"] >= 1
     assert line["e2e"] == {"value": line["value"], "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}
     assert "workload" in line["config"]
+
+
+def test_page_allocator_host_logic():
+    a = B.PageAllocator(6)
+    x = a.alloc(4)
+    assert sorted(x) == x and len(set(x)) == 4 and a.free_pages == 2
+    a.free([x[1], x[2]])
+    y = a.alloc(3)
+    assert len(set(y) | {x[0], x[3]}) == 5 and a.free_pages == 1
+    with pytest.raises(B.B200Error):
+        a.alloc(2)                                   # exhausted
+    with pytest.raises(B.B200Error):
+        a.free([a.alloc(1)[0], 99])                  # not a page of this pool
