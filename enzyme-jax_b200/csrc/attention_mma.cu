@@ -71,8 +71,7 @@ __global__ void __launch_bounds__(A_THREADS, HS == 64 ? 2 : 1)
   uint64_t* s_full = bars + 5;      // S_j complete in TMEM
   uint64_t* s_empty = bars + 6;     // softmax has read S_j
   uint64_t* p_full = bars + 7;      // P_j is in shared memory
-  uint64_t* o_full = bars + 8;      // O_j complete in TMEM (P_j and the stage are free)
-  uint64_t* o_empty = bars + 9;     // softmax has read O_j
+  uint64_t* o_full = bars + 8;      // O += P_j V_j complete in TMEM (P_j and the stage are free, O at rest)
   uint64_t* x_bar = bars + 10;      // the two threads of every row have published their block maximum
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 11);  // 11 barriers + 2 words = 96 bytes
   volatile uint32_t* abort_flag = tmem_slot + 1;
@@ -103,7 +102,6 @@ __global__ void __launch_bounds__(A_THREADS, HS == 64 ? 2 : 1)
     ptx::mbar_init(s_empty, 256);
     ptx::mbar_init(p_full, 256);
     ptx::mbar_init(o_full, 1);
-    ptx::mbar_init(o_empty, 256);
     ptx::mbar_init(x_bar, 256);
     ptx::fence_barrier_init();
     ptx::tma_prefetch_desc(&tmQ);

@@ -13,6 +13,11 @@
 // of the second CTA complete their bytes on the leader's mbarrier.  tcgen05.commit
 // reaches both CTAs' barriers.  All waits are bounded; the CTAs of a pair meet at
 // a cluster barrier before the first remote signal and before exit.
+//
+// Epilogue: four warps per CTA take the accumulator TMEM -> registers -> 32-row
+// boxes in shared memory (swizzled as the output tensor map expects) -> bulk
+// tensor stores, a few boxes in flight per warp; the residual add receives its
+// fp32 residual tile through TMA loads into the same boxes.
 #include <cuda.h>
 
 #include "gemm_epilogue.cuh"
