@@ -179,5 +179,10 @@ int32_t launch_bounded_wait_selftest(long long budget_cycles, uint32_t* reached_
 // CTA-pair (cta_group::2) variant for large K-major problems
 int32_t launch_gemm_tc2(const GemmArgs& g, cudaStream_t stream);
 bool gemm_tc2_supports(const GemmArgs& g);
+// CTA-pair variant for weight gradients (both operands MN-major, fp32 out, K cut into ranges through the scratch)
+int32_t launch_gemm_tc2_mn(const GemmArgs& g, cudaStream_t stream);
+bool gemm_tc2_mn_supports(const GemmArgs& g);
+// sums `splits` partial [M, N] fp32 results in g.splitk_scratch in split order and applies g's store epilogue
+int32_t launch_splitk_reduce(const GemmArgs& g, int splits, cudaStream_t stream);
 
 }  // namespace b200

@@ -465,6 +465,19 @@ int32_t launch_gemm_tc(const GemmArgs& g, cudaStream_t stream) {
   return fail(B200_ERR_BAD_DTYPE, "gemm: unsupported output dtype %d", g.out_dtype);
 }
 
+int32_t launch_splitk_reduce(const GemmArgs& g, int splits, cudaStream_t stream) {
+  if (g.kind != EPI_STORE) return fail(B200_ERR_UNSUPPORTED, "split-K reduction outside a GEMM launch covers the plain store only");
+  const int chunks = g.M * (g.N / 16);
+  if (g.out_dtype == B200_F32)
+    B200_CUDA_OK(launch_pdl(splitk_reduce_kernel<EPI_STORE, float>, dim3(cdiv(chunks, 256)), dim3(256), 0, stream,
+                            reinterpret_cast<const float*>(g.splitk_scratch), splits, g.M, g.N, g.epi));
+  else
+    B200_CUDA_OK(launch_pdl(splitk_reduce_kernel<EPI_STORE, bf16>, dim3(cdiv(chunks, 256)), dim3(256), 0, stream,
+                            reinterpret_cast<const float*>(g.splitk_scratch), splits, g.M, g.N, g.epi));
+  B200_LAUNCH_OK("splitk_reduce_kernel");
+  return B200_OK;
+}
+
 int32_t launch_gemm(const GemmArgs& g, int impl, cudaStream_t stream) {
   const bool tc = impl == 1 || (impl != 2 && gemm_tc_supports(g));
   ProfScope prof(tc ? PROF_GEMM_TC : PROF_GEMM_SIMT, 2.0 * g.M * (double)g.N * g.K, stream);
@@ -472,6 +485,8 @@ int32_t launch_gemm(const GemmArgs& g, int impl, cudaStream_t stream) {
   // B200_GEMM_PAIR=0 keeps every problem on the single-CTA kernel
   static const int use_pair = env_int("B200_GEMM_PAIR", 1);
   if (use_pair && gemm_tc2_supports(g)) return launch_gemm_tc2(g, stream);
+  static const int pair_mn = env_int("B200_GEMM_PAIR_MN", 1);  // 0 keeps weight gradients on the single-CTA kernel
+  if (use_pair && pair_mn && gemm_tc2_mn_supports(g)) return launch_gemm_tc2_mn(g, stream);
   return launch_gemm_tc(g, stream);
 }
 

@@ -98,12 +98,16 @@ __device__ __forceinline__ void mma_pair_commit(uint64_t* bar) {
                : "memory");
 }
 
-template <int BN, int KIND, typename TOut>
+// MN: both operands are MN-major (A stored [K, M], B stored [K, N]: the weight-gradient products dY^T X).  Their
+// tiles arrive as boxes of 64 columns x 64 k-rows and are described to the MMA as MN-major.  `splits` > 1 cuts K
+// into that many ranges handled as separate work items whose fp32 partial tiles go to rows split * split_rows + m
+// of the output map (a scratch of [splits * M, N]); a reduction kernel sums them in split order.
+template <int BN, int KIND, typename TOut, bool MN>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(P_THREADS, 1)
     gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                     const __grid_constant__ CUtensorMap tmO, const __grid_constant__ CUtensorMap tmR,
                     const __grid_constant__ CUtensorMap tmG, const __grid_constant__ CUtensorMap tmU, int M, int N,
-                    int K, EpiParams ep, uint32_t* status) {
+                    int K, EpiParams ep, int splits, int split_rows, uint32_t* status) {
   using Cfg = PairCfg<BN, KIND>;
   constexpr int S = Cfg::kStages;
   extern __shared__ uint8_t smem_raw[];
@@ -125,6 +129,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(P_THREADS, 1)
   const int n_tiles = (N + BN - 1) / BN;
   const int num_tiles = m_tiles * n_tiles;
   const int num_kb = (K + PK - 1) / PK;
+  const int num_items = num_tiles * splits;  // item = (tile, K range): tile = item % num_tiles, split = item / num_tiles
+  constexpr int kMnBox = 64 * PK * 2;        // bytes of one MN-major box: 64 columns x 64 k-rows
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < S; ++i) {
@@ -160,19 +166,29 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(P_THREADS, 1)
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int tile = pair; tile < num_tiles && ok; tile += n_pairs) {
+      for (int item = pair; item < num_items && ok; item += n_pairs) {
+        const int tile = item % num_tiles, split = item / num_tiles;
+        const int kb0 = (int)((long)split * num_kb / splits), kb1 = (int)((long)(split + 1) * num_kb / splits);
         int mt, nt;
         tile_coords(tile, m_tiles, n_tiles, 8, mt, nt);
         const int m0 = mt * (2 * PM) + (int)rank * PM;
         const int n0 = nt * BN + (int)rank * (BN / 2);
-        for (int kb = 0; kb < num_kb; ++kb) {
+        for (int kb = kb0; kb < kb1; ++kb) {
           ok = ptx::mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag, status, ST_PAIR_PRODUCER);
           if (!ok) break;
           uint8_t* sa = smem + stage * Cfg::kStageBytes;
           const uint32_t leader_full = map_to_cta(ptx::smem_u32(&full_bar[stage]), 0);
           if (rank == 0) ptx::mbar_arrive_expect_tx(&full_bar[stage], 2 * Cfg::kStageBytes);
-          tma_load_2d_pair(sa, &tmA, kb * PK, m0, leader_full);
-          tma_load_2d_pair(sa + Cfg::kABytes, &tmB, kb * PK, n0, leader_full);
+          if constexpr (MN) {
+#pragma unroll
+            for (int i = 0; i < PM / 64; ++i) tma_load_2d_pair(sa + i * kMnBox, &tmA, m0 + 64 * i, kb * PK, leader_full);
+#pragma unroll
+            for (int i = 0; i < BN / 128; ++i)
+              tma_load_2d_pair(sa + Cfg::kABytes + i * kMnBox, &tmB, n0 + 64 * i, kb * PK, leader_full);
+          } else {
+            tma_load_2d_pair(sa, &tmA, kb * PK, m0, leader_full);
+            tma_load_2d_pair(sa + Cfg::kABytes, &tmB, kb * PK, n0, leader_full);
+          }
           if (++stage == S) { stage = 0; phase ^= 1u; }
         }
       }
@@ -180,23 +196,28 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(P_THREADS, 1)
     __syncwarp();
   } else if (warp == 1) {
     if (lane == 0 && rank == 0) {
-      constexpr uint32_t idesc = ptx::idesc_bf16_f32(2 * PM, BN);
+      constexpr uint32_t idesc = ptx::idesc_bf16_f32(2 * PM, BN) | (MN ? ((1u << 15) | (1u << 16)) : 0u);
+      constexpr uint64_t k_step = MN ? (16 * 128) / 16 : 2;  // start-address step per 16 K-elements, in 16-byte units
       // descriptors of stage 0, built once: a stage adds its byte offset >> 4 to the 14-bit address field (shared-memory
       // addresses stay below 2^18, so it never carries); this thread's instruction stream is what bounds narrow tiles
       const uint32_t s0 = ptx::smem_u32(smem);
-      const uint64_t a_base = ptx::smem_desc_sw128(s0), b_base = ptx::smem_desc_sw128(s0 + Cfg::kABytes);
+      const uint64_t a_base = MN ? ptx::smem_desc_sw128_mn(s0, kMnBox) : ptx::smem_desc_sw128(s0);
+      const uint64_t b_base = MN ? ptx::smem_desc_sw128_mn(s0 + Cfg::kABytes, kMnBox)
+                                 : ptx::smem_desc_sw128(s0 + Cfg::kABytes);
       constexpr uint64_t stage_step = Cfg::kStageBytes >> 4;
       int stage = 0;
       uint32_t phase = 0;
       int acc = 0;
       uint32_t acc_phase = 0;
       bool ok = true;
-      for (int tile = pair; tile < num_tiles && ok; tile += n_pairs) {
+      for (int item = pair; item < num_items && ok; item += n_pairs) {
+        const int split = item / num_tiles;
+        const int kb0 = (int)((long)split * num_kb / splits), kb1 = (int)((long)(split + 1) * num_kb / splits);
         ok = ptx::mbar_wait(&acc_empty[acc], acc_phase ^ 1u, abort_flag, status, ST_PAIR_MMA);
         if (!ok) break;
         ptx::tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + (uint32_t)(acc * Cfg::kAccStride);
-        for (int kb = 0; kb < num_kb; ++kb) {
+        for (int kb = kb0; kb < kb1; ++kb) {
           ok = ptx::mbar_wait(&full_bar[stage], phase, abort_flag, status, ST_PAIR_MMA);
           if (!ok) break;
           ptx::tc_fence_after_sync();
@@ -204,8 +225,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(P_THREADS, 1)
           const uint64_t bdesc = b_base + (uint64_t)stage * stage_step;
 #pragma unroll
           for (int k = 0; k < PK / 16; ++k)
-            mma_pair_bf16_ss(d_tmem, adesc + (uint64_t)(2 * k), bdesc + (uint64_t)(2 * k), idesc,
-                             (kb > 0 || k > 0) ? 1u : 0u);
+            mma_pair_bf16_ss(d_tmem, adesc + k_step * k, bdesc + k_step * k, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
           mma_pair_commit(&empty_bar[stage]);
           if (++stage == S) { stage = 0; phase ^= 1u; }
         }
@@ -233,12 +253,14 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(P_THREADS, 1)
     int acc = 0;
     uint32_t acc_phase = 0;
     bool ok = true;
-    for (int tile = pair; tile < num_tiles && ok; tile += n_pairs) {
+    for (int item = pair; item < num_items && ok; item += n_pairs) {
+      const int tile = item % num_tiles, split = item / num_tiles;
       int mt, nt;
       tile_coords(tile, m_tiles, n_tiles, 8, mt, nt);
       const int m0 = mt * (2 * PM) + (int)rank * PM;
       const int n0 = nt * BN;
       const int mrow0 = m0 + q * 32;  // first row of this warp's boxes; rows past M are clipped by the store
+      const int yrow0 = mrow0 + split * split_rows;  // row of the output map (partial sums: one M-row band per split)
       const int m = mrow0 + lane;
       const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * Cfg::kAccStride);
       const EpiRow erow = epi_row_begin<KIND>(ep, m < M ? m : 0);
@@ -329,7 +351,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(P_THREADS, 1)
               ptx::fence_proxy_async();
               __syncwarp();
               if (lane == 0) {
-                ptx::tma_store_2d(&tmO, stg + (uint32_t)((ring % NBUF) * BUFB), n0 + c, mrow0);
+                ptx::tma_store_2d(&tmO, stg + (uint32_t)((ring % NBUF) * BUFB), n0 + c, yrow0);
                 ptx::tma_store_commit();
               }
               ++ring;
@@ -355,7 +377,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(P_THREADS, 1)
                 ptx::fence_proxy_async();
                 __syncwarp();
                 if (lane == 0) {
-                  ptx::tma_store_2d(&tmO, stg + (uint32_t)((ring % NBUF) * BUFB), n0 + c - 32, mrow0);
+                  ptx::tma_store_2d(&tmO, stg + (uint32_t)((ring % NBUF) * BUFB), n0 + c - 32, yrow0);
                   ptx::tma_store_commit();
                 }
                 ++ring;
@@ -478,13 +500,23 @@ int pair_tile_width(int M, int N) {
   return bn;
 }
 
-template <int BN, int KIND, typename TOut>
-int32_t launch_pair_cfg(const GemmArgs& g, cudaStream_t stream) {
+template <int BN, int KIND, typename TOut, bool MN = false>
+int32_t launch_pair_cfg(const GemmArgs& g, cudaStream_t stream, int splits = 1) {
   using Cfg = PairCfg<BN, KIND>;
   CUtensorMap tmA, tmB, tmO, tmR, tmG, tmU;
-  B200_TRY(make_map_2d(&tmA, g.A, g.M, g.K, g.lda, PM));
-  B200_TRY(make_map_2d(&tmB, g.B, g.N, g.K, g.ldb, BN / 2));
-  if (KIND == EPI_SWIGLU) {
+  if (MN) {
+    // operands stored [K, M] and [K, N]: boxes of 64 columns x 64 k-rows; fp32 partial tiles of every K range go to
+    // the scratch, [splits * M, N]
+    B200_TRY(make_map_2d(&tmA, g.A, g.K, g.M, g.lda, PK));
+    B200_TRY(make_map_2d(&tmB, g.B, g.K, g.N, g.ldb, PK));
+    B200_TRY(make_map_out(&tmO, g.splitk_scratch, splits * g.M, g.N, g.N, 4, 128));
+    tmR = tmG = tmU = tmO;
+  } else {
+    B200_TRY(make_map_2d(&tmA, g.A, g.M, g.K, g.lda, PM));
+    B200_TRY(make_map_2d(&tmB, g.B, g.N, g.K, g.ldb, BN / 2));
+  }
+  if (MN) {
+  } else if (KIND == EPI_SWIGLU) {
     B200_TRY(make_map_out(&tmO, g.epi.out, g.M, g.N / 2, g.epi.ldo, 2, 64));
     tmG = tmU = tmO;
     if (g.epi.out_gate) {
@@ -497,7 +529,7 @@ int32_t launch_pair_cfg(const GemmArgs& g, cudaStream_t stream) {
     tmR = tmG = tmU = tmO;
     if (KIND == EPI_RESID) B200_TRY(make_map_out(&tmR, g.epi.resid_in, g.M, g.N, g.epi.ldo, 4, 128));
   }
-  auto kern = gemm_tc2_kernel<BN, KIND, TOut>;
+  auto kern = gemm_tc2_kernel<BN, KIND, TOut, MN>;
   static bool attr_set = false;
   if (!attr_set) {
     B200_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
@@ -523,14 +555,33 @@ int32_t launch_pair_cfg(const GemmArgs& g, cudaStream_t stream) {
     }
     max_pairs = n < sm_count() / 2 ? n : sm_count() / 2;
   }
-  const int tiles = cdiv(g.M, 2 * PM) * cdiv(g.N, BN);
+  const int items = cdiv(g.M, 2 * PM) * cdiv(g.N, BN) * splits;
   int pairs = max_pairs;
   if (g.max_ctas > 0 && g.max_ctas / 2 < pairs) pairs = g.max_ctas / 2;
-  if (pairs > tiles) pairs = tiles;
+  if (pairs > items) pairs = items;
   B200_CUDA_OK(launch_pdl(kern, dim3(2 * pairs), dim3(P_THREADS), Cfg::kSmemBytes, stream, tmA, tmB, tmO, tmR, tmG,
-                          tmU, g.M, g.N, g.K, g.epi, device_status_word()));
+                          tmU, g.M, g.N, g.K, g.epi, splits, MN ? g.M : 0, device_status_word()));
   B200_LAUNCH_OK("gemm_tc2_kernel");
   return B200_OK;
+}
+
+// Weight-gradient shape: both operands MN-major, fp32 output (+= when accumulate).  K is always cut into ranges
+// whose partial tiles go through the scratch; launch_splitk_reduce sums them in split order and applies the store.
+int32_t launch_pair_mn(const GemmArgs& g, cudaStream_t stream) {
+  const int pairs = sm_count() / 2;
+  const int bn = g.N % 256 == 0 ? 256 : 128;
+  const int tiles = (g.M / (2 * PM)) * (g.N / bn);
+  const int num_kb = cdiv(g.K, PK);
+  int best = 1;
+  double best_cost = 1e30;
+  for (int s = 1; s <= 16 && (s == 1 || num_kb / s >= 8); ++s) {
+    if ((size_t)s * g.M * g.N * sizeof(float) > g.splitk_bytes) break;
+    const double cost = (double)cdiv(tiles * s, pairs) / s + 0.02 * s;  // rounds of the grid, each 1/s long, + partial traffic
+    if (cost < best_cost) { best = s; best_cost = cost; }
+  }
+  if (bn == 256) B200_TRY((launch_pair_cfg<256, EPI_STORE, float, true>(g, stream, best)));
+  else B200_TRY((launch_pair_cfg<128, EPI_STORE, float, true>(g, stream, best)));
+  return launch_splitk_reduce(g, best, stream);
 }
 
 template <int KIND, typename TOut>
@@ -569,6 +620,22 @@ bool gemm_tc2_supports(const GemmArgs& g) {
   if (g.kind == EPI_SWIGLU && g.epi.out_gate && (!aligned16(g.epi.out_gate) || !aligned16(g.epi.out_up))) return false;
   const long tiles = (long)cdiv(g.M, 2 * PM) * (g.N / pair_tile_width(g.M, g.N));
   return g.M >= 2 * PM && tiles >= sm_count() / 2;
+}
+
+// MN-major pair path: dW = dY^T X with both operands stored [K, .], fp32 output, whole 256-row tiles, scratch for the
+// partial sums of at least one K range.
+bool gemm_tc2_mn_supports(const GemmArgs& g) {
+  if (!g.ta || !g.tb || g.kind != EPI_STORE || g.in_dtype != B200_BF16 || g.out_dtype != B200_F32) return false;
+  if (g.M % (2 * PM) || g.N % 128 || g.K % 8 || g.K < 8 * PK) return false;
+  if (!g.splitk_scratch || g.splitk_bytes < (size_t)g.M * g.N * sizeof(float)) return false;
+  if (!aligned16(g.A) || !aligned16(g.B) || !aligned16(g.splitk_scratch) || g.lda % 8 || g.ldb % 8) return false;
+  if (!aligned16(g.epi.out) || g.epi.ldo % 4) return false;
+  return true;
+}
+
+int32_t launch_gemm_tc2_mn(const GemmArgs& g, cudaStream_t stream) {
+  if (!gemm_tc2_mn_supports(g)) return fail(B200_ERR_UNSUPPORTED, "the MN-major CTA-pair gemm does not cover this problem");
+  return launch_pair_mn(g, stream);
 }
 
 int32_t launch_gemm_tc2(const GemmArgs& g, cudaStream_t stream) {
