@@ -1,11 +1,14 @@
 """Benchmark of the llama forward / VJP hot path.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c2|c1|c3|c4|c5] [--impl reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c4|c2|c1|c3|c5] [--impl reference]
 
-Default: the 110M-parameter bf16 prefill forward (dim 768, 12 layers, batch 8 x
-1024 tokens), one step = one forward over the batch, tokens/s over all ranks.
-For N > 1 launch under ``torch.distributed.run`` (one rank per GPU, NCCL).
-Prints ONE JSON line on rank 0.
+Default: the Llama-2-7B-shape bf16 prefill forward (dim 4096, 32 layers, batch 4 x
+2048 tokens), the largest single-GPU configuration, tensor parallel over all N
+ranks (N = 1: one GPU holds the whole model); one step = one forward over the
+batch, tokens/s of the whole job.  For N > 1 launch under
+``torch.distributed.run`` (one rank per GPU, NCCL + peer memory over NVLink).
+Prints ONE JSON line on rank 0's standard output; everything else any rank or
+library prints (NCCL's log included) goes to standard error.
 
 ``--impl reference`` times the CPU restatement of the reference model (the
 oracle, torch-CPU fp32 on all host threads) on a bounded sample of the same
@@ -57,6 +60,50 @@ def peaks():
         return dict(hbm_gbs=p["hbm_gbs"], tflops_burst=p["bf16_tflops"], tflops_sustained=p["bf16_tflops_sustained"],
                     source="measured")
     return dict(hbm_gbs=6650.0, tflops_burst=1590.0, tflops_sustained=1400.0, source="fallback")
+
+
+KERNEL_OF_CLASS = {
+    "gemm_tcgen05_pair": "gemm_tc2_kernel", "gemm_tcgen05": "gemm_tc_kernel", "gemm_ffma": "gemm_simt_kernel",
+    "attention_fwd": "attn_fwd_tc_kernel", "attention_bwd": "attn_bwd_tc_kernel",
+    "attention_decode": "attn_decode_vec_kernel", "allreduce": "peer_rownorm_kernel",
+}
+
+
+def _profile_table_rows(name):
+    """Rows of the markdown table in profiles/<name> as lists of cell strings (no header, no rule)."""
+    path = os.path.join(ROOT, "profiles", name)
+    if not os.path.exists(path):
+        return []
+    rows = []
+    for ln in open(path):
+        cells = [c.strip() for c in ln.strip().strip("|").split("|")]
+        if ln.lstrip().startswith("|") and len(cells) >= 3 and not set(cells[0]) <= set("-: "):
+            rows.append(cells)
+    return rows
+
+
+def traffic_from_profiles(workload, kernel):
+    """DRAM bytes per launch of `kernel` in `workload`, read from the table of ncu captures kept in
+    profiles/dram_traffic_per_launch.md (columns: workload, kernel, bytes per launch, capture).  None when no
+    capture of that pair has been recorded: the number is never a constant of this file."""
+    for cells in _profile_table_rows("dram_traffic_per_launch.md"):
+        if cells[0] == workload and cells[1] == kernel:
+            try:
+                return float(cells[2]), "profiles/dram_traffic_per_launch.md: " + (cells[3] if len(cells) > 3 else "")
+            except ValueError:
+                pass
+    return None, None
+
+
+def fp32_peak_from_profiles():
+    """Measured FFMA rate of the GPU in TFLOP/s (profiles/fp32_ffma_peak.md, a table row `fp32_ffma | <TFLOP/s> | how`)."""
+    for cells in _profile_table_rows("fp32_ffma_peak.md"):
+        if cells[0] == "fp32_ffma":
+            try:
+                return float(cells[1])
+            except ValueError:
+                pass
+    return None
 
 
 class ClockSampler:
@@ -186,50 +233,89 @@ def cpu_oracle_rate(cfg, seq, sample_batch, reps, vjp=False):
     return sample_batch * seq / best, threads, best
 
 
-def run_reference(args, rank, world):
-    if rank != 0:
-        return
-    cfg, dtype, batch, seq, desc = WORKLOADS[args.workload]
-    if args.workload in ("c4", "c5"):
-        cfg = dict(cfg, n_layers=2)  # two layers of the 7B shape fit the time budget; rate scaled per layer below
-    sample_b = 1
-    from oracle import llama_ref as O  # noqa: F401
-    times = []
+def cpu_extrapolated_7b(cfg, batch, seq, reps, past=0):
+    """Seconds per step (`batch` sequences of `seq` new tokens, `past` cached rows each) of the full-depth 7B-shape
+    oracle, from timing a 1-layer and a 2-layer model of the same widths (embedding, final norm and the logits
+    projection are in both): t(L) = t1 + (L - 1) * (t2 - t1)."""
+    from oracle import llama_ref as O
     threads = os.cpu_count() or 1
     torch.set_num_threads(threads)
-    w = O.make_weights(cfg, 2, torch.float32)
-    tokens = O.make_tokens(cfg, sample_b, seq if args.workload != "c5" else 1, 2)
-    vjp = args.workload == "c3"
-    dl = torch.randn(sample_b, seq, cfg["vocab_size"]) if vjp else None
-
-    def step():
-        if vjp:
-            O.vjp_sequence(tokens, cfg, w, dl)
-        else:
+    best = {}
+    w2 = O.make_weights(dict(cfg, n_layers=2), 2, torch.float32)
+    tokens = O.make_tokens(cfg, batch, seq, 2)
+    pk = pv = None
+    if past:
+        g = torch.Generator().manual_seed(3)
+        pk = torch.randn(2, batch, past, cfg["dim"], generator=g)
+        pv = torch.randn(2, batch, past, cfg["dim"], generator=g)
+    for layers in (1, 2):
+        c = dict(cfg, n_layers=layers)
+        w = {k: (v[:layers] if v.dim() == 3 or k in ("rms_att_weight", "rms_ffn_weight") else v) for k, v in w2.items()}
+        b = float("inf")
+        for _ in range(reps + 1):  # the first pass warms the thread pool and the allocator
+            t0 = time.perf_counter()
             with torch.no_grad():
-                O.forward_sequence(tokens, cfg, w)
+                O.forward_sequence(tokens, c, w, past_k=pk[:layers] if past else None,
+                                   past_v=pv[:layers] if past else None)
+            b = min(b, time.perf_counter() - t0)
+        best[layers] = b
+    per_layer = max(best[2] - best[1], 1e-9)
+    return best[1] + (cfg["n_layers"] - 1) * per_layer, threads, best
 
-    for _ in range(max(1, min(args.warmup, 1))):
-        step()
+
+def run_reference(args, rank, world):
+    if rank != 0:
+        return None
+    cfg, dtype, batch, seq, desc = WORKLOADS[args.workload]
+    from oracle import llama_ref as O  # noqa: F401
+    threads = os.cpu_count() or 1
+    torch.set_num_threads(threads)
     steps = max(1, min(args.steps, 5))
-    t0 = time.perf_counter()
-    for _ in range(steps):
-        step()
-    dt = (time.perf_counter() - t0) / steps
-    value = sample_b * tokens.shape[1] / dt
-    sample = f"{sample_b} sequence(s) of {tokens.shape[1]} tokens per step, {steps} steps, torch-CPU fp32 oracle"
     if args.workload in ("c4", "c5"):
-        sample += "; 2 of 32 layers (rate is for the 2-layer model, not extrapolated)"
-    line = {
+        prefill = args.workload == "c4"
+        sb, ss, past = (1, seq, 0) if prefill else (8, 1, seq)  # decode: 8 sequences, one new token, 4096 cached rows
+        secs = []
+        for _ in range(min(steps, 2)):
+            t_full, threads, best = cpu_extrapolated_7b(cfg, sb, ss, 1, past)
+            secs.append(t_full)
+        dt = min(secs)
+        value = sb * ss / dt
+        what = f"1 sequence of {ss} tokens" if prefill else f"{sb} sequences, one new token each over {past} cached rows"
+        sample = (f"EXTRAPOLATED: {what} through a 1-layer and a 2-layer model of the 7B widths "
+                  f"(torch-CPU fp32 oracle, {best[1]:.2f} s and {best[2]:.2f} s per step); full depth = t1 + 31 * (t2 - t1); "
+                  "embedding, final norm and the 32000-wide logits projection are in t1")
+        steps = len(secs)
+    else:
+        w = O.make_weights(cfg, 2, torch.float32)
+        tokens = O.make_tokens(cfg, 1, seq, 2)
+        vjp = args.workload == "c3"
+        dl = torch.randn(1, seq, cfg["vocab_size"]) if vjp else None
+
+        def step():
+            if vjp:
+                O.vjp_sequence(tokens, cfg, w, dl)
+            else:
+                with torch.no_grad():
+                    O.forward_sequence(tokens, cfg, w)
+
+        for _ in range(max(1, min(args.warmup, 1))):
+            step()
+        t0 = time.perf_counter()
+        for _ in range(steps):
+            step()
+        dt = (time.perf_counter() - t0) / steps
+        value = tokens.shape[1] / dt
+        sample = f"1 sequence of {tokens.shape[1]} tokens per step, {steps} steps, torch-CPU fp32 oracle"
+    return {
         "impl": "reference", "metric": "tokens_per_second", "value": value, "unit": "tokens/s", "n_gpus": args.gpus,
-        "steps": steps, "warmup": 1, "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak",
+        "steps": steps, "warmup": 1, "ms_per_step": dt * 1e3, "higher_is_better": True,
+        "scaling": "strong" if args.workload in ("c3", "c4", "c5") else "weak",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {"workload": WORKLOADS[args.workload][4]},
         "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": threads, "kind": "port", "sample": sample},
         "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "note": "reference (JAX/XLA) is not installable here; this is the CPU restatement of test/llama.py",
     }
-    print(json.dumps(line))
 
 
 def synth_weights(cfg, dtype, device, seed=1):
@@ -385,24 +471,33 @@ def run_prefill(args, rank, world, local, B, dist):
     tokens_per_step = batch * seq * replicas
     value = tokens_per_step / (ms / args.steps / 1e3)
     e2e = tokens_per_step / (ms_e2e / args.steps / 1e3)
-    dom_name = max(("gemm_tcgen05", "gemm_ffma", "attention_fwd"), key=lambda k: prof[k]["ms"])
+    dom_name = max(("gemm_tcgen05_pair", "gemm_tcgen05", "gemm_ffma", "attention_fwd"), key=lambda k: prof[k]["ms"])
     dom = prof[dom_name]
     tensor_bound = dname == "bf16"
     ach = dom["work"] / (dom["ms"] / 1e3) / 1e12 if dom["ms"] > 0 else 0.0
-    peak = pk["tflops_sustained"]
-    # DRAM bytes per launch of the GEMM class from the ncu capture of one full-size step
-    # (dram__bytes_read.sum + dram__bytes_write.sum over the 49 GEMM launches of config 2: 2841 MB)
-    traffic = 57.8e6 if (args.workload == "c2" and args.batch == 0 and args.layers == 0 and dom_name == "gemm_tcgen05") else None
+    peak, peak_burst = pk["tflops_sustained"], pk["tflops_burst"]
+    full_size = args.batch == 0 and args.layers == 0
+    traffic, traffic_src = traffic_from_profiles(args.workload, KERNEL_OF_CLASS[dom_name]) if full_size else (None, None)
+    step_flops = fwd_flops(cfg, batch, seq) / tp
     roofline = {
-        "bound": "tensor", "kernel": dom_name, "achieved": ach, "peak": peak, "unit": "TFLOP/s",
-        "frac": ach / peak, "traffic": traffic, "traffic_unit": "bytes per launch (ncu, mean over the GEMM launches of a step)", "peak_source": pk["source"] + " (sustained bf16 matmul)",
+        "bound": "tensor", "kernel": KERNEL_OF_CLASS[dom_name], "achieved": ach, "peak": peak, "unit": "TFLOP/s",
+        "frac": ach / peak, "peak_burst": peak_burst, "frac_burst": ach / peak_burst,
+        "traffic": traffic, "traffic_unit": "DRAM bytes per launch, mean over this kernel's launches of one step (ncu)",
+        "traffic_source": traffic_src,
+        "peak_source": pk["source"] + " (bf16 matmul: `peak` is the seconds-long figure under the power cap, "
+                                      "`peak_burst` the best of 10 isolated runs)",
         "launches": dom["launches"], "kernel_ms_per_step": dom["ms"] / args.steps,
         "share_of_step": dom["ms"] / max(1e-9, sum(v["ms"] for v in prof.values())),
-        "whole_step_frac": fwd_flops(cfg, batch, seq) / tp / (ms / args.steps / 1e3) / 1e12 / peak,
-        "other_kernels_ms_per_step": {k: v["ms"] / args.steps for k, v in prof.items() if v["launches"]},
+        "whole_step_frac": step_flops / (ms / args.steps / 1e3) / 1e12 / peak,
+        "whole_step_frac_burst": step_flops / (ms / args.steps / 1e3) / 1e12 / peak_burst,
+        "kernels_ms_per_step": {k: v["ms"] / args.steps for k, v in prof.items() if v["launches"]},
     }
     if not tensor_bound:
-        roofline["note"] = "fp32 configuration: FFMA kernels, fraction quoted against the bf16 tensor peak for reference only"
+        fp32 = fp32_peak_from_profiles()
+        roofline["note"] = ("fp32 configuration: FFMA kernels; `frac` is against the bf16 tensor peak for reference only, "
+                            "`frac_fp32` against the measured FFMA rate of the GPU")
+        roofline["peak_fp32"] = fp32
+        roofline["frac_fp32"] = ach / fp32 if fp32 else None
     line = {
         "metric": "tokens_per_second", "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
@@ -420,15 +515,27 @@ def run_prefill(args, rank, world, local, B, dist):
                             "timed region"},
         "gpu_launches": launches, "roofline": roofline, "clocks": clocks,
     }
+    if tp > 1:
+        line["config"]["exchange"] = ("row-sharded residual stream over peer memory (one fused reduce + add + RMSNorm + "
+                                      "gather kernel per block)" if comm.peer_memory() and
+                                      os.environ.get("B200_TP_ROW_SHARD", "1") != "0" else "all-reduce per block")
+        line["exchange_ms_per_step"] = prof["allreduce"]["ms"] / args.steps
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         sample_b = 1
         reps = 2 if args.workload != "c1" else 5
-        cpu_cfg = cfg if args.workload != "c4" else dict(cfg, n_layers=1)
-        rate, threads, best = cpu_oracle_rate(cpu_cfg, seq, sample_b, reps)
-        line["cpu_baseline"] = {
-            "value": rate, "unit": "tokens/s", "cores": threads, "kind": "port",
-            "sample": f"{sample_b} sequence of {seq} tokens, best of {reps}, torch-CPU fp32 restatement of test/llama.py"
-                      + (" (1 of 32 layers)" if args.workload == "c4" else "")}
+        if args.workload == "c4":
+            t_full, threads, best = cpu_extrapolated_7b(cfg, 1, seq, 1)
+            line["cpu_baseline"] = {
+                "value": seq / t_full, "unit": "tokens/s", "cores": threads, "kind": "port",
+                "sample": f"EXTRAPOLATED: 1 sequence of {seq} tokens through a 1-layer and a 2-layer model of the 7B "
+                          f"widths (torch-CPU fp32 restatement of test/llama.py, {best[1]:.2f} s and {best[2]:.2f} s); "
+                          f"full depth = t1 + {cfg['n_layers'] - 1} * (t2 - t1)"}
+        else:
+            rate, threads, best = cpu_oracle_rate(cfg, seq, sample_b, reps)
+            line["cpu_baseline"] = {
+                "value": rate, "unit": "tokens/s", "cores": threads, "kind": "port",
+                "sample": f"{sample_b} sequence of {seq} tokens, best of {reps}, torch-CPU fp32 restatement of "
+                          "test/llama.py"}
     if comm:
         comm.destroy()
     return line
@@ -523,8 +630,11 @@ def run_vjp(args, rank, world, local, B, dist):
                 "h2d_bytes_per_step": per_rank * seq * 4, "d2h_bytes_per_step": 4, "ms_per_step": ms_e2e / args.steps,
                 "result": "first gradient element after the all-reduce (the gradients stay on the device)"},
         "gpu_launches": launches,
-        "roofline": {"bound": "tensor", "kernel": dom_name, "achieved": ach, "peak": peak, "unit": "TFLOP/s",
-                     "frac": ach / peak, "traffic": None, "peak_source": pk["source"] + " (sustained bf16 matmul)",
+        "roofline": {"bound": "tensor", "kernel": KERNEL_OF_CLASS[dom_name], "achieved": ach, "peak": peak,
+                     "unit": "TFLOP/s", "frac": ach / peak, "peak_burst": pk["tflops_burst"],
+                     "frac_burst": ach / pk["tflops_burst"],
+                     "traffic": traffic_from_profiles("c3", KERNEL_OF_CLASS[dom_name])[0] if args.batch == 0 else None,
+                     "peak_source": pk["source"] + " (bf16 matmul, sustained; burst beside it)",
                      "launches": dom["launches"],
                      "whole_step_frac": vjp_flops(cfg, per_rank, seq) / (ms / args.steps / 1e3) / 1e12 / peak,
                      "kernels_ms_per_step": {k: v["ms"] / psteps for k, v in prof.items() if v["launches"]}},
@@ -619,8 +729,10 @@ def run_decode(args, rank, world, local, B, dist):
                 "d2h_bytes_per_step": batch * plan.vocab_local * 4, "ms_per_step": ms_e2e / steps,
                 "result": "logits of the new token of every sequence"},
         "gpu_launches": launches,
-        "roofline": {"bound": "hbm", "kernel": "attention_decode", "achieved": ach, "peak": pk["hbm_gbs"],
-                     "unit": "GB/s", "frac": ach / pk["hbm_gbs"], "traffic": None,
+        "roofline": {"bound": "hbm", "kernel": KERNEL_OF_CLASS["attention_decode"], "achieved": ach,
+                     "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": ach / pk["hbm_gbs"],
+                     "traffic": traffic_from_profiles("c5", KERNEL_OF_CLASS["attention_decode"])[0]
+                     if args.batch == 0 and args.layers == 0 else None,
                      "peak_source": pk["source"] + " (copy bandwidth)", "launches": att["launches"],
                      "whole_step_frac": bytes_step / (ms / steps / 1e3) / 1e9 / pk["hbm_gbs"],
                      "kernels_ms_per_step": {k: v["ms"] / steps for k, v in prof.items() if v["launches"]}},
@@ -631,12 +743,22 @@ def run_decode(args, rank, world, local, B, dist):
     return line
 
 
+def claim_stdout():
+    """Keeps a private handle on the real standard output for the one JSON line and points file descriptor 1 at
+    standard error, so that whatever libraries print (NCCL_DEBUG=INFO writes to stdout) cannot split the line."""
+    sys.stdout.flush()
+    real = os.fdopen(os.dup(1), "w")
+    os.dup2(2, 1)
+    return real
+
+
 def main():
+    real_stdout = claim_stdout()
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
-    ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
+    ap.add_argument("--workload", default="c4", choices=sorted(WORKLOADS))
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--batch", type=int, default=0, help="override the batch per rank (profiling on a small case)")
@@ -648,14 +770,16 @@ def main():
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
     if args.impl == "reference":
-        run_reference(args, rank, world)
+        line = run_reference(args, rank, world)
+        if line is not None:
+            real_stdout.write(json.dumps(line) + "\n")
+            real_stdout.flush()
         return
     args.warmup = max(args.warmup, 3)
 
     import torch.distributed as dist
     import b200_llama as B
 
-    os.environ["NCCL_DEBUG"] = os.environ.get("B200_NCCL_DEBUG", "WARN")  # keep NCCL's banner off stdout: one JSON line
     torch.cuda.set_device(local)
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
@@ -671,7 +795,8 @@ def main():
             dist.barrier()
             dist.destroy_process_group()
     if rank == 0 and line is not None:
-        print(json.dumps(line))
+        real_stdout.write(json.dumps(line) + "\n")
+        real_stdout.flush()
 
 
 if __name__ == "__main__":

@@ -34,6 +34,7 @@ EXPORTS = (
     "b200_comm_destroy", "b200_launch_count", "b200_profile_enable", "b200_profile_read",
     "b200_attention_decode_scratch_bytes", "b200_attention_decode", "b200_attention_decode_static",
     "b200_attention_backward", "b200_comm_peer_memory", "b200_selftest_bounded_wait", "b200_argmax",
+    "b200_selftest_peer_wait", "b200_plan_cached", "b200_ffi_available", "b200_ffi_handler",
 )
 
 
@@ -64,8 +65,13 @@ def lib() -> ctypes.CDLL:
         l.b200_version.restype = c_char_p
         for name in EXPORTS:
             fn = getattr(l, name)
-            if name not in ("b200_last_error", "b200_version"):
+            if name not in ("b200_last_error", "b200_version", "b200_ffi_handler"):
                 fn.restype = c_int32
+        l.b200_ffi_handler.restype = c_void_p
+        l.b200_ffi_handler.argtypes = [c_char_p]
+        l.registerEnzymeJaXB200FFI.restype = c_int32
+        l.b200_plan_cached.argtypes = [POINTER(_Config), c_int32, c_int32, c_void_p, POINTER(c_void_p)]
+        l.b200_selftest_peer_wait.argtypes = [ctypes.c_int64, c_void_p, c_void_p]
         l.b200_launch_count.restype = ctypes.c_int64
         l.b200_profile_enable.argtypes = [c_int32]
         l.b200_profile_read.argtypes = [c_int32, POINTER(ctypes.c_double), POINTER(ctypes.c_double),
@@ -136,7 +142,8 @@ def launch_count() -> int:
     return int(lib().b200_launch_count())
 
 
-PROFILE_CLASSES = ("gemm_tcgen05", "gemm_ffma", "attention_fwd", "attention_bwd", "attention_decode", "allreduce")
+PROFILE_CLASSES = ("gemm_tcgen05", "gemm_ffma", "attention_fwd", "attention_bwd", "attention_decode", "allreduce",
+                   "gemm_tcgen05_pair")
 
 
 def profile_enable(on: bool) -> None:
@@ -278,18 +285,37 @@ class PageAllocator:
         self._free.extend(reversed(list(pages)))
 
 
+def _new_unique_id() -> bytes:
+    ident = ctypes.create_string_buffer(128)
+    check(lib().b200_comm_unique_id(ident))
+    return ident.raw
+
+
+def share_unique_id(rank: int, world: int, make_id, group=None) -> bytes:
+    """Host-side hand-off of the 128-byte communicator id: rank 0 makes it, every rank receives it, and every rank
+    then confirms to every other that it is there.  A rank that died or never joined makes the hand-off fail on the
+    others within the process group's timeout; that surfaces as ``B200Error`` with the NCCL status code, before any
+    GPU work that would wait for the missing rank has been launched."""
+    import torch.distributed as dist
+    box = [make_id() if rank == 0 else None]
+    try:
+        dist.broadcast_object_list(box, src=0, group=group)
+        present = [None] * world
+        dist.all_gather_object(present, rank, group=group)
+    except Exception as exc:  # a timeout or a closed connection: some rank is not there
+        raise B200Error(8, f"the communicator id did not reach every rank (rank {rank} of {world}): {exc}") from exc
+    if sorted(present) != list(range(world)) or not isinstance(box[0], (bytes, bytearray)) or len(box[0]) != 128:
+        raise B200Error(8, f"communicator hand-off incomplete: ranks present {present}")
+    return bytes(box[0])
+
+
 class Comm:
     """NCCL communicator created from a unique id that rank 0 shares through
     ``torch.distributed`` (any backend: the id is 128 bytes of host data)."""
 
     def __init__(self, rank: int, world: int, group=None):
-        import torch.distributed as dist
-        ident = ctypes.create_string_buffer(128)
-        if rank == 0:
-            check(lib().b200_comm_unique_id(ident))
-        box = [ident.raw]
-        dist.broadcast_object_list(box, src=0, group=group)
-        ident = ctypes.create_string_buffer(box[0], 128)
+        raw = share_unique_id(rank, world, _new_unique_id, group)
+        ident = ctypes.create_string_buffer(raw, 128)
         handle = c_void_p()
         check(lib().b200_comm_init_rank(ident, rank, world, byref(handle)))
         self.handle, self.rank, self.world = handle, rank, world
@@ -330,6 +356,7 @@ class Plan:
         self.packed: Optional[torch.Tensor] = None
         self.with_transposed = False
         self._ws: Optional[torch.Tensor] = None
+        self._ws_pinned_by_graphs = []  # workspaces that captured graphs point into: kept alive with the plan
         self.vocab_local = config["vocab_size"] // tp_size
         self.d_local = config["dim"] // tp_size
 
@@ -353,9 +380,15 @@ class Plan:
     def workspace(self, mode: int, batch: int, seq: int) -> torch.Tensor:
         need = self._bytes(lib().b200_workspace_bytes, mode, batch, seq)
         if self._ws is None or self._ws.numel() < need:
-            self._ws = None
+            if not any(self._ws is t for t in self._ws_pinned_by_graphs):
+                self._ws = None  # free before the larger allocation, unless a captured graph still points into it
             self._ws = torch.empty(need, dtype=torch.uint8, device=self.device)
         return self._ws
+
+    def _check_capturable(self) -> None:
+        if self.tp_size > 1:
+            raise B200Error(10, "a tensor-parallel plan cannot be captured into a CUDA graph: the peer exchange "
+                                "numbers its rounds from the host; launch its steps eagerly")
 
     def saved_bytes(self, batch: int, seq: int) -> int:
         return self._bytes(lib().b200_saved_bytes, batch, seq)
@@ -400,9 +433,12 @@ class Plan:
     def capture_forward(self, tokens: torch.Tensor, logits: torch.Tensor) -> "torch.cuda.CUDAGraph":
         """Captures one forward over fixed token / logits buffers into a CUDA graph (the kernel sequence of a
         plan is static, so a replay costs one launch instead of 1 + 7L + 2).  Run one eager forward first so that
-        the workspace exists and every kernel attribute is set outside the capture."""
+        the workspace exists and every kernel attribute is set outside the capture.  The graph points into the plan's
+        workspace of this moment, which the plan keeps alive from here on even when a later, larger call replaces it."""
+        self._check_capturable()
         self.forward(tokens, logits=logits)
         torch.cuda.synchronize()
+        self._ws_pinned_by_graphs.append(self._ws)
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph):
             self.forward(tokens, logits=logits)
@@ -416,8 +452,10 @@ class Plan:
         copy calls between replays cost more than the copies themselves."""
         if not (host_tokens.is_pinned() and host_last_logits.is_pinned()):
             raise B200Error(1, "host buffers of a captured step must be pinned")
+        self._check_capturable()
         self.forward(tokens, logits=logits)
         torch.cuda.synchronize()
+        self._ws_pinned_by_graphs.append(self._ws)
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph):
             tokens.copy_(host_tokens, non_blocking=True)

@@ -23,8 +23,13 @@ LIB = os.path.join(LIBDIR, "libb200_llama.so")
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
-    "--use_fast_math", "-Xcompiler", "-fPIC,-fvisibility=hidden", "-Xptxas", "-v",
+    "-Xcompiler", "-fPIC,-fvisibility=hidden", "-Xptxas", "-v",
 ]
+# Only the bf16 tensor-core kernels (2e-2 bar) are built with fast math.  The files that serve the fp32
+# configuration (FFMA GEMM, fp32 attention, RMSNorm and the other elementwise kernels; 1e-4 / 1e-5 bar and
+# equal argmax) keep IEEE division and square roots, denormals, and the accurate expf.
+FAST_MATH_FILES = {"attention_mma.cu", "attention_bwd_tc.cu", "attention_decode.cu", "gemm_tc.cu", "gemm_tc2.cu",
+                   "comm.cu", "gemv_decode.cu"}
 
 
 def _nvcc() -> str:
@@ -36,8 +41,28 @@ def _newest(paths) -> float:
     return max(os.path.getmtime(p) for p in paths)
 
 
+def _xla_ffi_include():
+    """Directory holding xla/ffi/api/ffi.h (jaxlib ships it), or None.  B200_XLA_FFI_INCLUDE overrides."""
+    cand = [os.environ.get("B200_XLA_FFI_INCLUDE")]
+    try:
+        import importlib.util
+        spec = importlib.util.find_spec("jaxlib")
+        if spec and spec.submodule_search_locations:
+            cand.append(os.path.join(list(spec.submodule_search_locations)[0], "include"))
+    except Exception:
+        pass
+    for c in cand:
+        if c and os.path.exists(os.path.join(c, "xla", "ffi", "api", "ffi.h")):
+            return c
+    return None
+
+
 def _compile(src: str, obj: str, log: str):
-    cmd = [_nvcc(), *NVCC_FLAGS, "-c", src, "-o", obj]
+    fast = ["--use_fast_math", "-DB200_FAST_MATH=1"] if os.path.basename(src) in FAST_MATH_FILES else []
+    if src.endswith(".cc"):  # the XLA FFI shim: handlers are compiled in only where the XLA FFI headers exist
+        inc = _xla_ffi_include()
+        fast = ["-I", inc] if inc else []
+    cmd = [_nvcc(), *NVCC_FLAGS, *fast, "-c", src, "-o", obj]
     r = subprocess.run(cmd, capture_output=True, text=True)
     with open(log, "w") as f:
         f.write(" ".join(cmd) + "\n" + r.stdout + r.stderr)
@@ -47,7 +72,7 @@ def _compile(src: str, obj: str, log: str):
 
 
 def build(force: bool = False, verbose: bool = False) -> str:
-    srcs = sorted(glob.glob(os.path.join(CSRC, "*.cu")))
+    srcs = sorted(glob.glob(os.path.join(CSRC, "*.cu"))) + sorted(glob.glob(os.path.join(CSRC, "ffi", "*.cc")))
     hdrs = sorted(glob.glob(os.path.join(CSRC, "*.cuh"))) + [os.path.join(HERE, "..", "include", "b200_llama.h")]
     if not srcs:
         raise RuntimeError("no CUDA sources found")
@@ -57,7 +82,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
     jobs = []
     objs = []
     for s in srcs:
-        o = os.path.join(OBJDIR, os.path.basename(s)[:-3] + ".o")
+        o = os.path.join(OBJDIR, os.path.splitext(os.path.basename(s))[0] + ".o")
         objs.append(o)
         if force or not os.path.exists(o) or os.path.getmtime(o) < max(os.path.getmtime(s), hdr_time):
             jobs.append((s, o, o[:-2] + ".log"))

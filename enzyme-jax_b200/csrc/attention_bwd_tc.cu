@@ -374,12 +374,12 @@ int32_t launch_attn_bwd_tc(const AttnBwdArgs& a, cudaStream_t stream) {
   B200_TRY(make_map_3d(&tk, f.k, f.batch, f.seq, cols, f.ldkv));
   B200_TRY(make_map_3d(&tv, f.v, f.batch, f.seq, cols, f.ldkv));
   B200_TRY(make_map_3d(&tdo, a.d_o, f.batch, f.seq, cols, a.lddo));
-  static bool attr_set = false;
-  if (!attr_set) {
+  static PerDeviceOnce attr_once;
+  B200_TRY(attr_once.run([&](int&) -> int32_t {
     B200_CUDA_OK(cudaFuncSetAttribute(attn_bwd_tc_kernel<MODE_DKV>, cudaFuncAttributeMaxDynamicSharedMemorySize, kBwdSmem));
     B200_CUDA_OK(cudaFuncSetAttribute(attn_bwd_tc_kernel<MODE_DQ>, cudaFuncAttributeMaxDynamicSharedMemorySize, kBwdSmem));
-    attr_set = true;
-  }
+    return B200_OK;
+  }));
   BwdParams prm;
   prm.lse = f.lse; prm.delta = a.delta; prm.seq = f.seq; prm.n_heads = f.n_heads;
   prm.scale = 1.f / sqrtf(64.f);

@@ -369,11 +369,11 @@ int32_t launch_hs(const AttnArgs& a, cudaStream_t stream) {
   B200_TRY(make_map_3d(&tk, a.k, a.batch, a.seq, cols, a.ldkv));
   B200_TRY(make_map_3d(&tv, a.v, a.batch, a.seq, cols, a.ldkv));
   auto kern = attn_fwd_tc_kernel<HS>;
-  static bool attr_set = false;
-  if (!attr_set) {
+  static PerDeviceOnce attr_once;
+  B200_TRY(attr_once.run([&](int&) -> int32_t {
     B200_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes));
-    attr_set = true;
-  }
+    return B200_OK;
+  }));
   dim3 grid(a.n_heads, a.batch, cdiv(a.seq, AQ));
   B200_CUDA_OK(launch_pdl(kern, grid, dim3(A_THREADS), C::kSmemBytes, stream, tq, tk, tv, (bf16*)a.o, a.lse, a.seq,
                           a.n_heads, a.ldo, 1.f / sqrtf((float)HS), device_status_word()));

@@ -67,13 +67,13 @@ __global__ void __launch_bounds__(128) attn_fwd_simt_kernel(const T* __restrict_
     }
     if (bm > -INFINITY) {
       const float nm = fmaxf(mx, bm);
-      const float corr = __expf(mx - nm);
+      const float corr = exp_by_build(mx - nm);
       l *= corr;
 #pragma unroll
       for (int i = 0; i < DPT; ++i) acc[i] *= corr;
 #pragma unroll
       for (int uu = 0; uu < KB; ++uu) {
-        const float p = __expf(s[uu] - nm);
+        const float p = exp_by_build(s[uu] - nm);
         l += p;
 #pragma unroll
         for (int i = 0; i < DPT; ++i) acc[i] = fmaf(p, Vs[uu][part + 4 * i], acc[i]);
@@ -178,7 +178,7 @@ __global__ void __launch_bounds__(128)
       dp += __shfl_xor_sync(0xffffffffu, dp, 1);
       dp += __shfl_xor_sync(0xffffffffu, dp, 2);
       const bool live = row_ok && (u0 + uu <= t);
-      const float p = live ? __expf(s * scale - my_lse) : 0.f;
+      const float p = live ? exp_by_build(s * scale - my_lse) : 0.f;
       const float ds = p * (dp - my_delta) * scale;
 #pragma unroll
       for (int i = 0; i < DPT; ++i) acc[i] = fmaf(ds, Ks[uu][part + 4 * i], acc[i]);
@@ -241,7 +241,7 @@ __global__ void __launch_bounds__(128)
       dp += __shfl_xor_sync(0xffffffffu, dp, 2);
       const int t = t0 + tt;
       const bool live = row_ok && t < seq && t >= u;
-      const float p = live ? __expf(s * scale - Ls[tt]) : 0.f;
+      const float p = live ? exp_by_build(s * scale - Ls[tt]) : 0.f;
       const float ds = p * (dp - Dl[tt]) * scale;
 #pragma unroll
       for (int i = 0; i < DPT; ++i) {

@@ -90,6 +90,7 @@ struct Comm {
   NcclComm nccl = nullptr;
   int rank = 0, world = 1;
   PeerMem pm;
+  long long wait_budget = 4000000000LL;  // SM clocks a kernel waits for its peers before it gives up (B200_PEER_WAIT_MCYCLES)
 };
 
 namespace {
@@ -108,7 +109,7 @@ void setup_peer_memory(Comm* c) {
   if (c->world < 2 || c->world > kMaxPeers || env_int("B200_P2P", 1) == 0) return;
   NcclApi& a = api();
   PeerMem& pm = c->pm;
-  pm.bytes = (size_t)env_int("B200_P2P_MB", 72) << 20;
+  pm.bytes = (size_t)env_int("B200_P2P_MB", 136) << 20;
   void* lbuf = nullptr;
   uint32_t* lflags = nullptr;
   uint8_t* dscratch = nullptr;  // [world + 1] blobs, then one float for the agreement
@@ -204,6 +205,7 @@ namespace {
 
 enum : uint32_t { ST_PEER_TIMEOUT = 1u << 12 };
 constexpr int kReadyBase = 0, kDoneBase = 8, kCounter = 32;
+constexpr long long kPeerWaitCycles = 4000000000LL;
 
 __device__ __forceinline__ void flag_store_sys(uint32_t* p, uint32_t v) {
   asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
@@ -227,17 +229,18 @@ struct PeerPtrs {
 };
 
 // Thread 0 of the CTA waits until every rank's flag word `base + r` in this
-// rank's flag array has reached `epoch`; about two seconds at most.  Returns
-// false (for the whole CTA) when the wait ran out.
+// rank's flag array has reached `epoch`, for at most `budget` SM clocks in all
+// (the default, kPeerWaitCycles, is about two seconds).  Returns false (for the
+// whole CTA) when the wait ran out; the status word then carries ST_PEER_TIMEOUT.
 __device__ __forceinline__ bool wait_all_peers(const uint32_t* my_flags, int base, int world, uint32_t epoch,
-                                               uint32_t* status) {
+                                               uint32_t* status, long long budget) {
   __shared__ int s_ok;
   if (threadIdx.x == 0) {
     int ok = 1;
     const long long t0 = clock64();
     for (int r = 0; r < world && ok; ++r) {
       while ((int32_t)(flag_load_sys(my_flags + base + r) - epoch) < 0) {
-        if (clock64() - t0 > 4000000000LL) {
+        if (clock64() - t0 > budget) {
           ok = 0;
           atomicOr(status, ST_PEER_TIMEOUT);
           break;
@@ -269,13 +272,13 @@ __device__ __forceinline__ void accum8(const uint4& raw, float (&acc)[8], float)
 // into every rank's buffer.  The last CTA to finish tells the peers.
 template <typename T>
 __global__ void __launch_bounds__(512) peer_reduce_kernel(PeerPtrs pp, int rank, int world, size_t n_vec16,
-                                                          uint32_t epoch, uint32_t* status) {
+                                                          uint32_t epoch, uint32_t* status, long long budget) {
   uint32_t* my_flags = pp.flags[rank];
   if (blockIdx.x == 0 && threadIdx.x < world) {
     __threadfence_system();
     flag_store_sys(pp.flags[threadIdx.x] + kReadyBase + rank, epoch);
   }
-  const bool ok = wait_all_peers(my_flags, kReadyBase, world, epoch, status);
+  const bool ok = wait_all_peers(my_flags, kReadyBase, world, epoch, status, budget);
   if (ok) {
     const size_t per = (n_vec16 + world - 1) / world;
     const size_t v0 = (size_t)rank * per, v1 = min(n_vec16, v0 + per);
@@ -317,8 +320,8 @@ __global__ void __launch_bounds__(512) peer_reduce_kernel(PeerPtrs pp, int rank,
 template <typename T>
 __global__ void __launch_bounds__(512) peer_add_kernel(PeerPtrs pp, int rank, int world, size_t n_vec16,
                                                        uint32_t epoch, const float* __restrict__ resid,
-                                                       float* __restrict__ out, uint32_t* status) {
-  if (!wait_all_peers(pp.flags[rank], kDoneBase, world, epoch, status)) return;
+                                                       float* __restrict__ out, uint32_t* status, long long budget) {
+  if (!wait_all_peers(pp.flags[rank], kDoneBase, world, epoch, status, budget)) return;
   constexpr int E = 16 / sizeof(T);  // elements per 16 bytes
   for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n_vec16; i += (size_t)gridDim.x * blockDim.x) {
     const uint4 raw = load16_sys(reinterpret_cast<const uint4*>(pp.buf[rank]) + i);
@@ -341,12 +344,12 @@ template <typename T>
 __global__ void __launch_bounds__(512) peer_oneshot_kernel(PeerPtrs pp, int rank, int world, size_t n_vec16,
                                                            size_t half_off, uint32_t epoch,
                                                            const float* __restrict__ resid, float* __restrict__ out,
-                                                           uint32_t* status) {
+                                                           uint32_t* status, long long budget) {
   if (blockIdx.x == 0 && threadIdx.x < world) {
     __threadfence_system();
     flag_store_sys(pp.flags[threadIdx.x] + kReadyBase + rank, epoch);
   }
-  if (!wait_all_peers(pp.flags[rank], kReadyBase, world, epoch, status)) return;
+  if (!wait_all_peers(pp.flags[rank], kReadyBase, world, epoch, status, budget)) return;
   constexpr int E = 16 / sizeof(T);
   for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n_vec16; i += (size_t)gridDim.x * blockDim.x) {
     uint4 raw[kMaxPeers];
@@ -364,6 +367,138 @@ __global__ void __launch_bounds__(512) peer_oneshot_kernel(PeerPtrs pp, int rank
       *reinterpret_cast<float4*>(out + i * E + 4) = make_float4(b.x + s[4], b.y + s[5], b.z + s[6], b.w + s[7]);
     }
   }
+}
+
+// Row-sharded residual stream (tensor-parallel prefill).  Every rank owns T / world consecutive rows of the fp32
+// residual stream.  One kernel replaces the all-reduce, the residual add and the RMSNorm that follows them:
+//   - tell the peers this rank's partial product (all T rows, in its exchange buffer) is complete, wait for theirs;
+//   - for every own row: sum the row's partials over the ranks with plain peer loads (rank order, fp32), add the
+//     sum to the residual row (kept in fp32, never rounded), take the row's RMS, and store gain * x * rinv in the
+//     activation type into the gathered-activation region of EVERY rank (plain peer stores);
+//   - the last CTA tells the peers this rank's rows are written and then waits until every peer has said the same,
+//     so that the kernel's completion means this rank's gathered activations are whole.
+// The reduce-scatter and the all-gather thus cross NVLink once each, and the residual stream, the add and the norm
+// touch T / world rows per rank instead of T.  REDUCE = false skips the partial sums (the norm after the embedding).
+// A CTA takes one row at a time; a thread keeps its 16-byte chunks of the row in registers between the two passes
+// (rows wider than kRowChunks * 256 chunks are re-read from the residual buffer, which is local).
+constexpr int kRowChunks = 4;
+
+template <typename T, bool REDUCE>
+__global__ void __launch_bounds__(256) peer_rownorm_kernel(PeerPtrs pp, int rank, int world, size_t part_off,
+                                                           size_t xb_off, int rows, int row0, int d,
+                                                           float* __restrict__ x_own, const float* __restrict__ gain,
+                                                           float eps, uint32_t epoch, uint32_t* status,
+                                                           long long budget) {
+  constexpr int E = 16 / sizeof(T);  // elements per 16-byte chunk
+  __shared__ float red[32];
+  __shared__ int s_last;
+  uint32_t* my_flags = pp.flags[rank];
+  if (blockIdx.x == 0 && threadIdx.x < world) {
+    __threadfence_system();
+    flag_store_sys(pp.flags[threadIdx.x] + kReadyBase + rank, epoch);
+  }
+  const bool ok = wait_all_peers(my_flags, kReadyBase, world, epoch, status, budget);
+  const int n_chunks = d / E;
+  if (ok) {
+    for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+      const size_t grow = (size_t)(row0 + row);
+      float* xr = x_own + (size_t)row * d;
+      float v[kRowChunks][E];
+      float ss = 0.f;
+#pragma unroll
+      for (int k = 0; k < kRowChunks; ++k) {
+        const int c = threadIdx.x + k * 256;
+        if (c < n_chunks) {
+          float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+          if (REDUCE) {
+            uint4 raw[kMaxPeers];
+            const size_t off = part_off + (grow * d + (size_t)c * E) * sizeof(T);
+#pragma unroll
+            for (int r = 0; r < kMaxPeers; ++r)
+              if (r < world) raw[r] = load16_sys(reinterpret_cast<const uint8_t*>(pp.buf[r]) + off);
+#pragma unroll
+            for (int r = 0; r < kMaxPeers; ++r)
+              if (r < world) accum8(raw[r], acc, T());
+          }
+#pragma unroll
+          for (int i = 0; i < E; i += 4) {
+            float4 a = *reinterpret_cast<const float4*>(xr + c * E + i);
+            a.x += acc[i]; a.y += acc[i + 1]; a.z += acc[i + 2]; a.w += acc[i + 3];
+            if (REDUCE) *reinterpret_cast<float4*>(xr + c * E + i) = a;
+            v[k][i] = a.x; v[k][i + 1] = a.y; v[k][i + 2] = a.z; v[k][i + 3] = a.w;
+            ss = fmaf(a.x, a.x, fmaf(a.y, a.y, fmaf(a.z, a.z, fmaf(a.w, a.w, ss))));
+          }
+        }
+      }
+      // rows wider than the register tile: same arithmetic, the residual row is re-read below
+      for (int c = threadIdx.x + kRowChunks * 256; c < n_chunks; c += 256) {
+        float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        if (REDUCE) {
+          const size_t off = part_off + (grow * d + (size_t)c * E) * sizeof(T);
+          for (int r = 0; r < world; ++r) accum8(load16_sys(reinterpret_cast<const uint8_t*>(pp.buf[r]) + off), acc, T());
+        }
+        for (int i = 0; i < E; ++i) {
+          const float a = xr[c * E + i] + acc[i];
+          if (REDUCE) xr[c * E + i] = a;
+          ss = fmaf(a, a, ss);
+        }
+      }
+      ss = block_sum(ss, red);
+      const float rinv = rsqrtf(ss / (float)d + eps);
+      auto emit = [&](int c, const float* val) {
+        float y[8];
+#pragma unroll
+        for (int i = 0; i < E; i += 4) {
+          const float4 g = *reinterpret_cast<const float4*>(gain + c * E + i);
+          y[i] = g.x * val[i] * rinv; y[i + 1] = g.y * val[i + 1] * rinv;
+          y[i + 2] = g.z * val[i + 2] * rinv; y[i + 3] = g.w * val[i + 3] * rinv;
+        }
+        uint4 out;
+        if (sizeof(T) == 2) {
+          __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&out);
+#pragma unroll
+          for (int k2 = 0; k2 < 4; ++k2) h[k2] = __floats2bfloat162_rn(y[2 * k2], y[2 * k2 + 1]);
+        } else {
+          out = make_uint4(__float_as_uint(y[0]), __float_as_uint(y[1]), __float_as_uint(y[2]), __float_as_uint(y[3]));
+        }
+        const size_t off = xb_off + (grow * d + (size_t)c * E) * sizeof(T);
+#pragma unroll
+        for (int r = 0; r < kMaxPeers; ++r)
+          if (r < world) *reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(pp.buf[r]) + off) = out;
+      };
+#pragma unroll
+      for (int k = 0; k < kRowChunks; ++k) {
+        const int c = threadIdx.x + k * 256;
+        if (c < n_chunks) emit(c, v[k]);
+      }
+      for (int c = threadIdx.x + kRowChunks * 256; c < n_chunks; c += 256) {
+        float val[8];
+        for (int i = 0; i < E; ++i) val[i] = xr[c * E + i];
+        emit(c, val);
+      }
+    }
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const uint32_t done = atomicAdd(my_flags + kCounter, 1u);
+    s_last = done == gridDim.x - 1;
+    if (s_last) {
+      my_flags[kCounter] = 0u;
+      __threadfence_system();
+      for (int r = 0; r < world; ++r) flag_store_sys(pp.flags[r] + kDoneBase + rank, epoch);
+    }
+  }
+  __syncthreads();
+  if (s_last && ok) wait_all_peers(my_flags, kDoneBase, world, epoch, status, budget);
+}
+
+// One CTA waits, with the given budget, on peer flags that nothing ever sets (a flag array private to this
+// self-test): the wait gives up, the status word receives ST_PEER_TIMEOUT, the kernel writes 1 to *reached_end.
+__device__ uint32_t g_selftest_peer_flags[kFlagWords];
+__global__ void peer_wait_selftest_kernel(long long budget, uint32_t* reached_end, uint32_t* status) {
+  const bool ok = wait_all_peers(g_selftest_peer_flags, kReadyBase, 2, 1u, status, budget);
+  if (threadIdx.x == 0) *reached_end = ok ? 2u : 1u;
 }
 
 constexpr size_t kOneShotMaxBytes = (size_t)2 << 20;
@@ -384,6 +519,73 @@ void* comm_peer_buffer(void* comm, size_t bytes) {
   return base + 2 * kOneShotMaxBytes;
 }
 
+static int32_t reject_capture(cudaStream_t stream, const char* what) {
+  cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
+  if (cudaStreamIsCapturing(stream, &cs) != cudaSuccess) {
+    cudaGetLastError();
+    return B200_OK;
+  }
+  if (cs != cudaStreamCaptureStatusNone)
+    return fail(B200_ERR_UNSUPPORTED,
+                "%s cannot be captured into a CUDA graph: its epoch number is a launch argument, so a replay would "
+                "find the peers' flags already set; launch tensor-parallel steps eagerly", what);
+  return B200_OK;
+}
+
+// Regions of this rank's exchange buffer for the row-sharded prefill: `part` receives this rank's partial product
+// [T, d], `xb` is where every rank deposits its rows of the normed activations.  False when the peer path is off or
+// the two regions do not fit.
+bool comm_peer_rowshard_buffers(void* comm, size_t bytes_each, void** part, void** xb) {
+  if (!comm) return false;
+  Comm* c = reinterpret_cast<Comm*>(comm);
+  const size_t each = align_up(bytes_each, 256);
+  if (!c->pm.on || c->pm.bytes < 2 * kOneShotMaxBytes + 2 * each) return false;
+  uint8_t* base = reinterpret_cast<uint8_t*>(c->pm.buf[c->rank]) + 2 * kOneShotMaxBytes;
+  *part = base;
+  *xb = base + each;
+  return true;
+}
+
+int32_t comm_peer_reduce_norm(void* comm, int T, int d, int dtype, bool reduce, float* x_own, const float* gain,
+                              float eps, cudaStream_t stream) {
+  Comm* c = reinterpret_cast<Comm*>(comm);
+  if (!c || !c->pm.on) return fail(B200_ERR_INVALID_ARG, "peer memory is not set up for this communicator");
+  const size_t es = dtype == B200_BF16 ? 2 : 4;
+  if (T % c->world || ((size_t)d * es) % 16 || d % 4)
+    return fail(B200_ERR_BAD_SHAPE, "row-sharded exchange: %d rows over %d ranks, row of %d elements", T, c->world, d);
+  B200_TRY(reject_capture(stream, "the tensor-parallel exchange over peer memory"));
+  const size_t each = align_up((size_t)T * d * es, 256);
+  ProfScope prof(PROF_COMM, (double)T * d * es, stream);
+  PeerPtrs pp;
+  for (int r = 0; r < kMaxPeers; ++r) {
+    pp.buf[r] = c->pm.buf[r];
+    pp.flags[r] = c->pm.flags[r];
+  }
+  const uint32_t epoch = ++c->pm.epoch;
+  const int rows = T / c->world, row0 = c->rank * rows;
+  const size_t part_off = 2 * kOneShotMaxBytes, xb_off = part_off + each;
+  int grid = sm_count() * 2;  // two CTAs of 256 threads are resident per SM (register tile of the row)
+  if (grid > rows) grid = rows;
+  uint32_t* status = device_status_word();
+#define B200_ROWNORM(TT, RR)                                                                                       \
+  peer_rownorm_kernel<TT, RR><<<grid, 256, 0, stream>>>(pp, c->rank, c->world, part_off, xb_off, rows, row0, d,    \
+                                                        x_own, gain, eps, epoch, status, c->wait_budget)
+  if (dtype == B200_BF16) {
+    if (reduce) B200_ROWNORM(bf16, true); else B200_ROWNORM(bf16, false);
+  } else {
+    if (reduce) B200_ROWNORM(float, true); else B200_ROWNORM(float, false);
+  }
+#undef B200_ROWNORM
+  B200_LAUNCH_OK("peer_rownorm_kernel");
+  return B200_OK;
+}
+
+int32_t launch_peer_wait_selftest(long long budget, uint32_t* reached_end, cudaStream_t stream) {
+  peer_wait_selftest_kernel<<<1, 32, 0, stream>>>(budget, reached_end, device_status_word());
+  B200_LAUNCH_OK("peer_wait_selftest_kernel");
+  return B200_OK;
+}
+
 int32_t comm_peer_allreduce_add(void* comm, size_t count, int dtype, const float* resid, float* out,
                                 cudaStream_t stream) {
   Comm* c = reinterpret_cast<Comm*>(comm);
@@ -391,6 +593,7 @@ int32_t comm_peer_allreduce_add(void* comm, size_t count, int dtype, const float
   const size_t es = dtype == B200_BF16 ? 2 : 4;
   if ((count * es) % 16 || count * es > c->pm.bytes - 2 * kOneShotMaxBytes)
     return fail(B200_ERR_BAD_SHAPE, "peer all-reduce: bad size");
+  B200_TRY(reject_capture(stream, "the tensor-parallel all-reduce over peer memory"));
   ProfScope prof(PROF_COMM, (double)count * es, stream);
   const bool small = count * es <= kOneShotMaxBytes;
   PeerPtrs pp;
@@ -407,9 +610,9 @@ int32_t comm_peer_allreduce_add(void* comm, size_t count, int dtype, const float
     int g1 = (int)((n_vec + 511) / 512);
     if (g1 > sm_count()) g1 = sm_count();
     if (dtype == B200_BF16)
-      peer_oneshot_kernel<bf16><<<g1, 512, 0, stream>>>(pp, c->rank, c->world, n_vec, half_off, epoch, resid, out, status);
+      peer_oneshot_kernel<bf16><<<g1, 512, 0, stream>>>(pp, c->rank, c->world, n_vec, half_off, epoch, resid, out, status, c->wait_budget);
     else
-      peer_oneshot_kernel<float><<<g1, 512, 0, stream>>>(pp, c->rank, c->world, n_vec, half_off, epoch, resid, out, status);
+      peer_oneshot_kernel<float><<<g1, 512, 0, stream>>>(pp, c->rank, c->world, n_vec, half_off, epoch, resid, out, status, c->wait_budget);
     B200_LAUNCH_OK("peer_oneshot_kernel");
     return B200_OK;
   }
@@ -417,17 +620,17 @@ int32_t comm_peer_allreduce_add(void* comm, size_t count, int dtype, const float
   const size_t want = (n_vec / c->world + 511) / 512;
   if ((size_t)grid > want) grid = want < 1 ? 1 : (int)want;
   if (dtype == B200_BF16)
-    peer_reduce_kernel<bf16><<<grid, 512, 0, stream>>>(pp, c->rank, c->world, n_vec, epoch, status);
+    peer_reduce_kernel<bf16><<<grid, 512, 0, stream>>>(pp, c->rank, c->world, n_vec, epoch, status, c->wait_budget);
   else
-    peer_reduce_kernel<float><<<grid, 512, 0, stream>>>(pp, c->rank, c->world, n_vec, epoch, status);
+    peer_reduce_kernel<float><<<grid, 512, 0, stream>>>(pp, c->rank, c->world, n_vec, epoch, status, c->wait_budget);
   B200_LAUNCH_OK("peer_reduce_kernel");
   int grid2 = sm_count() * 2;
   const size_t want2 = (n_vec + 511) / 512;
   if ((size_t)grid2 > want2) grid2 = want2 < 1 ? 1 : (int)want2;
   if (dtype == B200_BF16)
-    peer_add_kernel<bf16><<<grid2, 512, 0, stream>>>(pp, c->rank, c->world, n_vec, epoch, resid, out, status);
+    peer_add_kernel<bf16><<<grid2, 512, 0, stream>>>(pp, c->rank, c->world, n_vec, epoch, resid, out, status, c->wait_budget);
   else
-    peer_add_kernel<float><<<grid2, 512, 0, stream>>>(pp, c->rank, c->world, n_vec, epoch, resid, out, status);
+    peer_add_kernel<float><<<grid2, 512, 0, stream>>>(pp, c->rank, c->world, n_vec, epoch, resid, out, status, c->wait_budget);
   B200_LAUNCH_OK("peer_add_kernel");
   return B200_OK;
 }
@@ -461,6 +664,8 @@ int32_t b200_comm_init_rank(const void* id128, int32_t rank, int32_t world, void
   c->nccl = nc;
   c->rank = rank;
   c->world = world;
+  const int budget_m = env_int("B200_PEER_WAIT_MCYCLES", 4000);  // millions of SM clocks
+  c->wait_budget = (long long)(budget_m > 0 ? budget_m : 4000) * 1000000LL;
   setup_peer_memory(c);
   *comm = c;
   return B200_OK;
@@ -472,6 +677,18 @@ int32_t b200_comm_destroy(void* comm) {
   NcclApi& a = api();
   if (!a.ok) return fail(B200_ERR_NCCL, "NCCL is not available in this process");
   cudaDeviceSynchronize();
+  // The exchange buffer and flag words are mapped by the peers: nobody frees them until every rank has finished
+  // its own work (a slower peer may still be reading this rank's buffer or storing into its flags).  A one-float
+  // all-reduce is the agreement; a rank whose peers are gone gets an error from it and frees anyway.
+  if (c->world > 1) {
+    float* token = nullptr;
+    if (cudaMalloc(&token, 256) == cudaSuccess) {
+      cudaMemset(token, 0, 256);
+      if (a.all_reduce(token, token, 1, kNcclFloat32, kNcclSum, c->nccl, 0) == 0) cudaStreamSynchronize(0);
+      cudaFree(token);
+    }
+    cudaGetLastError();
+  }
   free_peer_memory(c);
   const int rc = a.comm_destroy(c->nccl);
   delete c;
@@ -481,6 +698,12 @@ int32_t b200_comm_destroy(void* comm) {
 
 int32_t b200_allreduce_f32(void* comm, float* data, size_t count, b200_stream_t stream) {
   return comm_allreduce(comm, data, count, B200_F32, reinterpret_cast<cudaStream_t>(stream));
+}
+
+int32_t b200_selftest_peer_wait(int64_t budget_cycles, uint32_t* reached_end_device, b200_stream_t stream) {
+  if (!reached_end_device) return fail(B200_ERR_INVALID_ARG, "null argument");
+  if (budget_cycles <= 0 || budget_cycles > 4000000000LL) return fail(B200_ERR_INVALID_ARG, "budget out of range");
+  return launch_peer_wait_selftest(budget_cycles, reached_end_device, reinterpret_cast<cudaStream_t>(stream));
 }
 
 int32_t b200_comm_peer_memory(void* comm, int32_t* enabled) {

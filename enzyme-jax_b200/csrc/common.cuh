@@ -7,6 +7,8 @@
 #include <stdint.h>
 #include <stdio.h>
 
+#include <mutex>
+
 #include "../../include/b200_llama.h"
 
 namespace b200 {
@@ -41,7 +43,7 @@ int32_t fail(int32_t code, const char* fmt, ...);
 void count_launch();
 
 // Event-pair profiling of kernel classes (off unless enabled through the ABI).
-enum ProfClass : int { PROF_GEMM_TC = 0, PROF_GEMM_SIMT = 1, PROF_ATTN_FWD = 2, PROF_ATTN_BWD = 3, PROF_ATTN_DECODE = 4, PROF_COMM = 5, PROF_NUM = 6 };
+enum ProfClass : int { PROF_GEMM_TC = 0, PROF_GEMM_SIMT = 1, PROF_ATTN_FWD = 2, PROF_ATTN_BWD = 3, PROF_ATTN_DECODE = 4, PROF_COMM = 5, PROF_GEMM_PAIR = 6, PROF_NUM = 7 };
 struct ProfScope {
   int slot = -1;
   cudaStream_t stream;
@@ -77,6 +79,28 @@ inline cudaError_t launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3 block, siz
   cfg.numAttrs = pdl_enabled() ? 1 : 0;
   return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
 }
+
+// One-time set-up per device (kernel attributes, occupancy queries are per device, and a process may
+// drive several).  run(f) calls f(value) once for the current device, under a lock, and later returns
+// the value it left; concurrent callers on the same device wait for the first to finish.
+struct PerDeviceOnce {
+  std::mutex mu;
+  bool done[64] = {};
+  int value[64] = {};
+  template <typename F> int32_t run(F&& f, int* out = nullptr) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64)
+      return ::b200::fail(B200_ERR_CUDA, "no current CUDA device");
+    std::lock_guard<std::mutex> lk(mu);
+    if (!done[dev]) {
+      const int32_t st = f(value[dev]);
+      if (st != B200_OK) return st;
+      done[dev] = true;
+    }
+    if (out) *out = value[dev];
+    return B200_OK;
+  }
+};
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
@@ -158,6 +182,16 @@ __device__ __forceinline__ void load8_wide(const float* p, float (&v)[8]) {
   } else {
     load8(p, v);
   }
+}
+
+// exp(x): the fast approximation in files built with fast math (B200_FAST_MATH, the bf16 tensor-core kernels), the accurate
+// library function elsewhere (the fp32 configuration).
+__device__ __forceinline__ float exp_by_build(float x) {
+#ifdef B200_FAST_MATH
+  return __expf(x);
+#else
+  return expf(x);
+#endif
 }
 
 __device__ __forceinline__ float warp_sum(float v) {

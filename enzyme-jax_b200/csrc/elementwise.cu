@@ -356,7 +356,7 @@ __global__ void swiglu_bwd_kernel(const T* __restrict__ gate, const T* __restric
     load8(dh + (size_t)r * hidden + c, d);
 #pragma unroll
     for (int k = 0; k < 8; ++k) {
-      const float sg = 1.f / (1.f + __expf(-a[k]));
+      const float sg = 1.f / (1.f + exp_by_build(-a[k]));
       db[k] = d[k] * a[k] * sg;
       da[k] = d[k] * b[k] * sg * (1.f + a[k] * (1.f - sg));
     }

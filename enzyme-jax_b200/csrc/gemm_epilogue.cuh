@@ -127,7 +127,7 @@ __device__ __forceinline__ void epi_apply16(const EpiParams& p, const EpiRow& ro
     for (int i = 0; i < 8; ++i) {
       g[i] = v[i];
       u[i] = v[8 + i];
-      h[i] = g[i] / (1.f + __expf(-g[i])) * u[i];
+      h[i] = g[i] / (1.f + exp_by_build(-g[i])) * u[i];
     }
     store8(reinterpret_cast<TOut*>(p.out) + off, h);
     if (p.out_gate) {

@@ -352,11 +352,11 @@ int32_t launch_cfg(const GemmArgs& g, cudaStream_t stream) {
   if (BMN) B200_TRY(make_map_2d(&tmB, g.B, g.K, g.N, g.ldb, TBK));
   else B200_TRY(make_map_2d(&tmB, g.B, g.N, g.K, g.ldb, BN));
   auto kern = gemm_tc_kernel<BN, KIND, TOut, AMN, BMN>;
-  static bool attr_set = false;  // per instantiation
-  if (!attr_set) {
+  static PerDeviceOnce attr_once;  // per instantiation
+  B200_TRY(attr_once.run([&](int&) -> int32_t {
     B200_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
-    attr_set = true;
-  }
+    return B200_OK;
+  }));
   const int tiles = cdiv(g.M, TBM) * cdiv(g.N, BN);
   const int splits = pick_splits(g, tiles);
   const int items = tiles * splits;
@@ -480,13 +480,16 @@ int32_t launch_splitk_reduce(const GemmArgs& g, int splits, cudaStream_t stream)
 
 int32_t launch_gemm(const GemmArgs& g, int impl, cudaStream_t stream) {
   const bool tc = impl == 1 || (impl != 2 && gemm_tc_supports(g));
-  ProfScope prof(tc ? PROF_GEMM_TC : PROF_GEMM_SIMT, 2.0 * g.M * (double)g.N * g.K, stream);
-  if (!tc) return launch_gemm_simt(g, stream);
   // B200_GEMM_PAIR=0 keeps every problem on the single-CTA kernel
   static const int use_pair = env_int("B200_GEMM_PAIR", 1);
-  if (use_pair && gemm_tc2_supports(g)) return launch_gemm_tc2(g, stream);
   static const int pair_mn = env_int("B200_GEMM_PAIR_MN", 1);  // 0 keeps weight gradients on the single-CTA kernel
-  if (use_pair && pair_mn && gemm_tc2_mn_supports(g)) return launch_gemm_tc2_mn(g, stream);
+  const bool pair = tc && use_pair && gemm_tc2_supports(g);
+  const bool pair_t = tc && !pair && use_pair && pair_mn && gemm_tc2_mn_supports(g);
+  ProfScope prof(!tc ? PROF_GEMM_SIMT : (pair || pair_t) ? PROF_GEMM_PAIR : PROF_GEMM_TC,
+                 2.0 * g.M * (double)g.N * g.K, stream);
+  if (!tc) return launch_gemm_simt(g, stream);
+  if (pair) return launch_gemm_tc2(g, stream);
+  if (pair_t) return launch_gemm_tc2_mn(g, stream);
   return launch_gemm_tc(g, stream);
 }
 

@@ -530,15 +530,13 @@ int32_t launch_pair_cfg(const GemmArgs& g, cudaStream_t stream, int splits = 1) 
     if (KIND == EPI_RESID) B200_TRY(make_map_out(&tmR, g.epi.resid_in, g.M, g.N, g.epi.ldo, 4, 128));
   }
   auto kern = gemm_tc2_kernel<BN, KIND, TOut, MN>;
-  static bool attr_set = false;
-  if (!attr_set) {
+  // The shared-memory attribute and the number of resident clusters are per device.  Clusters are placed inside one
+  // GPC, so fewer than sm_count()/2 pairs may be resident at once; the grid is persistent with a static tile
+  // assignment, so launch exactly the resident number.
+  static PerDeviceOnce setup_once;  // per instantiation
+  int max_pairs = 0;
+  B200_TRY(setup_once.run([&](int& pairs_out) -> int32_t {
     B200_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
-    attr_set = true;
-  }
-  // Clusters are placed inside one GPC, so fewer than sm_count()/2 pairs may be resident at once; the
-  // grid is persistent with a static tile assignment, so launch exactly the resident number.
-  static int max_pairs = 0;
-  if (max_pairs == 0) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(sm_count() & ~1, 1, 1);
     cfg.blockDim = dim3(P_THREADS, 1, 1);
@@ -553,8 +551,9 @@ int32_t launch_pair_cfg(const GemmArgs& g, cudaStream_t stream, int splits = 1) 
       cudaGetLastError();
       n = sm_count() / 2;
     }
-    max_pairs = n < sm_count() / 2 ? n : sm_count() / 2;
-  }
+    pairs_out = n < sm_count() / 2 ? n : sm_count() / 2;
+    return B200_OK;
+  }, &max_pairs));
   const int items = cdiv(g.M, 2 * PM) * cdiv(g.N, BN) * splits;
   int pairs = max_pairs;
   if (g.max_ctas > 0 && g.max_ctas / 2 < pairs) pairs = g.max_ctas / 2;

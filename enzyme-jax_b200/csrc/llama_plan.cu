@@ -229,6 +229,77 @@ static int32_t proj_residual(const B200Plan& p, const void* A, int lda, const vo
   return launch_add_to_f32(x_out, tp_tmp, p.dtype, (size_t)T * p.d, stream);
 }
 
+// Tensor-parallel forward with a row-sharded residual stream (peer memory up, T a multiple of the ranks).  This rank
+// keeps the fp32 residual rows [rank * T/tp, (rank + 1) * T/tp) only.  The row-parallel projections (Wo, W2) leave
+// their bf16 partial product, all T rows, in the exchange buffer; comm_peer_reduce_norm then sums every own row over
+// the ranks, adds it to the residual row, norms it and deposits the normed row with every rank, so that the next
+// column-parallel projection (QKV, W1|W3, logits) finds all T normed rows in local memory.  Per block: one kernel
+// and one crossing of NVLink in each direction instead of all-reduce + add + norm over all T rows.
+static int32_t forward_row_sharded(B200Plan* p, const int32_t* tokens, int B, int S, const uint8_t* w,
+                                   const PackedLayout& wl, float* logits, void* kv_out, const LayerActs& a,
+                                   void* part, void* xbg, cudaStream_t stream) {
+  const int T = B * S, d = p->d, dl = p->d_loc, hl = p->h_loc;
+  const int rows = T / p->tp_size, row0 = p->tp_rank * rows;
+  const float* g_att = reinterpret_cast<const float*>(w + wl.g_att);
+  const float* g_ffn = reinterpret_cast<const float*>(w + wl.g_ffn);
+  const float* g_fin = reinterpret_cast<const float*>(w + wl.g_final);
+  const float eps = p->cfg.rms_eps;
+  float* x_own = a.x_in;  // [T, d] in the workspace; the first T/tp rows hold this rank's residual rows
+  B200_TRY(launch_embed(tokens + row0, w + wl.emb, p->dtype, x_own, rows, d, p->V, stream));
+  B200_TRY(comm_peer_reduce_norm(p->comm, T, d, p->dtype, false, x_own, g_att, eps, stream));
+  for (int l = 0; l < p->L; ++l) {
+    const LayerOffsets& o = wl.layer[l];
+    {
+      EpiParams e;
+      e.out = a.qkv; e.ldo = 3 * dl;
+      e.rope_cos = p->rope_cos; e.rope_sin = p->rope_sin;
+      e.seq_len = S; e.pos_base = 0; e.head_size = p->hs; e.rope_cols = 2 * dl;
+      B200_TRY(gemm(*p, xbg, d, w + o.wqkv, d, T, 3 * dl, d, EPI_ROPE, p->dtype, e, stream));
+    }
+    if (kv_out) {
+      uint8_t* dst = reinterpret_cast<uint8_t*>(kv_out) + (size_t)l * 2 * T * dl * p->esize;
+      const uint8_t* src = reinterpret_cast<const uint8_t*>(a.qkv);
+      for (int part_i = 0; part_i < 2; ++part_i)
+        B200_CUDA_OK(cudaMemcpy2DAsync(dst + (size_t)part_i * T * dl * p->esize, (size_t)dl * p->esize,
+                                       src + (size_t)(1 + part_i) * dl * p->esize, (size_t)3 * dl * p->esize,
+                                       (size_t)dl * p->esize, T, cudaMemcpyDeviceToDevice, stream));
+    }
+    {
+      AttnArgs at;
+      const uint8_t* base = reinterpret_cast<const uint8_t*>(a.qkv);
+      at.q = base; at.k = base + (size_t)dl * p->esize; at.v = base + (size_t)2 * dl * p->esize;
+      at.o = a.o; at.lse = a.lse;
+      at.batch = B; at.seq = S; at.n_heads = p->H_loc; at.head_size = p->hs;
+      at.ldq = 3 * dl; at.ldkv = 3 * dl; at.ldo = dl; at.dtype = p->dtype;
+      B200_TRY(launch_attn_fwd(at, p->attn_impl, stream));
+    }
+    {
+      EpiParams e;
+      e.out = part; e.ldo = d;
+      B200_TRY(gemm(*p, a.o, dl, w + o.wo, dl, T, d, dl, EPI_STORE, p->dtype, e, stream));
+    }
+    B200_TRY(comm_peer_reduce_norm(p->comm, T, d, p->dtype, true, x_own, g_ffn + (size_t)l * d, eps, stream));
+    {
+      EpiParams e;
+      e.out = a.hg; e.ldo = hl;
+      B200_TRY(gemm(*p, xbg, d, w + o.w13, d, T, 2 * hl, d, EPI_SWIGLU, p->dtype, e, stream));
+    }
+    {
+      EpiParams e;
+      e.out = part; e.ldo = d;
+      B200_TRY(gemm(*p, a.hg, hl, w + o.w2, hl, T, d, hl, EPI_STORE, p->dtype, e, stream));
+    }
+    const float* g_next = l + 1 < p->L ? g_att + (size_t)(l + 1) * d : g_fin;
+    B200_TRY(comm_peer_reduce_norm(p->comm, T, d, p->dtype, true, x_own, g_next, eps, stream));
+  }
+  if (logits) {
+    EpiParams e;
+    e.out = logits; e.ldo = p->V_loc;
+    B200_TRY(gemm(*p, xbg, d, w + wl.wcls, d, T, p->V_loc, d, EPI_STORE, B200_F32, e, stream));
+  }
+  return B200_OK;
+}
+
 static int32_t forward_impl(B200Plan* p, const int32_t* tokens, int B, int S, const uint8_t* w, const PackedLayout& wl,
                             float* logits, void* saved, void* kv_out, void* ws, size_t ws_bytes,
                             cudaStream_t stream) {
@@ -244,6 +315,11 @@ static int32_t forward_impl(B200Plan* p, const int32_t* tokens, int B, int S, co
   }
   void* tp_tmp = p->tp_size > 1 ? wa.take((size_t)T * p->d * p->esize) : nullptr;
   if (wa.used > ws_bytes) return fail(B200_ERR_WORKSPACE, "forward needs %zu workspace bytes, got %zu", wa.used, ws_bytes);
+  if (p->tp_size > 1 && !keep && T % p->tp_size == 0 && p->row_shard) {
+    void *part = nullptr, *xbg = nullptr;
+    if (comm_peer_rowshard_buffers(p->comm, (size_t)T * p->d * p->esize, &part, &xbg))
+      return forward_row_sharded(p, tokens, B, S, w, wl, logits, kv_out, acts.layer[0], part, xbg, stream);
+  }
 
   const float* g_att = reinterpret_cast<const float*>(w + wl.g_att);
   const float* g_ffn = reinterpret_cast<const float*>(w + wl.g_ffn);
@@ -424,6 +500,7 @@ int32_t b200_plan_create(const B200LlamaConfig* cfg, int32_t tp_rank, int32_t tp
   if (tp_size > 1) {
     // Chunked projections with the all-reduce of chunk c overlapping the GEMM of chunk c+1 measured SLOWER
     // than one all-reduce per block on 4 GPUs (45.3 ms vs 48.9 / 54.1 ms for 2 / 4 chunks), so the default is 1.
+    p->row_shard = env_int("B200_TP_ROW_SHARD", 1) != 0;
     p->reserve_sms = env_int("B200_TP_RESERVE_SMS", 0);
     p->tp_chunks = env_int("B200_TP_CHUNKS", 1);
     if (p->tp_chunks < 1) p->tp_chunks = 1;
@@ -451,6 +528,44 @@ int32_t b200_plan_destroy(B200Plan* p) {
   }
   if (p->comm_stream) cudaStreamDestroy(p->comm_stream);
   delete p;
+  return B200_OK;
+}
+
+// Registry of plans for callers that cannot keep a handle (custom-call handlers): keyed by the config, the
+// tensor-parallel placement, the communicator and the device; entries live until the process exits.
+namespace {
+struct PlanKey {
+  B200LlamaConfig cfg;
+  int tp_rank, tp_size, device;
+  void* comm;
+};
+struct PlanEntry { PlanKey key; B200Plan* plan; };
+std::mutex g_plans_mu;
+std::vector<PlanEntry> g_plans;
+bool same_key(const PlanKey& a, const PlanKey& b) {
+  return a.cfg.dim == b.cfg.dim && a.cfg.hidden_dim == b.cfg.hidden_dim && a.cfg.n_layers == b.cfg.n_layers &&
+         a.cfg.n_heads == b.cfg.n_heads && a.cfg.n_kv_heads == b.cfg.n_kv_heads && a.cfg.vocab_size == b.cfg.vocab_size &&
+         a.cfg.seq_len == b.cfg.seq_len && a.cfg.dtype == b.cfg.dtype && a.cfg.rope_theta == b.cfg.rope_theta &&
+         a.cfg.rms_eps == b.cfg.rms_eps && a.tp_rank == b.tp_rank && a.tp_size == b.tp_size && a.device == b.device &&
+         a.comm == b.comm;
+}
+}  // namespace
+
+int32_t b200_plan_cached(const B200LlamaConfig* cfg, int32_t tp_rank, int32_t tp_size, void* comm, B200Plan** out) {
+  if (!cfg || !out) return fail(B200_ERR_INVALID_ARG, "cfg and out must not be null");
+  PlanKey key;
+  key.cfg = *cfg; key.tp_rank = tp_rank; key.tp_size = tp_size; key.comm = comm; key.device = -1;
+  B200_CUDA_OK(cudaGetDevice(&key.device));
+  std::lock_guard<std::mutex> lk(g_plans_mu);
+  for (const PlanEntry& e : g_plans)
+    if (same_key(e.key, key)) {
+      *out = e.plan;
+      return B200_OK;
+    }
+  B200Plan* p = nullptr;
+  B200_TRY(b200_plan_create(cfg, tp_rank, tp_size, comm, &p));
+  g_plans.push_back(PlanEntry{key, p});
+  *out = p;
   return B200_OK;
 }
 

@@ -82,6 +82,7 @@ struct B200Plan {
   cudaEvent_t ev_fork[8] = {}, ev_join[8] = {};
   int reserve_sms = 0;
   int tp_chunks = 1;
+  bool row_shard = true;  // tensor-parallel prefill keeps T/tp residual rows per rank when peer memory is up
   float* rope_cos = nullptr;  // [seq_len, hs/2], owned by the plan
   float* rope_sin = nullptr;
   b200::PackedLayout wl;   // weights
@@ -102,6 +103,15 @@ void* comm_peer_buffer(void* comm, size_t bytes);
 // out = resid + sum over ranks of the `count` elements each rank left in its exchange buffer
 int32_t comm_peer_allreduce_add(void* comm, size_t count, int dtype, const float* resid, float* out,
                                 cudaStream_t stream);
+
+// Row-sharded prefill: the two regions of this rank's exchange buffer (partial product, gathered activations) when
+// the peer path is up and both fit; comm_peer_reduce_norm sums the partials of this rank's T / world rows over the
+// ranks, adds them to x_own (fp32 [T / world, d], in place; skipped when !reduce), and leaves gain * x * rinv of those
+// rows in every rank's gathered-activation region.  Its completion means the region of this rank is whole.
+bool comm_peer_rowshard_buffers(void* comm, size_t bytes_each, void** part, void** xb);
+int32_t comm_peer_reduce_norm(void* comm, int T, int d, int dtype, bool reduce, float* x_own, const float* gain,
+                              float eps, cudaStream_t stream);
+int32_t launch_peer_wait_selftest(long long budget, uint32_t* reached_end, cudaStream_t stream);
 
 // Environment knobs (read once at plan creation): B200_GEMM_IMPL and
 // B200_ATTN_IMPL select 0 = pick, 1 = tensor-core kernels, 2 = CUDA-core kernels.

@@ -118,6 +118,13 @@ B200_API int32_t b200_argmax(const float* logits, int32_t rows, int32_t cols, in
  * failures surface as XLA errors, xla_ffi/cuda/throw_error.cc:20-35). */
 B200_API int32_t b200_selftest_bounded_wait(int64_t budget_cycles, uint32_t* reached_end_device, b200_stream_t stream);
 
+/* The same self-test for the waits on OTHER ranks (the flags that tensor-parallel kernels poll in peer-mapped
+ * memory): one CTA waits, for budget_cycles SM clocks, on peer flags that nothing sets.  The wait gives up,
+ * *reached_end_device receives 1, the next b200_device_status call answers B200_ERR_TIMEOUT, and the context stays
+ * usable.  Needs no second GPU and no communicator.  The budget of the real kernels is B200_PEER_WAIT_MCYCLES
+ * (millions of SM clocks, default 4000, read at b200_comm_init_rank). */
+B200_API int32_t b200_selftest_peer_wait(int64_t budget_cycles, uint32_t* reached_end_device, b200_stream_t stream);
+
 /* Number of kernels this library has launched in this process. */
 B200_API int64_t b200_launch_count(void);
 
@@ -125,8 +132,9 @@ B200_API int64_t b200_launch_count(void);
  * of the reference's profiler-based step timing (test/xprof_utils.py:71-157).
  * b200_profile_enable(1) clears earlier samples and brackets every GEMM and
  * attention launch with an event pair; b200_profile_read synchronises those
- * events and returns, for one kernel class (0 tcgen05 GEMM, 1 FFMA GEMM,
- * 2 attention forward, 3 attention backward, 4 decode attention, 5 all-reduce), the summed
+ * events and returns, for one kernel class (0 single-CTA tcgen05 GEMM gemm_tc_kernel, 1 FFMA GEMM,
+ * 2 attention forward, 3 attention backward, 4 decode attention, 5 exchange between ranks,
+ * 6 CTA-pair tcgen05 GEMM gemm_tc2_kernel), the summed
  * milliseconds, the summed algorithmic work (flops; bytes for classes 4 and 5) and
  * the launch count.  Off by default; costs two event records per launch. */
 B200_API int32_t b200_profile_enable(int32_t on);
@@ -143,6 +151,14 @@ B200_API int32_t b200_profile_read(int32_t kernel_class, double* total_ms, doubl
 B200_API int32_t b200_plan_create(const B200LlamaConfig* cfg, int32_t tp_rank, int32_t tp_size,
                                   void* comm, B200Plan** out);
 B200_API int32_t b200_plan_destroy(B200Plan* plan);
+
+/* The plan for (config, tensor-parallel rank/size, communicator) on the current device from a process-wide registry:
+ * created on first use, shared afterwards, destroyed at process exit.  This is what a custom-call handler uses, which
+ * is handed attributes and buffers on every call and has no place to keep a handle; it stands for the reference's
+ * registry of compiled kernels keyed by an identifier (enzyme_call.cc:173,263,282: a map behind a reader/writer
+ * lock).  Safe to call from several threads; plans are immutable after creation. */
+B200_API int32_t b200_plan_cached(const B200LlamaConfig* cfg, int32_t tp_rank, int32_t tp_size, void* comm,
+                                  B200Plan** out);
 
 /* Bytes of the packed weight buffer for this rank; with_transposed != 0 adds
  * the transposed copies the backward pass contracts against. */
@@ -283,10 +299,39 @@ B200_API int32_t b200_attention_decode_static(const void* q, const void* kv_page
 
 B200_API int32_t b200_comm_unique_id(void* id128 /* 128 bytes out */);
 B200_API int32_t b200_comm_init_rank(const void* id128, int32_t rank, int32_t world, void** comm);
+/* Collective over the ranks of the communicator: every rank calls it, after the last work that uses the
+ * communicator has been enqueued.  It synchronises the device and then agrees with the peers (a one-element
+ * all-reduce) before it frees the exchange buffer and flag words the peers have mapped, so no rank frees memory a
+ * slower peer is still reading.  A rank that leaves without calling it must not free that memory some other way
+ * while its peers still run kernels of this library. */
 B200_API int32_t b200_comm_destroy(void* comm);
 /* *enabled = 1 when the ranks of the communicator exchange the tensor-parallel partial sums through
  * peer-mapped memory (CUDA IPC over NVLink) instead of NCCL. */
 B200_API int32_t b200_comm_peer_memory(void* comm, int32_t* enabled);
+
+/* ---- XLA FFI registration -------------------------------------------------- */
+
+/* Custom-call targets of the typed FFI (api_version 4), the counterpart of registerEnzymeJaXXLAFFI()
+ * (src/enzyme_ad/jax/xla_ffi/register.cc:21-27, handlers bound as in xla_ffi/cuda/blas.cc:257-314):
+ *   enzymejax_b200_llama_pack         leaves (12 buffers, B200Leaf order) -> packed weights
+ *   enzymejax_b200_llama_fwd          tokens, packed -> logits, workspace
+ *   enzymejax_b200_llama_fwd_saved    tokens, packed -> logits, saved activations, workspace
+ *   enzymejax_b200_llama_bwd          tokens, packed, dlogits, saved -> packed gradients, workspace
+ *   enzymejax_b200_llama_unpack_grads packed gradients -> 12 gradient leaves
+ *   enzymejax_b200_llama_decode_step  tokens, packed, kv pages (aliased in place), page table -> logits, workspace
+ * The handlers exist only in a library built where the XLA FFI headers (xla/ffi/api/ffi.h, shipped inside jaxlib)
+ * are on the include path; b200_ffi_available() says whether this build has them.
+ *
+ * b200_ffi_handler(name) returns the handler's address (an XLA_FFI_Handler*), or NULL for an unknown name or a
+ * build without the headers.  A Python host wraps it in a PyCapsule named "xla._CUSTOM_CALL_TARGET" and hands it to
+ * jax.ffi.register_ffi_target(name, capsule, platform="CUDA") - the route the reference takes for its legacy
+ * targets (primitives.py:32-37, capsule made in enzyme_call.cc:527-530).
+ *
+ * registerEnzymeJaXB200FFI() registers all targets with the XLA instance linked into the calling process through
+ * XLA_FFI_REGISTER_HANDLER; idempotent; returns B200_ERR_UNSUPPORTED in a build without the headers. */
+B200_API int32_t b200_ffi_available(void);
+B200_API void* b200_ffi_handler(const char* target_name);
+B200_API int32_t registerEnzymeJaXB200FFI(void);
 
 #ifdef __cplusplus
 }

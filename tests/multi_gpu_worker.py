@@ -48,7 +48,28 @@ def main():
             e = float((lg.double().cpu() - mine[:, pos]).abs().max() / ref.abs().max())
             assert e < tol, ("tp decode", dtype, pos, e)
         assert B.device_status() == 0
+        if dtype == torch.bfloat16:
+            # a tensor-parallel plan refuses graph capture (the peer exchange numbers its rounds from the host)
+            try:
+                plan.capture_forward(tokens.int().cuda(), got)
+                raise AssertionError("capture of a tensor-parallel plan must be refused")
+            except B.B200Error as e:
+                assert e.status == 10
         plan.close()
+    # the same forward through the all-reduce per block (row sharding off): the path taken when peer memory is absent
+    os.environ["B200_TP_ROW_SHARD"] = "0"
+    w = {k: v.bfloat16() for k, v in O.make_weights(cfg, 3, torch.float32, std=0.05).items()}
+    tokens = O.make_tokens(cfg, 2, 128, 4)
+    ref = O.forward_sequence(tokens, cfg, {k: v.double() for k, v in w.items()})
+    plan = B.Plan(cfg, torch.bfloat16, tp_rank=rank, tp_size=world, comm=comm)
+    plan.pack_weights({k: v.cuda().contiguous() for k, v in w.items()})
+    got = plan.forward(tokens.int().cuda())
+    torch.cuda.synchronize()
+    vl = cfg["vocab_size"] // world
+    err = float((got.double().cpu() - ref[..., rank * vl:(rank + 1) * vl]).abs().max() / ref.abs().max())
+    assert err < 2e-2, ("tp forward, all-reduce path", err)
+    plan.close()
+    del os.environ["B200_TP_ROW_SHARD"]
     # long enough for the chunked projection + overlapped all-reduce path (4 chunks of 512 tokens)
     cfg_long = dict(cfg, seq_len=1024)
     w = {k: v.bfloat16() for k, v in O.make_weights(cfg_long, 8, torch.float32, std=0.05).items()}
@@ -61,7 +82,14 @@ def main():
     torch.cuda.synchronize()
     vl = cfg_long["vocab_size"] // world
     err = float((got.cpu() - ref[..., rank * vl:(rank + 1) * vl]).abs().max() / ref.abs().max())
-    assert err < 2e-2, ("tp forward, chunked", err)
+    assert err < 2e-2, ("tp forward, long", err)
+    # rows 7 of 8 per rank are a ragged share: T = 2 * 1000 tokens over the ranks
+    tok_r = tokens[:, :1000].contiguous()
+    ref_r = O.forward_sequence(tok_r, cfg_long, {k: v.float() for k, v in w.items()})
+    got_r = plan.forward(tok_r.int().cuda())
+    torch.cuda.synchronize()
+    err = float((got_r.cpu() - ref_r[..., rank * vl:(rank + 1) * vl]).abs().max() / ref_r.abs().max())
+    assert err < 2e-2, ("tp forward, 2000 tokens", err)
     assert B.device_status() == 0
     plan.close()
     # data parallel: each rank differentiates its own sequences, gradients are summed over the ranks

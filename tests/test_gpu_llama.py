@@ -106,8 +106,13 @@ def _grad_check(cfg, dtype, batch, seq, rtol, std):
     assert B.device_status() == 0
     leaves = p.unpack_grads(grads)
     for k, r in ref.items():
-        err = float((leaves[k].double().cpu() - r).abs().max() / r.abs().max())
+        got = leaves[k].double().cpu()
+        err = float((got - r).abs().max() / r.abs().max())
         assert err < rtol, (k, err)
+        if dtype == torch.float32:
+            # the fp32 bar element by element: 1e-4 relative, with the absolute floor of 1e-5 scaled to the leaf
+            # (gradients of a sum over 64 tokens x 512 logits have magnitudes far from 1)
+            assert torch.allclose(got, r, rtol=1e-4, atol=1e-5 * float(r.abs().max().clamp_min(1.0))), k
     return p, tok, dlogits, saved, leaves
 
 

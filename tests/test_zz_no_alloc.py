@@ -6,12 +6,14 @@ serving loop with a memory pool fixed at start-up, code that runs where
 cudaMalloc is not allowed.  ``b200_attention_decode_static`` keeps its scratch
 in a fixed array inside the library.  This test calls it twice in a row through
 the C ABI and compares each result with ``b200_attention_decode`` (caller-owned
-scratch) on the same inputs.  The two share their kernels, so the results must
-agree to the bit; the comparison still uses the tolerance of the other decode
-tests.  The file sorts last so that a run that stops at the first failure has
-already run everything else.
+scratch) on the same inputs, and with an fp64 torch computation of the same
+attention, so that a fault shared by both entry points cannot hide.  The two
+entry points share their kernels, so their results must agree to the bit; the
+comparisons use the tolerance of the other decode tests.  The file sorts last so
+that a run that stops at the first failure has already run everything else.
 """
 import gc
+import math
 
 import pytest
 import torch
@@ -33,6 +35,20 @@ def _case(batch, ctx, H, hs, dtype, page, seed):
     return q, kv, table
 
 
+def _torch_reference(q, kv, table, ctx, H):
+    """softmax(q K^T / sqrt(hs)) V per (sequence, head) over the first ctx rows the page table names, in fp64."""
+    batch, d = q.shape
+    hs = d // H
+    page = kv.shape[3]
+    rows = torch.arange(ctx, device=q.device)
+    pg = table.long()[:, rows // page]                                   # [batch, ctx]
+    off = (rows % page)[None, :].expand(batch, -1)
+    k = kv[0][pg, :, off, :].double()                                    # [batch, ctx, H, hs]
+    v = kv[1][pg, :, off, :].double()
+    att = torch.einsum("bhe,buhe->bhu", q.double().view(batch, H, hs), k) / math.sqrt(hs)
+    return torch.einsum("bhu,buhe->bhe", torch.softmax(att, -1), v).reshape(batch, d)
+
+
 @pytest.mark.parametrize("batch,ctx,H,hs,dtype,page", [(2, 1000, 2, 64, torch.bfloat16, 64),
                                                        (64, 300, 8, 128, torch.bfloat16, 128),
                                                        (1, 40, 6, 48, torch.float32, 16)])
@@ -49,6 +65,8 @@ def test_static_scratch_matches_caller_scratch_twice(batch, ctx, H, hs, dtype, p
         torch.cuda.synchronize()
         assert torch.allclose(out.float(), want.float(), rtol=tol, atol=tol)
         assert torch.equal(out, want)
+        ref = _torch_reference(q, kv, table, ctx + call, H)
+        assert torch.allclose(out.double(), ref, rtol=tol, atol=tol)
 
 
 def test_static_scratch_rejects_problems_beyond_its_size():
