@@ -35,6 +35,7 @@ EXPORTS = (
     "b200_attention_decode_scratch_bytes", "b200_attention_decode", "b200_attention_decode_static",
     "b200_attention_backward", "b200_comm_peer_memory", "b200_selftest_bounded_wait", "b200_argmax",
     "b200_selftest_peer_wait", "b200_plan_cached", "b200_ffi_available", "b200_ffi_handler",
+    "b200_token_vjp_workspace_bytes", "b200_token_vjp",
 )
 
 
@@ -72,6 +73,9 @@ def lib() -> ctypes.CDLL:
         l.registerEnzymeJaXB200FFI.restype = c_int32
         l.b200_plan_cached.argtypes = [POINTER(_Config), c_int32, c_int32, c_void_p, POINTER(c_void_p)]
         l.b200_selftest_peer_wait.argtypes = [ctypes.c_int64, c_void_p, c_void_p]
+        l.b200_token_vjp_workspace_bytes.argtypes = [c_void_p, c_int32, POINTER(c_size_t)]
+        l.b200_token_vjp.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int32, c_void_p, c_void_p, c_void_p,
+                                     c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_size_t, c_void_p]
         l.b200_launch_count.restype = ctypes.c_int64
         l.b200_profile_enable.argtypes = [c_int32]
         l.b200_profile_read.argtypes = [c_int32, POINTER(ctypes.c_double), POINTER(ctypes.c_double),
@@ -493,6 +497,36 @@ class Plan:
         arr = (c_void_p * len(LEAF_ORDER))(*[out[k].data_ptr() for k in LEAF_ORDER])
         check(lib().b200_unpack_grads(self._h, grads.data_ptr(), arr, _stream()))
         return out
+
+    def token_vjp(self, x: torch.Tensor, key_cache: torch.Tensor, value_cache: torch.Tensor, d_hidden: torch.Tensor):
+        """Reverse mode of the reference's own call ``forward(x, weights, key_cache, value_cache) -> hidden`` with
+        respect to all of its inputs.  ``x`` fp32 [d]; caches [L, pos, d]; ``d_hidden`` fp32 [d].  Returns
+        ``(hidden, dx, packed_grads, d_key_cache, d_value_cache)``; ``unpack_grads`` turns the packed gradients into
+        the per-leaf dict (``wcls`` and the embedding come out exactly zero: the result does not depend on them)."""
+        if not self.with_transposed:
+            raise B200Error(1, "token_vjp needs weights packed with with_transposed=True")
+        L, d = self.config["n_layers"], self.config["dim"]
+        pos = int(key_cache.shape[1])
+        if tuple(key_cache.shape) != (L, pos, d) or tuple(value_cache.shape) != (L, pos, d):
+            raise B200Error(2, f"caches must be [{L}, pos, {d}], got {tuple(key_cache.shape)} and {tuple(value_cache.shape)}")
+        dev = self.device
+        xin = x.to(dev, torch.float32).reshape(d).contiguous()
+        dh = d_hidden.to(dev, torch.float32).reshape(d).contiguous()
+        kc = key_cache.to(dev, self.dtype).contiguous()
+        vc = value_cache.to(dev, self.dtype).contiguous()
+        hidden = torch.empty(d, dtype=torch.float32, device=dev)
+        dx = torch.empty(d, dtype=torch.float32, device=dev)
+        dkc = torch.zeros(L, pos, d, dtype=torch.float32, device=dev)
+        dvc = torch.zeros(L, pos, d, dtype=torch.float32, device=dev)
+        grads = torch.empty(self.grad_bytes() // 4, dtype=torch.float32, device=dev)
+        need = self._bytes(lib().b200_token_vjp_workspace_bytes, pos)
+        ws = torch.empty(need, dtype=torch.uint8, device=dev)
+        check(lib().b200_token_vjp(self._h, xin.data_ptr(), kc.data_ptr() if pos else None,
+                                   vc.data_ptr() if pos else None, pos, self.packed.data_ptr(), dh.data_ptr(),
+                                   hidden.data_ptr(), dx.data_ptr(), grads.data_ptr(),
+                                   dkc.data_ptr() if pos else None, dvc.data_ptr() if pos else None, ws.data_ptr(),
+                                   ws.numel(), _stream()))
+        return hidden, dx, grads, dkc, dvc
 
     # ---- decode ----------------------------------------------------------
     def new_kv_pages(self, n_pages: int, page_size: int) -> torch.Tensor:

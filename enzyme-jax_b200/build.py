@@ -92,10 +92,12 @@ def build(force: bool = False, verbose: bool = False) -> str:
                 if verbose:
                     print(f"--- {os.path.basename(s)}\n{out}")
     if jobs or not os.path.exists(LIB):
-        cmd = [_nvcc(), "-shared", "-o", LIB, *objs, "-ldl"]
+        tmp = LIB + ".linking"
+        cmd = [_nvcc(), "-shared", "-o", tmp, *objs, "-ldl"]
         r = subprocess.run(cmd, capture_output=True, text=True)
         if r.returncode != 0:
             raise RuntimeError(f"link failed:\n{r.stdout}\n{r.stderr}")
+        os.replace(tmp, LIB)  # a reader never sees a half-written library
     return LIB
 
 

@@ -206,6 +206,27 @@ B200_API int32_t b200_packed_grad_bytes(const B200Plan* plan, size_t* bytes);
 B200_API int32_t b200_unpack_grads(const B200Plan* plan, const float* grads, float* const* leaves,
                                    b200_stream_t stream);
 
+/* Reverse mode of the reference's own call: forward(x, weights, key_cache, value_cache) -> hidden
+ * (test/llama.py:35-238), differentiated with respect to ALL of its inputs as the reference's test does
+ * (test/llama.py:315-317 `ins`/`dins`, test/test_utils.py:505-514 splatvjp): the residual vector, every weight leaf
+ * and both caches.
+ *   x            fp32 [d]
+ *   key_cache    [L, pos, d] of the config dtype (value_cache alike); may be NULL when pos == 0
+ *   packed_w     weights packed with the transposed copies
+ *   d_hidden     fp32 [d], the cotangent of the returned hidden state
+ *   hidden_out   NULL, or fp32 [d] receiving the primal result (the reference's `revprimal`)
+ *   dx           fp32 [d]
+ *   grads        fp32, packed like b200_backward's (overwritten).  The hidden state does not depend on wcls
+ *                (test/llama.py:236 is commented out) nor on an embedding table: those gradients are exactly
+ *                zero, as the reference emits for arguments JAX drops as dead (primitives.py:733-744, :1550-1569).
+ *   d_key_cache  fp32 [L, pos, d] (d_value_cache alike)
+ * One sequence; the workspace size comes from b200_token_vjp_workspace_bytes. */
+B200_API int32_t b200_token_vjp_workspace_bytes(const B200Plan* plan, int32_t pos, size_t* bytes);
+B200_API int32_t b200_token_vjp(B200Plan* plan, const float* x, const void* key_cache, const void* value_cache,
+                                int32_t pos, const void* packed_w, const float* d_hidden, float* hidden_out,
+                                float* dx, float* grads, float* d_key_cache, float* d_value_cache, void* workspace,
+                                size_t workspace_bytes, b200_stream_t stream);
+
 /* Sums `count` floats over the ranks of the communicator in place (the
  * data-parallel gradient exchange). */
 B200_API int32_t b200_allreduce_f32(void* comm, float* data, size_t count, b200_stream_t stream);

@@ -244,6 +244,28 @@ def vjp_sequence(tokens, cfg, w, dlogits):
     return logits.detach(), {k: (v.grad if v.grad is not None else torch.zeros_like(v)) for k, v in leaves.items()}
 
 
+def vjp_token(x, cfg, w, key_cache, value_cache, d_hidden):
+    """Reverse mode of the reference's own call, forward(x, weights, key_cache, value_cache) -> hidden
+    (test/llama.py:35-238), with respect to ALL inputs, as the reference's test differentiates it
+    (test/llama.py:315-317, test/test_utils.py:505-514).  x [d]; caches [L, pos, d]; returns
+    (hidden, dx, {leaf: grad}, d_key_cache, d_value_cache).  Level 1 serves: a one-row embedding table holding x
+    turns the residual vector into a differentiable input; wcls and the real embedding table receive zero."""
+    dt = w["wq"].dtype
+    leaves = {k: v.detach().clone().requires_grad_(True) for k, v in w.items() if k != "token_embedding_table"}
+    xin = x.detach().clone().to(dt).requires_grad_(True)
+    kc = key_cache.detach().clone().to(dt).requires_grad_(True)
+    vc = value_cache.detach().clone().to(dt).requires_grad_(True)
+    full = dict(leaves, token_embedding_table=xin[None, :])
+    tokens = torch.zeros(1, 1, dtype=torch.int64)
+    _, aux = forward_sequence(tokens, cfg, full, past_k=kc[:, None] if kc.shape[1] else None,
+                              past_v=vc[:, None] if vc.shape[1] else None, return_aux=True)
+    hidden = aux["xf"][0, 0]
+    hidden.backward(d_hidden.to(dt))
+    grads = {k: (v.grad if v.grad is not None else torch.zeros_like(v)) for k, v in leaves.items()}
+    zero = lambda t: torch.zeros_like(t) if t.grad is None else t.grad
+    return hidden.detach(), zero(xin), grads, zero(kc), zero(vc)
+
+
 def cast_weights(w, dtype):
     return {k: v.to(dtype) for k, v in w.items()}
 

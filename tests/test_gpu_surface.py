@@ -83,3 +83,44 @@ def test_harness_rows_and_csv(tmp_path, monkeypatch):
     assert rows[0] == CSV_HEADER and len(rows) == 5
     assert [r[3] for r in rows[1:]] == ["Primal", "PreRev", "PostRev", "BothRev"]
     assert all(r[:3] == ["llama", "B200", "gpu"] and float(r[4]) > 0 for r in rows[1:])
+
+
+@pytest.mark.parametrize("pos,zero_cache", [(1, True), (5, False), (0, False)])
+def test_token_vjp_all_inputs_matches_oracle(pos, zero_cache):
+    """The reference's differentiated call (test/llama.py:315-317): gradients with respect to x, every weight leaf and
+    both caches, at the shipped shape (config 1, a one-row zero cache) and with a random 5-row cache."""
+    import b200_llama as B
+    cfg = O.CONFIGS["c1"]
+    L, d = cfg["n_layers"], cfg["dim"]
+    w = O.make_weights(cfg, 13, torch.float32, std=0.05, gains_one=False)
+    g = torch.Generator().manual_seed(14)
+    x = torch.randn(d, generator=g)
+    kc = torch.zeros(L, pos, d) if zero_cache else torch.randn(L, pos, d, generator=g)
+    vc = torch.zeros(L, pos, d) if zero_cache else torch.randn(L, pos, d, generator=g)
+    dh = torch.randn(d, generator=g)
+    hidden, dx, grads, dk, dv = O.vjp_token(x.double(), cfg, {k: v.double() for k, v in w.items()}, kc.double(),
+                                            vc.double(), dh.double())
+    p = B.Plan(cfg, torch.float32)
+    p.pack_weights({k: v.cuda().contiguous() for k, v in w.items()}, with_transposed=True)
+    got_h, got_dx, packed, got_dk, got_dv = p.token_vjp(x, kc, vc, dh)
+    torch.cuda.synchronize()
+    assert B.device_status() == 0
+
+    def close(a, b, what):
+        scale = float(b.abs().max().clamp_min(1e-30))
+        err = float((a.double().cpu() - b).abs().max()) / scale
+        assert err < 1e-4, (what, err)
+
+    close(got_h, hidden, "hidden")
+    close(got_dx, dx, "dx")
+    if pos:
+        close(got_dk, dk, "d key_cache")
+        close(got_dv, dv, "d value_cache")
+    leaves = p.unpack_grads(packed)
+    for k, r in grads.items():
+        if k == "wcls":
+            assert float(leaves[k].abs().max()) == 0.0   # a dead argument: identically zero
+        else:
+            close(leaves[k], r, k)
+    assert float(leaves["token_embedding_table"].abs().max()) == 0.0
+    p.close()

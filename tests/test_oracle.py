@@ -104,3 +104,38 @@ def test_fp32_vs_fp64_rounding_bound():
     a = O.forward_sequence(tokens, cfg, w64)
     b = O.forward_sequence(tokens, cfg, w32).double()
     assert (a - b).abs().max() <= 1e-5 + 1e-4 * a.abs().max()
+
+
+def test_token_vjp_against_level0_and_finite_differences():
+    """vjp_token (all-input reverse mode of the reference's call shape): its primal equals Level 0, its cotangents of
+    x and of a cache row equal central finite differences of Level 0, and wcls gets exactly zero."""
+    import numpy as np
+    cfg = O.CONFIGS["tiny"]
+    w = O.make_weights(cfg, 3, torch.float64, std=0.2, gains_one=False)
+    g = torch.Generator().manual_seed(1)
+    L, d = cfg["n_layers"], cfg["dim"]
+    x = torch.randn(d, generator=g, dtype=torch.float64)
+    kc = torch.randn(L, 3, d, generator=g, dtype=torch.float64)
+    vc = torch.randn(L, 3, d, generator=g, dtype=torch.float64)
+    dh = torch.randn(d, generator=g, dtype=torch.float64)
+    hidden, dx, grads, dk, dv = O.vjp_token(x, cfg, w, kc, vc, dh)
+    wn = O.to_numpy(w)
+    assert np.abs(hidden.numpy() - O.forward_token(x.numpy(), cfg, wn, kc.numpy(), vc.numpy())).max() < 1e-12
+
+    def f(x_, kc_, vc_):
+        return float((torch.from_numpy(O.forward_token(x_.numpy(), cfg, wn, kc_.numpy(), vc_.numpy())) * dh).sum())
+
+    eps = 1e-6
+    for i in (0, 5, d - 1):
+        xp, xm = x.clone(), x.clone()
+        xp[i] += eps
+        xm[i] -= eps
+        assert abs((f(xp, kc, vc) - f(xm, kc, vc)) / (2 * eps) - float(dx[i])) < 1e-7
+    for idx in ((0, 0, 3), (1, 2, 7)):
+        for cache, grad, which in ((kc, dk, 0), (vc, dv, 1)):
+            cp, cm = cache.clone(), cache.clone()
+            cp[idx] += eps
+            cm[idx] -= eps
+            fd = (f(x, cp, vc) - f(x, cm, vc)) if which == 0 else (f(x, kc, cp) - f(x, kc, cm))
+            assert abs(fd / (2 * eps) - float(grad[idx])) < 1e-7
+    assert float(grads["wcls"].abs().max()) == 0.0
