@@ -11,17 +11,26 @@
 //               key blocks).  S of block j+1 is issued as soon as the softmax
 //               threads hold S of block j in registers, so it is computed
 //               beside block j's exponentials.
-//   warps 2..9  softmax, two threads per query row (64 keys each): read S from
-//               TMEM once, mask the diagonal block, running reference maximum
-//               and row sum in fp32, write P as bf16 into shared memory in the
+//   warps 2..9  softmax.  A warp owns 16 query rows and all 128 keys of a block:
+//               it reads S with the 16-lane x 256-bit TMEM load, which hands every
+//               thread two rows (lane/4 and lane/4 + 8) and two of every eight
+//               columns, the accumulator-fragment layout.  A row is therefore
+//               spread over the four lanes of a quad: its maximum and its sum
+//               take two shuffles, and no warp ever waits for another one
+//               inside a block (no exchange through shared memory).  One pass:
+//               S is read once, masked on the diagonal block, compared with the
+//               row's reference maximum, turned into probabilities (packed fp32x2
+//               arithmetic, exp2) and written as bf16 into shared memory in the
 //               swizzled K-major layout the MMA reads.  The reference maximum of
 //               a row is only raised -- and O in TMEM and the row sum rescaled --
 //               when a block's maximum exceeds it by more than 2^8; until then
 //               probabilities are taken against the older reference (they stay
 //               below 2^8; O / l at the end is exact either way).
 // V is consumed as an MN-major operand straight from its row-major layout.
-// TMEM use is 256 columns so that two CTAs share an SM and one CTA's softmax
-// overlaps the other's MMAs.  All waits are bounded.
+// Head size 64: TMEM use is 256 columns and 115 KB of shared memory, so that two
+// CTAs share an SM and one CTA's softmax overlaps the other's MMAs.  Head size
+// 128 (one CTA per SM): P has two buffers, so the exponentials of block j+1 run
+// beside O += P_j V_j.  All waits are bounded.
 #include <cuda.h>
 
 #include <mutex>
@@ -46,16 +55,86 @@ template <int HS> struct ACfg {
   static constexpr int kTileBytes = kSubs * SUB;      // Q, K_j or V_j
   static constexpr int kStages = 2;
   static constexpr int kPBytes = 2 * SUB;             // P: 128 rows x 128 keys
+  static constexpr int kPBufs = HS == 128 ? 2 : 1;    // one CTA per SM at head size 128: room for a second P
   static constexpr int kQOff = 0;
   static constexpr int kKOff = kTileBytes;
   static constexpr int kVOff = kKOff + kStages * kTileBytes;
   static constexpr int kPOff = kVOff + kStages * kTileBytes;
-  static constexpr int kXchgOff = kPOff + kPBytes;      // [2][128] bf16 block maxima exchanged between the halves of a row
-  static constexpr int kBarOff = kXchgOff + 2 * 128 * 2;
-  static constexpr int kSmemBytes = kBarOff + 128;      // hs = 64: 115,328 B, two CTAs fit the 228 KB of an SM
+  static constexpr int kBarOff = kPOff + kPBufs * kPBytes;
+  static constexpr int kSmemBytes = kBarOff + 128;      // hs = 64: 114,816 B, two CTAs fit the 228 KB of an SM; hs = 128: 229,504 B
   static constexpr int kTmemCols = 256;
   static constexpr int kOCol = 128;
 };
+
+// 16 TMEM lanes x 256 bits per column group: thread t of the warp receives, for every group of 8 columns, the
+// columns 2*(t%4) and 2*(t%4)+1 of lane (t/4) in r[4g], r[4g+1] and of lane (t/4 + 8) in r[4g+2], r[4g+3]
+// (the layout of a 16x8 fp32 accumulator fragment).  taddr names the first of the 16 lanes and the first column.
+__device__ __forceinline__ void tmem_ld_16x256b_x16(uint32_t taddr, float (&v)[64]) {
+  uint32_t r[64];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.16x256b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, "
+      "%32, %33, %34, %35, %36, %37, %38, %39, %40, %41, %42, %43, %44, %45, %46, %47, "
+      "%48, %49, %50, %51, %52, %53, %54, %55, %56, %57, %58, %59, %60, %61, %62, %63}, [%64];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31]), "=r"(r[32]),
+        "=r"(r[33]), "=r"(r[34]), "=r"(r[35]), "=r"(r[36]), "=r"(r[37]), "=r"(r[38]), "=r"(r[39]), "=r"(r[40]),
+        "=r"(r[41]), "=r"(r[42]), "=r"(r[43]), "=r"(r[44]), "=r"(r[45]), "=r"(r[46]), "=r"(r[47]), "=r"(r[48]),
+        "=r"(r[49]), "=r"(r[50]), "=r"(r[51]), "=r"(r[52]), "=r"(r[53]), "=r"(r[54]), "=r"(r[55]), "=r"(r[56]),
+        "=r"(r[57]), "=r"(r[58]), "=r"(r[59]), "=r"(r[60]), "=r"(r[61]), "=r"(r[62]), "=r"(r[63])
+      : "r"(taddr)
+      : "memory");
+#pragma unroll
+  for (int i = 0; i < 64; ++i) v[i] = __uint_as_float(r[i]);
+}
+// The same shape over 64 columns (8 groups): 32 registers.
+__device__ __forceinline__ void tmem_ld_16x256b_x8(uint32_t taddr, float (&v)[32]) {
+  uint32_t r[32];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.16x256b.x8.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+#pragma unroll
+  for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+// 16 columns (2 groups): 8 registers.  The rare rescale of O goes through these so that it adds little to the
+// register need of the main path.
+__device__ __forceinline__ void tmem_ld_16x256b_x2(uint32_t taddr, float (&v)[8]) {
+  uint32_t r[8];
+  asm volatile("tcgen05.ld.sync.aligned.16x256b.x2.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+               : "r"(taddr)
+               : "memory");
+#pragma unroll
+  for (int i = 0; i < 8; ++i) v[i] = __uint_as_float(r[i]);
+}
+__device__ __forceinline__ void tmem_st_16x256b_x2(uint32_t taddr, const float (&v)[8]) {
+  asm volatile("tcgen05.st.sync.aligned.16x256b.x2.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"r"(taddr),
+               "r"(__float_as_uint(v[0])), "r"(__float_as_uint(v[1])), "r"(__float_as_uint(v[2])),
+               "r"(__float_as_uint(v[3])), "r"(__float_as_uint(v[4])), "r"(__float_as_uint(v[5])),
+               "r"(__float_as_uint(v[6])), "r"(__float_as_uint(v[7]))
+               : "memory");
+}
+__device__ __forceinline__ void st_shared_b32(uint32_t addr, uint32_t v) {
+  asm volatile("st.shared.b32 [%0], %1;" ::"r"(addr), "r"(v) : "memory");
+}
+__device__ __forceinline__ float quad_max(float v) {
+  v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 1));
+  return fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 2));
+}
+__device__ __forceinline__ float quad_sum(float v) {
+  v += __shfl_xor_sync(0xffffffffu, v, 1);
+  return v + __shfl_xor_sync(0xffffffffu, v, 2);
+}
 
 template <int HS>
 __global__ void __launch_bounds__(A_THREADS, HS == 64 ? 2 : 1)
@@ -63,6 +142,7 @@ __global__ void __launch_bounds__(A_THREADS, HS == 64 ? 2 : 1)
                        const __grid_constant__ CUtensorMap tmV, bf16* __restrict__ o, float* __restrict__ lse, int seq,
                        int n_heads, int ldo, float scale, uint32_t* status) {
   using C = ACfg<HS>;
+  constexpr int NP = C::kPBufs;
   extern __shared__ __align__(1024) uint8_t smem[];
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::kBarOff);
   uint64_t* q_full = bars;          // Q landed
@@ -70,9 +150,8 @@ __global__ void __launch_bounds__(A_THREADS, HS == 64 ? 2 : 1)
   uint64_t* kv_empty = bars + 3;    // [2] both MMAs of block j are done with the stage
   uint64_t* s_full = bars + 5;      // S_j complete in TMEM
   uint64_t* s_empty = bars + 6;     // softmax has read S_j
-  uint64_t* p_full = bars + 7;      // P_j is in shared memory
-  uint64_t* o_full = bars + 8;      // O += P_j V_j complete in TMEM (P_j and the stage are free, O at rest)
-  uint64_t* x_bar = bars + 10;      // the two threads of every row have published their block maximum
+  uint64_t* p_full = bars + 7;      // [2] P_j is in its shared-memory buffer
+  uint64_t* o_full = bars + 9;      // [2] O += P_j V_j complete in TMEM (P's buffer and the stage are free)
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 11);  // 11 barriers + 2 words = 96 bytes
   volatile uint32_t* abort_flag = tmem_slot + 1;
 
@@ -97,12 +176,11 @@ __global__ void __launch_bounds__(A_THREADS, HS == 64 ? 2 : 1)
     for (int i = 0; i < 2; ++i) {
       ptx::mbar_init(&kv_full[i], 1);
       ptx::mbar_init(&kv_empty[i], 1);
+      ptx::mbar_init(&p_full[i], 256);
+      ptx::mbar_init(&o_full[i], 1);
     }
     ptx::mbar_init(s_full, 1);
     ptx::mbar_init(s_empty, 256);
-    ptx::mbar_init(p_full, 256);
-    ptx::mbar_init(o_full, 1);
-    ptx::mbar_init(x_bar, 256);
     ptx::fence_barrier_init();
     ptx::tma_prefetch_desc(&tmQ);
     ptx::tma_prefetch_desc(&tmK);
@@ -171,181 +249,160 @@ __global__ void __launch_bounds__(A_THREADS, HS == 64 ? 2 : 1)
       }
       for (int j = 0; j < n_blocks && ok; ++j) {
         const int st = j & 1;
-        const uint32_t jp = (uint32_t)j & 1u;
+        const int pb = j % NP;
         if (j + 1 < n_blocks) {
           // scores of the next block, once this block's are in the softmax threads' registers
           ok = ptx::mbar_wait(&kv_full[st ^ 1], (uint32_t)((j + 1) >> 1) & 1u, abort_flag, status, ST_ATTN_TIMEOUT) &&
-               ptx::mbar_wait(s_empty, jp, abort_flag, status, ST_ATTN_TIMEOUT);
+               ptx::mbar_wait(s_empty, (uint32_t)j & 1u, abort_flag, status, ST_ATTN_TIMEOUT);
           if (!ok) break;
           ptx::tc_fence_after_sync();
           issue_s(st ^ 1);
         }
-        ok = ptx::mbar_wait(p_full, jp, abort_flag, status, ST_ATTN_TIMEOUT);
+        ok = ptx::mbar_wait(&p_full[pb], (uint32_t)(j / NP) & 1u, abort_flag, status, ST_ATTN_TIMEOUT);
         if (!ok) break;
         ptx::tc_fence_after_sync();
         const uint64_t va = v_desc + (uint64_t)st * (C::kTileBytes >> 4);
+        const uint64_t pa = p_desc + (uint64_t)pb * (C::kPBytes >> 4);
 #pragma unroll
         for (int k = 0; k < AK / 16; ++k)  // O += P V, contraction over the 128 keys of the block, 16 rows of V per step
-          ptx::mma_bf16_ss(tmem_base + C::kOCol, p_desc + (uint64_t)(((k >> 2) * SUB + (k & 3) * 32) >> 4),
+          ptx::mma_bf16_ss(tmem_base + C::kOCol, pa + (uint64_t)(((k >> 2) * SUB + (k & 3) * 32) >> 4),
                            va + (uint64_t)(k * (2048 >> 4)), idesc_o, (j > 0 || k > 0) ? 1u : 0u);
-        ptx::mma_commit(o_full);
+        ptx::mma_commit(&o_full[pb]);
         ptx::mma_commit(&kv_empty[st]);
       }
     }
     __syncwarp();
   } else {
-    // 8 softmax warps: warps 2..5 take keys 0..63 of every block and the first
-    // half of the output columns, warps 6..9 the other halves; the two threads
-    // of a row exchange their block maxima through shared memory.
+    // 8 softmax warps.  Warp w may touch TMEM lanes 32*(w%4) .. +31; of those, warps 2..5 take the first 16
+    // and warps 6..9 the other 16.  Thread: rows r0 = lane/4 and r0 + 8 of the warp's 16, columns 2*(lane%4)
+    // and +1 of every group of 8.
     const int qd = warp & 3;
     const int hf = (warp - 2) >> 2;
-    const int row = qd * 32 + lane;  // row of the tile == TMEM lane
-    const int t = t0 + row;
-    constexpr int OH = HS / 2;       // output columns per thread
-    const uint32_t t_s = tmem_base + ((uint32_t)(qd * 32) << 16) + (uint32_t)(hf * 64);
-    const uint32_t t_o = tmem_base + ((uint32_t)(qd * 32) << 16) + (uint32_t)(C::kOCol + hf * OH);
+    const int q4 = lane & 3;
+    const int row0 = qd * 32 + hf * 16 + (lane >> 2);  // row of the tile == TMEM lane; the second row is row0 + 8
+    const int ta = t0 + row0, tb = ta + 8;
+    const uint32_t t_lane = tmem_base + ((uint32_t)(qd * 32 + hf * 16) << 16);
+    const uint32_t t_o = t_lane + (uint32_t)C::kOCol;
     const float sl2 = scale * 1.4426950408889634f;  // scores are scaled inside the exp2
-    uint8_t* p_row = smem + C::kPOff + hf * SUB + row * 128;
-    bf16* xchg = reinterpret_cast<bf16*>(smem + C::kXchgOff);  // [2][128]
-    float ms = -INFINITY;  // reference maximum of the row, in exp2 units (score * sl2)
-    float l = 0.f;
+    // byte offsets of this thread's two P rows inside a 64-key sub-tile (rows are 128 B; the 16-byte chunk index is
+    // XOR-ed with row % 8 by the swizzle; the thread's two keys of a chunk are 4 bytes at 4 * q4)
+    const uint32_t p_base = ptx::smem_u32(smem + C::kPOff);
+    const uint32_t pa_off = (uint32_t)row0 * 128u + 4u * (uint32_t)q4, pb_off = pa_off + 8u * 128u;
+    const uint32_t swz = (uint32_t)(row0 & 7);  // (row0 + 8) % 8 is the same
+    float ms_a = -INFINITY, ms_b = -INFINITY;  // reference maxima of the two rows, in exp2 units (score * sl2)
+    float l_a = 0.f, l_b = 0.f;                // this thread's share of the row sums
     bool ok = true;
     for (int j = 0; j < n_blocks; ++j) {
-      const uint32_t jp = (uint32_t)j & 1u;
-      ok = ptx::mbar_wait(s_full, jp, abort_flag, status, ST_ATTN_TIMEOUT);
-      ok = __all_sync(0xffffffffu, ok);
+      const int pbuf = j % NP;
+      ok = ptx::mbar_wait_warp(s_full, (uint32_t)j & 1u, abort_flag, status, ST_ATTN_TIMEOUT);
       if (!ok) break;
       ptx::tc_fence_after_sync();
-      const bool diag = (j == qt);  // diagonal block: keys after the query are masked
-      const int u0 = j * AK + hf * 64;
-      // pass 1: maximum of this thread's 64 scores, 32 at a time (the 64 live values of pass 2 and the
-      // 32 of a rescale would not fit the register budget of two CTAs per SM together)
-      float bm = -INFINITY;
+      float sv[64];  // sv[4g + {0,1}]: row a, keys 8g + 2*q4 + {0,1};  sv[4g + {2,3}]: row b
+      tmem_ld_16x256b_x16(t_lane, sv);
+      ptx::tmem_ld_wait();
+      ptx::tc_fence_before_sync();
+      ptx::mbar_arrive(s_empty);  // the MMA warp may overwrite S with the next block's scores
+      if (j == qt) {  // diagonal block: keys after the query are masked
+        const int u0 = j * AK + 2 * q4;
 #pragma unroll
-      for (int c = 0; c < 64; c += 32) {
-        float s32[32];
-        ptx::tmem_ld32(t_s + (uint32_t)c, s32);
-        ptx::tmem_ld_wait();
-        if (diag) {
+        for (int g = 0; g < 16; ++g) {
 #pragma unroll
-          for (int i = 0; i < 32; ++i)
-            if (u0 + c + i > t) s32[i] = -INFINITY;
+          for (int e = 0; e < 2; ++e) {
+            if (u0 + 8 * g + e > ta) sv[4 * g + e] = -INFINITY;
+            if (u0 + 8 * g + e > tb) sv[4 * g + 2 + e] = -INFINITY;
+          }
         }
-#pragma unroll
-        for (int i = 0; i < 32; i += 2) bm = ptx::max3(bm, s32[i], s32[i + 1]);
       }
-      // Both threads of a row must adopt the same maximum, but it need not be
-      // exact: each rounds its own to bf16 and both take the larger of the two
-      // rounded values.
-      const bf16 bmh = __float2bfloat16_rn(bm);
-      xchg[hf * 128 + row] = bmh;
-      ptx::mbar_arrive(x_bar);  // release: the store above is visible to whoever sees the phase complete
-      ok = ptx::mbar_wait(x_bar, jp, abort_flag, status, ST_ATTN_TIMEOUT);
-      ok = __all_sync(0xffffffffu, ok);
-      if (!ok) break;
-      bm = fmaxf(__bfloat162float(bmh), __bfloat162float(xchg[(hf ^ 1) * 128 + row]));
-      const float bms = bm * sl2;  // finite or -inf only for a fully masked half, which the partner's value covers
+      float bm_a = -INFINITY, bm_b = -INFINITY;
+#pragma unroll
+      for (int g = 0; g < 16; ++g) {
+        bm_a = ptx::max3(bm_a, sv[4 * g], sv[4 * g + 1]);
+        bm_b = ptx::max3(bm_b, sv[4 * g + 2], sv[4 * g + 3]);
+      }
+      bm_a = quad_max(bm_a) * sl2;  // every row of the diagonal block keeps at least its own key: finite
+      bm_b = quad_max(bm_b) * sl2;
       bool o_waited = false;
       if (j == 0) {
-        ms = bms;
-      } else if (__any_sync(0xffffffffu, bms > ms + 8.f)) {
-        // raise the reference of every row of the warp (tcgen05.ld/st are warp-wide); the partner warp sees the same
-        // maxima and decides the same.  O must be at rest: O += P_{j-1} V_{j-1} has completed.
-        const float nm = fmaxf(ms, bms);
-        const float corr = exp2f(ms - nm);
-        ms = nm;
-        l *= corr;
-        ok = ptx::mbar_wait(o_full, jp ^ 1u, abort_flag, status, ST_ATTN_TIMEOUT);
-        ok = __all_sync(0xffffffffu, ok);
+        ms_a = bm_a;
+        ms_b = bm_b;
+      } else if (__any_sync(0xffffffffu, bm_a > ms_a + 8.f || bm_b > ms_b + 8.f)) {
+        // raise the references of the warp's rows (tcgen05.ld/st are warp-wide; rows that need no raise get the
+        // factor 1).  O must be at rest: every O += P V issued so far has completed.
+        const float nm_a = bm_a > ms_a + 8.f ? bm_a : ms_a, nm_b = bm_b > ms_b + 8.f ? bm_b : ms_b;
+        const float corr_a = exp2f(ms_a - nm_a), corr_b = exp2f(ms_b - nm_b);
+        ms_a = nm_a; ms_b = nm_b;
+        l_a *= corr_a; l_b *= corr_b;
+        ok = ptx::mbar_wait_warp(&o_full[(j - 1) % NP], (uint32_t)((j - 1) / NP) & 1u, abort_flag, status, ST_ATTN_TIMEOUT);
         if (!ok) break;
         ptx::tc_fence_after_sync();
         o_waited = true;
-#pragma unroll
-        for (int c = 0; c < OH; c += 32) {
-          float v[32];
-          ptx::tmem_ld32(t_o + (uint32_t)c, v);
+#pragma unroll 1
+        for (int c = 0; c < HS; c += 16) {
+          float v[8];
+          tmem_ld_16x256b_x2(t_o + (uint32_t)c, v);
           ptx::tmem_ld_wait();
-#pragma unroll
-          for (int i = 0; i < 32; ++i) v[i] *= corr;
-          ptx::tmem_st32(t_o + (uint32_t)c, v);
+          v[0] *= corr_a; v[1] *= corr_a; v[2] *= corr_b; v[3] *= corr_b;
+          v[4] *= corr_a; v[5] *= corr_a; v[6] *= corr_b; v[7] *= corr_b;
+          tmem_st_16x256b_x2(t_o + (uint32_t)c, v);
         }
         ptx::tmem_st_wait();
         ptx::tc_fence_before_sync();
       }
-      if (j > 0 && !o_waited) {
-        // P_{j-1} is being read until O += P_{j-1} V_{j-1} completes
-        ok = ptx::mbar_wait(o_full, jp ^ 1u, abort_flag, status, ST_ATTN_TIMEOUT);
-        ok = __all_sync(0xffffffffu, ok);
+      if (j >= NP && !(o_waited && NP == 1)) {
+        // this block's P buffer is being read until O += P_{j-NP} V_{j-NP} completes
+        ok = ptx::mbar_wait_warp(&o_full[pbuf], (uint32_t)(j / NP - 1) & 1u, abort_flag, status, ST_ATTN_TIMEOUT);
         if (!ok) break;
       }
-      // pass 2: the 64 scores into registers; the MMA warp may then overwrite S with the next block's scores
-      // (the partner's maximum was read above, so the partner, which waits for those scores, cannot have
-      // reused the exchange slot before)
-      float sv[64];
-      ptx::tmem_ld32_at<0>(t_s, sv);
-      ptx::tmem_ld32_at<32>(t_s + 32u, sv);
-      ptx::tmem_ld_wait();
-      ptx::tc_fence_before_sync();
-      ptx::mbar_arrive(s_empty);
-      if (diag) {
-#pragma unroll
-        for (int i = 0; i < 64; ++i)
-          if (u0 + i > t) sv[i] = -INFINITY;
-      }
       // probabilities against the reference -> bf16 -> shared memory
-      float2 rs2 = make_float2(0.f, 0.f);
-      const float2 sl2v = make_float2(sl2, sl2), nmsv = make_float2(-ms, -ms);
+      float2 rs_a = make_float2(0.f, 0.f), rs_b = make_float2(0.f, 0.f);
+      const float2 sl2v = make_float2(sl2, sl2);
+      const float2 nm_av = make_float2(-ms_a, -ms_a), nm_bv = make_float2(-ms_b, -ms_b);
+      const uint32_t pw = p_base + (uint32_t)(pbuf * C::kPBytes);
 #pragma unroll
-      for (int c = 0; c < 64; c += 8) {  // 16-byte pieces of 8 keys
-        uint4 raw;
-        __nv_bfloat162* hp = reinterpret_cast<__nv_bfloat162*>(&raw);
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {  // packed fp32x2 arithmetic: two keys per instruction
-          const float2 x = __ffma2_rn(make_float2(sv[c + 2 * i], sv[c + 2 * i + 1]), sl2v, nmsv);
-          const float2 pr = make_float2(exp2f(x.x), exp2f(x.y));
-          rs2 = __fadd2_rn(rs2, pr);
-          hp[i] = __floats2bfloat162_rn(pr.x, pr.y);
-        }
-        *reinterpret_cast<uint4*>(p_row + (((c >> 3) ^ (row & 7)) << 4)) = raw;
+      for (int g = 0; g < 16; ++g) {
+        const float2 xa = __ffma2_rn(make_float2(sv[4 * g], sv[4 * g + 1]), sl2v, nm_av);
+        const float2 xb = __ffma2_rn(make_float2(sv[4 * g + 2], sv[4 * g + 3]), sl2v, nm_bv);
+        const float2 pa = make_float2(exp2f(xa.x), exp2f(xa.y));
+        const float2 pb = make_float2(exp2f(xb.x), exp2f(xb.y));
+        rs_a = __fadd2_rn(rs_a, pa);
+        rs_b = __fadd2_rn(rs_b, pb);
+        const __nv_bfloat162 ha = __floats2bfloat162_rn(pa.x, pa.y), hb = __floats2bfloat162_rn(pb.x, pb.y);
+        const uint32_t chunk = (uint32_t)(g >> 3) * (uint32_t)SUB + ((((uint32_t)g & 7u) ^ swz) << 4);
+        st_shared_b32(pw + chunk + pa_off, *reinterpret_cast<const uint32_t*>(&ha));
+        st_shared_b32(pw + chunk + pb_off, *reinterpret_cast<const uint32_t*>(&hb));
       }
-      l += rs2.x + rs2.y;
+      l_a += rs_a.x + rs_a.y;
+      l_b += rs_b.x + rs_b.y;
       ptx::fence_proxy_async();  // make the generic-proxy writes of P visible to the MMA's async proxy
-      ptx::mbar_arrive(p_full);
+      ptx::mbar_arrive(&p_full[pbuf]);
     }
-    if (ok) {
-      ok = ptx::mbar_wait(o_full, (uint32_t)(n_blocks - 1) & 1u, abort_flag, status, ST_ATTN_TIMEOUT);
-      ok = __all_sync(0xffffffffu, ok);
-    }
-    // the two halves of a row hold partial sums under the same running maximum
-    if (ok) {
-      // every MMA that reads Q has completed (the last s_full was consumed): its tile holds the partial sums
-      float* lx = reinterpret_cast<float*>(smem + C::kQOff);
-      lx[hf * 128 + row] = l;
-      ptx::mbar_arrive(x_bar);
-      ok = ptx::mbar_wait(x_bar, (uint32_t)n_blocks & 1u, abort_flag, status, ST_ATTN_TIMEOUT);
-      if (ok) l += lx[(hf ^ 1) * 128 + row];
-    }
-    ok = __all_sync(0xffffffffu, ok);
+    if (ok) ok = ptx::mbar_wait_warp(&o_full[(n_blocks - 1) % NP], (uint32_t)((n_blocks - 1) / NP) & 1u, abort_flag,
+                                     status, ST_ATTN_TIMEOUT);
     if (ok) {
       ptx::tc_fence_after_sync();
-      const float inv = 1.f / l;
-      bf16* dst = o + ((size_t)b * seq + t) * ldo + h * HS + hf * OH;
+      l_a = quad_sum(l_a);
+      l_b = quad_sum(l_b);
+      const float inv_a = 1.f / l_a, inv_b = 1.f / l_b;
+      bf16* dst_a = o + ((size_t)b * seq + ta) * ldo + h * HS + 2 * q4;
+      bf16* dst_b = dst_a + (size_t)8 * ldo;
 #pragma unroll
-      for (int c = 0; c < OH; c += 32) {
+      for (int c = 0; c < HS; c += 64) {
         float v[32];
-        ptx::tmem_ld32(t_o + (uint32_t)c, v);
+        tmem_ld_16x256b_x8(t_o + (uint32_t)c, v);
         ptx::tmem_ld_wait();
-        if (t < seq) {
 #pragma unroll
-          for (int g = 0; g < 32; g += 8) {
-            float w8[8];
-#pragma unroll
-            for (int i = 0; i < 8; ++i) w8[i] = v[g + i] * inv;
-            store8(dst + c + g, w8);
-          }
+        for (int g = 0; g < 8; ++g) {
+          if (ta < seq)
+            *reinterpret_cast<__nv_bfloat162*>(dst_a + c + 8 * g) = __floats2bfloat162_rn(v[4 * g] * inv_a, v[4 * g + 1] * inv_a);
+          if (tb < seq)
+            *reinterpret_cast<__nv_bfloat162*>(dst_b + c + 8 * g) = __floats2bfloat162_rn(v[4 * g + 2] * inv_b, v[4 * g + 3] * inv_b);
         }
       }
-      if (lse && hf == 0 && t < seq) lse[((size_t)b * n_heads + h) * seq + t] = ms * 0.6931471805599453f + __logf(l);
+      if (lse && q4 == 0) {
+        float* lrow = lse + ((size_t)b * n_heads + h) * seq;
+        if (ta < seq) lrow[ta] = ms_a * 0.6931471805599453f + __logf(l_a);
+        if (tb < seq) lrow[tb] = ms_b * 0.6931471805599453f + __logf(l_b);
+      }
     }
   }
 

@@ -379,17 +379,45 @@ __global__ void __launch_bounds__(512) peer_oneshot_kernel(PeerPtrs pp, int rank
 //     so that the kernel's completion means this rank's gathered activations are whole.
 // The reduce-scatter and the all-gather thus cross NVLink once each, and the residual stream, the add and the norm
 // touch T / world rows per rank instead of T.  REDUCE = false skips the partial sums (the norm after the embedding).
-// A CTA takes one row at a time; a thread keeps its 16-byte chunks of the row in registers between the two passes
-// (rows wider than kRowChunks * 256 chunks are re-read from the residual buffer, which is local).
-constexpr int kRowChunks = 4;
+// A CTA takes one row at a time; a thread keeps its NCH 16-byte chunks of the row in registers between the two
+// passes.  While a row is reduced, normed and stored, the loads of the CTA's next row (from every rank, over NVLink)
+// are already in flight: the peer-load latency of one row hides behind the arithmetic and the stores of the one
+// before (PREFETCH; chosen on the host where the second set of loads fits the register budget of two CTAs per SM).
+// NW is the number of ranks rounded up to 2, 4 or 8 (0: no partial sums, the norm after the embedding) and NCH the
+// chunks per thread, both compile-time so that the loads stay in registers.
+template <typename T, int NW, int NCH>
+struct RowRegs {
+  static constexpr int E = 16 / sizeof(T);
+  uint4 part[NW > 0 ? NW : 1][NCH];
+  float4 x[NCH][E / 4];
+};
 
-template <typename T, bool REDUCE>
-__global__ void __launch_bounds__(256) peer_rownorm_kernel(PeerPtrs pp, int rank, int world, size_t part_off,
-                                                           size_t xb_off, int rows, int row0, int d,
-                                                           float* __restrict__ x_own, const float* __restrict__ gain,
-                                                           float eps, uint32_t epoch, uint32_t* status,
-                                                           long long budget) {
+template <typename T, int NW, int NCH>
+__device__ __forceinline__ void rownorm_load(RowRegs<T, NW, NCH>& g, const PeerPtrs& pp, int world, size_t part_off,
+                                             size_t grow, int d, const float* xr, int n_chunks) {
+  constexpr int E = 16 / sizeof(T);
+#pragma unroll
+  for (int k = 0; k < NCH; ++k) {
+    const int c = threadIdx.x + k * 256;
+    if (c < n_chunks) {
+      const size_t off = part_off + (grow * d + (size_t)c * E) * sizeof(T);
+#pragma unroll
+      for (int r = 0; r < NW; ++r)
+        if (r < world) g.part[r][k] = load16_sys(reinterpret_cast<const uint8_t*>(pp.buf[r]) + off);
+#pragma unroll
+      for (int i = 0; i < E / 4; ++i) g.x[k][i] = *reinterpret_cast<const float4*>(xr + c * E + 4 * i);
+    }
+  }
+}
+
+template <typename T, int NW, int NCH, bool PREFETCH>
+__global__ void __launch_bounds__(256, 2) peer_rownorm_kernel(PeerPtrs pp, int rank, int world, size_t part_off,
+                                                              size_t xb_off, int rows, int row0, int d,
+                                                              float* __restrict__ x_own, const float* __restrict__ gain,
+                                                              float eps, uint32_t epoch, uint32_t* status,
+                                                              long long budget) {
   constexpr int E = 16 / sizeof(T);  // elements per 16-byte chunk
+  constexpr bool REDUCE = NW > 0;
   __shared__ float red[32];
   __shared__ int s_last;
   uint32_t* my_flags = pp.flags[rank];
@@ -400,29 +428,28 @@ __global__ void __launch_bounds__(256) peer_rownorm_kernel(PeerPtrs pp, int rank
   const bool ok = wait_all_peers(my_flags, kReadyBase, world, epoch, status, budget);
   const int n_chunks = d / E;
   if (ok) {
-    for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+    RowRegs<T, NW, NCH> cur, nxt;
+    int row = blockIdx.x;
+    if (row < rows) rownorm_load(cur, pp, world, part_off, (size_t)(row0 + row), d, x_own + (size_t)row * d, n_chunks);
+    for (; row < rows; row += gridDim.x) {
       const size_t grow = (size_t)(row0 + row);
       float* xr = x_own + (size_t)row * d;
-      float v[kRowChunks][E];
+      const int next = row + gridDim.x;
+      if (PREFETCH && next < rows)
+        rownorm_load(nxt, pp, world, part_off, (size_t)(row0 + next), d, x_own + (size_t)next * d, n_chunks);
+      float v[NCH][E];
       float ss = 0.f;
 #pragma unroll
-      for (int k = 0; k < kRowChunks; ++k) {
+      for (int k = 0; k < NCH; ++k) {
         const int c = threadIdx.x + k * 256;
         if (c < n_chunks) {
           float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-          if (REDUCE) {
-            uint4 raw[kMaxPeers];
-            const size_t off = part_off + (grow * d + (size_t)c * E) * sizeof(T);
 #pragma unroll
-            for (int r = 0; r < kMaxPeers; ++r)
-              if (r < world) raw[r] = load16_sys(reinterpret_cast<const uint8_t*>(pp.buf[r]) + off);
-#pragma unroll
-            for (int r = 0; r < kMaxPeers; ++r)
-              if (r < world) accum8(raw[r], acc, T());
-          }
+          for (int r = 0; r < NW; ++r)
+            if (r < world) accum8(cur.part[r][k], acc, T());  // rank order: the sum is the same on every run
 #pragma unroll
           for (int i = 0; i < E; i += 4) {
-            float4 a = *reinterpret_cast<const float4*>(xr + c * E + i);
+            float4 a = cur.x[k][i / 4];
             a.x += acc[i]; a.y += acc[i + 1]; a.z += acc[i + 2]; a.w += acc[i + 3];
             if (REDUCE) *reinterpret_cast<float4*>(xr + c * E + i) = a;
             v[k][i] = a.x; v[k][i + 1] = a.y; v[k][i + 2] = a.z; v[k][i + 3] = a.w;
@@ -430,51 +457,37 @@ __global__ void __launch_bounds__(256) peer_rownorm_kernel(PeerPtrs pp, int rank
           }
         }
       }
-      // rows wider than the register tile: same arithmetic, the residual row is re-read below
-      for (int c = threadIdx.x + kRowChunks * 256; c < n_chunks; c += 256) {
-        float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-        if (REDUCE) {
-          const size_t off = part_off + (grow * d + (size_t)c * E) * sizeof(T);
-          for (int r = 0; r < world; ++r) accum8(load16_sys(reinterpret_cast<const uint8_t*>(pp.buf[r]) + off), acc, T());
-        }
-        for (int i = 0; i < E; ++i) {
-          const float a = xr[c * E + i] + acc[i];
-          if (REDUCE) xr[c * E + i] = a;
-          ss = fmaf(a, a, ss);
-        }
-      }
       ss = block_sum(ss, red);
       const float rinv = rsqrtf(ss / (float)d + eps);
-      auto emit = [&](int c, const float* val) {
-        float y[8];
 #pragma unroll
-        for (int i = 0; i < E; i += 4) {
-          const float4 g = *reinterpret_cast<const float4*>(gain + c * E + i);
-          y[i] = g.x * val[i] * rinv; y[i + 1] = g.y * val[i + 1] * rinv;
-          y[i + 2] = g.z * val[i + 2] * rinv; y[i + 3] = g.w * val[i + 3] * rinv;
-        }
-        uint4 out;
-        if (sizeof(T) == 2) {
-          __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&out);
-#pragma unroll
-          for (int k2 = 0; k2 < 4; ++k2) h[k2] = __floats2bfloat162_rn(y[2 * k2], y[2 * k2 + 1]);
-        } else {
-          out = make_uint4(__float_as_uint(y[0]), __float_as_uint(y[1]), __float_as_uint(y[2]), __float_as_uint(y[3]));
-        }
-        const size_t off = xb_off + (grow * d + (size_t)c * E) * sizeof(T);
-#pragma unroll
-        for (int r = 0; r < kMaxPeers; ++r)
-          if (r < world) *reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(pp.buf[r]) + off) = out;
-      };
-#pragma unroll
-      for (int k = 0; k < kRowChunks; ++k) {
+      for (int k = 0; k < NCH; ++k) {
         const int c = threadIdx.x + k * 256;
-        if (c < n_chunks) emit(c, v[k]);
+        if (c < n_chunks) {
+          float y[8];
+#pragma unroll
+          for (int i = 0; i < E; i += 4) {
+            const float4 gn = *reinterpret_cast<const float4*>(gain + c * E + i);
+            y[i] = gn.x * v[k][i] * rinv; y[i + 1] = gn.y * v[k][i + 1] * rinv;
+            y[i + 2] = gn.z * v[k][i + 2] * rinv; y[i + 3] = gn.w * v[k][i + 3] * rinv;
+          }
+          uint4 out;
+          if (sizeof(T) == 2) {
+            __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&out);
+#pragma unroll
+            for (int k2 = 0; k2 < 4; ++k2) h[k2] = __floats2bfloat162_rn(y[2 * k2], y[2 * k2 + 1]);
+          } else {
+            out = make_uint4(__float_as_uint(y[0]), __float_as_uint(y[1]), __float_as_uint(y[2]), __float_as_uint(y[3]));
+          }
+          const size_t off = xb_off + (grow * d + (size_t)c * E) * sizeof(T);
+#pragma unroll
+          for (int r = 0; r < kMaxPeers; ++r)
+            if (r < world) *reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(pp.buf[r]) + off) = out;
+        }
       }
-      for (int c = threadIdx.x + kRowChunks * 256; c < n_chunks; c += 256) {
-        float val[8];
-        for (int i = 0; i < E; ++i) val[i] = xr[c * E + i];
-        emit(c, val);
+      if (PREFETCH) {
+        cur = nxt;
+      } else if (next < rows) {
+        rownorm_load(cur, pp, world, part_off, (size_t)(row0 + next), d, x_own + (size_t)next * d, n_chunks);
       }
     }
   }
@@ -567,14 +580,43 @@ int32_t comm_peer_reduce_norm(void* comm, int T, int d, int dtype, bool reduce, 
   int grid = sm_count() * 2;  // two CTAs of 256 threads are resident per SM (register tile of the row)
   if (grid > rows) grid = rows;
   uint32_t* status = device_status_word();
-#define B200_ROWNORM(TT, RR)                                                                                       \
-  peer_rownorm_kernel<TT, RR><<<grid, 256, 0, stream>>>(pp, c->rank, c->world, part_off, xb_off, rows, row0, d,    \
-                                                        x_own, gain, eps, epoch, status, c->wait_budget)
-  if (dtype == B200_BF16) {
-    if (reduce) B200_ROWNORM(bf16, true); else B200_ROWNORM(bf16, false);
-  } else {
-    if (reduce) B200_ROWNORM(float, true); else B200_ROWNORM(float, false);
-  }
+  const int n_chunks = (int)((size_t)d * es / 16);
+  const int nch = n_chunks <= 256 ? 1 : n_chunks <= 512 ? 2 : 4;
+  if (n_chunks > 1024)
+    return fail(B200_ERR_BAD_SHAPE, "row-sharded exchange: rows of %d elements exceed 16 KB", d);
+  const int nw = !reduce ? 0 : c->world <= 2 ? 2 : c->world <= 4 ? 4 : 8;
+  // registers of one row's loads: NW * NCH * 4 (partials) + NCH * (4 or 8) (residual); two sets fit below about 72
+  const int regs_row = (nw > 0 ? nw : 1) * nch * 4 + nch * (int)(16 / es);
+  static const int pf_env = env_int("B200_ROWNORM_PREFETCH", -1);  // -1: decide by the register estimate
+  const bool prefetch = pf_env >= 0 ? pf_env != 0 : regs_row <= 72;
+#define B200_ROWNORM(TT, NW, NCH)                                                                                    \
+  do {                                                                                                               \
+    if (prefetch)                                                                                                    \
+      peer_rownorm_kernel<TT, NW, NCH, true><<<grid, 256, 0, stream>>>(pp, c->rank, c->world, part_off, xb_off, rows, \
+                                                                       row0, d, x_own, gain, eps, epoch, status,     \
+                                                                       c->wait_budget);                              \
+    else                                                                                                             \
+      peer_rownorm_kernel<TT, NW, NCH, false><<<grid, 256, 0, stream>>>(pp, c->rank, c->world, part_off, xb_off,     \
+                                                                        rows, row0, d, x_own, gain, eps, epoch,      \
+                                                                        status, c->wait_budget);                     \
+  } while (0)
+#define B200_ROWNORM_NCH(TT, NW)                       \
+  do {                                                 \
+    if (nch == 1) B200_ROWNORM(TT, NW, 1);             \
+    else if (nch == 2) B200_ROWNORM(TT, NW, 2);        \
+    else B200_ROWNORM(TT, NW, 4);                      \
+  } while (0)
+#define B200_ROWNORM_NW(TT)                            \
+  do {                                                 \
+    if (nw == 0) B200_ROWNORM_NCH(TT, 0);              \
+    else if (nw == 2) B200_ROWNORM_NCH(TT, 2);         \
+    else if (nw == 4) B200_ROWNORM_NCH(TT, 4);         \
+    else B200_ROWNORM_NCH(TT, 8);                      \
+  } while (0)
+  if (dtype == B200_BF16) B200_ROWNORM_NW(bf16);
+  else B200_ROWNORM_NW(float);
+#undef B200_ROWNORM_NW
+#undef B200_ROWNORM_NCH
 #undef B200_ROWNORM
   B200_LAUNCH_OK("peer_rownorm_kernel");
   return B200_OK;
