@@ -516,9 +516,13 @@ def run_prefill(args, rank, world, local, B, dist):
         "gpu_launches": launches, "roofline": roofline, "clocks": clocks,
     }
     if tp > 1:
-        line["config"]["exchange"] = ("row-sharded residual stream over peer memory (one fused reduce + add + RMSNorm + "
-                                      "gather kernel per block)" if comm.peer_memory() and
-                                      os.environ.get("B200_TP_ROW_SHARD", "1") != "0" else "all-reduce per block")
+        mode = comm.peer_memory()
+        fused = mode and os.environ.get("B200_TP_ROW_SHARD", "1") != "0"
+        line["config"]["exchange"] = (
+            ("row-sharded residual stream: one fused reduce + add + RMSNorm + gather kernel per block, "
+             + ("summed inside the NVLink switch (multimem.ld_reduce / multimem.st)"
+                if mode == 2 and os.environ.get("B200_TP_MULTIMEM", "1") != "0" else "plain peer loads and stores"))
+            if fused else "all-reduce per block")
         line["exchange_ms_per_step"] = prof["allreduce"]["ms"] / args.steps
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         sample_b = 1

@@ -35,7 +35,8 @@ EXPORTS = (
     "b200_attention_decode_scratch_bytes", "b200_attention_decode", "b200_attention_decode_static",
     "b200_attention_backward", "b200_comm_peer_memory", "b200_selftest_bounded_wait", "b200_argmax",
     "b200_selftest_peer_wait", "b200_plan_cached", "b200_ffi_available", "b200_ffi_handler",
-    "b200_token_vjp_workspace_bytes", "b200_token_vjp",
+    "b200_token_vjp_workspace_bytes", "b200_token_vjp", "b200_comm_init_rank_ex", "b200_comm_setup_peer_memory",
+    "b200_comm_attach_memory", "b200_tp_exchange_buffers", "b200_tp_reduce_norm",
 )
 
 
@@ -108,6 +109,12 @@ def lib() -> ctypes.CDLL:
         l.b200_device_status.argtypes = [c_void_p, POINTER(c_uint32)]
         l.b200_comm_unique_id.argtypes = [c_void_p]
         l.b200_comm_init_rank.argtypes = [c_void_p, c_int32, c_int32, POINTER(c_void_p)]
+        l.b200_comm_init_rank_ex.argtypes = [c_void_p, c_int32, c_int32, c_int32, POINTER(c_void_p)]
+        l.b200_comm_setup_peer_memory.argtypes = [c_void_p]
+        l.b200_comm_attach_memory.argtypes = [c_void_p, c_size_t, POINTER(c_void_p), c_void_p]
+        l.b200_tp_exchange_buffers.argtypes = [c_void_p, c_size_t, POINTER(c_void_p), POINTER(c_void_p)]
+        l.b200_tp_reduce_norm.argtypes = [c_void_p, c_int32, c_int32, c_int32, c_int32, c_void_p, c_void_p, c_float,
+                                          c_void_p]
         l.b200_comm_destroy.argtypes = [c_void_p]
         l.b200_comm_peer_memory.argtypes = [c_void_p, POINTER(c_int32)]
         _lib = l
@@ -317,18 +324,75 @@ class Comm:
     """NCCL communicator created from a unique id that rank 0 shares through
     ``torch.distributed`` (any backend: the id is 128 bytes of host data)."""
 
-    def __init__(self, rank: int, world: int, group=None):
+    def __init__(self, rank: int, world: int, group=None, symmetric: Optional[bool] = None):
         raw = share_unique_id(rank, world, _new_unique_id, group)
         ident = ctypes.create_string_buffer(raw, 128)
         handle = c_void_p()
-        check(lib().b200_comm_init_rank(ident, rank, world, byref(handle)))
+        if symmetric is None:
+            symmetric = os.environ.get("B200_SYMM_MEM", "1") != "0"
+        symmetric = bool(symmetric) and world > 1
+        check(lib().b200_comm_init_rank_ex(ident, rank, world, 0 if symmetric else 1, byref(handle)))
         self.handle, self.rank, self.world = handle, rank, world
+        self._symm = None
+        if symmetric and not self._attach_symmetric(group):
+            check(lib().b200_comm_setup_peer_memory(handle))  # the library's own CUDA-IPC buffers instead
 
-    def peer_memory(self) -> bool:
-        """True when tensor-parallel partial sums travel through peer-mapped memory instead of NCCL."""
+    def _attach_symmetric(self, group) -> bool:
+        """Exchange memory from torch.distributed's symmetric-memory allocator: one block per rank, mapped into every
+        rank, and (on NVSwitch systems) bound to a multicast object, which lets the tensor-parallel exchange reduce
+        inside the switch.  Every rank reaches ``b200_comm_attach_memory`` whatever happened before it, so that the
+        ranks agree on the outcome; False means that no rank attached."""
+        import torch.distributed as dist
+        nbytes = (int(os.environ.get("B200_P2P_MB", "136")) << 20) + 4096
+        ptrs = (c_void_p * self.world)()
+        mc = None
+        keep = None
+        try:
+            import torch.distributed._symmetric_memory as symm_mem
+            dev = torch.device("cuda", torch.cuda.current_device())
+            block = symm_mem.empty(nbytes, dtype=torch.uint8, device=dev)
+            hdl = symm_mem.rendezvous(block, group=group if group is not None else dist.group.WORLD)
+            for r, p in enumerate(hdl.buffer_ptrs):
+                ptrs[r] = p
+            mc = int(hdl.multicast_ptr) or None
+            keep = (block, hdl)
+        except Exception:  # no symmetric memory here: attach nothing, but still take part in the agreement
+            ptrs = (c_void_p * self.world)()
+            mc = None
+        status = lib().b200_comm_attach_memory(self.handle, nbytes, ptrs, mc)
+        if status == 0:
+            self._symm = keep  # the library never frees it; it lives as long as this object
+            return True
+        if status != 10:
+            check(status)
+        return False
+
+    def peer_memory(self) -> int:
+        """0: tensor-parallel partial sums travel through NCCL; 1: through peer-mapped memory (plain loads and stores
+        over NVLink); 2: through peer-mapped memory bound to a multicast object (summed inside the NVLink switch)."""
         on = c_int32(0)
         check(lib().b200_comm_peer_memory(self.handle, byref(on)))
-        return bool(on.value)
+        return int(on.value)
+
+    def exchange_buffers(self, rows_total: int, dim: int, dtype: torch.dtype):
+        """(part, gathered): views of this rank's exchange memory, [rows_total, dim] of ``dtype`` each (see
+        ``b200_tp_exchange_buffers``).  They alias library-managed device memory: valid while the communicator lives."""
+        es = 2 if dtype == torch.bfloat16 else 4
+        n = rows_total * dim * es
+        part, gath = c_void_p(), c_void_p()
+        check(lib().b200_tp_exchange_buffers(self.handle, n, byref(part), byref(gath)))
+
+        def view(ptr):
+            class _Raw:  # __cuda_array_interface__ lets torch wrap device memory it does not own
+                __cuda_array_interface__ = {"shape": (n,), "typestr": "|u1", "data": (ptr.value, False), "version": 2}
+            return torch.as_tensor(_Raw(), device="cuda").view(dtype).view(rows_total, dim)
+
+        return view(part), view(gath)
+
+    def reduce_norm(self, rows_total: int, dim: int, dtype: torch.dtype, x_own: torch.Tensor, gain: torch.Tensor,
+                    eps: float = 1e-5, reduce: bool = True) -> None:
+        check(lib().b200_tp_reduce_norm(self.handle, rows_total, dim, _dt(dtype), int(reduce), x_own.data_ptr(),
+                                        gain.data_ptr(), eps, _stream()))
 
     def allreduce_f32(self, t: torch.Tensor) -> None:
         check(lib().b200_allreduce_f32(self.handle, t.data_ptr(), t.numel(), _stream()))
@@ -337,6 +401,7 @@ class Comm:
         if self.handle:
             check(lib().b200_comm_destroy(self.handle))
             self.handle = None
+            self._symm = None
 
 
 # --------------------------------------------------------------------------

@@ -81,6 +81,8 @@ struct PeerMem {
   void* buf[kMaxPeers] = {};       // buf[r]: rank r's exchange buffer as seen from this process
   uint32_t* flags[kMaxPeers] = {}; // flags[r]: rank r's flag words
   uint32_t epoch = 0;
+  bool external = false;           // the memory belongs to the caller (b200_comm_attach_memory): never freed here
+  uint8_t* mc = nullptr;           // multicast address of the same buffers (NVLink SHARP), or null
 };
 
 }  // namespace
@@ -172,6 +174,10 @@ void setup_peer_memory(Comm* c) {
 void free_peer_memory(Comm* c) {
   PeerMem& pm = c->pm;
   if (!pm.on) return;
+  if (pm.external) {
+    pm = PeerMem();
+    return;
+  }
   for (int r = 0; r < c->world; ++r) {
     if (r == c->rank) continue;
     cudaIpcCloseMemHandle(pm.buf[r]);
@@ -394,7 +400,7 @@ struct RowRegs {
 
 template <typename T, int NW, int NCH>
 __device__ __forceinline__ void rownorm_load(RowRegs<T, NW, NCH>& g, const PeerPtrs& pp, int world, size_t part_off,
-                                             size_t grow, int d, const float* xr, int n_chunks) {
+                                             size_t grow, int d, const float* xr, int n_chunks, int only = -1) {
   constexpr int E = 16 / sizeof(T);
 #pragma unroll
   for (int k = 0; k < NCH; ++k) {
@@ -403,7 +409,7 @@ __device__ __forceinline__ void rownorm_load(RowRegs<T, NW, NCH>& g, const PeerP
       const size_t off = part_off + (grow * d + (size_t)c * E) * sizeof(T);
 #pragma unroll
       for (int r = 0; r < NW; ++r)
-        if (r < world) g.part[r][k] = load16_sys(reinterpret_cast<const uint8_t*>(pp.buf[r]) + off);
+        if (r < world) g.part[r][k] = load16_sys(reinterpret_cast<const uint8_t*>(pp.buf[only >= 0 ? only : r]) + off);
 #pragma unroll
       for (int i = 0; i < E / 4; ++i) g.x[k][i] = *reinterpret_cast<const float4*>(xr + c * E + 4 * i);
     }
@@ -415,9 +421,10 @@ __global__ void __launch_bounds__(256, 2) peer_rownorm_kernel(PeerPtrs pp, int r
                                                               size_t xb_off, int rows, int row0, int d,
                                                               float* __restrict__ x_own, const float* __restrict__ gain,
                                                               float eps, uint32_t epoch, uint32_t* status,
-                                                              long long budget) {
+                                                              long long budget, int dbg) {
   constexpr int E = 16 / sizeof(T);  // elements per 16-byte chunk
   constexpr bool REDUCE = NW > 0;
+  const int only = (dbg & 1) ? rank : -1;  // measurement aid: every load from this rank's own buffer
   __shared__ float red[32];
   __shared__ int s_last;
   uint32_t* my_flags = pp.flags[rank];
@@ -430,13 +437,13 @@ __global__ void __launch_bounds__(256, 2) peer_rownorm_kernel(PeerPtrs pp, int r
   if (ok) {
     RowRegs<T, NW, NCH> cur, nxt;
     int row = blockIdx.x;
-    if (row < rows) rownorm_load(cur, pp, world, part_off, (size_t)(row0 + row), d, x_own + (size_t)row * d, n_chunks);
+    if (row < rows) rownorm_load(cur, pp, world, part_off, (size_t)(row0 + row), d, x_own + (size_t)row * d, n_chunks, only);
     for (; row < rows; row += gridDim.x) {
       const size_t grow = (size_t)(row0 + row);
       float* xr = x_own + (size_t)row * d;
       const int next = row + gridDim.x;
       if (PREFETCH && next < rows)
-        rownorm_load(nxt, pp, world, part_off, (size_t)(row0 + next), d, x_own + (size_t)next * d, n_chunks);
+        rownorm_load(nxt, pp, world, part_off, (size_t)(row0 + next), d, x_own + (size_t)next * d, n_chunks, only);
       float v[NCH][E];
       float ss = 0.f;
 #pragma unroll
@@ -481,14 +488,135 @@ __global__ void __launch_bounds__(256, 2) peer_rownorm_kernel(PeerPtrs pp, int r
           const size_t off = xb_off + (grow * d + (size_t)c * E) * sizeof(T);
 #pragma unroll
           for (int r = 0; r < kMaxPeers; ++r)
-            if (r < world) *reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(pp.buf[r]) + off) = out;
+            if (r < world && (!(dbg & 2) || r == rank)) *reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(pp.buf[r]) + off) = out;
         }
       }
       if (PREFETCH) {
         cur = nxt;
       } else if (next < rows) {
-        rownorm_load(cur, pp, world, part_off, (size_t)(row0 + next), d, x_own + (size_t)next * d, n_chunks);
+        rownorm_load(cur, pp, world, part_off, (size_t)(row0 + next), d, x_own + (size_t)next * d, n_chunks, only);
       }
+    }
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const uint32_t done = atomicAdd(my_flags + kCounter, 1u);
+    s_last = done == gridDim.x - 1;
+    if (s_last) {
+      my_flags[kCounter] = 0u;
+      __threadfence_system();
+      for (int r = 0; r < world; ++r) flag_store_sys(pp.flags[r] + kDoneBase + rank, epoch);
+    }
+  }
+  __syncthreads();
+  if (s_last && ok) wait_all_peers(my_flags, kDoneBase, world, epoch, status, budget);
+}
+
+// ---- the same exchange through the NVLink switch (multimem) -----------------------------------------------------
+// When the ranks' exchange buffers are bound to one multicast object, a load from the multicast address returns the
+// SUM of the addressed word over all ranks, added inside the switch (multimem.ld_reduce), and a store to it lands in
+// every rank's buffer (multimem.st).  A rank then pulls only its own rows - already reduced - and sends its normed
+// rows once: 1/world of the bytes of the peer-load version cross each link.  Flags stay plain peer stores.
+__device__ __forceinline__ uint4 mc_ld_reduce(const uint8_t* p, bf16) {
+  uint4 v;
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p)
+               : "memory");
+  return v;
+}
+__device__ __forceinline__ uint4 mc_ld_reduce(const uint8_t* p, float) {
+  uint4 v;
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p)
+               : "memory");
+  return v;
+}
+__device__ __forceinline__ void mc_st(uint8_t* p, const uint4& v) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z),
+               "r"(v.w)
+               : "memory");
+}
+
+template <typename T, int NCH, bool REDUCE>
+__global__ void __launch_bounds__(256, 4) peer_rownorm_mc_kernel(PeerPtrs pp, uint8_t* mc, int rank, int world,
+                                                                 size_t part_off, size_t xb_off, int rows, int row0,
+                                                                 int d, float* __restrict__ x_own,
+                                                                 const float* __restrict__ gain, float eps,
+                                                                 uint32_t epoch, uint32_t* status, long long budget) {
+  constexpr int E = 16 / sizeof(T);
+  __shared__ float red[32];
+  __shared__ int s_last;
+  uint32_t* my_flags = pp.flags[rank];
+  if (blockIdx.x == 0 && threadIdx.x < world) {
+    __threadfence_system();
+    flag_store_sys(pp.flags[threadIdx.x] + kReadyBase + rank, epoch);
+  }
+  const bool ok = wait_all_peers(my_flags, kReadyBase, world, epoch, status, budget);
+  const int n_chunks = d / E;
+  if (ok) {
+    uint4 cur[NCH], nxt[NCH];
+    auto load = [&](uint4 (&g)[NCH], int row) {
+      if (!REDUCE) return;
+#pragma unroll
+      for (int k = 0; k < NCH; ++k) {
+        const int c = threadIdx.x + k * 256;
+        if (c < n_chunks) g[k] = mc_ld_reduce(mc + part_off + ((size_t)(row0 + row) * d + (size_t)c * E) * sizeof(T), T());
+      }
+    };
+    int row = blockIdx.x;
+    if (row < rows) load(cur, row);
+    for (; row < rows; row += gridDim.x) {
+      const size_t grow = (size_t)(row0 + row);
+      float* xr = x_own + (size_t)row * d;
+      const int next = row + gridDim.x;
+      if (next < rows) load(nxt, next);
+      float v[NCH][E];
+      float ss = 0.f;
+#pragma unroll
+      for (int k = 0; k < NCH; ++k) {
+        const int c = threadIdx.x + k * 256;
+        if (c < n_chunks) {
+          float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+          if (REDUCE) accum8(cur[k], acc, T());
+#pragma unroll
+          for (int i = 0; i < E; i += 4) {
+            float4 a = *reinterpret_cast<const float4*>(xr + c * E + i);
+            a.x += acc[i]; a.y += acc[i + 1]; a.z += acc[i + 2]; a.w += acc[i + 3];
+            if (REDUCE) *reinterpret_cast<float4*>(xr + c * E + i) = a;
+            v[k][i] = a.x; v[k][i + 1] = a.y; v[k][i + 2] = a.z; v[k][i + 3] = a.w;
+            ss = fmaf(a.x, a.x, fmaf(a.y, a.y, fmaf(a.z, a.z, fmaf(a.w, a.w, ss))));
+          }
+        }
+      }
+      ss = block_sum(ss, red);
+      const float rinv = rsqrtf(ss / (float)d + eps);
+#pragma unroll
+      for (int k = 0; k < NCH; ++k) {
+        const int c = threadIdx.x + k * 256;
+        if (c < n_chunks) {
+          float y[8];
+#pragma unroll
+          for (int i = 0; i < E; i += 4) {
+            const float4 gn = *reinterpret_cast<const float4*>(gain + c * E + i);
+            y[i] = gn.x * v[k][i] * rinv; y[i + 1] = gn.y * v[k][i + 1] * rinv;
+            y[i + 2] = gn.z * v[k][i + 2] * rinv; y[i + 3] = gn.w * v[k][i + 3] * rinv;
+          }
+          uint4 out;
+          if (sizeof(T) == 2) {
+            __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&out);
+#pragma unroll
+            for (int k2 = 0; k2 < 4; ++k2) h[k2] = __floats2bfloat162_rn(y[2 * k2], y[2 * k2 + 1]);
+          } else {
+            out = make_uint4(__float_as_uint(y[0]), __float_as_uint(y[1]), __float_as_uint(y[2]), __float_as_uint(y[3]));
+          }
+          mc_st(mc + xb_off + (grow * d + (size_t)c * E) * sizeof(T), out);
+        }
+      }
+#pragma unroll
+      for (int k = 0; k < NCH; ++k) cur[k] = nxt[k];
     }
   }
   __threadfence_system();
@@ -585,20 +713,45 @@ int32_t comm_peer_reduce_norm(void* comm, int T, int d, int dtype, bool reduce, 
   if (n_chunks > 1024)
     return fail(B200_ERR_BAD_SHAPE, "row-sharded exchange: rows of %d elements exceed 16 KB", d);
   const int nw = !reduce ? 0 : c->world <= 2 ? 2 : c->world <= 4 ? 4 : 8;
+  static const int use_mc = env_int("B200_TP_MULTIMEM", 1);
+  if (c->pm.mc && use_mc) {
+    int grid_mc = sm_count() * 4;
+    if (grid_mc > rows) grid_mc = rows;
+#define B200_ROWNORM_MC(TT, NCH)                                                                                    \
+  do {                                                                                                              \
+    if (reduce)                                                                                                     \
+      peer_rownorm_mc_kernel<TT, NCH, true><<<grid_mc, 256, 0, stream>>>(pp, c->pm.mc, c->rank, c->world, part_off, \
+                                                                         xb_off, rows, row0, d, x_own, gain, eps,   \
+                                                                         epoch, status, c->wait_budget);            \
+    else                                                                                                            \
+      peer_rownorm_mc_kernel<TT, NCH, false><<<grid_mc, 256, 0, stream>>>(pp, c->pm.mc, c->rank, c->world, part_off, \
+                                                                          xb_off, rows, row0, d, x_own, gain, eps,  \
+                                                                          epoch, status, c->wait_budget);           \
+  } while (0)
+    if (dtype == B200_BF16) {
+      if (nch == 1) B200_ROWNORM_MC(bf16, 1); else if (nch == 2) B200_ROWNORM_MC(bf16, 2); else B200_ROWNORM_MC(bf16, 4);
+    } else {
+      if (nch == 1) B200_ROWNORM_MC(float, 1); else if (nch == 2) B200_ROWNORM_MC(float, 2); else B200_ROWNORM_MC(float, 4);
+    }
+#undef B200_ROWNORM_MC
+    B200_LAUNCH_OK("peer_rownorm_mc_kernel");
+    return B200_OK;
+  }
   // registers of one row's loads: NW * NCH * 4 (partials) + NCH * (4 or 8) (residual); two sets fit below about 72
   const int regs_row = (nw > 0 ? nw : 1) * nch * 4 + nch * (int)(16 / es);
   static const int pf_env = env_int("B200_ROWNORM_PREFETCH", -1);  // -1: decide by the register estimate
+  static const int dbg = env_int("B200_EXCH_LOCAL_ONLY", 0);       // measurement aid: 1 loads, 2 stores stay on this GPU
   const bool prefetch = pf_env >= 0 ? pf_env != 0 : regs_row <= 72;
 #define B200_ROWNORM(TT, NW, NCH)                                                                                    \
   do {                                                                                                               \
     if (prefetch)                                                                                                    \
       peer_rownorm_kernel<TT, NW, NCH, true><<<grid, 256, 0, stream>>>(pp, c->rank, c->world, part_off, xb_off, rows, \
                                                                        row0, d, x_own, gain, eps, epoch, status,     \
-                                                                       c->wait_budget);                              \
+                                                                       c->wait_budget, dbg);                         \
     else                                                                                                             \
       peer_rownorm_kernel<TT, NW, NCH, false><<<grid, 256, 0, stream>>>(pp, c->rank, c->world, part_off, xb_off,     \
                                                                         rows, row0, d, x_own, gain, eps, epoch,      \
-                                                                        status, c->wait_budget);                     \
+                                                                        status, c->wait_budget, dbg);                \
   } while (0)
 #define B200_ROWNORM_NCH(TT, NW)                       \
   do {                                                 \
@@ -713,6 +866,79 @@ int32_t b200_comm_init_rank(const void* id128, int32_t rank, int32_t world, void
   return B200_OK;
 }
 
+// A communicator whose peer-mapped exchange memory the caller brings (b200_comm_attach_memory) does not set up its
+// own at creation.
+int32_t b200_comm_init_rank_ex(const void* id128, int32_t rank, int32_t world, int32_t own_peer_memory, void** comm) {
+  if (!id128 || !comm) return fail(B200_ERR_INVALID_ARG, "null argument");
+  if (world < 1 || rank < 0 || rank >= world) return fail(B200_ERR_INVALID_ARG, "bad rank %d of %d", rank, world);
+  NcclApi& a = api();
+  if (!a.ok) return fail(B200_ERR_NCCL, "NCCL is not available in this process");
+  NcclUniqueId id;
+  memcpy(&id, id128, sizeof(id));
+  NcclComm nc = nullptr;
+  const int rc = a.comm_init_rank(&nc, world, id, rank);
+  if (rc != 0) return nccl_fail("ncclCommInitRank", rc);
+  Comm* c = new Comm();
+  c->nccl = nc;
+  c->rank = rank;
+  c->world = world;
+  const int budget_m = env_int("B200_PEER_WAIT_MCYCLES", 4000);  // millions of SM clocks
+  c->wait_budget = (long long)(budget_m > 0 ? budget_m : 4000) * 1000000LL;
+  if (own_peer_memory) setup_peer_memory(c);
+  *comm = c;
+  return B200_OK;
+}
+
+int32_t b200_comm_setup_peer_memory(void* comm) {
+  if (!comm) return fail(B200_ERR_INVALID_ARG, "communicator is null");
+  Comm* c = reinterpret_cast<Comm*>(comm);
+  if (c->pm.on) return B200_OK;
+  setup_peer_memory(c);
+  return B200_OK;
+}
+
+int32_t b200_comm_attach_memory(void* comm, size_t bytes, const void* const* peer_ptrs, void* multicast_ptr) {
+  if (!comm || !peer_ptrs) return fail(B200_ERR_INVALID_ARG, "null argument");
+  Comm* c = reinterpret_cast<Comm*>(comm);
+  NcclApi& a = api();
+  if (!a.ok) return fail(B200_ERR_NCCL, "NCCL is not available in this process");
+  if (c->world < 2 || c->world > kMaxPeers) return fail(B200_ERR_UNSUPPORTED, "peer memory serves 2..%d ranks", kMaxPeers);
+  if (c->pm.on) return fail(B200_ERR_INVALID_ARG, "the communicator already has exchange memory");
+  constexpr size_t kFlagBytes = 4096;
+  bool ok = bytes >= 4 * kOneShotMaxBytes + kFlagBytes && bytes % 256 == 0;
+  for (int r = 0; ok && r < c->world; ++r) ok = peer_ptrs[r] != nullptr && aligned16(peer_ptrs[r]);
+  PeerMem pm;
+  if (ok) {
+    pm.bytes = bytes - kFlagBytes;
+    for (int r = 0; r < c->world; ++r) {
+      pm.buf[r] = const_cast<void*>(peer_ptrs[r]);
+      pm.flags[r] = reinterpret_cast<uint32_t*>(reinterpret_cast<uint8_t*>(pm.buf[r]) + pm.bytes);
+    }
+    pm.mc = reinterpret_cast<uint8_t*>(multicast_ptr);
+    pm.external = true;
+    // this rank's flag words start at zero; nobody may signal before every rank has cleared its own
+    ok = cudaMemset(pm.flags[c->rank], 0, kFlagBytes) == cudaSuccess && cudaDeviceSynchronize() == cudaSuccess;
+  }
+  // agreement (doubles as the barrier after the clearing): every rank must have accepted its pointers, and either all
+  // or none bring a multicast address
+  float verdict[2] = {ok ? 1.f : 0.f, (ok && multicast_ptr) ? 1.f : 0.f}, total[2] = {0.f, 0.f};
+  float* dv = nullptr;
+  const bool agreed = cudaMalloc(&dv, 256) == cudaSuccess &&
+                      cudaMemcpy(dv, verdict, 8, cudaMemcpyHostToDevice) == cudaSuccess &&
+                      a.all_reduce(dv, dv, 2, kNcclFloat32, kNcclSum, c->nccl, 0) == 0 &&
+                      cudaStreamSynchronize(0) == cudaSuccess &&
+                      cudaMemcpy(total, dv, 8, cudaMemcpyDeviceToHost) == cudaSuccess;
+  if (dv) cudaFree(dv);
+  if (!agreed || total[0] != (float)c->world) {
+    cudaGetLastError();
+    return fail(B200_ERR_UNSUPPORTED, "not every rank could attach its exchange memory");
+  }
+  if (total[1] != (float)c->world) pm.mc = nullptr;
+  pm.on = true;
+  c->pm = pm;
+  return B200_OK;
+}
+
 int32_t b200_comm_destroy(void* comm) {
   if (!comm) return B200_OK;
   Comm* c = reinterpret_cast<Comm*>(comm);
@@ -742,6 +968,23 @@ int32_t b200_allreduce_f32(void* comm, float* data, size_t count, b200_stream_t 
   return comm_allreduce(comm, data, count, B200_F32, reinterpret_cast<cudaStream_t>(stream));
 }
 
+int32_t b200_tp_exchange_buffers(void* comm, size_t bytes_each, void** part, void** gathered) {
+  if (!comm || !part || !gathered) return fail(B200_ERR_INVALID_ARG, "null argument");
+  if (!comm_peer_rowshard_buffers(comm, bytes_each, part, gathered))
+    return fail(B200_ERR_UNSUPPORTED, "the communicator has no exchange memory for two regions of %zu bytes", bytes_each);
+  return B200_OK;
+}
+
+int32_t b200_tp_reduce_norm(void* comm, int32_t rows_total, int32_t dim, int32_t dtype, int32_t reduce, float* x_own,
+                            const float* gain, float eps, b200_stream_t stream) {
+  if (!comm || !x_own || !gain) return fail(B200_ERR_INVALID_ARG, "null argument");
+  if (dtype != B200_F32 && dtype != B200_BF16) return fail(B200_ERR_BAD_DTYPE, "dtype must be fp32 or bf16");
+  if (rows_total <= 0 || dim <= 0) return fail(B200_ERR_BAD_SHAPE, "rows=%d dim=%d", rows_total, dim);
+  if (!aligned16(x_own) || !aligned16(gain)) return fail(B200_ERR_MISALIGNED, "buffers must be 16-byte aligned");
+  return comm_peer_reduce_norm(comm, rows_total, dim, dtype, reduce != 0, x_own, gain, eps,
+                               reinterpret_cast<cudaStream_t>(stream));
+}
+
 int32_t b200_selftest_peer_wait(int64_t budget_cycles, uint32_t* reached_end_device, b200_stream_t stream) {
   if (!reached_end_device) return fail(B200_ERR_INVALID_ARG, "null argument");
   if (budget_cycles <= 0 || budget_cycles > 4000000000LL) return fail(B200_ERR_INVALID_ARG, "budget out of range");
@@ -750,7 +993,8 @@ int32_t b200_selftest_peer_wait(int64_t budget_cycles, uint32_t* reached_end_dev
 
 int32_t b200_comm_peer_memory(void* comm, int32_t* enabled) {
   if (!comm || !enabled) return fail(B200_ERR_INVALID_ARG, "null argument");
-  *enabled = reinterpret_cast<Comm*>(comm)->pm.on ? 1 : 0;
+  const Comm* c = reinterpret_cast<Comm*>(comm);
+  *enabled = !c->pm.on ? 0 : (c->pm.mc ? 2 : 1);
   return B200_OK;
 }
 

@@ -14,8 +14,18 @@ into whatever reads the reference's CSV files.  What differs, by construction:
 * one pipeline (``B200``) and one backend (``gpu``);
 * ``PreRev`` / ``PostRev`` / ``BothRev`` name the place of the AD pass relative
   to the optimisation passes of a compiler pipeline.  There is no pass pipeline
-  here: all three rows time the same kernel sequence (forward keeping the
-  activations, then the backward pass), and are measured separately;
+  here: all three rows time the same kernel sequence and are measured
+  separately.  As in the reference, ``revprimal`` chooses between the call that
+  also returns the primal result (``splatvjp``, test/test_utils.py:499-505) and
+  the one that returns the cotangents only (``splatvjp_noprim``, :508-514; the
+  reference's llama test sets ``revprimal = False``, test/llama.py:311);
+* the reverse rows differentiate with respect to EVERY input of the call, as
+  the reference does: ``(x, weights, key_cache, value_cache)`` for the
+  reference's own call shape, the weights for the token-sequence shape;
+* results are cross-checked like the reference's ``recursive_check``
+  (test/test_utils.py:522-550, :678-681) against a baseline the caller passes
+  (there, the first pipeline; here, e.g. the CPU oracle), leaf by leaf with
+  ``atol`` / ``rtol`` (1e-3 in the reference's llama test);
 * no ``Forward`` (JVP) row: forward mode is not built;
 * times are CUDA-event times on the launching stream, not profiler traces.
 """
@@ -27,10 +37,38 @@ from typing import Callable, Dict, List, Optional
 
 import torch
 
-from .primitives import _LlamaRoute
+from .primitives import _LlamaRoute, vjp
 
 CSV_HEADER = ["Benchmark Name", "Pass Pipeline", "Backend", "Key", "Time"]
 REVERSE_KEYS = ("PreRev", "PostRev", "BothRev")
+
+
+def recursive_check(tester, lhs, rhs, pname=None) -> None:
+    """Leaf-by-leaf comparison of two result trees (dicts, lists / tuples, tensors, None) with the tester's
+    ``atol`` / ``rtol``; raises ``AssertionError`` naming the first leaf that differs (test/test_utils.py:522-550)."""
+
+    def walk(a, b, path):
+        if a is None and b is None:
+            return
+        if isinstance(a, dict):
+            assert isinstance(b, dict) and sorted(a) == sorted(b), f"{pname}: keys differ at {path or 'root'}"
+            for k in a:
+                walk(a[k], b[k], f"{path}.{k}" if path else str(k))
+            return
+        if isinstance(a, (list, tuple)):
+            assert isinstance(b, (list, tuple)) and len(a) == len(b), f"{pname}: lengths differ at {path or 'root'}"
+            for i, (x, y) in enumerate(zip(a, b)):
+                walk(x, y, f"{path}[{i}]")
+            return
+        x = torch.as_tensor(a).detach().double().cpu()
+        y = torch.as_tensor(b).detach().double().cpu()
+        assert x.shape == y.shape, f"{pname}: shapes differ at {path or 'root'}: {tuple(x.shape)} vs {tuple(y.shape)}"
+        if not torch.allclose(x, y, atol=tester.atol, rtol=tester.rtol):
+            err = float((x - y).abs().max())
+            raise AssertionError(f"{tester.__class__.__name__} {pname}: leaf {path or 'root'} differs, max error {err:.3e} "
+                                 f"(atol {tester.atol}, rtol {tester.rtol})")
+
+    walk(lhs, rhs, "")
 
 
 class EnzymeJaxTest:
@@ -46,6 +84,8 @@ class EnzymeJaxTest:
         self.warmup = int(warmup)
         self.results: List[str] = []
         self.revprimal = True
+        self.atol = 1e-3
+        self.rtol = 1e-3
 
     # -- output ---------------------------------------------------------------
     def pretty_print_table(self, name, pname, backend, key, time):
@@ -78,39 +118,54 @@ class EnzymeJaxTest:
         torch.cuda.synchronize()
         return t0.elapsed_time(t1) * 1e-3 / self.repeat
 
-    def harness(self, name: str, fn: Callable, ins, douts: Optional[torch.Tensor] = None) -> Dict[str, float]:
-        """Times ``fn`` (a decorated llama function) on ``ins``.
+    def harness(self, name: str, fn: Callable, ins, douts: Optional[torch.Tensor] = None, *, baseline_primal=None,
+                baseline_grads=None) -> Dict[str, float]:
+        """Times ``fn`` (a decorated llama function) on ``ins`` and cross-checks its results.
 
-        ``ins`` is ``(x, weights, key_cache, value_cache)`` -- the reference's own
-        call, Primal row only -- or ``(tokens, weights)``; with a logits cotangent
-        ``douts`` the three reverse rows are timed too.  Returns ``{key: seconds}``.
+        ``ins`` is ``(x, weights, key_cache, value_cache)`` -- the reference's own call -- or ``(tokens, weights)``.
+        With a cotangent ``douts`` of the result the three reverse rows are timed too, differentiating with respect
+        to every input.  ``baseline_primal`` / ``baseline_grads`` (the trees another implementation produced for the
+        same inputs) are compared with ours by ``recursive_check``.  Returns ``{key: seconds}``.
         """
         route: _LlamaRoute = getattr(fn, "_b200_route", None)
         if route is None:
             raise NotImplementedError("harness needs a function decorated with enzyme_jax_ir(pipeline_options=B200Pipeline(...))")
         out: Dict[str, float] = {}
-        fn(*ins)  # packs the weights, creates the plan
+        primal = fn(*ins)  # packs the weights, creates the plan
+        if baseline_primal is not None:
+            recursive_check(self, primal, baseline_primal, "Primal")
         out["Primal"] = self._avg_seconds(lambda: fn(*ins))
         self.pretty_print_table(name, self.pipeline_name, self.backend, "Primal", out["Primal"])
         if douts is None:
             return out
-        if len(ins) != 2:
-            raise NotImplementedError("reverse mode is built for the (tokens, weights) call")
-        tokens, weights = ins
-        plan = route._ensure(weights, True)
-        tok = tokens.to(plan.device, torch.int32).contiguous()
-        dlog = douts.to(plan.device, torch.float32).contiguous()
-        saved, grads = plan.new_saved(*tok.shape), plan.new_grads()
+        result, pullback = vjp(fn, *ins)
+        grads = pullback(douts)
+        if baseline_grads is not None:
+            recursive_check(self, grads, baseline_grads, "Reverse")
+        if len(ins) == 4:
+            x, weights, kc, vc = ins
+            plan = route._ensure(weights, True)
 
-        def reverse():
-            # revprimal: the primal result is produced along with the gradients
+            def reverse():  # primal and cotangents: token_vjp returns the hidden state along with them
+                plan.token_vjp(x, kc, vc, douts)
+
+            reverse_noprim = reverse  # one fused call either way: the primal costs nothing extra to return
+        else:
+            tokens, weights = ins
+            plan = route._ensure(weights, True)
+            tok = tokens.to(plan.device, torch.int32).contiguous()
+            dlog = douts.to(plan.device, torch.float32).contiguous()
+            saved, packed = plan.new_saved(*tok.shape), plan.new_grads()
+
+            def reverse():
+                # revprimal: the primal result is produced along with the gradients
+                plan.forward(tok, saved=saved)
+                plan.backward(tok, dlog, saved, packed)
+
+            def reverse_noprim():
+                plan.backward(tok, dlog, saved, packed)
+
             plan.forward(tok, saved=saved)
-            plan.backward(tok, dlog, saved, grads)
-
-        def reverse_noprim():
-            plan.backward(tok, dlog, saved, grads)
-
-        plan.forward(tok, saved=saved)
         call = reverse if self.revprimal else reverse_noprim
         for key in REVERSE_KEYS:
             out[key] = self._avg_seconds(call)
@@ -120,4 +175,10 @@ class EnzymeJaxTest:
 
 class Llama(EnzymeJaxTest):
     """The reference's ``test/llama.py`` class name, so that the default output
-    file is ``results_Llama.csv`` as there (``test/test_utils.py:600-601``)."""
+    file is ``results_Llama.csv`` as there (``test/test_utils.py:600-601``), with
+    that test's settings (``revprimal = False``, ``atol = rtol = 1e-3``,
+    test/llama.py:311-319)."""
+
+    def __init__(self, repeat: int = 50, warmup: int = 3):
+        super().__init__(repeat, warmup)
+        self.revprimal = False

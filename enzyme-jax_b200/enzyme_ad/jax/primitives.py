@@ -7,9 +7,13 @@ Mirrors the names of the reference's ``enzyme_ad.jax`` package
 decorated function takes and returns torch CUDA tensors; under JAX the same
 routing sits behind ``jax.ffi.ffi_call`` and ``jax.custom_vjp``.
 
-Only the llama path is implemented.  A function decorated with
-``enzyme_jax_ir(pipeline_options=B200Pipeline(config))`` is recognised by its
-arguments:
+Only the llama path is implemented.  ``B200Pipeline(config)`` is the caller's
+declaration that the decorated function IS the llama forward of that config; the
+decorator then holds the call to it: the function must accept the arguments it
+is called with (``inspect.signature``), the weight dict must have exactly the
+reference's leaves with the shapes the config implies (test/llama.py:270-282),
+and the other arguments the shapes of test/llama.py:288-301.  Anything else
+raises instead of silently computing llama.  Two call shapes exist:
 
 * ``fn(x, weights, key_cache, value_cache)`` -- the reference's own call
   (``test/llama.py:35``, ``:288-292``): one fp32 residual vector ``[dim]`` and
@@ -23,6 +27,7 @@ Everything else of the reference's surface (MLIR pipelines, ``cpp_call``,
 from __future__ import annotations
 
 import functools
+import inspect
 from typing import Callable, Dict, Optional, Tuple
 
 import torch
@@ -129,6 +134,44 @@ optimization_passes = _unsupported("optimization_passes")
 full_optimization_pass_pipeline = _unsupported("full_optimization_pass_pipeline")
 
 
+def reference_weight_shapes(config: Dict[str, int]) -> Dict[str, Tuple[int, ...]]:
+    """Leaf names and shapes of the reference's weight dict (test/llama.py:270-282; the projections are used as
+    [out, in], :149-157, and kv_dim == dim because n_kv_heads == n_heads)."""
+    L, d, h, V = config["n_layers"], config["dim"], config["hidden_dim"], config["vocab_size"]
+    return {"rms_att_weight": (L, d), "rms_ffn_weight": (L, d), "rms_final_weight": (d,), "w1": (L, h, d),
+            "w2": (L, d, h), "w3": (L, h, d), "wcls": (V, d), "wk": (L, d, d), "wo": (L, d, d), "wq": (L, d, d),
+            "wv": (L, d, d)}
+
+
+def check_weights(weights, config: Dict[str, int], need_embedding: bool) -> None:
+    """Raises unless ``weights`` is the reference's weight dict for ``config`` (plus ``token_embedding_table``
+    [vocab, dim] for the token call shape)."""
+    if not isinstance(weights, dict):
+        raise TypeError("weights must be the reference's dict of weight leaves")
+    want = reference_weight_shapes(config)
+    if need_embedding:
+        want["token_embedding_table"] = (config["vocab_size"], config["dim"])
+    extra = sorted(set(weights) - set(want) - {"token_embedding_table"})
+    missing = sorted(set(want) - set(weights))
+    if extra or missing:
+        raise ValueError(f"not the llama weight dict: missing leaves {missing}, unknown leaves {extra}")
+    for name, shape in want.items():
+        if tuple(weights[name].shape) != shape:
+            raise ValueError(f"leaf {name} has shape {tuple(weights[name].shape)}, the config implies {shape}")
+
+
+def _bind_or_raise(func: Callable, args) -> None:
+    """The decorated function must accept the call: the decorator replaces its body, not its signature."""
+    try:
+        sig = inspect.signature(func)
+    except (TypeError, ValueError):
+        return  # builtins and the like carry no signature
+    try:
+        sig.bind(*args)
+    except TypeError as exc:
+        raise TypeError(f"{getattr(func, '__name__', 'function')} cannot be called with {len(args)} arguments: {exc}") from exc
+
+
 class _LlamaRoute:
     """One plan per (device, weight identity): packs the weights on first use."""
 
@@ -156,7 +199,22 @@ class _LlamaRoute:
         return self.plan
 
     # fn(x, weights, key_cache, value_cache) -> hidden [dim]
+    def check_token_call(self, x, weights, key_cache, value_cache):
+        cfg = self.pipe.config
+        check_weights(weights, cfg, need_embedding=False)
+        L, d = cfg["n_layers"], cfg["dim"]
+        if tuple(x.shape) != (d,) or not x.dtype.is_floating_point:
+            raise ValueError(f"x must be a floating-point vector [{d}] (test/llama.py:288), got {tuple(x.shape)} {x.dtype}")
+        for name, c in (("key_cache", key_cache), ("value_cache", value_cache)):
+            if c.dim() != 3 or c.shape[0] != L or c.shape[2] != d:
+                raise ValueError(f"{name} must be [{L}, pos, {d}] (test/llama.py:299-301), got {tuple(c.shape)}")
+        if key_cache.shape != value_cache.shape:
+            raise ValueError("key_cache and value_cache must have the same shape")
+        if key_cache.shape[1] >= cfg["seq_len"]:
+            raise ValueError(f"a cache of {key_cache.shape[1]} rows leaves no position below seq_len={cfg['seq_len']}")
+
     def decode_hidden(self, x, weights, key_cache, value_cache):
+        self.check_token_call(x, weights, key_cache, value_cache)
         plan = self._ensure(weights, False)
         cfg = self.pipe.config
         L, pos = key_cache.shape[0], key_cache.shape[1]
@@ -174,7 +232,16 @@ class _LlamaRoute:
         return hidden[0]
 
     # fn(tokens, weights) -> logits
+    def check_sequence_call(self, tokens, weights):
+        cfg = self.pipe.config
+        check_weights(weights, cfg, need_embedding=True)
+        if tokens.dim() != 2 or tokens.dtype.is_floating_point:
+            raise ValueError(f"tokens must be integers [batch, seq], got {tuple(tokens.shape)} {tokens.dtype}")
+        if tokens.shape[1] > cfg["seq_len"]:
+            raise ValueError(f"{tokens.shape[1]} positions exceed seq_len={cfg['seq_len']}")
+
     def forward_logits(self, tokens, weights, saved=None):
+        self.check_sequence_call(tokens, weights)
         plan = self._ensure(weights, saved is not None)
         return plan.forward(tokens.to(plan.device, torch.int32).contiguous(), saved=saved)
 
@@ -193,9 +260,10 @@ def enzyme_jax_ir(argv=(), pipeline_options=None, jit_options=None, inner_jit=Tr
         def wrapped(*args, **kwargs):
             if kwargs:
                 raise NotImplementedError("keyword arguments are not part of the llama call shapes")
+            _bind_or_raise(func, args)
             if len(args) == 4 and isinstance(args[1], dict):
                 return route.decode_hidden(*args)
-            if len(args) == 2 and isinstance(args[1], dict) and not args[0].dtype.is_floating_point:
+            if len(args) == 2 and isinstance(args[1], dict):
                 return route.forward_logits(*args)
             raise NotImplementedError(
                 "unrecognised call: expected (x, weights, key_cache, value_cache) or (tokens, weights)")
@@ -206,22 +274,83 @@ def enzyme_jax_ir(argv=(), pipeline_options=None, jit_options=None, inner_jit=Tr
     return decorator
 
 
-def vjp(fn: Callable, tokens: torch.Tensor, weights: Dict[str, torch.Tensor]) -> Tuple[torch.Tensor, Callable]:
-    """``jax.vjp``-shaped helper for a decorated ``fn(tokens, weights)``: returns the
-    logits and a function mapping a logits cotangent to the dict of weight
-    gradients (what the reference's ``enzyme_vjp`` rule yields for the weight
-    arguments, primitives.py:1381-1469)."""
+def vjp(fn: Callable, *primals):
+    """``jax.vjp``-shaped helper for a decorated llama function: ``out, pullback = vjp(fn, *primals)``;
+    ``pullback(cotangent)`` returns one cotangent per primal, as ``jax.vjp`` does through the reference's
+    ``enzyme_vjp`` rule (primitives.py:1381-1469).
+
+    * ``vjp(fn, x, weights, key_cache, value_cache)`` -- the reference's differentiated call (test/llama.py:315-317,
+      test/test_utils.py:505-514): ``out`` is the hidden state ``[dim]``, the pullback maps ``d_hidden`` to
+      ``(dx, dweights, d_key_cache, d_value_cache)``.  ``dweights`` has the keys of ``weights``; ``wcls`` comes out
+      identically zero -- the function does not use it, and the reference likewise emits zeros for arguments JAX
+      drops as dead (primitives.py:733-744, :1550-1569).
+    * ``vjp(fn, tokens, weights)`` -- the sequence form: ``out`` is the logits, the pullback maps ``dlogits`` to
+      ``(None, dweights)`` (integer tokens carry no cotangent)."""
     route: _LlamaRoute = getattr(fn, "_b200_route", None)
     if route is None:
         raise NotImplementedError("vjp needs a function decorated with enzyme_jax_ir(pipeline_options=B200Pipeline(...))")
+    if len(primals) == 4:
+        x, weights, key_cache, value_cache = primals
+        route.check_token_call(x, weights, key_cache, value_cache)
+        plan = route._ensure(weights, True)
+        out = route.decode_hidden(x, weights, key_cache, value_cache)
+
+        def pullback_token(d_hidden: torch.Tensor):
+            _, dx, packed, dkc, dvc = plan.token_vjp(x, key_cache, value_cache, d_hidden)
+            leaves = plan.unpack_grads(packed)
+            return dx, {k: leaves[k] for k in weights}, dkc, dvc
+
+        return out, pullback_token
+    if len(primals) != 2:
+        raise NotImplementedError("vjp takes (fn, x, weights, key_cache, value_cache) or (fn, tokens, weights)")
+    tokens, weights = primals
+    route.check_sequence_call(tokens, weights)
     plan = route._ensure(weights, True)
     tok = tokens.to(plan.device, torch.int32).contiguous()
     saved = plan.new_saved(*tok.shape)
     logits = plan.forward(tok, saved=saved)
 
-    def pullback(dlogits: torch.Tensor) -> Dict[str, torch.Tensor]:
+    def pullback(dlogits: torch.Tensor):
         grads = plan.backward(tok, dlogits.to(plan.device, torch.float32).contiguous(), saved, plan.new_grads())
         leaves = plan.unpack_grads(grads)
-        return {k: leaves[k] for k in weights}
+        return None, {k: leaves[k] for k in weights}
 
     return logits, pullback
+
+
+FFI_TARGETS = ("enzymejax_b200_llama_pack", "enzymejax_b200_llama_fwd", "enzymejax_b200_llama_fwd_saved",
+               "enzymejax_b200_llama_bwd", "enzymejax_b200_llama_unpack_grads", "enzymejax_b200_llama_decode_step")
+
+
+def register_ffi_targets(jax_ffi=None) -> Tuple[str, ...]:
+    """Registers the library's XLA typed-FFI handlers with JAX, once per process, the way the reference registers its
+    own at import (primitives.py:32-40): every handler address from ``b200_ffi_handler`` is wrapped in a PyCapsule
+    named ``xla._CUSTOM_CALL_TARGET`` and passed to ``jax.ffi.register_ffi_target(name, capsule, platform="CUDA")``.
+    ``jax_ffi`` defaults to ``jax.ffi``.  Raises ``NotImplementedError`` where JAX is missing or the library was built
+    without the XLA FFI headers."""
+    import ctypes
+    lib = _B.lib()
+    if jax_ffi is None:
+        try:
+            import jax.ffi as jax_ffi  # type: ignore
+        except Exception as exc:  # no JAX in this environment
+            raise NotImplementedError(f"jax.ffi is not importable here ({exc}); the handlers cannot be registered") from exc
+    if not lib.b200_ffi_available():
+        raise NotImplementedError("the library was built without the XLA FFI headers (xla/ffi/api/ffi.h); rebuild it "
+                                  "where jaxlib is installed")
+    global _FFI_REGISTERED
+    if _FFI_REGISTERED:
+        return FFI_TARGETS
+    capsule_new = ctypes.pythonapi.PyCapsule_New
+    capsule_new.restype = ctypes.py_object
+    capsule_new.argtypes = [ctypes.c_void_p, ctypes.c_char_p, ctypes.c_void_p]
+    for name in FFI_TARGETS:
+        addr = lib.b200_ffi_handler(name.encode())
+        if not addr:
+            raise NotImplementedError(f"the library has no handler named {name}")
+        jax_ffi.register_ffi_target(name, capsule_new(addr, b"xla._CUSTOM_CALL_TARGET", None), platform="CUDA")
+    _FFI_REGISTERED = True
+    return FFI_TARGETS
+
+
+_FFI_REGISTERED = False

@@ -326,9 +326,43 @@ B200_API int32_t b200_comm_init_rank(const void* id128, int32_t rank, int32_t wo
  * slower peer is still reading.  A rank that leaves without calling it must not free that memory some other way
  * while its peers still run kernels of this library. */
 B200_API int32_t b200_comm_destroy(void* comm);
-/* *enabled = 1 when the ranks of the communicator exchange the tensor-parallel partial sums through
- * peer-mapped memory (CUDA IPC over NVLink) instead of NCCL. */
+/* *enabled = 0 when the tensor-parallel partial sums travel through NCCL, 1 when the ranks exchange them through
+ * peer-mapped memory over NVLink with plain loads and stores, 2 when that memory is also bound to a multicast
+ * object and the exchange reduces inside the NVLink switch (multimem). */
 B200_API int32_t b200_comm_peer_memory(void* comm, int32_t* enabled);
+
+/* b200_comm_init_rank with own_peer_memory = 0 creates the communicator without its own exchange buffers, for a
+ * caller that brings them with b200_comm_attach_memory; b200_comm_setup_peer_memory (collective) creates the
+ * library's own (CUDA IPC) afterwards, e.g. when the attach was refused. */
+B200_API int32_t b200_comm_init_rank_ex(const void* id128, int32_t rank, int32_t world, int32_t own_peer_memory,
+                                        void** comm);
+B200_API int32_t b200_comm_setup_peer_memory(void* comm);
+
+/* Hands the communicator exchange memory the CALLER owns: `bytes` (a multiple of 256, at least 8 MiB + 4 KiB) of
+ * device memory on every rank, of which peer_ptrs[r] is rank r's block as mapped into this process
+ * (peer_ptrs[rank] is this rank's own), and multicast_ptr the address of a multicast mapping of the same blocks
+ * (cuMulticastCreate / cuMulticastBindMem; NULL when there is none).  Collective: every rank calls it with its own
+ * view, before the communicator is used by a plan.  The last 4 KiB of the block hold the flag words and are cleared
+ * here.  The library never frees this memory; the caller keeps it alive until after b200_comm_destroy.  Returns
+ * B200_ERR_UNSUPPORTED on every rank when some rank could not attach (the communicator then still has no exchange
+ * memory).  With a multicast address the tensor-parallel exchange of the prefill sums inside the NVLink switch
+ * (multimem.ld_reduce / multimem.st): 1/world of the bytes cross each link.
+ * The reference has no counterpart (it has no multi-GPU runtime); symmetric-memory allocators (for example
+ * torch.distributed's, which the Python host of this library uses) provide such blocks. */
+B200_API int32_t b200_comm_attach_memory(void* comm, size_t bytes, const void* const* peer_ptrs, void* multicast_ptr);
+
+/* The exchange of the tensor-parallel prefill as a single kernel (unit-testable piece of the path).  Every rank owns
+ * rows_total / world consecutive rows of the fp32 residual stream (x_own, [rows_total / world, dim]).
+ * b200_tp_exchange_buffers gives the two regions of this rank's exchange memory: `part`, where the rank leaves its
+ * partial product [rows_total, dim] of `dtype` (what the row-parallel Wo / W2 projection writes), and `gathered`,
+ * where the normed rows of ALL ranks arrive.  b200_tp_reduce_norm (collective, same arguments on every rank) then,
+ * for this rank's rows: x_own += sum over ranks of part (skipped when reduce == 0), and gain * x_own * rsqrt(mean
+ * x_own^2 + eps) goes to `gathered` on every rank; when the call's kernel has completed, this rank's `gathered`
+ * holds all rows_total rows.  It stands for test/llama.py:211-219 (`x += wo @ ...` followed by rmsnorm) under the
+ * Megatron split, where the reference has no multi-GPU code. */
+B200_API int32_t b200_tp_exchange_buffers(void* comm, size_t bytes_each, void** part, void** gathered);
+B200_API int32_t b200_tp_reduce_norm(void* comm, int32_t rows_total, int32_t dim, int32_t dtype, int32_t reduce,
+                                     float* x_own, const float* gain, float eps, b200_stream_t stream);
 
 /* ---- XLA FFI registration -------------------------------------------------- */
 

@@ -21,7 +21,7 @@ def main():
     rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
     torch.cuda.set_device(local)
     dist.init_process_group("nccl", device_id=torch.device("cuda", local))
-    comm = B.Comm(rank, world)
+    comm = B.Comm(rank, world, symmetric=os.environ.get("B200_TEST_SYMM", "1") == "1")
     if rank == 0:
         print("PEER_MEMORY", comm.peer_memory())
     cfg = dict(dim=256, hidden_dim=512, n_layers=2, n_heads=4, n_kv_heads=4, vocab_size=1024, seq_len=160)

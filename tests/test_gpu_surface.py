@@ -48,7 +48,8 @@ def test_vjp_helper_and_unsupported_entries():
     wd = {k: v.cuda() for k, v in w.items()}
     logits, pull = EJ.vjp(model, tokens, wd)
     assert torch.allclose(logits.double().cpu(), ref_logits, rtol=1e-4, atol=1e-5)
-    grads = pull(dl)
+    no_token_cotangent, grads = pull(dl)
+    assert no_token_cotangent is None
     for k, r in ref.items():
         assert float((grads[k].double().cpu() - r).abs().max() / r.abs().max()) < 1e-4, k
     with pytest.raises(NotImplementedError):
@@ -72,7 +73,11 @@ def test_harness_rows_and_csv(tmp_path, monkeypatch):
         raise AssertionError
 
     h = Llama(repeat=5, warmup=1)
-    times = h.harness("llama", model, (tokens, w), dl)
+    h.revprimal = True
+    ref_logits, ref = O.vjp_sequence(tokens, cfg, {k: v.double().cpu() for k, v in w.items()}, dl.double())
+    # bf16 model against the fp64 oracle on the same bf16 weights: 2e-2 of the largest logit
+    h.atol, h.rtol = 2e-2 * float(ref_logits.abs().max()), 2e-2
+    times = h.harness("llama", model, (tokens, w), dl, baseline_primal=ref_logits)
     assert list(times) == ["Primal", "PreRev", "PostRev", "BothRev"]
     assert all(0 < t < 1 for t in times.values())
     assert times["BothRev"] > times["Primal"]  # reverse rows include the primal (revprimal)
@@ -124,3 +129,48 @@ def test_token_vjp_all_inputs_matches_oracle(pos, zero_cache):
             close(leaves[k], r, k)
     assert float(leaves["token_embedding_table"].abs().max()) == 0.0
     p.close()
+
+
+def test_harness_reference_call_all_input_gradients_checked_against_oracle(tmp_path, monkeypatch):
+    """The reference's test end to end: fn(x, weights, key_cache, value_cache) with pos = 1 zero caches, Primal and the
+    three reverse rows, gradients with respect to all four inputs, results checked leaf by leaf (recursive_check) at
+    the reference's own tolerance (atol = rtol = 1e-3, test/llama.py:318-319); a wrong baseline must be caught."""
+    import enzyme_ad.jax as EJ
+    from enzyme_ad.jax.harness import Llama, recursive_check
+    cfg = O.CONFIGS["c1"]
+    L, d = cfg["n_layers"], cfg["dim"]
+    w = O.make_weights(cfg, 17, torch.float32, std=0.05, gains_one=False)
+    w.pop("token_embedding_table")
+    g = torch.Generator().manual_seed(18)
+    x, dx = torch.randn(d, generator=g), torch.randn(d, generator=g)
+    kc, vc = torch.zeros(L, 1, d), torch.zeros(L, 1, d)
+
+    @EJ.enzyme_jax_ir(pipeline_options=EJ.B200Pipeline(cfg, torch.float32))
+    def forward(x, weights, key_cache, value_cache):
+        raise AssertionError("the body is never traced here")
+
+    wfull = dict(w, token_embedding_table=torch.zeros(cfg["vocab_size"], d))
+    hidden, rdx, rgrads, rdk, rdv = O.vjp_token(x.double(), cfg, {k: v.double() for k, v in wfull.items()}, kc.double(),
+                                                vc.double(), dx.double())
+    wd = {k: v.cuda() for k, v in w.items()}
+    h = Llama(repeat=3, warmup=1)
+    assert h.revprimal is False and h.atol == 1e-3   # the reference's settings for this test
+    times = h.harness("llama", forward, (x, wd, kc, vc), dx, baseline_primal=hidden,
+                      baseline_grads=(rdx, {k: rgrads[k] for k in wd}, rdk, rdv))
+    assert list(times) == ["Primal", "PreRev", "PostRev", "BothRev"]
+    bad = hidden.clone()
+    bad[3] += 1.0
+    with pytest.raises(AssertionError):
+        recursive_check(h, forward(x, wd, kc, vc), bad, "Primal")
+    # a function that cannot take the call, or a weight dict that is not llama's, is refused
+    @EJ.enzyme_jax_ir(pipeline_options=EJ.B200Pipeline(cfg, torch.float32))
+    def two_args(a, b):
+        raise AssertionError
+    with pytest.raises(TypeError):
+        two_args(x, wd, kc, vc)
+    with pytest.raises(ValueError):
+        forward(x, dict(wd, extra_leaf=torch.zeros(1)), kc, vc)
+    with pytest.raises(ValueError):
+        forward(x, {k: v for k, v in wd.items() if k != "wq"}, kc, vc)
+    with pytest.raises(ValueError):
+        forward(x, dict(wd, wq=wd["wq"][:, :10]), kc, vc)
