@@ -4,7 +4,9 @@
 //
 // A CTA owns 128 query rows of one (batch, head) and walks the key/value blocks
 // of 128 rows it may attend to.  Warp roles:
-//   warp 0      TMA producer: Q once, then K_j / V_j into a 2-stage ring
+//   warp 0      TMA producer: Q once, then K_j and V_j into two 2-stage rings of their own: a K stage is
+//               free as soon as S_j is complete (its only reader), a V stage when O += P_j V_j is, so K runs a
+//               whole block ahead and S_{j+1} never waits for its operand
 //   warp 1      one lane issues tcgen05.mma:  S = Q K_j^T  (fp32, TMEM columns
 //               0..127) and, once the probabilities are in shared memory,
 //               O += P_j V_j (TMEM columns 128..128+hs, accumulated over all
@@ -61,7 +63,7 @@ template <int HS> struct ACfg {
   static constexpr int kVOff = kKOff + kStages * kTileBytes;
   static constexpr int kPOff = kVOff + kStages * kTileBytes;
   static constexpr int kBarOff = kPOff + kPBufs * kPBytes;
-  static constexpr int kSmemBytes = kBarOff + 128;      // hs = 64: 114,816 B, two CTAs fit the 228 KB of an SM; hs = 128: 229,504 B
+  static constexpr int kSmemBytes = kBarOff + 160;      // hs = 64: 114,816 B, two CTAs fit the 228 KB of an SM; hs = 128: 229,504 B
   static constexpr int kTmemCols = 256;
   static constexpr int kOCol = 128;
 };
@@ -146,13 +148,15 @@ __global__ void __launch_bounds__(A_THREADS, HS == 64 ? 2 : 1)
   extern __shared__ __align__(1024) uint8_t smem[];
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::kBarOff);
   uint64_t* q_full = bars;          // Q landed
-  uint64_t* kv_full = bars + 1;     // [2] K_j and V_j landed
-  uint64_t* kv_empty = bars + 3;    // [2] both MMAs of block j are done with the stage
-  uint64_t* s_full = bars + 5;      // S_j complete in TMEM
-  uint64_t* s_empty = bars + 6;     // softmax has read S_j
-  uint64_t* p_full = bars + 7;      // [2] P_j is in its shared-memory buffer
-  uint64_t* o_full = bars + 9;      // [2] O += P_j V_j complete in TMEM (P's buffer and the stage are free)
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 11);  // 11 barriers + 2 words = 96 bytes
+  uint64_t* k_full = bars + 1;      // [2] K_j landed
+  uint64_t* v_full = bars + 3;      // [2] V_j landed
+  uint64_t* k_empty = bars + 5;     // [2] S_j is complete: its K stage is free
+  uint64_t* v_empty = bars + 7;     // [2] O += P_j V_j is complete: its V stage is free
+  uint64_t* s_full = bars + 9;      // S_j complete in TMEM
+  uint64_t* s_empty = bars + 10;    // softmax has read S_j
+  uint64_t* p_full = bars + 11;     // [2] P_j is in its shared-memory buffer
+  uint64_t* o_full = bars + 13;     // [2] O += P_j V_j complete in TMEM (P's buffer is free)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 15);  // 15 barriers + 2 words = 128 bytes
   volatile uint32_t* abort_flag = tmem_slot + 1;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -174,8 +178,10 @@ __global__ void __launch_bounds__(A_THREADS, HS == 64 ? 2 : 1)
     }
     ptx::mbar_init(q_full, 1);
     for (int i = 0; i < 2; ++i) {
-      ptx::mbar_init(&kv_full[i], 1);
-      ptx::mbar_init(&kv_empty[i], 1);
+      ptx::mbar_init(&k_full[i], 1);
+      ptx::mbar_init(&v_full[i], 1);
+      ptx::mbar_init(&k_empty[i], 1);
+      ptx::mbar_init(&v_empty[i], 1);
       ptx::mbar_init(&p_full[i], 256);
       ptx::mbar_init(&o_full[i], 1);
     }
@@ -208,14 +214,18 @@ __global__ void __launch_bounds__(A_THREADS, HS == 64 ? 2 : 1)
       for (int j = 0; j < n_blocks && ok; ++j) {
         const int st = j & 1;
         const uint32_t ph = (uint32_t)(j >> 1) & 1u;
-        ok = ptx::mbar_wait(&kv_empty[st], ph ^ 1u, abort_flag, status, ST_ATTN_TIMEOUT);
+        ok = ptx::mbar_wait(&k_empty[st], ph ^ 1u, abort_flag, status, ST_ATTN_TIMEOUT);
         if (!ok) break;
-        ptx::mbar_arrive_expect_tx(&kv_full[st], 2 * C::kTileBytes);
+        ptx::mbar_arrive_expect_tx(&k_full[st], C::kTileBytes);
 #pragma unroll
-        for (int s = 0; s < C::kSubs; ++s) {
-          ptx::tma_load_3d(smem + C::kKOff + st * C::kTileBytes + s * SUB, &tmK, h * HS + 64 * s, j * AK, b, &kv_full[st]);
-          ptx::tma_load_3d(smem + C::kVOff + st * C::kTileBytes + s * SUB, &tmV, h * HS + 64 * s, j * AK, b, &kv_full[st]);
-        }
+        for (int s = 0; s < C::kSubs; ++s)
+          ptx::tma_load_3d(smem + C::kKOff + st * C::kTileBytes + s * SUB, &tmK, h * HS + 64 * s, j * AK, b, &k_full[st]);
+        ok = ptx::mbar_wait(&v_empty[st], ph ^ 1u, abort_flag, status, ST_ATTN_TIMEOUT);
+        if (!ok) break;
+        ptx::mbar_arrive_expect_tx(&v_full[st], C::kTileBytes);
+#pragma unroll
+        for (int s = 0; s < C::kSubs; ++s)
+          ptx::tma_load_3d(smem + C::kVOff + st * C::kTileBytes + s * SUB, &tmV, h * HS + 64 * s, j * AK, b, &v_full[st]);
       }
     }
     __syncwarp();
@@ -240,9 +250,10 @@ __global__ void __launch_bounds__(A_THREADS, HS == 64 ? 2 : 1)
           ptx::mma_bf16_ss(tmem_base, q_desc + off, ka + off, idesc_s, k > 0 ? 1u : 0u);
         }
         ptx::mma_commit(s_full);
+        ptx::mma_commit(&k_empty[st]);
       };
       bool ok = ptx::mbar_wait(q_full, 0, abort_flag, status, ST_ATTN_TIMEOUT) &&
-                ptx::mbar_wait(&kv_full[0], 0, abort_flag, status, ST_ATTN_TIMEOUT);
+                ptx::mbar_wait(&k_full[0], 0, abort_flag, status, ST_ATTN_TIMEOUT);
       if (ok) {
         ptx::tc_fence_after_sync();
         issue_s(0);
@@ -252,13 +263,14 @@ __global__ void __launch_bounds__(A_THREADS, HS == 64 ? 2 : 1)
         const int pb = j % NP;
         if (j + 1 < n_blocks) {
           // scores of the next block, once this block's are in the softmax threads' registers
-          ok = ptx::mbar_wait(&kv_full[st ^ 1], (uint32_t)((j + 1) >> 1) & 1u, abort_flag, status, ST_ATTN_TIMEOUT) &&
+          ok = ptx::mbar_wait(&k_full[st ^ 1], (uint32_t)((j + 1) >> 1) & 1u, abort_flag, status, ST_ATTN_TIMEOUT) &&
                ptx::mbar_wait(s_empty, (uint32_t)j & 1u, abort_flag, status, ST_ATTN_TIMEOUT);
           if (!ok) break;
           ptx::tc_fence_after_sync();
           issue_s(st ^ 1);
         }
-        ok = ptx::mbar_wait(&p_full[pb], (uint32_t)(j / NP) & 1u, abort_flag, status, ST_ATTN_TIMEOUT);
+        ok = ptx::mbar_wait(&v_full[st], (uint32_t)(j >> 1) & 1u, abort_flag, status, ST_ATTN_TIMEOUT) &&
+             ptx::mbar_wait(&p_full[pb], (uint32_t)(j / NP) & 1u, abort_flag, status, ST_ATTN_TIMEOUT);
         if (!ok) break;
         ptx::tc_fence_after_sync();
         const uint64_t va = v_desc + (uint64_t)st * (C::kTileBytes >> 4);
@@ -268,7 +280,7 @@ __global__ void __launch_bounds__(A_THREADS, HS == 64 ? 2 : 1)
           ptx::mma_bf16_ss(tmem_base + C::kOCol, pa + (uint64_t)(((k >> 2) * SUB + (k & 3) * 32) >> 4),
                            va + (uint64_t)(k * (2048 >> 4)), idesc_o, (j > 0 || k > 0) ? 1u : 0u);
         ptx::mma_commit(&o_full[pb]);
-        ptx::mma_commit(&kv_empty[st]);
+        ptx::mma_commit(&v_empty[st]);
       }
     }
     __syncwarp();
@@ -348,16 +360,12 @@ __global__ void __launch_bounds__(A_THREADS, HS == 64 ? 2 : 1)
         ptx::tmem_st_wait();
         ptx::tc_fence_before_sync();
       }
-      if (j >= NP && !(o_waited && NP == 1)) {
-        // this block's P buffer is being read until O += P_{j-NP} V_{j-NP} completes
-        ok = ptx::mbar_wait_warp(&o_full[pbuf], (uint32_t)(j / NP - 1) & 1u, abort_flag, status, ST_ATTN_TIMEOUT);
-        if (!ok) break;
-      }
-      // probabilities against the reference -> bf16 -> shared memory
+      // probabilities against the reference -> bf16 pairs in registers.  The exponentials do not touch P's buffer,
+      // so they run before the wait for the MMA that still reads it.
       float2 rs_a = make_float2(0.f, 0.f), rs_b = make_float2(0.f, 0.f);
       const float2 sl2v = make_float2(sl2, sl2);
       const float2 nm_av = make_float2(-ms_a, -ms_a), nm_bv = make_float2(-ms_b, -ms_b);
-      const uint32_t pw = p_base + (uint32_t)(pbuf * C::kPBytes);
+      uint32_t pk[32];  // pk[2g]: row a, pk[2g + 1]: row b (sv is dead once they are built)
 #pragma unroll
       for (int g = 0; g < 16; ++g) {
         const float2 xa = __ffma2_rn(make_float2(sv[4 * g], sv[4 * g + 1]), sl2v, nm_av);
@@ -367,9 +375,20 @@ __global__ void __launch_bounds__(A_THREADS, HS == 64 ? 2 : 1)
         rs_a = __fadd2_rn(rs_a, pa);
         rs_b = __fadd2_rn(rs_b, pb);
         const __nv_bfloat162 ha = __floats2bfloat162_rn(pa.x, pa.y), hb = __floats2bfloat162_rn(pb.x, pb.y);
+        pk[2 * g] = *reinterpret_cast<const uint32_t*>(&ha);
+        pk[2 * g + 1] = *reinterpret_cast<const uint32_t*>(&hb);
+      }
+      if (j >= NP && !(o_waited && NP == 1)) {
+        // this block's P buffer is being read until O += P_{j-NP} V_{j-NP} completes
+        ok = ptx::mbar_wait_warp(&o_full[pbuf], (uint32_t)(j / NP - 1) & 1u, abort_flag, status, ST_ATTN_TIMEOUT);
+        if (!ok) break;
+      }
+      const uint32_t pw = p_base + (uint32_t)(pbuf * C::kPBytes);
+#pragma unroll
+      for (int g = 0; g < 16; ++g) {
         const uint32_t chunk = (uint32_t)(g >> 3) * (uint32_t)SUB + ((((uint32_t)g & 7u) ^ swz) << 4);
-        st_shared_b32(pw + chunk + pa_off, *reinterpret_cast<const uint32_t*>(&ha));
-        st_shared_b32(pw + chunk + pb_off, *reinterpret_cast<const uint32_t*>(&hb));
+        st_shared_b32(pw + chunk + pa_off, pk[2 * g]);
+        st_shared_b32(pw + chunk + pb_off, pk[2 * g + 1]);
       }
       l_a += rs_a.x + rs_a.y;
       l_b += rs_b.x + rs_b.y;
