@@ -36,7 +36,8 @@ EXPORTS = (
     "b200_attention_backward", "b200_comm_peer_memory", "b200_selftest_bounded_wait", "b200_argmax",
     "b200_selftest_peer_wait", "b200_plan_cached", "b200_ffi_available", "b200_ffi_handler",
     "b200_token_vjp_workspace_bytes", "b200_token_vjp", "b200_comm_init_rank_ex", "b200_comm_setup_peer_memory",
-    "b200_comm_attach_memory", "b200_tp_exchange_buffers", "b200_tp_reduce_norm",
+    "b200_comm_attach_memory", "b200_tp_exchange_buffers", "b200_tp_reduce_norm", "b200_token_forward",
+    "b200_static_sizes",
 )
 
 
@@ -75,6 +76,10 @@ def lib() -> ctypes.CDLL:
         l.b200_plan_cached.argtypes = [POINTER(_Config), c_int32, c_int32, c_void_p, POINTER(c_void_p)]
         l.b200_selftest_peer_wait.argtypes = [ctypes.c_int64, c_void_p, c_void_p]
         l.b200_token_vjp_workspace_bytes.argtypes = [c_void_p, c_int32, POINTER(c_size_t)]
+        l.b200_token_forward.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int32, c_void_p, c_void_p, c_void_p,
+                                         c_size_t, c_void_p]
+        l.b200_static_sizes.argtypes = [POINTER(_Config), c_int32, c_int32, POINTER(c_size_t), POINTER(c_size_t),
+                                        POINTER(c_size_t)]
         l.b200_token_vjp.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int32, c_void_p, c_void_p, c_void_p,
                                      c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_size_t, c_void_p]
         l.b200_launch_count.restype = ctypes.c_int64
@@ -140,6 +145,16 @@ def _dt(dtype: torch.dtype) -> int:
     if dtype == torch.bfloat16:
         return BF16
     raise B200Error(3, f"unsupported dtype {dtype}")
+
+
+def static_sizes(config: Dict[str, int], dtype: torch.dtype = torch.float32, with_transposed: bool = False,
+                 pos: int = 0, rope_theta: float = 10000.0, rms_eps: float = 1e-5) -> Dict[str, int]:
+    """Byte sizes of the packed weights, the packed gradients and the workspace of the reference-shaped call for a
+    model on one GPU, computed without a device (``b200_static_sizes``)."""
+    c = _Config(*[int(config[k]) for k in CONFIG_KEYS], _dt(dtype), rope_theta, rms_eps)
+    a, b, w = c_size_t(0), c_size_t(0), c_size_t(0)
+    check(lib().b200_static_sizes(byref(c), int(with_transposed), pos, byref(a), byref(b), byref(w)))
+    return {"packed_bytes": a.value, "grad_bytes": b.value, "token_workspace_bytes": w.value}
 
 
 def device_status() -> int:
@@ -562,6 +577,25 @@ class Plan:
         arr = (c_void_p * len(LEAF_ORDER))(*[out[k].data_ptr() for k in LEAF_ORDER])
         check(lib().b200_unpack_grads(self._h, grads.data_ptr(), arr, _stream()))
         return out
+
+    def token_forward(self, x: torch.Tensor, key_cache: torch.Tensor, value_cache: torch.Tensor) -> torch.Tensor:
+        """The reference's call over flat caches: ``forward(x, weights, key_cache, value_cache) -> hidden`` with
+        ``x`` fp32 [d] and caches [L, pos, d]."""
+        L, d = self.config["n_layers"], self.config["dim"]
+        pos = int(key_cache.shape[1])
+        if tuple(key_cache.shape) != (L, pos, d) or tuple(value_cache.shape) != (L, pos, d):
+            raise B200Error(2, f"caches must be [{L}, pos, {d}], got {tuple(key_cache.shape)} and {tuple(value_cache.shape)}")
+        dev = self.device
+        xin = x.to(dev, torch.float32).reshape(d).contiguous()
+        kc = key_cache.to(dev, self.dtype).contiguous()
+        vc = value_cache.to(dev, self.dtype).contiguous()
+        hidden = torch.empty(d, dtype=torch.float32, device=dev)
+        need = self._bytes(lib().b200_token_vjp_workspace_bytes, pos)
+        ws = torch.empty(need, dtype=torch.uint8, device=dev)
+        check(lib().b200_token_forward(self._h, xin.data_ptr(), kc.data_ptr() if pos else None,
+                                       vc.data_ptr() if pos else None, pos, self.packed.data_ptr(), hidden.data_ptr(),
+                                       ws.data_ptr(), ws.numel(), _stream()))
+        return hidden
 
     def token_vjp(self, x: torch.Tensor, key_cache: torch.Tensor, value_cache: torch.Tensor, d_hidden: torch.Tensor):
         """Reverse mode of the reference's own call ``forward(x, weights, key_cache, value_cache) -> hidden`` with

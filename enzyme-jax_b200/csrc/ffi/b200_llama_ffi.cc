@@ -268,6 +268,64 @@ const XLA_FFI_Api* b200_xla_api() {
   return api;
 }
 
+// ---- the reference's own call over flat caches [L, pos, d] ---------------------------------------------
+ffi::Error TokenFwdImpl(cudaStream_t stream, B200_MODEL_ATTRS, ffi::AnyBuffer x, ffi::AnyBuffer packed,
+                        ffi::AnyBuffer key_cache, ffi::AnyBuffer value_cache, ffi::Result<ffi::AnyBuffer> hidden,
+                        ffi::Result<ffi::AnyBuffer> workspace) {
+  B200Plan* plan = nullptr;
+  if (ffi::Error e = plan_for(B200_MODEL_ATTRS_PACK, &plan); e.failure()) return e;
+  const auto kd = key_cache.dimensions();
+  if (kd.size() != 3 || x.element_type() != ffi::DataType::F32)
+    return ffi::Error::InvalidArgument("b200_llama token_fwd: x f32[dim], caches [n_layers, pos, dim]");
+  B200_FFI_TRY(b200_token_forward(plan, static_cast<const float*>(x.untyped_data()), key_cache.untyped_data(),
+                                  value_cache.untyped_data(), (int32_t)kd[1], packed.untyped_data(),
+                                  static_cast<float*>(hidden->untyped_data()), workspace->untyped_data(),
+                                  workspace->size_bytes(), stream));
+  return ffi::Error::Success();
+}
+XLA_FFI_DEFINE_HANDLER_SYMBOL(B200LlamaTokenFwd, TokenFwdImpl,
+                              B200_BIND_MODEL_ATTRS(ffi::Ffi::Bind().Ctx<ffi::PlatformStream<cudaStream_t>>())
+                                  .Arg<ffi::AnyBuffer>()
+                                  .Arg<ffi::AnyBuffer>()
+                                  .Arg<ffi::AnyBuffer>()
+                                  .Arg<ffi::AnyBuffer>()
+                                  .Ret<ffi::AnyBuffer>()
+                                  .Ret<ffi::AnyBuffer>());
+
+ffi::Error TokenVjpImpl(cudaStream_t stream, B200_MODEL_ATTRS, ffi::AnyBuffer x, ffi::AnyBuffer packed,
+                        ffi::AnyBuffer key_cache, ffi::AnyBuffer value_cache, ffi::AnyBuffer d_hidden,
+                        ffi::Result<ffi::AnyBuffer> hidden, ffi::Result<ffi::AnyBuffer> dx,
+                        ffi::Result<ffi::AnyBuffer> grads, ffi::Result<ffi::AnyBuffer> d_key_cache,
+                        ffi::Result<ffi::AnyBuffer> d_value_cache, ffi::Result<ffi::AnyBuffer> workspace) {
+  B200Plan* plan = nullptr;
+  if (ffi::Error e = plan_for(B200_MODEL_ATTRS_PACK, &plan); e.failure()) return e;
+  const auto kd = key_cache.dimensions();
+  if (kd.size() != 3 || x.element_type() != ffi::DataType::F32 || d_hidden.element_type() != ffi::DataType::F32)
+    return ffi::Error::InvalidArgument("b200_llama token_vjp: x and d_hidden f32[dim], caches [n_layers, pos, dim]");
+  B200_FFI_TRY(b200_token_vjp(plan, static_cast<const float*>(x.untyped_data()), key_cache.untyped_data(),
+                              value_cache.untyped_data(), (int32_t)kd[1], packed.untyped_data(),
+                              static_cast<const float*>(d_hidden.untyped_data()),
+                              static_cast<float*>(hidden->untyped_data()), static_cast<float*>(dx->untyped_data()),
+                              static_cast<float*>(grads->untyped_data()),
+                              static_cast<float*>(d_key_cache->untyped_data()),
+                              static_cast<float*>(d_value_cache->untyped_data()), workspace->untyped_data(),
+                              workspace->size_bytes(), stream));
+  return ffi::Error::Success();
+}
+XLA_FFI_DEFINE_HANDLER_SYMBOL(B200LlamaTokenVjp, TokenVjpImpl,
+                              B200_BIND_MODEL_ATTRS(ffi::Ffi::Bind().Ctx<ffi::PlatformStream<cudaStream_t>>())
+                                  .Arg<ffi::AnyBuffer>()
+                                  .Arg<ffi::AnyBuffer>()
+                                  .Arg<ffi::AnyBuffer>()
+                                  .Arg<ffi::AnyBuffer>()
+                                  .Arg<ffi::AnyBuffer>()
+                                  .Ret<ffi::AnyBuffer>()
+                                  .Ret<ffi::AnyBuffer>()
+                                  .Ret<ffi::AnyBuffer>()
+                                  .Ret<ffi::AnyBuffer>()
+                                  .Ret<ffi::AnyBuffer>()
+                                  .Ret<ffi::AnyBuffer>());
+
 struct Target { const char* name; XLA_FFI_Handler* handler; };
 const Target kTargets[] = {
     {"enzymejax_b200_llama_pack", B200LlamaPack},
@@ -276,6 +334,8 @@ const Target kTargets[] = {
     {"enzymejax_b200_llama_bwd", B200LlamaBwd},
     {"enzymejax_b200_llama_unpack_grads", B200LlamaUnpackGrads},
     {"enzymejax_b200_llama_decode_step", B200LlamaDecodeStep},
+    {"enzymejax_b200_llama_token_fwd", B200LlamaTokenFwd},
+    {"enzymejax_b200_llama_token_vjp", B200LlamaTokenVjp},
 };
 
 }  // namespace
@@ -305,6 +365,8 @@ int32_t registerEnzymeJaXB200FFI(void) {
     XLA_FFI_REGISTER_HANDLER(b200_xla_api(), "enzymejax_b200_llama_bwd", "CUDA", B200LlamaBwd);
     XLA_FFI_REGISTER_HANDLER(b200_xla_api(), "enzymejax_b200_llama_unpack_grads", "CUDA", B200LlamaUnpackGrads);
     XLA_FFI_REGISTER_HANDLER(b200_xla_api(), "enzymejax_b200_llama_decode_step", "CUDA", B200LlamaDecodeStep);
+    XLA_FFI_REGISTER_HANDLER(b200_xla_api(), "enzymejax_b200_llama_token_fwd", "CUDA", B200LlamaTokenFwd);
+    XLA_FFI_REGISTER_HANDLER(b200_xla_api(), "enzymejax_b200_llama_token_vjp", "CUDA", B200LlamaTokenVjp);
     result = B200_OK;
   });
   return result;

@@ -101,25 +101,17 @@ size_t token_vjp_workspace_bytes(const B200Plan& p, int pos) {
   return a.used;
 }
 
-int32_t token_vjp_impl(B200Plan* p, const float* x, const void* key_cache, const void* value_cache, int pos,
-                       const uint8_t* w, const float* d_hidden, float* hidden_out, float* dx_out, float* grads,
-                       float* dkc, float* dvc, void* ws, size_t ws_bytes, cudaStream_t stream) {
+// Forward of the reference call shape, keeping in `t` what the backward needs.  `hidden` receives the final-normed
+// hidden state (fp32 [d]).
+static int32_t token_forward_run(B200Plan* p, const TokWs& t, const float* x, const void* key_cache,
+                                 const void* value_cache, int pos, const uint8_t* w, const PackedLayout& wl,
+                                 float* hidden, cudaStream_t stream) {
   const int d = p->d, h = p->h, dt = p->dtype, S = pos + 1;
   const size_t es = p->esize;
-  const PackedLayout& wl = p->wlt;
-  const PackedLayout& gl = p->gl;
-  Arena wa(ws);
-  TokWs t;
-  carve_token(*p, wa, S, &t);
-  if (wa.used > ws_bytes) return fail(B200_ERR_WORKSPACE, "token VJP needs %zu workspace bytes, got %zu", wa.used, ws_bytes);
   const float* g_att = reinterpret_cast<const float*>(w + wl.g_att);
   const float* g_ffn = reinterpret_cast<const float*>(w + wl.g_ffn);
   const float* g_fin = reinterpret_cast<const float*>(w + wl.g_final);
   const float eps = p->cfg.rms_eps;
-  const float* cos_p = p->rope_cos + (size_t)pos * (p->hs / 2);
-  const float* sin_p = p->rope_sin + (size_t)pos * (p->hs / 2);
-
-  // ---- forward, keeping what the backward needs ----
   B200_CUDA_OK(cudaMemcpyAsync(t.layer[0].x_in, x, (size_t)d * 4, cudaMemcpyDeviceToDevice, stream));
   for (int l = 0; l < p->L; ++l) {
     const TokLayer& a = t.layer[l];
@@ -171,9 +163,37 @@ int32_t token_vjp_impl(B200Plan* p, const float* x, const void* key_cache, const
       B200_TRY(gemm_epi(*p, t, a.hg, h, w + o.w2, h, d, h, EPI_RESID, B200_F32, e, stream));
     }
   }
-  // the hidden state the reference returns; when the caller does not want it, the factor 1/rms is still needed
-  float* hidden = hidden_out ? hidden_out : t.dx;
-  B200_TRY(launch_rmsnorm(t.x_last, g_fin, hidden, t.rinv_f, 1, d, eps, B200_F32, stream));
+  return launch_rmsnorm(t.x_last, g_fin, hidden, t.rinv_f, 1, d, eps, B200_F32, stream);
+}
+
+int32_t token_forward_impl(B200Plan* p, const float* x, const void* key_cache, const void* value_cache, int pos,
+                           const uint8_t* w, float* hidden_out, void* ws, size_t ws_bytes, cudaStream_t stream) {
+  Arena wa(ws);
+  TokWs t;
+  carve_token(*p, wa, pos + 1, &t);
+  if (wa.used > ws_bytes) return fail(B200_ERR_WORKSPACE, "token forward needs %zu workspace bytes, got %zu", wa.used, ws_bytes);
+  return token_forward_run(p, t, x, key_cache, value_cache, pos, w, p->wl, hidden_out, stream);
+}
+
+int32_t token_vjp_impl(B200Plan* p, const float* x, const void* key_cache, const void* value_cache, int pos,
+                       const uint8_t* w, const float* d_hidden, float* hidden_out, float* dx_out, float* grads,
+                       float* dkc, float* dvc, void* ws, size_t ws_bytes, cudaStream_t stream) {
+  const int d = p->d, h = p->h, dt = p->dtype, S = pos + 1;
+  const size_t es = p->esize;
+  const PackedLayout& wl = p->wlt;
+  const PackedLayout& gl = p->gl;
+  Arena wa(ws);
+  TokWs t;
+  carve_token(*p, wa, S, &t);
+  if (wa.used > ws_bytes) return fail(B200_ERR_WORKSPACE, "token VJP needs %zu workspace bytes, got %zu", wa.used, ws_bytes);
+  const float* g_att = reinterpret_cast<const float*>(w + wl.g_att);
+  const float* g_ffn = reinterpret_cast<const float*>(w + wl.g_ffn);
+  const float* g_fin = reinterpret_cast<const float*>(w + wl.g_final);
+  const float* cos_p = p->rope_cos + (size_t)pos * (p->hs / 2);
+  const float* sin_p = p->rope_sin + (size_t)pos * (p->hs / 2);
+
+  // ---- forward, keeping what the backward needs; when the caller does not want the hidden state it goes to scratch
+  B200_TRY(token_forward_run(p, t, x, key_cache, value_cache, pos, w, wl, hidden_out ? hidden_out : t.dx, stream));
 
   // ---- backward ----
   uint8_t* g = reinterpret_cast<uint8_t*>(grads);
@@ -244,6 +264,46 @@ int32_t b200_token_vjp_workspace_bytes(const B200Plan* p, int32_t pos, size_t* b
   if (pos < 0 || pos >= p->cfg.seq_len) return fail(B200_ERR_BAD_SHAPE, "pos=%d outside the plan's seq_len=%d", pos, p->cfg.seq_len);
   *bytes = token_vjp_workspace_bytes(*p, pos) + 256;
   return B200_OK;
+}
+
+// Sizes a compiler pass needs before any device exists (the types of the custom call's packed-weight operand and
+// scratch result): the layout arithmetic of the plan without creating one.
+int32_t b200_static_sizes(const B200LlamaConfig* cfg, int32_t with_transposed, int32_t pos, size_t* packed_bytes,
+                          size_t* grad_bytes, size_t* token_workspace_bytes) {
+  if (!cfg) return fail(B200_ERR_INVALID_ARG, "cfg is null");
+  if (cfg->dim <= 0 || cfg->hidden_dim <= 0 || cfg->n_layers <= 0 || cfg->n_heads <= 0 || cfg->vocab_size <= 0 ||
+      cfg->dim % cfg->n_heads || pos < 0)
+    return fail(B200_ERR_BAD_SHAPE, "bad config");
+  B200Plan p;
+  p.cfg = *cfg;
+  p.d = cfg->dim; p.h = cfg->hidden_dim; p.L = cfg->n_layers; p.H = cfg->n_heads; p.hs = cfg->dim / cfg->n_heads;
+  p.V = cfg->vocab_size;
+  p.d_loc = p.d; p.h_loc = p.h; p.V_loc = p.V; p.H_loc = p.H;
+  p.dtype = cfg->dtype;
+  p.esize = cfg->dtype == B200_BF16 ? 2 : 4;
+  PackedLayout wl, gl;
+  build_layout(p, p.esize, with_transposed != 0, &wl);
+  build_layout(p, 4, false, &gl);
+  if (packed_bytes) *packed_bytes = wl.total;
+  if (grad_bytes) *grad_bytes = gl.total;
+  if (token_workspace_bytes) *token_workspace_bytes = token_vjp_workspace_bytes(p, pos) + 256;
+  return B200_OK;
+}
+
+int32_t b200_token_forward(B200Plan* p, const float* x, const void* key_cache, const void* value_cache, int32_t pos,
+                           const void* packed_w, float* hidden_out, void* ws, size_t ws_bytes, b200_stream_t stream) {
+  if (!p) return fail(B200_ERR_INVALID_ARG, "plan is null");
+  if (p->tp_size != 1) return fail(B200_ERR_UNSUPPORTED, "the token forward over flat caches runs on one GPU (tp_size must be 1)");
+  if (pos < 0 || pos >= p->cfg.seq_len) return fail(B200_ERR_BAD_SHAPE, "pos=%d outside the plan's seq_len=%d", pos, p->cfg.seq_len);
+  if (!x || !packed_w || !hidden_out || !ws || (pos > 0 && (!key_cache || !value_cache)))
+    return fail(B200_ERR_INVALID_ARG, "null argument");
+  if (!aligned16(x) || !aligned16(packed_w) || !aligned16(hidden_out) || !aligned16(ws) ||
+      (pos > 0 && (!aligned16(key_cache) || !aligned16(value_cache))))
+    return fail(B200_ERR_MISALIGNED, "buffers must be 16-byte aligned");
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev != p->device) return fail(B200_ERR_INVALID_ARG, "wrong current device");
+  return token_forward_impl(p, x, key_cache, value_cache, pos, reinterpret_cast<const uint8_t*>(packed_w), hidden_out, ws,
+                            ws_bytes, reinterpret_cast<cudaStream_t>(stream));
 }
 
 int32_t b200_token_vjp(B200Plan* p, const float* x, const void* key_cache, const void* value_cache, int32_t pos,

@@ -13,3 +13,5 @@ from enzyme_ad.jax.primitives import (  # noqa: F401
     vjp,
     register_ffi_targets,
 )
+from enzyme_ad.jax.hlo_matcher import MatchError, match_llama_forward, rewrite_to_custom_calls  # noqa: F401
+

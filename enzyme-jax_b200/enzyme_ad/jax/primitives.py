@@ -319,7 +319,8 @@ def vjp(fn: Callable, *primals):
 
 
 FFI_TARGETS = ("enzymejax_b200_llama_pack", "enzymejax_b200_llama_fwd", "enzymejax_b200_llama_fwd_saved",
-               "enzymejax_b200_llama_bwd", "enzymejax_b200_llama_unpack_grads", "enzymejax_b200_llama_decode_step")
+               "enzymejax_b200_llama_bwd", "enzymejax_b200_llama_unpack_grads", "enzymejax_b200_llama_decode_step",
+               "enzymejax_b200_llama_token_fwd", "enzymejax_b200_llama_token_vjp")
 
 
 def register_ffi_targets(jax_ffi=None) -> Tuple[str, ...]:

@@ -222,6 +222,17 @@ B200_API int32_t b200_unpack_grads(const B200Plan* plan, const float* grads, flo
  *   d_key_cache  fp32 [L, pos, d] (d_value_cache alike)
  * One sequence; the workspace size comes from b200_token_vjp_workspace_bytes. */
 B200_API int32_t b200_token_vjp_workspace_bytes(const B200Plan* plan, int32_t pos, size_t* bytes);
+/* The primal alone: forward(x, weights, key_cache, value_cache) -> hidden over flat caches [L, pos, d] (the
+ * reference's call, test/llama.py:35-238), for a caller that holds the cache as the reference does rather than in
+ * pages.  Same workspace size as the VJP. */
+B200_API int32_t b200_token_forward(B200Plan* plan, const float* x, const void* key_cache, const void* value_cache,
+                                    int32_t pos, const void* packed_w, float* hidden_out, void* workspace,
+                                    size_t workspace_bytes, b200_stream_t stream);
+/* Buffer sizes for a model on one GPU without a plan and without a device: what a compile-time rewrite needs to type
+ * the packed-weight operand, the packed-gradient result and the scratch result of the custom calls it emits (the
+ * reference computes its scratch size at lowering time too, primitives.py:712-727).  Any output pointer may be NULL. */
+B200_API int32_t b200_static_sizes(const B200LlamaConfig* cfg, int32_t with_transposed, int32_t pos,
+                                   size_t* packed_bytes, size_t* grad_bytes, size_t* token_workspace_bytes);
 B200_API int32_t b200_token_vjp(B200Plan* plan, const float* x, const void* key_cache, const void* value_cache,
                                 int32_t pos, const void* packed_w, const float* d_hidden, float* hidden_out,
                                 float* dx, float* grads, float* d_key_cache, float* d_value_cache, void* workspace,
@@ -374,6 +385,9 @@ B200_API int32_t b200_tp_reduce_norm(void* comm, int32_t rows_total, int32_t dim
  *   enzymejax_b200_llama_bwd          tokens, packed, dlogits, saved -> packed gradients, workspace
  *   enzymejax_b200_llama_unpack_grads packed gradients -> 12 gradient leaves
  *   enzymejax_b200_llama_decode_step  tokens, packed, kv pages (aliased in place), page table -> logits, workspace
+ *   enzymejax_b200_llama_token_fwd    x, packed, key_cache, value_cache -> hidden, workspace   (the reference's call)
+ *   enzymejax_b200_llama_token_vjp    x, packed, key_cache, value_cache, d_hidden -> hidden, dx, packed gradients,
+ *                                     d_key_cache, d_value_cache, workspace
  * The handlers exist only in a library built where the XLA FFI headers (xla/ffi/api/ffi.h, shipped inside jaxlib)
  * are on the include path; b200_ffi_available() says whether this build has them.
  *

@@ -65,7 +65,9 @@ def uniform_weights(cfg, seed, dtype):
 
 
 def main():
-    ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) < 2:
+        sys.exit("usage: make_golden.py <path of the reference tree>")
+    ref_root = sys.argv[1]
     ref = load_reference_llama(ref_root)
     import torch
     from oracle import llama_ref as O
