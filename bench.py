@@ -521,7 +521,8 @@ def run_prefill(args, rank, world, local, B, dist):
         line["config"]["exchange"] = (
             ("row-sharded residual stream: one fused reduce + add + RMSNorm + gather kernel per block, "
              + ("summed inside the NVLink switch (multimem.ld_reduce / multimem.st)"
-                if mode == 2 and os.environ.get("B200_TP_MULTIMEM", "1") != "0" else "plain peer loads and stores"))
+                if mode == 2 and (os.environ.get("B200_TP_MULTIMEM", "1" if world >= 4 else "0") != "0")
+                else "plain peer loads and stores"))
             if fused else "all-reduce per block")
         line["exchange_ms_per_step"] = prof["allreduce"]["ms"] / args.steps
     if rank == 0 and world == 1 and not args.no_cpu_baseline:

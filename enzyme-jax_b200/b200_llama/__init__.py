@@ -37,7 +37,7 @@ EXPORTS = (
     "b200_selftest_peer_wait", "b200_plan_cached", "b200_ffi_available", "b200_ffi_handler",
     "b200_token_vjp_workspace_bytes", "b200_token_vjp", "b200_comm_init_rank_ex", "b200_comm_setup_peer_memory",
     "b200_comm_attach_memory", "b200_tp_exchange_buffers", "b200_tp_reduce_norm", "b200_token_forward",
-    "b200_static_sizes",
+    "b200_static_sizes", "b200_jvp_workspace_bytes", "b200_forward_jvp",
 )
 
 
@@ -78,6 +78,9 @@ def lib() -> ctypes.CDLL:
         l.b200_token_vjp_workspace_bytes.argtypes = [c_void_p, c_int32, POINTER(c_size_t)]
         l.b200_token_forward.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int32, c_void_p, c_void_p, c_void_p,
                                          c_size_t, c_void_p]
+        l.b200_jvp_workspace_bytes.argtypes = [c_void_p, c_int32, c_int32, POINTER(c_size_t)]
+        l.b200_forward_jvp.argtypes = [c_void_p, c_void_p, c_int32, c_int32, c_void_p, c_void_p, c_void_p, c_void_p,
+                                       c_void_p, c_size_t, c_void_p]
         l.b200_static_sizes.argtypes = [POINTER(_Config), c_int32, c_int32, POINTER(c_size_t), POINTER(c_size_t),
                                         POINTER(c_size_t)]
         l.b200_token_vjp.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int32, c_void_p, c_void_p, c_void_p,
@@ -499,6 +502,42 @@ class Plan:
         check(lib().b200_pack_weights(self._h, arr, _dt(dts.pop()), int(with_transposed), self.packed.data_ptr(),
                                       _stream()))
         self.with_transposed = with_transposed
+
+    def pack_tangents(self, tangents: Dict[str, torch.Tensor]) -> torch.Tensor:
+        """Packs a dict of weight-leaf tangents (same names and shapes as the weights; missing leaves count as zero)
+        into the layout of the weights, for ``forward_jvp``."""
+        cfg = self.config
+        L, d, h, V = cfg["n_layers"], cfg["dim"], cfg["hidden_dim"], cfg["vocab_size"]
+        shapes = {"rms_att_weight": (L, d), "rms_ffn_weight": (L, d), "rms_final_weight": (d,),
+                  "token_embedding_table": (V, d), "w1": (L, h, d), "w2": (L, d, h), "w3": (L, h, d), "wcls": (V, d),
+                  "wk": (L, d, d), "wo": (L, d, d), "wq": (L, d, d), "wv": (L, d, d)}
+        leaves = []
+        for name in LEAF_ORDER:
+            t = tangents.get(name)
+            t = torch.zeros(shapes[name], dtype=self.dtype, device=self.device) if t is None else \
+                t.to(self.device, self.dtype).contiguous()
+            if tuple(t.shape) != shapes[name]:
+                raise B200Error(2, f"tangent of {name} has shape {tuple(t.shape)}, expected {shapes[name]}")
+            leaves.append(t)
+        n = self._bytes(lib().b200_packed_weight_bytes, 0)
+        packed = torch.empty(n, dtype=torch.uint8, device=self.device)
+        arr = (c_void_p * len(leaves))(*[t.data_ptr() for t in leaves])
+        check(lib().b200_pack_weights(self._h, arr, _dt(self.dtype), 0, packed.data_ptr(), _stream()))
+        return packed
+
+    def forward_jvp(self, tokens: torch.Tensor, tangents: Dict[str, torch.Tensor]):
+        """``jax.jvp``-shaped: returns ``(logits, dlogits)`` for the tangents of the weight leaves."""
+        B, S = tokens.shape
+        tok = tokens.to(self.device, torch.int32).contiguous()
+        saved = self.new_saved(B, S)
+        logits = self.forward(tok, saved=saved)
+        packed_dw = self.pack_tangents(tangents)
+        dlogits = torch.empty(B, S, self.vocab_local, dtype=torch.float32, device=self.device)
+        need = self._bytes(lib().b200_jvp_workspace_bytes, B, S)
+        ws = torch.empty(need, dtype=torch.uint8, device=self.device)
+        check(lib().b200_forward_jvp(self._h, tok.data_ptr(), B, S, self.packed.data_ptr(), packed_dw.data_ptr(),
+                                     saved.data_ptr(), dlogits.data_ptr(), ws.data_ptr(), ws.numel(), _stream()))
+        return logits, dlogits
 
     # ---- forward / backward ---------------------------------------------
     def forward(self, tokens: torch.Tensor, *, saved: Optional[torch.Tensor] = None,

@@ -713,7 +713,11 @@ int32_t comm_peer_reduce_norm(void* comm, int T, int d, int dtype, bool reduce, 
   if (n_chunks > 1024)
     return fail(B200_ERR_BAD_SHAPE, "row-sharded exchange: rows of %d elements exceed 16 KB", d);
   const int nw = !reduce ? 0 : c->world <= 2 ? 2 : c->world <= 4 ? 4 : 8;
-  static const int use_mc = env_int("B200_TP_MULTIMEM", 1);
+  // In-switch reduction halves the bytes on every link from four ranks on ((world + 1) / world of the buffer each
+  // way instead of 2 (world - 1) / world); between two ranks it only adds the loop through the switch (measured
+  // 200 us against 118 us per exchange of 64 MiB).  B200_TP_MULTIMEM = 0 / 1 forces the choice.
+  static const int mc_env = env_int("B200_TP_MULTIMEM", -1);
+  const bool use_mc = mc_env >= 0 ? mc_env != 0 : c->world >= 4;
   if (c->pm.mc && use_mc) {
     int grid_mc = sm_count() * 4;
     if (grid_mc > rows) grid_mc = rows;

@@ -26,7 +26,9 @@ into whatever reads the reference's CSV files.  What differs, by construction:
   (test/test_utils.py:522-550, :678-681) against a baseline the caller passes
   (there, the first pipeline; here, e.g. the CPU oracle), leaf by leaf with
   ``atol`` / ``rtol`` (1e-3 in the reference's llama test);
-* no ``Forward`` (JVP) row: forward mode is not built;
+* the ``Forward`` row (``jax.jvp`` in the reference, test/test_utils.py:689-735) is timed for the token-sequence
+  shape when tangents of the weight leaves are passed (``dins``): the forward that keeps the activations followed by
+  the tangent pass;
 * times are CUDA-event times on the launching stream, not profiler traces.
 """
 from __future__ import annotations
@@ -118,14 +120,15 @@ class EnzymeJaxTest:
         torch.cuda.synchronize()
         return t0.elapsed_time(t1) * 1e-3 / self.repeat
 
-    def harness(self, name: str, fn: Callable, ins, douts: Optional[torch.Tensor] = None, *, baseline_primal=None,
-                baseline_grads=None) -> Dict[str, float]:
+    def harness(self, name: str, fn: Callable, ins, douts: Optional[torch.Tensor] = None, *, dins=None,
+                baseline_primal=None, baseline_grads=None, baseline_tangent=None) -> Dict[str, float]:
         """Times ``fn`` (a decorated llama function) on ``ins`` and cross-checks its results.
 
         ``ins`` is ``(x, weights, key_cache, value_cache)`` -- the reference's own call -- or ``(tokens, weights)``.
         With a cotangent ``douts`` of the result the three reverse rows are timed too, differentiating with respect
-        to every input.  ``baseline_primal`` / ``baseline_grads`` (the trees another implementation produced for the
-        same inputs) are compared with ours by ``recursive_check``.  Returns ``{key: seconds}``.
+        to every input; with tangents ``dins`` of the weight leaves (token-sequence shape) the ``Forward`` row.
+        ``baseline_primal`` / ``baseline_tangent`` / ``baseline_grads`` (the trees another implementation produced for
+        the same inputs) are compared with ours by ``recursive_check``.  Returns ``{key: seconds}``.
         """
         route: _LlamaRoute = getattr(fn, "_b200_route", None)
         if route is None:
@@ -136,6 +139,15 @@ class EnzymeJaxTest:
             recursive_check(self, primal, baseline_primal, "Primal")
         out["Primal"] = self._avg_seconds(lambda: fn(*ins))
         self.pretty_print_table(name, self.pipeline_name, self.backend, "Primal", out["Primal"])
+        if dins is not None:
+            if len(ins) != 2:
+                raise NotImplementedError("forward mode is built for the (tokens, weights) call")
+            plan = route._ensure(ins[1], False)
+            _, tangent = plan.forward_jvp(ins[0], dins)
+            if baseline_tangent is not None:
+                recursive_check(self, tangent, baseline_tangent, "Forward")
+            out["Forward"] = self._avg_seconds(lambda: plan.forward_jvp(ins[0], dins))
+            self.pretty_print_table(name, self.pipeline_name, self.backend, "Forward", out["Forward"])
         if douts is None:
             return out
         result, pullback = vjp(fn, *ins)

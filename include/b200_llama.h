@@ -206,6 +206,19 @@ B200_API int32_t b200_packed_grad_bytes(const B200Plan* plan, size_t* bytes);
 B200_API int32_t b200_unpack_grads(const B200Plan* plan, const float* grads, float* const* leaves,
                                    b200_stream_t stream);
 
+/* Forward mode (JVP) of b200_forward with respect to every weight leaf: the tangent of the logits for given
+ * tangents of the leaves - the `Forward` row of the reference's harness, jax.jvp of the decorated function
+ * (test/test_utils.py:689-735), with the forward rules of Implementations/HLODerivatives.td:964-1339 composed per
+ * fused block.
+ *   packed_dw  the tangents of the 12 leaves, packed with b200_pack_weights exactly like the weights
+ *   saved      the activations a b200_forward call with `saved` kept for the same tokens and weights
+ *   dlogits    fp32 [batch*seq, vocab], the tangent of the logits
+ * One GPU.  The workspace size comes from b200_jvp_workspace_bytes. */
+B200_API int32_t b200_jvp_workspace_bytes(const B200Plan* plan, int32_t batch, int32_t seq, size_t* bytes);
+B200_API int32_t b200_forward_jvp(B200Plan* plan, const int32_t* tokens, int32_t batch, int32_t seq,
+                                  const void* packed_w, const void* packed_dw, const void* saved, float* dlogits,
+                                  void* workspace, size_t workspace_bytes, b200_stream_t stream);
+
 /* Reverse mode of the reference's own call: forward(x, weights, key_cache, value_cache) -> hidden
  * (test/llama.py:35-238), differentiated with respect to ALL of its inputs as the reference's test does
  * (test/llama.py:315-317 `ins`/`dins`, test/test_utils.py:505-514 splatvjp): the residual vector, every weight leaf

@@ -244,6 +244,18 @@ def vjp_sequence(tokens, cfg, w, dlogits):
     return logits.detach(), {k: (v.grad if v.grad is not None else torch.zeros_like(v)) for k, v in leaves.items()}
 
 
+def jvp_sequence(tokens, cfg, w, dw):
+    """Forward mode of Level 1: (logits, tangent of the logits) for tangents ``dw`` of the weight leaves (missing
+    leaves count as zero), by torch's forward-mode AD; the reference's harness computes the same with jax.jvp
+    (test/test_utils.py:689-735)."""
+    import torch.autograd.forward_ad as fwAD
+    with fwAD.dual_level():
+        dual = {k: fwAD.make_dual(v, dw[k].to(v.dtype) if k in dw else torch.zeros_like(v)) for k, v in w.items()}
+        out = forward_sequence(tokens, cfg, dual)
+        primal, tangent = fwAD.unpack_dual(out)
+        return primal.detach(), (tangent if tangent is not None else torch.zeros_like(primal)).detach()
+
+
 def vjp_token(x, cfg, w, key_cache, value_cache, d_hidden):
     """Reverse mode of the reference's own call, forward(x, weights, key_cache, value_cache) -> hidden
     (test/llama.py:35-238), with respect to ALL inputs, as the reference's test differentiates it

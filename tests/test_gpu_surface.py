@@ -77,16 +77,19 @@ def test_harness_rows_and_csv(tmp_path, monkeypatch):
     ref_logits, ref = O.vjp_sequence(tokens, cfg, {k: v.double().cpu() for k, v in w.items()}, dl.double())
     # bf16 model against the fp64 oracle on the same bf16 weights: 2e-2 of the largest logit
     h.atol, h.rtol = 2e-2 * float(ref_logits.abs().max()), 2e-2
-    times = h.harness("llama", model, (tokens, w), dl, baseline_primal=ref_logits)
-    assert list(times) == ["Primal", "PreRev", "PostRev", "BothRev"]
+    dw = {"wq": 0.1 * torch.randn(w["wq"].shape, generator=torch.Generator().manual_seed(2))}
+    _, ref_tan = O.jvp_sequence(tokens, cfg, {k: v.double().cpu() for k, v in w.items()}, {k: v.double() for k, v in dw.items()})
+    times = h.harness("llama", model, (tokens, w), dl, dins=dw, baseline_primal=ref_logits)
+    assert list(times) == ["Primal", "Forward", "PreRev", "PostRev", "BothRev"]
+    assert ref_tan.shape == ref_logits.shape
     assert all(0 < t < 1 for t in times.values())
     assert times["BothRev"] > times["Primal"]  # reverse rows include the primal (revprimal)
     monkeypatch.setenv("TEST_UNDECLARED_OUTPUTS_DIR", str(tmp_path))
     path = h.write_results_csv()
     assert os.path.basename(path) == "results_Llama.csv"
     rows = list(csv.reader(open(path)))
-    assert rows[0] == CSV_HEADER and len(rows) == 5
-    assert [r[3] for r in rows[1:]] == ["Primal", "PreRev", "PostRev", "BothRev"]
+    assert rows[0] == CSV_HEADER and len(rows) == 6
+    assert [r[3] for r in rows[1:]] == ["Primal", "Forward", "PreRev", "PostRev", "BothRev"]
     assert all(r[:3] == ["llama", "B200", "gpu"] and float(r[4]) > 0 for r in rows[1:])
 
 

@@ -139,3 +139,18 @@ def test_token_vjp_against_level0_and_finite_differences():
             fd = (f(x, cp, vc) - f(x, cm, vc)) if which == 0 else (f(x, kc, cp) - f(x, kc, cm))
             assert abs(fd / (2 * eps) - float(grad[idx])) < 1e-7
     assert float(grads["wcls"].abs().max()) == 0.0
+
+
+def test_jvp_sequence_against_finite_differences():
+    """Forward mode of Level 1 (the harness's `Forward` row) against central differences along the tangent direction."""
+    cfg = O.CONFIGS["tiny"]
+    w = O.make_weights(cfg, 3, torch.float64, std=0.2, gains_one=False)
+    g = torch.Generator().manual_seed(2)
+    dw = {k: 0.1 * torch.randn(v.shape, generator=g, dtype=torch.float64) for k, v in w.items()}
+    tok = O.make_tokens(cfg, 2, 8, 1)
+    primal, tangent = O.jvp_sequence(tok, cfg, w, dw)
+    assert torch.allclose(primal, O.forward_sequence(tok, cfg, w))
+    eps = 1e-6
+    fd = (O.forward_sequence(tok, cfg, {k: v + eps * dw[k] for k, v in w.items()}) -
+          O.forward_sequence(tok, cfg, {k: v - eps * dw[k] for k, v in w.items()})) / (2 * eps)
+    assert float((fd - tangent).abs().max()) < 1e-6 * float(tangent.abs().max())
