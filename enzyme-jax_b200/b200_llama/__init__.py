@@ -37,7 +37,8 @@ EXPORTS = (
     "b200_selftest_peer_wait", "b200_plan_cached", "b200_ffi_available", "b200_ffi_handler",
     "b200_token_vjp_workspace_bytes", "b200_token_vjp", "b200_comm_init_rank_ex", "b200_comm_setup_peer_memory",
     "b200_comm_attach_memory", "b200_tp_exchange_buffers", "b200_tp_reduce_norm", "b200_token_forward",
-    "b200_static_sizes", "b200_jvp_workspace_bytes", "b200_forward_jvp",
+    "b200_static_sizes", "b200_jvp_workspace_bytes", "b200_forward_jvp", "b200_token_jvp_workspace_bytes",
+    "b200_token_jvp",
 )
 
 
@@ -81,6 +82,9 @@ def lib() -> ctypes.CDLL:
         l.b200_jvp_workspace_bytes.argtypes = [c_void_p, c_int32, c_int32, POINTER(c_size_t)]
         l.b200_forward_jvp.argtypes = [c_void_p, c_void_p, c_int32, c_int32, c_void_p, c_void_p, c_void_p, c_void_p,
                                        c_void_p, c_size_t, c_void_p]
+        l.b200_token_jvp_workspace_bytes.argtypes = [c_void_p, c_int32, POINTER(c_size_t)]
+        l.b200_token_jvp.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int32, c_void_p, c_void_p, c_void_p,
+                                     c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_size_t, c_void_p]
         l.b200_static_sizes.argtypes = [POINTER(_Config), c_int32, c_int32, POINTER(c_size_t), POINTER(c_size_t),
                                         POINTER(c_size_t)]
         l.b200_token_vjp.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int32, c_void_p, c_void_p, c_void_p,
@@ -635,6 +639,31 @@ class Plan:
                                        vc.data_ptr() if pos else None, pos, self.packed.data_ptr(), hidden.data_ptr(),
                                        ws.data_ptr(), ws.numel(), _stream()))
         return hidden
+
+    def token_jvp(self, x, key_cache, value_cache, dx, dweights: Dict[str, torch.Tensor], d_key_cache, d_value_cache):
+        """Forward mode of the reference's own call with tangents for all of its inputs (``jax.jvp(fn, ins, dins)``).
+        Returns ``(hidden, d_hidden)``, both fp32 [d]."""
+        L, d = self.config["n_layers"], self.config["dim"]
+        pos = int(key_cache.shape[1])
+        for name, c in (("key_cache", key_cache), ("value_cache", value_cache), ("d_key_cache", d_key_cache),
+                        ("d_value_cache", d_value_cache)):
+            if tuple(c.shape) != (L, pos, d):
+                raise B200Error(2, f"{name} must be [{L}, {pos}, {d}], got {tuple(c.shape)}")
+        dev = self.device
+        f32 = lambda t: t.to(dev, torch.float32).reshape(d).contiguous()
+        cd = lambda t: t.to(dev, self.dtype).contiguous()
+        xin, dxin = f32(x), f32(dx)
+        kc, vc, dkc, dvc = cd(key_cache), cd(value_cache), cd(d_key_cache), cd(d_value_cache)
+        packed_dw = self.pack_tangents(dweights)
+        hidden = torch.empty(d, dtype=torch.float32, device=dev)
+        d_hidden = torch.empty(d, dtype=torch.float32, device=dev)
+        need = self._bytes(lib().b200_token_jvp_workspace_bytes, pos)
+        ws = torch.empty(need, dtype=torch.uint8, device=dev)
+        ptr = lambda t: t.data_ptr() if pos else None
+        check(lib().b200_token_jvp(self._h, xin.data_ptr(), ptr(kc), ptr(vc), pos, self.packed.data_ptr(),
+                                   dxin.data_ptr(), packed_dw.data_ptr(), ptr(dkc), ptr(dvc), hidden.data_ptr(),
+                                   d_hidden.data_ptr(), ws.data_ptr(), ws.numel(), _stream()))
+        return hidden, d_hidden
 
     def token_vjp(self, x: torch.Tensor, key_cache: torch.Tensor, value_cache: torch.Tensor, d_hidden: torch.Tensor):
         """Reverse mode of the reference's own call ``forward(x, weights, key_cache, value_cache) -> hidden`` with

@@ -19,6 +19,7 @@
 #include "elementwise.cuh"
 #include "gemm_epilogue.cuh"
 #include "plan.cuh"
+#include "token_path.cuh"
 
 namespace b200 {
 
@@ -317,11 +318,87 @@ int32_t forward_jvp_impl(B200Plan* p, const int32_t* tokens, int B, int S, const
   return B200_OK;
 }
 
+size_t token_jvp_workspace_bytes(const B200Plan& p, int pos) {
+  Arena a(nullptr);
+  TokWs t;
+  carve_token(p, a, pos + 1, &t);
+  JvpWs w;
+  carve_jvp(p, a, 1, (size_t)pos + 1, &w);
+  return a.used + 256;
+}
+
+// The reference's own call: tangents of x, the weight leaves and both caches -> tangent of the hidden state.
+int32_t token_jvp_impl(B200Plan* p, const float* x, const void* key_cache, const void* value_cache, int pos,
+                       const uint8_t* w, const float* dx_in, const uint8_t* dw, const void* d_key_cache,
+                       const void* d_value_cache, float* hidden_out, float* d_hidden, void* ws_, size_t ws_bytes,
+                       cudaStream_t stream) {
+  const int d = p->d, S = pos + 1;
+  const size_t es = p->esize;
+  const PackedLayout& wl = p->wl;
+  Arena wa(ws_);
+  TokWs t;
+  carve_token(*p, wa, S, &t);
+  JvpWs ws;
+  carve_jvp(*p, wa, 1, (size_t)S, &ws);
+  if (wa.used > ws_bytes) return fail(B200_ERR_WORKSPACE, "token forward mode needs %zu workspace bytes, got %zu", wa.used, ws_bytes);
+  B200_TRY(token_forward_run(p, t, x, key_cache, value_cache, pos, w, wl, hidden_out ? hidden_out : t.dx, stream));
+  auto gains = [&](const uint8_t* base, size_t off) { return reinterpret_cast<const float*>(base + off); };
+  B200_CUDA_OK(cudaMemcpyAsync(ws.dx, dx_in, (size_t)d * 4, cudaMemcpyDeviceToDevice, stream));
+  for (int l = 0; l < p->L; ++l) {
+    const TokLayer& a = t.layer[l];
+    uint8_t* dqkv = reinterpret_cast<uint8_t*>(ws.dqkv);
+    if (pos > 0) {
+      // rows 0..pos-1: zero query tangents, the tangents of the cache rows as dK and dV
+      B200_CUDA_OK(cudaMemset2DAsync(dqkv, (size_t)3 * d * es, 0, (size_t)d * es, pos, stream));
+      const uint8_t* dk = reinterpret_cast<const uint8_t*>(d_key_cache) + (size_t)l * pos * d * es;
+      const uint8_t* dv = reinterpret_cast<const uint8_t*>(d_value_cache) + (size_t)l * pos * d * es;
+      B200_CUDA_OK(cudaMemcpy2DAsync(dqkv + (size_t)d * es, (size_t)3 * d * es, dk, (size_t)d * es, (size_t)d * es, pos,
+                                     cudaMemcpyDeviceToDevice, stream));
+      B200_CUDA_OK(cudaMemcpy2DAsync(dqkv + (size_t)2 * d * es, (size_t)3 * d * es, dv, (size_t)d * es, (size_t)d * es, pos,
+                                     cudaMemcpyDeviceToDevice, stream));
+    }
+    LayerPrimal pr{a.x_in, a.xb, a.rinv1, a.qkv, a.o, a.lse, a.x_mid, a.xb2, a.rinv2, a.gate, a.up, a.hg};
+    B200_TRY(layer_tangent(*p, ws, pr, wl.layer[l], w, dw, gains(w, wl.g_att) + (size_t)l * d,
+                           gains(dw, wl.g_att) + (size_t)l * d, gains(w, wl.g_ffn) + (size_t)l * d,
+                           gains(dw, wl.g_ffn) + (size_t)l * d, 1, 1, S, pos, pos, stream));
+  }
+  return launch_rmsnorm_jvp(t.x_last, ws.dx, gains(w, wl.g_final), gains(dw, wl.g_final), t.rinv_f, d_hidden, 1, d,
+                            B200_F32, stream);
+}
+
 }  // namespace b200
 
 using namespace b200;
 
 extern "C" {
+
+int32_t b200_token_jvp_workspace_bytes(const B200Plan* p, int32_t pos, size_t* bytes) {
+  if (!p || !bytes) return fail(B200_ERR_INVALID_ARG, "null argument");
+  if (pos < 0 || pos >= p->cfg.seq_len) return fail(B200_ERR_BAD_SHAPE, "pos=%d outside the plan's seq_len=%d", pos, p->cfg.seq_len);
+  *bytes = token_jvp_workspace_bytes(*p, pos);
+  return B200_OK;
+}
+
+int32_t b200_token_jvp(B200Plan* p, const float* x, const void* key_cache, const void* value_cache, int32_t pos,
+                       const void* packed_w, const float* dx, const void* packed_dw, const void* d_key_cache,
+                       const void* d_value_cache, float* hidden_out, float* d_hidden, void* ws, size_t ws_bytes,
+                       b200_stream_t stream) {
+  if (!p) return fail(B200_ERR_INVALID_ARG, "plan is null");
+  if (p->tp_size != 1) return fail(B200_ERR_UNSUPPORTED, "forward mode runs on one GPU (tp_size must be 1)");
+  if (pos < 0 || pos >= p->cfg.seq_len) return fail(B200_ERR_BAD_SHAPE, "pos=%d outside the plan's seq_len=%d", pos, p->cfg.seq_len);
+  if (!x || !packed_w || !dx || !packed_dw || !d_hidden || !ws ||
+      (pos > 0 && (!key_cache || !value_cache || !d_key_cache || !d_value_cache)))
+    return fail(B200_ERR_INVALID_ARG, "null argument");
+  if (!aligned16(x) || !aligned16(packed_w) || !aligned16(dx) || !aligned16(packed_dw) || !aligned16(d_hidden) ||
+      !aligned16(ws) || (hidden_out && !aligned16(hidden_out)) ||
+      (pos > 0 && (!aligned16(key_cache) || !aligned16(value_cache) || !aligned16(d_key_cache) || !aligned16(d_value_cache))))
+    return fail(B200_ERR_MISALIGNED, "buffers must be 16-byte aligned");
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev != p->device) return fail(B200_ERR_INVALID_ARG, "wrong current device");
+  return token_jvp_impl(p, x, key_cache, value_cache, pos, reinterpret_cast<const uint8_t*>(packed_w), dx,
+                        reinterpret_cast<const uint8_t*>(packed_dw), d_key_cache, d_value_cache, hidden_out, d_hidden, ws,
+                        ws_bytes, reinterpret_cast<cudaStream_t>(stream));
+}
 
 int32_t b200_jvp_workspace_bytes(const B200Plan* p, int32_t B, int32_t S, size_t* bytes) {
   if (!p || !bytes) return fail(B200_ERR_INVALID_ARG, "null argument");

@@ -20,22 +20,9 @@
 #include "elementwise.cuh"
 #include "gemm_epilogue.cuh"
 #include "plan.cuh"
+#include "token_path.cuh"
 
 namespace b200 {
-
-namespace {
-
-struct TokLayer {
-  float* x_in; void* xb; float* rinv1; void* qkv; void* o; float* lse;
-  float* x_mid; void* xb2; float* rinv2; void* gate; void* up; void* hg;
-};
-struct TokWs {
-  std::vector<TokLayer> layer;
-  float* x_last; float* rinv_f;
-  float* dx; void* dxb; void* dhg; void* dgu; void* d_o; void* dqkv; float* delta; float* dg_part;
-  void* splitk; size_t splitk_bytes;
-  int n_parts;
-};
 
 void carve_token(const B200Plan& p, Arena& a, int S, TokWs* w) {
   const size_t es = p.esize, d = p.d, h = p.h;
@@ -72,6 +59,8 @@ void carve_token(const B200Plan& p, Arena& a, int S, TokWs* w) {
   w->splitk = a.take(w->splitk_bytes);
 }
 
+namespace {
+
 int32_t gemm_epi(const B200Plan& p, const TokWs& ws, const void* A, int lda, const void* W, int ldw, int N, int K,
                  int kind, int out_dtype, const EpiParams& epi, cudaStream_t stream) {
   GemmArgs g;
@@ -103,7 +92,7 @@ size_t token_vjp_workspace_bytes(const B200Plan& p, int pos) {
 
 // Forward of the reference call shape, keeping in `t` what the backward needs.  `hidden` receives the final-normed
 // hidden state (fp32 [d]).
-static int32_t token_forward_run(B200Plan* p, const TokWs& t, const float* x, const void* key_cache,
+int32_t token_forward_run(B200Plan* p, const TokWs& t, const float* x, const void* key_cache,
                                  const void* value_cache, int pos, const uint8_t* w, const PackedLayout& wl,
                                  float* hidden, cudaStream_t stream) {
   const int d = p->d, h = p->h, dt = p->dtype, S = pos + 1;

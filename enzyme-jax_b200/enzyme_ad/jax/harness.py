@@ -26,9 +26,9 @@ into whatever reads the reference's CSV files.  What differs, by construction:
   (test/test_utils.py:522-550, :678-681) against a baseline the caller passes
   (there, the first pipeline; here, e.g. the CPU oracle), leaf by leaf with
   ``atol`` / ``rtol`` (1e-3 in the reference's llama test);
-* the ``Forward`` row (``jax.jvp`` in the reference, test/test_utils.py:689-735) is timed for the token-sequence
-  shape when tangents of the weight leaves are passed (``dins``): the forward that keeps the activations followed by
-  the tangent pass;
+* the ``Forward`` row (``jax.jvp(fn, ins, dins)`` in the reference, test/test_utils.py:689-735) is timed when
+  tangents ``dins`` are passed: ``(dx, dweights, d_key_cache, d_value_cache)`` for the reference's own call shape, a
+  dict of weight-leaf tangents for the token-sequence shape;
 * times are CUDA-event times on the launching stream, not profiler traces.
 """
 from __future__ import annotations
@@ -139,9 +139,17 @@ class EnzymeJaxTest:
             recursive_check(self, primal, baseline_primal, "Primal")
         out["Primal"] = self._avg_seconds(lambda: fn(*ins))
         self.pretty_print_table(name, self.pipeline_name, self.backend, "Primal", out["Primal"])
-        if dins is not None:
-            if len(ins) != 2:
-                raise NotImplementedError("forward mode is built for the (tokens, weights) call")
+        if dins is not None and len(ins) == 4:
+            # the reference's call: dins = (dx, dweights, d_key_cache, d_value_cache), as test/llama.py:316
+            x, weights, kc, vc = ins
+            dx, dweights, dkc, dvc = dins
+            plan = route._ensure(weights, False)
+            _, tangent = plan.token_jvp(x, kc, vc, dx, dweights, dkc, dvc)
+            if baseline_tangent is not None:
+                recursive_check(self, tangent, baseline_tangent, "Forward")
+            out["Forward"] = self._avg_seconds(lambda: plan.token_jvp(x, kc, vc, dx, dweights, dkc, dvc))
+            self.pretty_print_table(name, self.pipeline_name, self.backend, "Forward", out["Forward"])
+        elif dins is not None:
             plan = route._ensure(ins[1], False)
             _, tangent = plan.forward_jvp(ins[0], dins)
             if baseline_tangent is not None:

@@ -219,6 +219,18 @@ B200_API int32_t b200_forward_jvp(B200Plan* plan, const int32_t* tokens, int32_t
                                   const void* packed_w, const void* packed_dw, const void* saved, float* dlogits,
                                   void* workspace, size_t workspace_bytes, b200_stream_t stream);
 
+/* Forward mode of the reference's own call, forward(x, weights, key_cache, value_cache) -> hidden, with tangents
+ * for ALL of its inputs, as the reference's harness passes them (jax.jvp(fn, ins, dins), test/test_utils.py:689-735;
+ * `dins` of test/llama.py:316).
+ *   dx            fp32 [d]                 packed_dw   the leaf tangents, packed like the weights
+ *   d_key_cache   [L, pos, d] of the config dtype (d_value_cache alike); may be NULL when pos == 0
+ *   hidden_out    NULL, or fp32 [d] receiving the primal;  d_hidden  fp32 [d], the tangent of the result */
+B200_API int32_t b200_token_jvp_workspace_bytes(const B200Plan* plan, int32_t pos, size_t* bytes);
+B200_API int32_t b200_token_jvp(B200Plan* plan, const float* x, const void* key_cache, const void* value_cache,
+                                int32_t pos, const void* packed_w, const float* dx, const void* packed_dw,
+                                const void* d_key_cache, const void* d_value_cache, float* hidden_out,
+                                float* d_hidden, void* workspace, size_t workspace_bytes, b200_stream_t stream);
+
 /* Reverse mode of the reference's own call: forward(x, weights, key_cache, value_cache) -> hidden
  * (test/llama.py:35-238), differentiated with respect to ALL of its inputs as the reference's test does
  * (test/llama.py:315-317 `ins`/`dins`, test/test_utils.py:505-514 splatvjp): the residual vector, every weight leaf

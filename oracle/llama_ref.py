@@ -256,6 +256,23 @@ def jvp_sequence(tokens, cfg, w, dw):
         return primal.detach(), (tangent if tangent is not None else torch.zeros_like(primal)).detach()
 
 
+def jvp_token(x, cfg, w, key_cache, value_cache, dx, dw, d_key_cache, d_value_cache):
+    """Forward mode of the reference's own call with tangents for all inputs (jax.jvp(fn, ins, dins),
+    test/test_utils.py:689-735): returns (hidden, tangent of hidden)."""
+    import torch.autograd.forward_ad as fwAD
+    dt = w["wq"].dtype
+    tokens = torch.zeros(1, 1, dtype=torch.int64)
+    with fwAD.dual_level():
+        dual = {k: fwAD.make_dual(v, dw[k].to(dt) if k in dw else torch.zeros_like(v)) for k, v in w.items()
+                if k != "token_embedding_table"}
+        dual["token_embedding_table"] = fwAD.make_dual(x.to(dt), dx.to(dt))[None, :]
+        pk = fwAD.make_dual(key_cache.to(dt), d_key_cache.to(dt))[:, None] if key_cache.shape[1] else None
+        pv = fwAD.make_dual(value_cache.to(dt), d_value_cache.to(dt))[:, None] if value_cache.shape[1] else None
+        _, aux = forward_sequence(tokens, cfg, dual, past_k=pk, past_v=pv, return_aux=True)
+        primal, tangent = fwAD.unpack_dual(aux["xf"][0, 0])
+        return primal.detach(), tangent.detach()
+
+
 def vjp_token(x, cfg, w, key_cache, value_cache, d_hidden):
     """Reverse mode of the reference's own call, forward(x, weights, key_cache, value_cache) -> hidden
     (test/llama.py:35-238), with respect to ALL inputs, as the reference's test differentiates it

@@ -111,3 +111,55 @@ def test_page_allocator_host_logic():
         a.alloc(2)                                   # exhausted
     with pytest.raises(B.B200Error):
         a.free([a.alloc(1)[0], 99])                  # not a page of this pool
+
+
+def test_ffi_registration_entry_points_and_python_glue(monkeypatch):
+    """The library always exports the three FFI functions; in a build without the XLA FFI headers they say so.  The
+    Python glue wraps every handler address in a PyCapsule named for XLA and hands it to jax.ffi.register_ffi_target:
+    checked against a stand-in for jax.ffi and a stand-in library that has handlers."""
+    import ctypes
+    import enzyme_ad.jax.primitives as P
+    lib = B.lib()
+    if not lib.b200_ffi_available():
+        assert lib.b200_ffi_handler(b"enzymejax_b200_llama_fwd") is None
+        assert lib.registerEnzymeJaXB200FFI() == 10      # B200_ERR_UNSUPPORTED
+        with pytest.raises(NotImplementedError):
+            P.register_ffi_targets(jax_ffi=object())
+
+    class FakeLib:
+        def b200_ffi_available(self):
+            return 1
+
+        def b200_ffi_handler(self, name):
+            return 0x1000 + len(name)   # any non-null address
+
+    class FakeJaxFfi:
+        def __init__(self):
+            self.calls = []
+
+        def register_ffi_target(self, name, capsule, platform=None, **kw):
+            self.calls.append((name, capsule, platform))
+
+    monkeypatch.setattr(P._B, "lib", lambda: FakeLib())
+    monkeypatch.setattr(P, "_FFI_REGISTERED", False)
+    fake = FakeJaxFfi()
+    names = P.register_ffi_targets(jax_ffi=fake)
+    assert [c[0] for c in fake.calls] == list(names) and len(names) == 8
+    assert all(c[2] == "CUDA" for c in fake.calls)
+    get_name = ctypes.pythonapi.PyCapsule_GetName
+    get_name.restype = ctypes.c_char_p
+    get_name.argtypes = [ctypes.py_object]
+    assert all(get_name(c[1]) == b"xla._CUSTOM_CALL_TARGET" for c in fake.calls)
+    P.register_ffi_targets(jax_ffi=fake)          # idempotent
+    assert len(fake.calls) == 8
+
+
+def test_static_sizes_need_no_device():
+    import torch
+    cfg = dict(dim=288, hidden_dim=768, n_layers=6, n_heads=6, n_kv_heads=6, vocab_size=32000, seq_len=256)
+    s32 = B.static_sizes(cfg, torch.float32, False, 1)
+    s16 = B.static_sizes(cfg, torch.bfloat16, True, 1)
+    n_params = 6 * (4 * 288 * 288 + 3 * 288 * 768) + 2 * 32000 * 288
+    assert s32["packed_bytes"] >= 4 * n_params and s32["packed_bytes"] < 4 * n_params + 64 * 1024
+    assert s16["packed_bytes"] > 2 * 2 * (n_params - 32000 * 288)   # bf16, with transposed copies of the matrices
+    assert s32["grad_bytes"] == s32["packed_bytes"] and s32["token_workspace_bytes"] > 0

@@ -158,9 +158,15 @@ def test_harness_reference_call_all_input_gradients_checked_against_oracle(tmp_p
     wd = {k: v.cuda() for k, v in w.items()}
     h = Llama(repeat=3, warmup=1)
     assert h.revprimal is False and h.atol == 1e-3   # the reference's settings for this test
-    times = h.harness("llama", forward, (x, wd, kc, vc), dx, baseline_primal=hidden,
-                      baseline_grads=(rdx, {k: rgrads[k] for k in wd}, rdk, rdv))
-    assert list(times) == ["Primal", "PreRev", "PostRev", "BothRev"]
+    gt = torch.Generator().manual_seed(19)
+    dins = (torch.randn(d, generator=gt), {k: 0.05 * torch.randn(v.shape, generator=gt) for k, v in w.items()},
+            torch.randn(L, 1, d, generator=gt), torch.randn(L, 1, d, generator=gt))
+    _, ref_tan = O.jvp_token(x.double(), cfg, {k: v.double() for k, v in wfull.items()}, kc.double(), vc.double(),
+                             dins[0].double(), {k: v.double() for k, v in dins[1].items()}, dins[2].double(),
+                             dins[3].double())
+    times = h.harness("llama", forward, (x, wd, kc, vc), dx, dins=dins, baseline_primal=hidden,
+                      baseline_tangent=ref_tan, baseline_grads=(rdx, {k: rgrads[k] for k in wd}, rdk, rdv))
+    assert list(times) == ["Primal", "Forward", "PreRev", "PostRev", "BothRev"]
     bad = hidden.clone()
     bad[3] += 1.0
     with pytest.raises(AssertionError):
@@ -177,3 +183,36 @@ def test_harness_reference_call_all_input_gradients_checked_against_oracle(tmp_p
         forward(x, {k: v for k, v in wd.items() if k != "wq"}, kc, vc)
     with pytest.raises(ValueError):
         forward(x, dict(wd, wq=wd["wq"][:, :10]), kc, vc)
+
+
+@pytest.mark.parametrize("pos", [1, 4])
+def test_token_jvp_all_inputs_matches_oracle(pos):
+    """jax.jvp(fn, ins, dins) of the reference's harness: tangents for x, every weight leaf and both caches, at config
+    1; and the forward / reverse pair is consistent: <d_hidden, J v> == <J^T d_hidden, v>."""
+    import b200_llama as B
+    cfg = O.CONFIGS["c1"]
+    L, d = cfg["n_layers"], cfg["dim"]
+    w = O.make_weights(cfg, 19, torch.float32, std=0.05, gains_one=False)
+    g = torch.Generator().manual_seed(20)
+    r = lambda *s: torch.randn(*s, generator=g)
+    x, kc, vc = r(d), r(L, pos, d), r(L, pos, d)
+    dx, dkc, dvc, dh = r(d), r(L, pos, d), r(L, pos, d), r(d)
+    dw = {k: 0.05 * r(*v.shape) for k, v in w.items() if k != "token_embedding_table"}
+    dbl = lambda t: t.double()
+    hidden, tangent = O.jvp_token(dbl(x), cfg, {k: dbl(v) for k, v in w.items()}, dbl(kc), dbl(vc), dbl(dx),
+                                  {k: dbl(v) for k, v in dw.items()}, dbl(dkc), dbl(dvc))
+    p = B.Plan(cfg, torch.float32)
+    p.pack_weights({k: v.cuda().contiguous() for k, v in w.items()}, with_transposed=True)
+    got_h, got_t = p.token_jvp(x, kc, vc, dx, dw, dkc, dvc)
+    torch.cuda.synchronize()
+    assert B.device_status() == 0
+    assert float((got_h.double().cpu() - hidden).abs().max() / hidden.abs().max()) < 1e-4
+    assert float((got_t.double().cpu() - tangent).abs().max() / tangent.abs().max()) < 1e-4
+    # transpose relation with the reverse mode of the same call
+    _, gx, packed, gk, gv = p.token_vjp(x, kc, vc, dh)
+    gw = p.unpack_grads(packed)
+    lhs = float((dh.double() * got_t.double().cpu()).sum())
+    rhs = float((gx.double().cpu() * dx).sum() + (gk.double().cpu() * dkc).sum() + (gv.double().cpu() * dvc).sum() +
+                sum((gw[k].double().cpu() * dw[k]).sum() for k in dw))
+    assert abs(lhs - rhs) < 1e-3 * max(1.0, abs(lhs))
+    p.close()
