@@ -521,9 +521,12 @@ def run_prefill(args, rank, world, local, B, dist):
         line["config"]["exchange"] = (
             ("row-sharded residual stream: one fused reduce + add + RMSNorm + gather kernel per block, "
              + ("summed inside the NVLink switch (multimem.ld_reduce / multimem.st)"
-                if mode == 2 and (os.environ.get("B200_TP_MULTIMEM", "1" if world >= 4 else "0") != "0")
+                if mode == 2 and (os.environ.get("B200_TP_MULTIMEM", "0") != "0")
                 else "plain peer loads and stores"))
             if fused else "all-reduce per block")
+        if fused and os.environ.get("B200_TP_PIPELINE", "1" if world >= 4 else "0") != "0" and batch % 2 == 0:
+            line["config"]["exchange"] += ("; two halves of the batch in flight: the exchange of one half runs on a "
+                                           "second stream beside the other half's GEMMs and attention")
         line["exchange_ms_per_step"] = prof["allreduce"]["ms"] / args.steps
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         sample_b = 1

@@ -417,11 +417,10 @@ __device__ __forceinline__ void rownorm_load(RowRegs<T, NW, NCH>& g, const PeerP
 }
 
 template <typename T, int NW, int NCH, bool PREFETCH>
-__global__ void __launch_bounds__(256, 2) peer_rownorm_kernel(PeerPtrs pp, int rank, int world, size_t part_off,
-                                                              size_t xb_off, int rows, int row0, int d,
-                                                              float* __restrict__ x_own, const float* __restrict__ gain,
-                                                              float eps, uint32_t epoch, uint32_t* status,
-                                                              long long budget, int dbg) {
+__device__ __forceinline__ void rownorm_body(const PeerPtrs& pp, int rank, int world, size_t part_off, size_t xb_off,
+                                             int rows, int row0, int d, float* __restrict__ x_own,
+                                             const float* __restrict__ gain, float eps, uint32_t epoch,
+                                             uint32_t* status, long long budget, int dbg) {
   constexpr int E = 16 / sizeof(T);  // elements per 16-byte chunk
   constexpr bool REDUCE = NW > 0;
   const int only = (dbg & 1) ? rank : -1;  // measurement aid: every load from this rank's own buffer
@@ -511,6 +510,30 @@ __global__ void __launch_bounds__(256, 2) peer_rownorm_kernel(PeerPtrs pp, int r
   }
   __syncthreads();
   if (s_last && ok) wait_all_peers(my_flags, kDoneBase, world, epoch, status, budget);
+}
+
+template <typename T, int NW, int NCH, bool PREFETCH>
+__global__ void __launch_bounds__(256, 2) peer_rownorm_kernel(PeerPtrs pp, int rank, int world, size_t part_off,
+                                                              size_t xb_off, int rows, int row0, int d,
+                                                              float* __restrict__ x_own, const float* __restrict__ gain,
+                                                              float eps, uint32_t epoch, uint32_t* status,
+                                                              long long budget, int dbg) {
+  rownorm_body<T, NW, NCH, PREFETCH>(pp, rank, world, part_off, xb_off, rows, row0, d, x_own, gain, eps, epoch, status,
+                                     budget, dbg);
+}
+
+// The same kernel held to 96 registers and launched with one CTA per SM: the form that runs BESIDE the compute
+// kernels of the other half of the batch (a GEMM CTA of 192 threads or an attention CTA of 320 leaves that many
+// registers and about 1.5 KB of shared memory on its SM), so that the exchange of one half crosses NVLink while the
+// other half computes.
+template <typename T, int NW, int NCH>
+__global__ void __maxnreg__(96) peer_rownorm_lean_kernel(PeerPtrs pp, int rank, int world, size_t part_off,
+                                                         size_t xb_off, int rows, int row0, int d,
+                                                         float* __restrict__ x_own, const float* __restrict__ gain,
+                                                         float eps, uint32_t epoch, uint32_t* status, long long budget,
+                                                         int dbg) {
+  rownorm_body<T, NW, NCH, false>(pp, rank, world, part_off, xb_off, rows, row0, d, x_own, gain, eps, epoch, status,
+                                  budget, dbg);
 }
 
 // ---- the same exchange through the NVLink switch (multimem) -----------------------------------------------------
@@ -689,13 +712,21 @@ bool comm_peer_rowshard_buffers(void* comm, size_t bytes_each, void** part, void
 
 int32_t comm_peer_reduce_norm(void* comm, int T, int d, int dtype, bool reduce, float* x_own, const float* gain,
                               float eps, cudaStream_t stream) {
+  const size_t each = align_up((size_t)T * d * (dtype == B200_BF16 ? 2 : 4), 256);
+  return comm_peer_reduce_norm_at(comm, T, d, dtype, reduce, x_own, gain, eps, 0, each, false, stream);
+}
+
+// The exchange over `T` rows whose partial products start `part_rel` bytes and whose gathered rows start `xb_rel`
+// bytes into the row-shard area of every rank's exchange memory.  lean: the form that runs beside compute kernels
+// (one CTA per SM, 96 registers).
+int32_t comm_peer_reduce_norm_at(void* comm, int T, int d, int dtype, bool reduce, float* x_own, const float* gain,
+                                 float eps, size_t part_rel, size_t xb_rel, bool lean, cudaStream_t stream) {
   Comm* c = reinterpret_cast<Comm*>(comm);
   if (!c || !c->pm.on) return fail(B200_ERR_INVALID_ARG, "peer memory is not set up for this communicator");
   const size_t es = dtype == B200_BF16 ? 2 : 4;
   if (T % c->world || ((size_t)d * es) % 16 || d % 4)
     return fail(B200_ERR_BAD_SHAPE, "row-sharded exchange: %d rows over %d ranks, row of %d elements", T, c->world, d);
   B200_TRY(reject_capture(stream, "the tensor-parallel exchange over peer memory"));
-  const size_t each = align_up((size_t)T * d * es, 256);
   ProfScope prof(PROF_COMM, (double)T * d * es, stream);
   PeerPtrs pp;
   for (int r = 0; r < kMaxPeers; ++r) {
@@ -704,8 +735,8 @@ int32_t comm_peer_reduce_norm(void* comm, int T, int d, int dtype, bool reduce, 
   }
   const uint32_t epoch = ++c->pm.epoch;
   const int rows = T / c->world, row0 = c->rank * rows;
-  const size_t part_off = 2 * kOneShotMaxBytes, xb_off = part_off + each;
-  int grid = sm_count() * 2;  // two CTAs of 256 threads are resident per SM (register tile of the row)
+  const size_t part_off = 2 * kOneShotMaxBytes + part_rel, xb_off = 2 * kOneShotMaxBytes + xb_rel;
+  int grid = sm_count() * (lean ? 1 : 2);  // two CTAs of 256 threads are resident per SM (register tile of the row)
   if (grid > rows) grid = rows;
   uint32_t* status = device_status_word();
   const int n_chunks = (int)((size_t)d * es / 16);
@@ -717,9 +748,9 @@ int32_t comm_peer_reduce_norm(void* comm, int T, int d, int dtype, bool reduce, 
   // way instead of 2 (world - 1) / world); between two ranks it only adds the loop through the switch (measured
   // 200 us against 118 us per exchange of 64 MiB).  B200_TP_MULTIMEM = 0 / 1 forces the choice.
   static const int mc_env = env_int("B200_TP_MULTIMEM", -1);
-  const bool use_mc = mc_env >= 0 ? mc_env != 0 : c->world >= 4;
+  const bool use_mc = mc_env >= 0 ? mc_env != 0 : false;
   if (c->pm.mc && use_mc) {
-    int grid_mc = sm_count() * 4;
+    int grid_mc = sm_count() * (lean ? 1 : 4);
     if (grid_mc > rows) grid_mc = rows;
 #define B200_ROWNORM_MC(TT, NCH)                                                                                    \
   do {                                                                                                              \
@@ -748,7 +779,11 @@ int32_t comm_peer_reduce_norm(void* comm, int T, int d, int dtype, bool reduce, 
   const bool prefetch = pf_env >= 0 ? pf_env != 0 : regs_row <= 72;
 #define B200_ROWNORM(TT, NW, NCH)                                                                                    \
   do {                                                                                                               \
-    if (prefetch)                                                                                                    \
+    if (lean)                                                                                                        \
+      peer_rownorm_lean_kernel<TT, NW, NCH><<<grid, 256, 0, stream>>>(pp, c->rank, c->world, part_off, xb_off, rows, \
+                                                                      row0, d, x_own, gain, eps, epoch, status,      \
+                                                                      c->wait_budget, dbg);                          \
+    else if (prefetch)                                                                                               \
       peer_rownorm_kernel<TT, NW, NCH, true><<<grid, 256, 0, stream>>>(pp, c->rank, c->world, part_off, xb_off, rows, \
                                                                        row0, d, x_own, gain, eps, epoch, status,     \
                                                                        c->wait_budget, dbg);                         \

@@ -44,11 +44,14 @@ template <int BN, int KIND> struct PairCfg {
   // pipeline stage, which the short mainloops (K = 768, 192-column tiles) need more than a deep epilogue.
   static constexpr int kBufs = KIND == EPI_SWIGLU ? 6 : (KIND == EPI_RESID ? (BN == 192 ? 3 : 2) : 2);
   static constexpr int kStagingBytes = 4 * kBufs * kBufBytes;
-  static constexpr int kBudget = 227 * 1024 - 2048 - kStagingBytes;  // 1 KB alignment slack, 1 KB barriers
+  // 1 KB alignment slack + 512 B of barriers; what is left of the SM's 228 KB (1.5 KB beside this CTA's own reserved
+  // kilobyte) lets a small CTA of another kernel - the exchange of the other half of a tensor-parallel batch - run
+  // on the same SM
+  static constexpr int kBudget = 227 * 1024 - 1536 - kStagingBytes;
   static constexpr int kStages = kBudget / kStageBytes > 8 ? 8 : kBudget / kStageBytes;
   static constexpr int kAccStride = BN == 192 ? 256 : BN;  // TMEM columns between the two accumulators
   static constexpr int kTmemCols = 2 * kAccStride;         // a power of two, as the allocator wants
-  static constexpr int kSmemBytes = kStages * kStageBytes + kStagingBytes + 2048;
+  static constexpr int kSmemBytes = kStages * kStageBytes + kStagingBytes + 1536;
 };
 
 enum : uint32_t { ST_PAIR_PRODUCER = 1u << 8, ST_PAIR_MMA = 1u << 9, ST_PAIR_EPILOGUE = 1u << 10 };
@@ -492,8 +495,9 @@ int pair_tile_width(int M, int N) {
   int bn = 128;
   const int widths[3] = {256, 192, 128};
   for (int w : widths) {
-    if (N % w) continue;
-    long cost = (long)cdiv((int)(mt * (N / w)), pairs) * w * 2;
+    // a width that does not divide N leaves a partly empty last column of tiles; its columns are computed and
+    // dropped, which the round count below already charges
+    long cost = (long)cdiv((int)(mt * cdiv(N, w)), pairs) * w * 2;
     if (w == 128) cost = cost * 3 / 2;
     if (best < 0 || cost < best) { best = cost; bn = w; }
   }
@@ -587,7 +591,7 @@ template <int KIND, typename TOut>
 int32_t launch_pair_bn(const GemmArgs& g, cudaStream_t stream) {
   static const int forced = env_int("B200_PAIR_BN", 0);  // tuning knob: 128, 192 or 256 overrides the choice below
   int bn = pair_tile_width(g.M, g.N);
-  if (forced == 128 || (forced == 192 && g.N % 192 == 0) || (forced == 256 && g.N % 256 == 0)) bn = forced;
+  if (forced == 128 || forced == 192 || forced == 256) bn = forced;
   if (bn == 256) return launch_pair_cfg<256, KIND, TOut>(g, stream);
   if (bn == 192) return launch_pair_cfg<192, KIND, TOut>(g, stream);
   return launch_pair_cfg<128, KIND, TOut>(g, stream);
@@ -609,7 +613,8 @@ int32_t launch_pair_kind(const GemmArgs& g, cudaStream_t stream) {
 // The pair kernel takes K-major operands and problems with enough 256-row tiles to occupy every SM pair.
 bool gemm_tc2_supports(const GemmArgs& g) {
   if (!gemm_tc_supports(g) || g.ta || g.tb) return false;
-  if (g.N % 128) return false;
+  // the epilogue stores whole boxes: 32 fp32 columns, 64 bf16 columns (SwiGLU: 64 accumulator columns -> 32 outputs)
+  if (g.N < 128 || g.N % (g.out_dtype == B200_F32 && g.kind != EPI_SWIGLU ? 32 : 64)) return false;
   // the staged epilogue writes whole tiles through TMA: no read-modify-write, 16-byte aligned rows
   if (g.kind == EPI_STORE && g.epi.accumulate) return false;
   if (g.kind == EPI_RESID && (g.out_dtype != B200_F32 || !g.epi.resid_in || !aligned16(g.epi.resid_in))) return false;
@@ -617,7 +622,7 @@ bool gemm_tc2_supports(const GemmArgs& g) {
   const int oes = g.out_dtype == B200_F32 ? 4 : 2;
   if (!aligned16(g.epi.out) || ((size_t)g.epi.ldo * oes) % 16) return false;
   if (g.kind == EPI_SWIGLU && g.epi.out_gate && (!aligned16(g.epi.out_gate) || !aligned16(g.epi.out_up))) return false;
-  const long tiles = (long)cdiv(g.M, 2 * PM) * (g.N / pair_tile_width(g.M, g.N));
+  const long tiles = (long)cdiv(g.M, 2 * PM) * cdiv(g.N, pair_tile_width(g.M, g.N));
   return g.M >= 2 * PM && tiles >= sm_count() / 2;
 }
 

@@ -31,7 +31,13 @@ static void carve_backward(const B200Plan& p, Arena& a, int B, int S, BwdWs* w) 
   w->delta = a.take<float>((size_t)B * p.H * S * 4);
   w->n_parts = rmsnorm_bwd_parts((int)T);
   w->dg_part = a.take<float>((size_t)w->n_parts * p.d * 4);
-  w->splitk_bytes = (size_t)64 << 20;  // K-split partials of the weight-gradient GEMMs
+  // K-split partials of the weight-gradient GEMMs: room for at least one full fp32 copy of the largest gradient
+  // (the classifier's, V x d), so that every weight gradient can take the K-range kernel
+  w->splitk_bytes = (size_t)64 << 20;
+  const size_t largest = align_up((size_t)p.V * p.d * 4, 256);
+  const size_t widest = align_up((size_t)2 * p.h * p.d * 4, 256);
+  if (w->splitk_bytes < largest) w->splitk_bytes = largest;
+  if (w->splitk_bytes < widest) w->splitk_bytes = widest;
   w->splitk = a.take(w->splitk_bytes);
 }
 

@@ -300,6 +300,127 @@ static int32_t forward_row_sharded(B200Plan* p, const int32_t* tokens, int B, in
   return B200_OK;
 }
 
+// The row-sharded forward over TWO halves of the batch whose exchanges overlap the other half's compute.  Half h
+// holds the sequences [h B/2, (h+1) B/2); each half has its own partial-product and gathered-activation regions and
+// its own T/(2 tp) residual rows per rank.  Compute kernels run on the caller's stream, the exchange kernels - in one
+// fixed order on every rank, which is what their flag protocol needs - on the plan's communication stream in their
+// lean form (one small CTA per SM, which fits beside a GEMM or attention CTA):
+//   compute:  QKV_0 ATT_0 WO_0 | QKV_1 ATT_1 WO_1 | W13_0 W2_0 | W13_1 W2_1 | next layer ...
+//   exchange:              EX1_0 ............ EX1_1 ....... EX2_0 ....... EX2_1 ...
+// so every exchange crosses NVLink while the tensor cores work on the other half.  Events order the two streams:
+// part_ready[h] (a projection left its partial product) and xb_ready[h] (the gathered rows of half h are whole).
+static int32_t forward_row_sharded_pipelined(B200Plan* p, const int32_t* tokens, int B, int S, const uint8_t* w,
+                                             const PackedLayout& wl, float* logits, void* kv_out, const LayerActs& a,
+                                             void* part, void* xbg, cudaStream_t stream) {
+  const int Bh = B / 2, Th = Bh * S, T = B * S, d = p->d, dl = p->d_loc, hl = p->h_loc;
+  const int rows = Th / p->tp_size, row0 = p->tp_rank * rows;
+  const size_t es = p->esize;
+  const float* g_att = reinterpret_cast<const float*>(w + wl.g_att);
+  const float* g_ffn = reinterpret_cast<const float*>(w + wl.g_ffn);
+  const float* g_fin = reinterpret_cast<const float*>(w + wl.g_final);
+  const float eps = p->cfg.rms_eps;
+  cudaStream_t cs = p->comm_stream;
+  const size_t half_bytes = align_up((size_t)Th * d * es, 256);
+  const size_t each = align_up((size_t)T * d * es, 256);  // the gathered area starts where it does for the whole batch
+  auto part_rel = [&](int h) { return (size_t)h * half_bytes; };
+  auto xb_rel = [&](int h) { return each + (size_t)h * half_bytes; };
+  auto part_h = [&](int h) { return reinterpret_cast<uint8_t*>(part) + part_rel(h); };
+  auto xb_h = [&](int h) { return reinterpret_cast<uint8_t*>(part) + xb_rel(h); };
+  (void)xbg;
+  auto rowsz = [&](int cols) { return (size_t)Th * cols * es; };
+  float* x_own[2] = {a.x_in, a.x_in + (size_t)rows * d};  // [rows, d] per half, inside the workspace's [T, d]
+  cudaEvent_t* part_ready = p->ev_fork;  // [h]
+  cudaEvent_t* xb_ready = p->ev_join;    // [h]
+  auto exchange = [&](int h, bool reduce, const float* gain) -> int32_t {
+    // on the communication stream, after the projection of half h has left its partial product
+    if (reduce) {
+      B200_CUDA_OK(cudaEventRecord(part_ready[h], stream));
+      B200_CUDA_OK(cudaStreamWaitEvent(cs, part_ready[h], 0));
+    }
+    B200_TRY(comm_peer_reduce_norm_at(p->comm, Th, d, p->dtype, reduce, x_own[h], gain, eps, part_rel(h), xb_rel(h),
+                                      /*lean=*/true, cs));
+    B200_CUDA_OK(cudaEventRecord(xb_ready[h], cs));
+    return B200_OK;
+  };
+  auto wait_xb = [&](int h) -> int32_t {
+    B200_CUDA_OK(cudaStreamWaitEvent(stream, xb_ready[h], 0));
+    return B200_OK;
+  };
+  // the communication stream starts behind everything the caller has queued (tokens, the previous call's readers)
+  B200_CUDA_OK(cudaEventRecord(p->ev_fork[2], stream));
+  B200_CUDA_OK(cudaStreamWaitEvent(cs, p->ev_fork[2], 0));
+  for (int h = 0; h < 2; ++h) {
+    // the embedding rows of this rank's share of half h; the first norm has no partial sums
+    B200_TRY(launch_embed(tokens + (size_t)h * Th + row0, w + wl.emb, p->dtype, x_own[h], rows, d, p->V, cs));
+    B200_TRY(exchange(h, false, g_att));
+  }
+  uint8_t* qkv = reinterpret_cast<uint8_t*>(a.qkv);
+  uint8_t* o = reinterpret_cast<uint8_t*>(a.o);
+  uint8_t* hg = reinterpret_cast<uint8_t*>(a.hg);
+  for (int l = 0; l < p->L; ++l) {
+    const LayerOffsets& lo = wl.layer[l];
+    for (int h = 0; h < 2; ++h) {
+      uint8_t* qkv_h = qkv + h * rowsz(3 * dl);
+      uint8_t* o_h = o + h * rowsz(dl);
+      B200_TRY(wait_xb(h));
+      {
+        EpiParams e;
+        e.out = qkv_h; e.ldo = 3 * dl;
+        e.rope_cos = p->rope_cos; e.rope_sin = p->rope_sin;
+        e.seq_len = S; e.pos_base = 0; e.head_size = p->hs; e.rope_cols = 2 * dl;
+        B200_TRY(gemm(*p, xb_h(h), d, w + lo.wqkv, d, Th, 3 * dl, d, EPI_ROPE, p->dtype, e, stream));
+      }
+      if (kv_out) {
+        // kv_out [L, 2, B, S, d_loc]: rotated keys and values of this layer, rows of half h
+        uint8_t* dst = reinterpret_cast<uint8_t*>(kv_out) + ((size_t)l * 2 * T + (size_t)h * Th) * dl * es;
+        for (int part_i = 0; part_i < 2; ++part_i)
+          B200_CUDA_OK(cudaMemcpy2DAsync(dst + (size_t)part_i * T * dl * es, (size_t)dl * es,
+                                         qkv_h + (size_t)(1 + part_i) * dl * es, (size_t)3 * dl * es, (size_t)dl * es, Th,
+                                         cudaMemcpyDeviceToDevice, stream));
+      }
+      {
+        AttnArgs at;
+        at.q = qkv_h; at.k = qkv_h + (size_t)dl * es; at.v = qkv_h + (size_t)2 * dl * es;
+        at.o = o_h; at.lse = a.lse + (size_t)h * Bh * p->H_loc * S;
+        at.batch = Bh; at.seq = S; at.n_heads = p->H_loc; at.head_size = p->hs;
+        at.ldq = 3 * dl; at.ldkv = 3 * dl; at.ldo = dl; at.dtype = p->dtype;
+        B200_TRY(launch_attn_fwd(at, p->attn_impl, stream));
+      }
+      {
+        EpiParams e;
+        e.out = part_h(h); e.ldo = d;
+        B200_TRY(gemm(*p, o_h, dl, w + lo.wo, dl, Th, d, dl, EPI_STORE, p->dtype, e, stream));
+      }
+      B200_TRY(exchange(h, true, g_ffn + (size_t)l * d));
+    }
+    for (int h = 0; h < 2; ++h) {
+      uint8_t* hg_h = hg + h * rowsz(hl);
+      B200_TRY(wait_xb(h));
+      {
+        EpiParams e;
+        e.out = hg_h; e.ldo = hl;
+        B200_TRY(gemm(*p, xb_h(h), d, w + lo.w13, d, Th, 2 * hl, d, EPI_SWIGLU, p->dtype, e, stream));
+      }
+      {
+        EpiParams e;
+        e.out = part_h(h); e.ldo = d;
+        B200_TRY(gemm(*p, hg_h, hl, w + lo.w2, hl, Th, d, hl, EPI_STORE, p->dtype, e, stream));
+      }
+      const float* g_next = l + 1 < p->L ? g_att + (size_t)(l + 1) * d : g_fin;
+      B200_TRY(exchange(h, true, g_next));
+    }
+  }
+  for (int h = 0; h < 2; ++h) {
+    B200_TRY(wait_xb(h));
+    if (logits) {
+      EpiParams e;
+      e.out = logits + (size_t)h * Th * p->V_loc; e.ldo = p->V_loc;
+      B200_TRY(gemm(*p, xb_h(h), d, w + wl.wcls, d, Th, p->V_loc, d, EPI_STORE, B200_F32, e, stream));
+    }
+  }
+  return B200_OK;
+}
+
 static int32_t forward_impl(B200Plan* p, const int32_t* tokens, int B, int S, const uint8_t* w, const PackedLayout& wl,
                             float* logits, void* saved, void* kv_out, void* ws, size_t ws_bytes,
                             cudaStream_t stream) {
@@ -317,8 +438,13 @@ static int32_t forward_impl(B200Plan* p, const int32_t* tokens, int B, int S, co
   if (wa.used > ws_bytes) return fail(B200_ERR_WORKSPACE, "forward needs %zu workspace bytes, got %zu", wa.used, ws_bytes);
   if (p->tp_size > 1 && !keep && T % p->tp_size == 0 && p->row_shard) {
     void *part = nullptr, *xbg = nullptr;
-    if (comm_peer_rowshard_buffers(p->comm, (size_t)T * p->d * p->esize, &part, &xbg))
+    if (comm_peer_rowshard_buffers(p->comm, (size_t)T * p->d * p->esize, &part, &xbg)) {
+      // two halves of the batch in flight when the batch splits into two equal sets of sequences whose rows divide
+      // over the ranks
+      if (p->tp_pipeline && B % 2 == 0 && (B / 2 * S) % p->tp_size == 0 && ((size_t)(B / 2) * S * p->d * p->esize) % 256 == 0)
+        return forward_row_sharded_pipelined(p, tokens, B, S, w, wl, logits, kv_out, acts.layer[0], part, xbg, stream);
       return forward_row_sharded(p, tokens, B, S, w, wl, logits, kv_out, acts.layer[0], part, xbg, stream);
+    }
   }
 
   const float* g_att = reinterpret_cast<const float*>(w + wl.g_att);
@@ -501,6 +627,10 @@ int32_t b200_plan_create(const B200LlamaConfig* cfg, int32_t tp_rank, int32_t tp
     // Chunked projections with the all-reduce of chunk c overlapping the GEMM of chunk c+1 measured SLOWER
     // than one all-reduce per block on 4 GPUs (45.3 ms vs 48.9 / 54.1 ms for 2 / 4 chunks), so the default is 1.
     p->row_shard = env_int("B200_TP_ROW_SHARD", 1) != 0;
+    // Two halves in flight pay from four ranks on (measured at the 7B shape: 30.1 against 34.0 ms per step at four
+    // ranks; at two ranks the exchange is a sixth of the step and the compute kernels lose more to the kernel running
+    // beside them than the overlap wins: 61.0 against 54.5 ms).  B200_TP_PIPELINE = 0 / 1 forces the choice.
+    p->tp_pipeline = env_int("B200_TP_PIPELINE", tp_size >= 4 ? 1 : 0) != 0;
     p->reserve_sms = env_int("B200_TP_RESERVE_SMS", 0);
     p->tp_chunks = env_int("B200_TP_CHUNKS", 1);
     if (p->tp_chunks < 1) p->tp_chunks = 1;

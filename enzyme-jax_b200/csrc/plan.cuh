@@ -82,6 +82,7 @@ struct B200Plan {
   cudaEvent_t ev_fork[8] = {}, ev_join[8] = {};
   int reserve_sms = 0;
   int tp_chunks = 1;
+  bool tp_pipeline = true;  // ... and runs two halves of the batch so that one half's exchange overlaps the other's compute
   bool row_shard = true;  // tensor-parallel prefill keeps T/tp residual rows per rank when peer memory is up
   float* rope_cos = nullptr;  // [seq_len, hs/2], owned by the plan
   float* rope_sin = nullptr;
@@ -111,6 +112,8 @@ int32_t comm_peer_allreduce_add(void* comm, size_t count, int dtype, const float
 bool comm_peer_rowshard_buffers(void* comm, size_t bytes_each, void** part, void** xb);
 int32_t comm_peer_reduce_norm(void* comm, int T, int d, int dtype, bool reduce, float* x_own, const float* gain,
                               float eps, cudaStream_t stream);
+int32_t comm_peer_reduce_norm_at(void* comm, int T, int d, int dtype, bool reduce, float* x_own, const float* gain,
+                                 float eps, size_t part_rel, size_t xb_rel, bool lean, cudaStream_t stream);
 int32_t launch_peer_wait_selftest(long long budget, uint32_t* reached_end, cudaStream_t stream);
 
 // Environment knobs (read once at plan creation): B200_GEMM_IMPL and

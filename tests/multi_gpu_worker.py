@@ -56,6 +56,23 @@ def main():
             except B.B200Error as e:
                 assert e.status == 10
         plan.close()
+    # an odd batch (cannot be split into two halves), and an even batch with the two-half pipeline forced on
+    for env_off, nb in ((None, 3), ("B200_TP_PIPELINE", 2)):
+        if env_off:
+            os.environ[env_off] = "1"   # the two-half pipeline is the default from four ranks on: force it here
+        w = {k: v.bfloat16() for k, v in O.make_weights(cfg, 3, torch.float32, std=0.05).items()}
+        tokens = O.make_tokens(cfg, nb, 128, 4)
+        ref = O.forward_sequence(tokens, cfg, {k: v.double() for k, v in w.items()})
+        plan = B.Plan(cfg, torch.bfloat16, tp_rank=rank, tp_size=world, comm=comm)
+        plan.pack_weights({k: v.cuda().contiguous() for k, v in w.items()})
+        got = plan.forward(tokens.int().cuda())
+        torch.cuda.synchronize()
+        vl = cfg["vocab_size"] // world
+        err = float((got.double().cpu() - ref[..., rank * vl:(rank + 1) * vl]).abs().max() / ref.abs().max())
+        assert err < 2e-2, ("tp forward, pipeline forced on" if env_off else "tp forward, odd batch", err)
+        plan.close()
+        if env_off:
+            del os.environ[env_off]
     # the same forward through the all-reduce per block (row sharding off): the path taken when peer memory is absent
     os.environ["B200_TP_ROW_SHARD"] = "0"
     w = {k: v.bfloat16() for k, v in O.make_weights(cfg, 3, torch.float32, std=0.05).items()}
@@ -70,7 +87,8 @@ def main():
     assert err < 2e-2, ("tp forward, all-reduce path", err)
     plan.close()
     del os.environ["B200_TP_ROW_SHARD"]
-    # long enough for the chunked projection + overlapped all-reduce path (4 chunks of 512 tokens)
+    # 2 x 1024 tokens, with the two-half pipeline on (the form four ranks and more run by default)
+    os.environ["B200_TP_PIPELINE"] = "1"
     cfg_long = dict(cfg, seq_len=1024)
     w = {k: v.bfloat16() for k, v in O.make_weights(cfg_long, 8, torch.float32, std=0.05).items()}
     tokens = O.make_tokens(cfg_long, 2, 1024, 9)
@@ -92,6 +110,7 @@ def main():
     assert err < 2e-2, ("tp forward, 2000 tokens", err)
     assert B.device_status() == 0
     plan.close()
+    del os.environ["B200_TP_PIPELINE"]
     # data parallel: each rank differentiates its own sequences, gradients are summed over the ranks
     dtype = torch.float32
     w = O.make_weights(cfg, 5, torch.float32, std=0.05, gains_one=False)

@@ -25,7 +25,10 @@ def _ints(shape, seed, lo=-2, hi=3, dtype=torch.bfloat16):
                                    # large enough for the CTA-pair kernel (256-row tiles), with M and K tails
                                    (4096, 768, 2048), (8192, 1024, 256), (5000, 1536, 704), (8192, 32000, 64),
                                    # 192-column pair tiles (N = 768, 1152), with an M tail
-                                   (8192, 768, 512), (8000, 1152, 192)])
+                                   (8192, 768, 512), (8000, 1152, 192),
+                                   # widths that no tile width divides (per-rank widths of 8-way tensor parallelism:
+                                   # 2 x 11008 / 8 = 2752, 32000 / 8 = 4000): a partly filled last column of tiles
+                                   (8192, 2752, 256), (4096, 4000, 128), (8192, 1376, 192), (8192, 2720, 64)])
 def test_gemm_bf16_exact_on_small_integers(impl, M, N, K):
     # integer operands in [-2,2]: every product and partial sum is exact in fp32
     a, b = _ints((M, K), 1), _ints((N, K), 2)
@@ -35,7 +38,7 @@ def test_gemm_bf16_exact_on_small_integers(impl, M, N, K):
     assert torch.equal(y, ref)
 
 
-@pytest.mark.parametrize("M,N", [(8192, 768), (8192, 1024), (8000, 1152), (8192, 640)])
+@pytest.mark.parametrize("M,N", [(8192, 768), (8192, 1024), (8000, 1152), (8192, 640), (8192, 2752), (8192, 1472)])
 def test_pair_gemm_bf16_output_exact(M, N):
     # K = 64 and operands in [-2,2]: |sums| <= 256, exact in bf16, so the staged bf16 store path is checked bit for bit
     a, b = _ints((M, 64), 3), _ints((N, 64), 4)

@@ -268,3 +268,20 @@ def test_forward_and_vjp_bf16_on_ragged_shapes():
     torch.cuda.synchronize()
     assert B.device_status() == 0
     assert _norm_rel(got, ref) < 2e-2
+
+
+def test_forward_bf16_with_widths_no_tile_divides():
+    """hidden 1376 and vocabulary 4000 are the per-rank widths of the 7B shape under 8-way tensor parallelism: the
+    gate|up product is 2752 columns wide and the logits 4000, which no tile width of the CTA-pair GEMM divides (a partly
+    filled last column of tiles, through the SwiGLU and the fp32 epilogues).  8192 tokens so that those GEMMs run."""
+    cfg = dict(dim=256, hidden_dim=1376, n_layers=1, n_heads=4, n_kv_heads=4, vocab_size=4000, seq_len=1024)
+    w = O.make_weights(cfg, 31, torch.float32, std=0.05)
+    wb = {k: v.bfloat16() for k, v in w.items()}
+    tokens = O.make_tokens(cfg, 8, 1024, 32)
+    with torch.no_grad():
+        ref = O.forward_sequence(tokens, cfg, {k: v.float() for k, v in wb.items()})
+    p = _plan(cfg, wb, torch.bfloat16)
+    got = p.forward(tokens.int().to(DEV))
+    torch.cuda.synchronize()
+    assert B.device_status() == 0
+    assert _norm_rel(got, ref) < 2e-2
