@@ -19,7 +19,7 @@ template <typename T, int HS>
 __global__ void __launch_bounds__(128) attn_fwd_simt_kernel(const T* __restrict__ q, const T* __restrict__ k,
                                                             const T* __restrict__ v, T* __restrict__ o,
                                                             float* __restrict__ lse, int seq, int n_heads, int ldq,
-                                                            int ldkv, int ldo, float scale) {
+                                                            int ldkv, int ldo, float scale, bool vec) {
   constexpr int DPT = HS / 4;  // dims per thread
   __shared__ float Ks[KB][HS];
   __shared__ float Vs[KB][HS];
@@ -39,20 +39,47 @@ __global__ void __launch_bounds__(128) attn_fwd_simt_kernel(const T* __restrict_
   float mx = -INFINITY, l = 0.f;
 
   const int last = min(t0 + QB, seq);  // keys needed by this CTA: [0, last)
+  // A K / V block travels global -> registers -> shared memory in 8-element pieces; the pieces of block i+1 are
+  // requested before the arithmetic of block i, so their round trip hides behind it.
+  constexpr int PIECES = KB * HS / 8, PER = (PIECES + 127) / 128;
+  float pk[PER][8], pv[PER][8];
+  auto fetch = [&](int u0) {
+#pragma unroll
+    for (int it = 0; it < PER; ++it) {
+      const int idx = tid + it * 128;
+      if (idx < PIECES) {
+        const int uu = idx / (HS / 8), d8 = (idx % (HS / 8)) * 8;
+        const int u = u0 + uu;
+        if (u < seq) {
+          const size_t off = (row0 + u) * ldkv + h * HS + d8;
+          if (vec) {
+            load8(k + off, pk[it]);
+            load8(v + off, pv[it]);
+          } else {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) { pk[it][j] = to_f32(k[off + j]); pv[it][j] = to_f32(v[off + j]); }
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) { pk[it][j] = 0.f; pv[it][j] = 0.f; }
+        }
+      }
+    }
+  };
+  fetch(0);
   for (int u0 = 0; u0 < last; u0 += KB) {
     __syncthreads();
-    for (int idx = tid; idx < KB * HS; idx += 128) {
-      const int uu = idx / HS, dd = idx % HS;
-      const int u = u0 + uu;
-      float kv = 0.f, vv = 0.f;
-      if (u < seq) {
-        kv = to_f32(k[(row0 + u) * ldkv + h * HS + dd]);
-        vv = to_f32(v[(row0 + u) * ldkv + h * HS + dd]);
+#pragma unroll
+    for (int it = 0; it < PER; ++it) {
+      const int idx = tid + it * 128;
+      if (idx < PIECES) {
+        const int uu = idx / (HS / 8), d8 = (idx % (HS / 8)) * 8;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) { Ks[uu][d8 + j] = pk[it][j]; Vs[uu][d8 + j] = pv[it][j]; }
       }
-      Ks[uu][dd] = kv;
-      Vs[uu][dd] = vv;
     }
     __syncthreads();
+    if (u0 + KB < last) fetch(u0 + KB);
     float s[KB];
     float bm = -INFINITY;
 #pragma unroll
@@ -94,7 +121,8 @@ int32_t launch_hs(const AttnArgs& a, cudaStream_t stream) {
   dim3 grid(cdiv(a.seq, QB), a.n_heads, a.batch);
   attn_fwd_simt_kernel<T, HS><<<grid, 128, 0, stream>>>((const T*)a.q, (const T*)a.k, (const T*)a.v, (T*)a.o, a.lse,
                                                         a.seq, a.n_heads, a.ldq, a.ldkv, a.ldo,
-                                                        1.f / sqrtf((float)a.head_size));
+                                                        1.f / sqrtf((float)a.head_size),
+                                                        aligned16(a.k) && aligned16(a.v) && a.ldkv % 8 == 0);
   B200_LAUNCH_OK("attn_fwd_simt_kernel");
   return B200_OK;
 }

@@ -246,6 +246,7 @@ __device__ __forceinline__ bool wait_all_peers(const uint32_t* my_flags, int bas
     const long long t0 = clock64();
     for (int r = 0; r < world && ok; ++r) {
       while ((int32_t)(flag_load_sys(my_flags + base + r) - epoch) < 0) {
+        __nanosleep(100);  // the waiting CTA may share its SM with a compute kernel: leave it the issue slots
         if (clock64() - t0 > budget) {
           ok = 0;
           atomicOr(status, ST_PEER_TIMEOUT);
@@ -522,12 +523,12 @@ __global__ void __launch_bounds__(256, 2) peer_rownorm_kernel(PeerPtrs pp, int r
                                      budget, dbg);
 }
 
-// The same kernel held to 96 registers and launched with one CTA per SM: the form that runs BESIDE the compute
-// kernels of the other half of the batch (a GEMM CTA of 192 threads or an attention CTA of 320 leaves that many
-// registers and about 1.5 KB of shared memory on its SM), so that the exchange of one half crosses NVLink while the
+// The same kernel held to 80 registers and launched with one CTA per SM: the form that runs BESIDE the compute
+// kernels of the other half of the batch (a GEMM CTA of 192 threads x 192 registers or an attention CTA of 320 x 128
+// leaves 24 K registers and about 1.5 KB of shared memory on its SM; 256 x 80 fits with room for the allocator's rounding), so that the exchange of one half crosses NVLink while the
 // other half computes.
 template <typename T, int NW, int NCH>
-__global__ void __maxnreg__(96) peer_rownorm_lean_kernel(PeerPtrs pp, int rank, int world, size_t part_off,
+__global__ void __maxnreg__(80) peer_rownorm_lean_kernel(PeerPtrs pp, int rank, int world, size_t part_off,
                                                          size_t xb_off, int rows, int row0, int d,
                                                          float* __restrict__ x_own, const float* __restrict__ gain,
                                                          float eps, uint32_t epoch, uint32_t* status, long long budget,
@@ -718,7 +719,7 @@ int32_t comm_peer_reduce_norm(void* comm, int T, int d, int dtype, bool reduce, 
 
 // The exchange over `T` rows whose partial products start `part_rel` bytes and whose gathered rows start `xb_rel`
 // bytes into the row-shard area of every rank's exchange memory.  lean: the form that runs beside compute kernels
-// (one CTA per SM, 96 registers).
+// (one CTA per SM, 80 registers).
 int32_t comm_peer_reduce_norm_at(void* comm, int T, int d, int dtype, bool reduce, float* x_own, const float* gain,
                                  float eps, size_t part_rel, size_t xb_rel, bool lean, cudaStream_t stream) {
   Comm* c = reinterpret_cast<Comm*>(comm);

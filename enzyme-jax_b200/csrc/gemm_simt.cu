@@ -28,8 +28,12 @@ template <typename TIn, typename TOut, int KIND, bool TA, bool TB, bool VEC, int
 __global__ void __launch_bounds__(NT) gemm_simt_kernel(const TIn* __restrict__ A, const TIn* __restrict__ B, int M,
                                                        int N, int K, int lda, int ldb, EpiParams ep) {
   constexpr int BM = 32 * RPT;
-  __shared__ __align__(16) float As[BK][BM + 4];
-  __shared__ __align__(16) float Bs[BK][BN + 4];
+  // k-elements per shared-memory tile.  The small-problem form (32-row tiles, a handful of CTAs per SM, 16 FMAs per
+  // k-step and thread) is bound by the round trip of each tile's global loads, so it takes 64 at a time: a 288-deep
+  // product is 5 trips instead of 18.
+  constexpr int BKT = RPT == 1 ? 64 : BK;
+  __shared__ __align__(16) float As[BKT][BM + 4];
+  __shared__ __align__(16) float Bs[BKT][BN + 4];
   const int tid = threadIdx.x;
   const int ty = tid >> 2, tx = tid & 3;
   const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
@@ -40,66 +44,71 @@ __global__ void __launch_bounds__(NT) gemm_simt_kernel(const TIn* __restrict__ A
 #pragma unroll
     for (int c = 0; c < 16; ++c) acc[r][c] = 0.f;
 
-  // Global loads of k-tile i+1 are issued before the FMAs of k-tile i and land in registers meanwhile; small
-  // problems (one or two CTAs of four warps per SM) would otherwise pay a full memory round trip per 16 k-steps.
-  constexpr int A_ITEMS = (2 * BM + NT - 1) / NT;  // 8-element pieces of the A tile per thread
-  float va[A_ITEMS][8], vb[8];
+  // Global loads of k-tile i+1 are issued before the FMAs of k-tile i and land in registers meanwhile.
+  constexpr int A_ITEMS = BM * BKT / 8 / NT;  // 8-element pieces of the A tile per thread
+  constexpr int B_ITEMS = BN * BKT / 8 / NT;
+  static_assert(BM * BKT % (8 * NT) == 0 && BN * BKT % (8 * NT) == 0, "tile pieces must divide over the threads");
+  float va[A_ITEMS][8], vb[B_ITEMS][8];
   auto fetch_tile = [&](int k0) {
 #pragma unroll
     for (int it = 0; it < A_ITEMS; ++it) {
       const int idx = tid + it * NT;
-      if (idx < 2 * BM) {
-        if constexpr (!TA) {
-          const int row = idx >> 1, k8 = (idx & 1) * 8;
-          fetch8<TIn, VEC>(A, lda, m0 + row, k0 + k8, M, K, va[it]);
-        } else {
-          const int k = idx / (BM / 8), m8 = (idx % (BM / 8)) * 8;
-          fetch8<TIn, VEC>(A, lda, k0 + k, m0 + m8, K, M, va[it]);
-        }
+      if constexpr (!TA) {
+        const int row = idx / (BKT / 8), k8 = (idx % (BKT / 8)) * 8;
+        fetch8<TIn, VEC>(A, lda, m0 + row, k0 + k8, M, K, va[it]);
+      } else {
+        const int k = idx / (BM / 8), m8 = (idx % (BM / 8)) * 8;
+        fetch8<TIn, VEC>(A, lda, k0 + k, m0 + m8, K, M, va[it]);
       }
     }
-    if constexpr (!TB) {
-      const int row = tid >> 1, k8 = (tid & 1) * 8;
-      fetch8<TIn, VEC>(B, ldb, n0 + row, k0 + k8, N, K, vb);
-    } else {
-      const int k = tid >> 3, n8 = (tid & 7) * 8;
-      fetch8<TIn, VEC>(B, ldb, k0 + k, n0 + n8, K, N, vb);
+#pragma unroll
+    for (int it = 0; it < B_ITEMS; ++it) {
+      const int idx = tid + it * NT;
+      if constexpr (!TB) {
+        const int row = idx / (BKT / 8), k8 = (idx % (BKT / 8)) * 8;
+        fetch8<TIn, VEC>(B, ldb, n0 + row, k0 + k8, N, K, vb[it]);
+      } else {
+        const int k = idx / (BN / 8), n8 = (idx % (BN / 8)) * 8;
+        fetch8<TIn, VEC>(B, ldb, k0 + k, n0 + n8, K, N, vb[it]);
+      }
     }
   };
   auto store_tile = [&]() {
 #pragma unroll
     for (int it = 0; it < A_ITEMS; ++it) {
       const int idx = tid + it * NT;
-      if (idx < 2 * BM) {
-        if constexpr (!TA) {
-          const int row = idx >> 1, k8 = (idx & 1) * 8;
+      if constexpr (!TA) {
+        const int row = idx / (BKT / 8), k8 = (idx % (BKT / 8)) * 8;
 #pragma unroll
-          for (int j = 0; j < 8; ++j) As[k8 + j][row] = va[it][j];
-        } else {
-          const int k = idx / (BM / 8), m8 = (idx % (BM / 8)) * 8;
+        for (int j = 0; j < 8; ++j) As[k8 + j][row] = va[it][j];
+      } else {
+        const int k = idx / (BM / 8), m8 = (idx % (BM / 8)) * 8;
 #pragma unroll
-          for (int j = 0; j < 8; ++j) As[k][m8 + j] = va[it][j];
-        }
+        for (int j = 0; j < 8; ++j) As[k][m8 + j] = va[it][j];
       }
     }
-    if constexpr (!TB) {
-      const int row = tid >> 1, k8 = (tid & 1) * 8;
 #pragma unroll
-      for (int j = 0; j < 8; ++j) Bs[k8 + j][row] = vb[j];
-    } else {
-      const int k = tid >> 3, n8 = (tid & 7) * 8;
+    for (int it = 0; it < B_ITEMS; ++it) {
+      const int idx = tid + it * NT;
+      if constexpr (!TB) {
+        const int row = idx / (BKT / 8), k8 = (idx % (BKT / 8)) * 8;
 #pragma unroll
-      for (int j = 0; j < 8; ++j) Bs[k][n8 + j] = vb[j];
+        for (int j = 0; j < 8; ++j) Bs[k8 + j][row] = vb[it][j];
+      } else {
+        const int k = idx / (BN / 8), n8 = (idx % (BN / 8)) * 8;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) Bs[k][n8 + j] = vb[it][j];
+      }
     }
   };
 
   fetch_tile(0);
-  for (int k0 = 0; k0 < K; k0 += BK) {
+  for (int k0 = 0; k0 < K; k0 += BKT) {
     store_tile();
     __syncthreads();
-    if (k0 + BK < K) fetch_tile(k0 + BK);
-#pragma unroll
-    for (int k = 0; k < BK; ++k) {
+    if (k0 + BKT < K) fetch_tile(k0 + BKT);
+#pragma unroll 16
+    for (int k = 0; k < BKT; ++k) {
       float a[RPT];
 #pragma unroll
       for (int r = 0; r < RPT; ++r) a[r] = As[k][ty * RPT + r];
