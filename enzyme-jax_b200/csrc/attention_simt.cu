@@ -4,7 +4,7 @@
 // the fallback for head sizes the tensor-core kernel does not cover.
 //
 // A CTA of 128 threads owns 32 query rows of one (batch, head); 4 threads share
-// a row and split the head dimension (dims part, part+4, ...).  Keys and values
+// a row and split the head dimension in four contiguous quarters.  Keys and values
 // stream through shared memory in blocks of 32 rows with an online softmax.
 #include "attention.cuh"
 
@@ -20,9 +20,10 @@ __global__ void __launch_bounds__(128) attn_fwd_simt_kernel(const T* __restrict_
                                                             const T* __restrict__ v, T* __restrict__ o,
                                                             float* __restrict__ lse, int seq, int n_heads, int ldq,
                                                             int ldkv, int ldo, float scale, bool vec) {
-  constexpr int DPT = HS / 4;  // dims per thread
-  __shared__ float Ks[KB][HS];
-  __shared__ float Vs[KB][HS];
+  constexpr int DPT = HS / 4;  // dims per thread: [part * DPT, (part + 1) * DPT), read from shared memory 16 bytes at a time
+  static_assert(DPT % 4 == 0, "head size must be a multiple of 16");
+  __shared__ __align__(16) float Ks[KB][HS];
+  __shared__ __align__(16) float Vs[KB][HS];
   const int tid = threadIdx.x, r = tid >> 2, part = tid & 3;
   const int qblk = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
   const int t0 = qblk * QB;
@@ -33,7 +34,7 @@ __global__ void __launch_bounds__(128) attn_fwd_simt_kernel(const T* __restrict_
   float qr[DPT], acc[DPT];
 #pragma unroll
   for (int i = 0; i < DPT; ++i) {
-    qr[i] = row_ok ? to_f32(q[(row0 + t) * ldq + h * HS + part + 4 * i]) * scale : 0.f;
+    qr[i] = row_ok ? to_f32(q[(row0 + t) * ldq + h * HS + part * DPT + i]) * scale : 0.f;
     acc[i] = 0.f;
   }
   float mx = -INFINITY, l = 0.f;
@@ -86,7 +87,10 @@ __global__ void __launch_bounds__(128) attn_fwd_simt_kernel(const T* __restrict_
     for (int uu = 0; uu < KB; ++uu) {
       float d = 0.f;
 #pragma unroll
-      for (int i = 0; i < DPT; ++i) d = fmaf(qr[i], Ks[uu][part + 4 * i], d);
+      for (int i = 0; i < DPT; i += 4) {
+        const float4 k4 = *reinterpret_cast<const float4*>(&Ks[uu][part * DPT + i]);
+        d = fmaf(qr[i], k4.x, fmaf(qr[i + 1], k4.y, fmaf(qr[i + 2], k4.z, fmaf(qr[i + 3], k4.w, d))));
+      }
       d += __shfl_xor_sync(0xffffffffu, d, 1);
       d += __shfl_xor_sync(0xffffffffu, d, 2);
       s[uu] = (u0 + uu <= t && row_ok) ? d : -INFINITY;
@@ -103,7 +107,11 @@ __global__ void __launch_bounds__(128) attn_fwd_simt_kernel(const T* __restrict_
         const float p = exp_by_build(s[uu] - nm);
         l += p;
 #pragma unroll
-        for (int i = 0; i < DPT; ++i) acc[i] = fmaf(p, Vs[uu][part + 4 * i], acc[i]);
+        for (int i = 0; i < DPT; i += 4) {
+          const float4 v4 = *reinterpret_cast<const float4*>(&Vs[uu][part * DPT + i]);
+          acc[i] = fmaf(p, v4.x, acc[i]); acc[i + 1] = fmaf(p, v4.y, acc[i + 1]);
+          acc[i + 2] = fmaf(p, v4.z, acc[i + 2]); acc[i + 3] = fmaf(p, v4.w, acc[i + 3]);
+        }
       }
       mx = nm;
     }
@@ -111,7 +119,7 @@ __global__ void __launch_bounds__(128) attn_fwd_simt_kernel(const T* __restrict_
   if (row_ok) {
     const float inv = 1.f / l;
 #pragma unroll
-    for (int i = 0; i < DPT; ++i) o[(row0 + t) * ldo + h * HS + part + 4 * i] = from_f32<T>(acc[i] * inv);
+    for (int i = 0; i < DPT; ++i) o[(row0 + t) * ldo + h * HS + part * DPT + i] = from_f32<T>(acc[i] * inv);
     if (lse && part == 0) lse[((size_t)b * n_heads + h) * seq + t] = mx + __logf(l);
   }
 }
