@@ -35,6 +35,8 @@ C2 = dict(dim=768, hidden_dim=2048, n_layers=12, n_heads=12, n_kv_heads=12, voca
 C1 = dict(dim=288, hidden_dim=768, n_layers=6, n_heads=6, n_kv_heads=6, vocab_size=32000, seq_len=256)
 C4 = dict(dim=4096, hidden_dim=11008, n_layers=32, n_heads=32, n_kv_heads=32, vocab_size=32000, seq_len=2048)
 
+L2_BYTES = 126 * 1024 * 1024
+
 WORKLOADS = {
     # name: (config, dtype, batch per step, seq, description)
     "c2": (C2, "bf16", 8, 1024, "llama-110M prefill forward, batch 8 x 1024 tokens, bf16 weights/activations, fp32 accumulate"),
@@ -336,19 +338,32 @@ def synth_weights(cfg, dtype, device, seed=1):
     return w
 
 
-def timed(fn, steps, world, dist):
-    """K steps bracketed by barrier + synchronize, CUDA events on the current stream, max over ranks."""
-    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+def timed(fn, steps, world, dist, flush=None):
+    """K steps bracketed by barrier + synchronize, CUDA events on the current stream, max over ranks.
+    With `flush` (a callable that overwrites a buffer larger than L2) every step gets its own event pair and the
+    flush runs between the pairs, outside the time that is summed."""
     torch.cuda.synchronize()
     if world > 1:
         dist.barrier()
         torch.cuda.synchronize()
-    a.record()
-    for i in range(steps):
-        fn(i)
-    b.record()
-    torch.cuda.synchronize()
-    ms = torch.tensor([a.elapsed_time(b)], dtype=torch.float64, device="cuda")
+    if flush is None:
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for i in range(steps):
+            fn(i)
+        b.record()
+        torch.cuda.synchronize()
+        total = a.elapsed_time(b)
+    else:
+        pairs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
+        for i, (a, b) in enumerate(pairs):
+            flush()
+            a.record()
+            fn(i)
+            b.record()
+        torch.cuda.synchronize()
+        total = sum(a.elapsed_time(b) for a, b in pairs)
+    ms = torch.tensor([total], dtype=torch.float64, device="cuda")
     if world > 1:
         dist.barrier()
         dist.all_reduce(ms, op=dist.ReduceOp.MAX)
@@ -452,10 +467,16 @@ def run_prefill(args, rank, world, local, B, dist):
     if rank == 0:
         sampler.start()
         time.sleep(0.3)
+    # A working set (weights + logits) that L2 could hold from one step to the next is evicted between steps.
+    working_set = plan.packed.numel() + logits.numel() * 4
+    flush = None
+    if working_set < 2 * L2_BYTES:
+        flush_buf = torch.empty(2 * L2_BYTES, dtype=torch.uint8, device=dev)
+        flush = flush_buf.zero_
     l0 = B.launch_count()
-    ms = timed(step_resident, args.steps, world, dist)
+    ms = timed(step_resident, args.steps, world, dist, flush)
     launches = (B.launch_count() - l0) if not use_graph else launches_per_forward * args.steps
-    ms_e2e = timed(step_e2e, args.steps, world, dist)
+    ms_e2e = timed(step_e2e, args.steps, world, dist, flush)
     clocks = sampler.stop() if rank == 0 else None
 
     # per-kernel event timing over the same K steps (a second pass, eager launches: the event
@@ -504,8 +525,10 @@ def run_prefill(args, rank, world, local, B, dist):
         "scaling": "strong" if tp > 1 else "weak", "vs_baseline": None, "dtype": dname, "data": "synthetic",
         "config": {"workload": desc, "batch_per_rank": batch, "seq_len": seq,
                    "parallelism": f"tp{tp}" if tp > 1 else (f"replicas{world}" if world > 1 else "single"),
-                   "l2_policy": "working set per step (weights + 1.05 GB of logits) exceeds the 126 MB L2; "
-                                "token buffers rotate",
+                   "l2_policy": (f"working set per step (weights + logits, {working_set / 1e6:.0f} MB) exceeds the 126 MB "
+                                 "L2; token buffers rotate" if flush is None else
+                                 f"working set per step ({working_set / 1e6:.0f} MB) would fit the 126 MB L2: a 252 MB "
+                                 "buffer is overwritten between steps, outside the per-step event pairs that are summed"),
                    "launch": "cuda graph replay" if use_graph else "eager launches"},
         "e2e": {"value": e2e, "unit": "tokens/s", "h2d_bytes_per_step": batch * seq * 4,
                 "d2h_bytes_per_step": batch * plan.vocab_local * 4, "ms_per_step": ms_e2e / args.steps,
