@@ -406,6 +406,13 @@ def run_prefill(args, rank, world, local, B, dist):
         launches_per_forward = (B.launch_count() - l_before) // (2 * n_bufs)
     last_dev = torch.empty(batch, plan.vocab_local, dtype=torch.float32, device=dev)
 
+    # Tensor parallel: time the two forms of the exchange schedule before the warm-up and keep the faster one (all
+    # ranks agree on it); B200_TP_PIPELINE pins the choice instead.
+    tuned = None
+    if tp > 1 and comm.peer_memory() and "B200_TP_PIPELINE" not in os.environ \
+            and os.environ.get("B200_TP_ROW_SHARD", "1") != "0":
+        tuned = plan.tune_tensor_parallel(dev_tokens[0], logits)
+
     def step_resident(i):
         if use_graph:
             graphs[i % n_bufs].replay()
@@ -547,9 +554,14 @@ def run_prefill(args, rank, world, local, B, dist):
                 if mode == 2 and (os.environ.get("B200_TP_MULTIMEM", "0") != "0")
                 else "plain peer loads and stores"))
             if fused else "all-reduce per block")
-        if fused and os.environ.get("B200_TP_PIPELINE", "1" if world >= 4 else "0") != "0" and batch % 2 == 0:
+        if fused and plan.get_option("tp_pipeline") and batch % 2 == 0:
             line["config"]["exchange"] += ("; two halves of the batch in flight: the exchange of one half runs on a "
                                            "second stream beside the other half's GEMMs and attention")
+        elif fused:
+            line["config"]["exchange"] += "; one batch, the exchange between the kernels"
+        if tuned:
+            line["config"]["exchange"] += (f" (chosen by timing both before the warm-up: one batch "
+                                           f"{tuned['one_batch_ms']:.2f} ms, two halves {tuned['two_halves_ms']:.2f} ms)")
         line["exchange_ms_per_step"] = prof["allreduce"]["ms"] / args.steps
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         sample_b = 1

@@ -38,7 +38,7 @@ EXPORTS = (
     "b200_token_vjp_workspace_bytes", "b200_token_vjp", "b200_comm_init_rank_ex", "b200_comm_setup_peer_memory",
     "b200_comm_attach_memory", "b200_tp_exchange_buffers", "b200_tp_reduce_norm", "b200_token_forward",
     "b200_static_sizes", "b200_jvp_workspace_bytes", "b200_forward_jvp", "b200_token_jvp_workspace_bytes",
-    "b200_token_jvp",
+    "b200_token_jvp", "b200_plan_set_option", "b200_plan_get_option",
 )
 
 
@@ -95,6 +95,8 @@ def lib() -> ctypes.CDLL:
                                         POINTER(ctypes.c_int64)]
         l.b200_plan_create.argtypes = [POINTER(_Config), c_int32, c_int32, c_void_p, POINTER(c_void_p)]
         l.b200_plan_destroy.argtypes = [c_void_p]
+        l.b200_plan_set_option.argtypes = [c_void_p, c_char_p, c_int32]
+        l.b200_plan_get_option.argtypes = [c_void_p, c_char_p, POINTER(c_int32)]
         l.b200_packed_weight_bytes.argtypes = [c_void_p, c_int32, POINTER(c_size_t)]
         l.b200_packed_grad_bytes.argtypes = [c_void_p, POINTER(c_size_t)]
         l.b200_pack_weights.argtypes = [c_void_p, POINTER(c_void_p), c_int32, c_int32, c_void_p, c_void_p]
@@ -542,6 +544,48 @@ class Plan:
         check(lib().b200_forward_jvp(self._h, tok.data_ptr(), B, S, self.packed.data_ptr(), packed_dw.data_ptr(),
                                      saved.data_ptr(), dlogits.data_ptr(), ws.data_ptr(), ws.numel(), _stream()))
         return logits, dlogits
+
+    # ---- run-time options -------------------------------------------------
+    def set_option(self, name: str, value: int) -> None:
+        """Sets a run-time option of the plan (``b200_plan_set_option``), e.g. ``"tp_pipeline"``; every rank of a
+        tensor-parallel plan must set the same value."""
+        check(lib().b200_plan_set_option(self._h, name.encode(), int(value)))
+
+    def get_option(self, name: str) -> int:
+        v = c_int32(0)
+        check(lib().b200_plan_get_option(self._h, name.encode(), byref(v)))
+        return int(v.value)
+
+    def tune_tensor_parallel(self, tokens: torch.Tensor, logits: Optional[torch.Tensor] = None, reps: int = 2,
+                             group=None) -> Dict[str, float]:
+        """Times the tensor-parallel prefill of ``tokens`` both ways - one batch with the exchange between the
+        kernels, and two halves with the exchange of one beside the compute of the other - and keeps the faster one
+        (``"tp_pipeline"``).  Which one wins depends on the rank count and on the NVLink fabric of the moment, so it is
+        measured, during warm-up, and not assumed.  Collective: every rank calls it with the same shapes; the ranks
+        agree through a MAX all-reduce of their device times over ``group`` (default: the world group), so they all
+        keep the same choice.  Returns the two times in ms and the choice."""
+        if self.tp_size < 2:
+            return {"one_batch_ms": 0.0, "two_halves_ms": 0.0, "tp_pipeline": 0}
+        import torch.distributed as dist
+        times = []
+        for mode in (0, 1):
+            self.set_option("tp_pipeline", mode)
+            self.forward(tokens, logits=logits)  # first call of a variant: kernel attributes, workspace
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            dist.barrier(group=group)
+            a.record()
+            for _ in range(reps):
+                self.forward(tokens, logits=logits)
+            b.record()
+            torch.cuda.synchronize()
+            times.append(a.elapsed_time(b) / reps)
+        t = torch.tensor(times, dtype=torch.float64, device=self.device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX, group=group)
+        one, two = float(t[0]), float(t[1])
+        choice = 1 if two < one else 0
+        self.set_option("tp_pipeline", choice)
+        return {"one_batch_ms": one, "two_halves_ms": two, "tp_pipeline": choice}
 
     # ---- forward / backward ---------------------------------------------
     def forward(self, tokens: torch.Tensor, *, saved: Optional[torch.Tensor] = None,

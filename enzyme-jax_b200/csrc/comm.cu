@@ -238,15 +238,18 @@ struct PeerPtrs {
 // rank's flag array has reached `epoch`, for at most `budget` SM clocks in all
 // (the default, kPeerWaitCycles, is about two seconds).  Returns false (for the
 // whole CTA) when the wait ran out; the status word then carries ST_PEER_TIMEOUT.
+__device__ int g_poll_ns = 100;  // pause between two looks at a peer flag (B200_PEER_POLL_NS; 0 = none)
+
 __device__ __forceinline__ bool wait_all_peers(const uint32_t* my_flags, int base, int world, uint32_t epoch,
                                                uint32_t* status, long long budget) {
   __shared__ int s_ok;
   if (threadIdx.x == 0) {
     int ok = 1;
     const long long t0 = clock64();
+    const int pause = g_poll_ns;
     for (int r = 0; r < world && ok; ++r) {
       while ((int32_t)(flag_load_sys(my_flags + base + r) - epoch) < 0) {
-        __nanosleep(100);  // the waiting CTA may share its SM with a compute kernel: leave it the issue slots
+        if (pause > 0) __nanosleep(pause);  // the waiting CTA may share its SM with a compute kernel: leave it the issue slots
         if (clock64() - t0 > budget) {
           ok = 0;
           atomicOr(status, ST_PEER_TIMEOUT);
@@ -417,7 +420,7 @@ __device__ __forceinline__ void rownorm_load(RowRegs<T, NW, NCH>& g, const PeerP
   }
 }
 
-template <typename T, int NW, int NCH, bool PREFETCH>
+template <typename T, int NW, int NCH, bool PREFETCH, bool LEAN = false>
 __device__ __forceinline__ void rownorm_body(const PeerPtrs& pp, int rank, int world, size_t part_off, size_t xb_off,
                                              int rows, int row0, int d, float* __restrict__ x_own,
                                              const float* __restrict__ gain, float eps, uint32_t epoch,
@@ -435,14 +438,17 @@ __device__ __forceinline__ void rownorm_body(const PeerPtrs& pp, int rank, int w
   const bool ok = wait_all_peers(my_flags, kReadyBase, world, epoch, status, budget);
   const int n_chunks = d / E;
   if (ok) {
-    RowRegs<T, NW, NCH> cur, nxt;
+    // LEAN: no row held ahead; each 16-byte chunk's loads (one per rank) are summed as they arrive, so that eight
+    // ranks' partials never sit in registers at once
+    RowRegs<T, LEAN ? 0 : NW, LEAN ? 1 : NCH> cur, nxt;
     int row = blockIdx.x;
-    if (row < rows) rownorm_load(cur, pp, world, part_off, (size_t)(row0 + row), d, x_own + (size_t)row * d, n_chunks, only);
+    if (!LEAN && row < rows)
+      rownorm_load(cur, pp, world, part_off, (size_t)(row0 + row), d, x_own + (size_t)row * d, n_chunks, only);
     for (; row < rows; row += gridDim.x) {
       const size_t grow = (size_t)(row0 + row);
       float* xr = x_own + (size_t)row * d;
       const int next = row + gridDim.x;
-      if (PREFETCH && next < rows)
+      if (PREFETCH && !LEAN && next < rows)
         rownorm_load(nxt, pp, world, part_off, (size_t)(row0 + next), d, x_own + (size_t)next * d, n_chunks, only);
       float v[NCH][E];
       float ss = 0.f;
@@ -451,12 +457,27 @@ __device__ __forceinline__ void rownorm_body(const PeerPtrs& pp, int rank, int w
         const int c = threadIdx.x + k * 256;
         if (c < n_chunks) {
           float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+          uint4 part[NW > 0 ? NW : 1];
+          float4 xk[E / 4];
+          if constexpr (LEAN) {
+            const size_t off = part_off + (grow * d + (size_t)c * E) * sizeof(T);
+#pragma unroll
+            for (int r = 0; r < NW; ++r)
+              if (r < world) part[r] = load16_sys(reinterpret_cast<const uint8_t*>(pp.buf[only >= 0 ? only : r]) + off);
+#pragma unroll
+            for (int i = 0; i < E / 4; ++i) xk[i] = *reinterpret_cast<const float4*>(xr + c * E + 4 * i);
+          } else {
+#pragma unroll
+            for (int r = 0; r < NW; ++r) part[r] = cur.part[r][k];
+#pragma unroll
+            for (int i = 0; i < E / 4; ++i) xk[i] = cur.x[k][i];
+          }
 #pragma unroll
           for (int r = 0; r < NW; ++r)
-            if (r < world) accum8(cur.part[r][k], acc, T());  // rank order: the sum is the same on every run
+            if (r < world) accum8(part[r], acc, T());  // rank order: the sum is the same on every run
 #pragma unroll
           for (int i = 0; i < E; i += 4) {
-            float4 a = cur.x[k][i / 4];
+            float4 a = xk[i / 4];
             a.x += acc[i]; a.y += acc[i + 1]; a.z += acc[i + 2]; a.w += acc[i + 3];
             if (REDUCE) *reinterpret_cast<float4*>(xr + c * E + i) = a;
             v[k][i] = a.x; v[k][i + 1] = a.y; v[k][i + 2] = a.z; v[k][i + 3] = a.w;
@@ -491,7 +512,8 @@ __device__ __forceinline__ void rownorm_body(const PeerPtrs& pp, int rank, int w
             if (r < world && (!(dbg & 2) || r == rank)) *reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(pp.buf[r]) + off) = out;
         }
       }
-      if (PREFETCH) {
+      if constexpr (LEAN) {
+      } else if (PREFETCH) {
         cur = nxt;
       } else if (next < rows) {
         rownorm_load(cur, pp, world, part_off, (size_t)(row0 + next), d, x_own + (size_t)next * d, n_chunks, only);
@@ -523,18 +545,20 @@ __global__ void __launch_bounds__(256, 2) peer_rownorm_kernel(PeerPtrs pp, int r
                                      budget, dbg);
 }
 
-// The same kernel held to 80 registers and launched with one CTA per SM: the form that runs BESIDE the compute
+// The same kernel held to 96 registers and launched with one CTA per SM: the form that runs BESIDE the compute
 // kernels of the other half of the batch (a GEMM CTA of 192 threads x 192 registers or an attention CTA of 320 x 128
-// leaves 24 K registers and about 1.5 KB of shared memory on its SM; 256 x 80 fits with room for the allocator's rounding), so that the exchange of one half crosses NVLink while the
+// leaves 24 K registers and about 1.5 KB of shared memory on its SM; 256 x 96 is exactly that), so that the exchange of one half crosses NVLink while the
 // other half computes.
 template <typename T, int NW, int NCH>
-__global__ void __maxnreg__(80) peer_rownorm_lean_kernel(PeerPtrs pp, int rank, int world, size_t part_off,
+__global__ void __maxnreg__(96) peer_rownorm_lean_kernel(PeerPtrs pp, int rank, int world, size_t part_off,
                                                          size_t xb_off, int rows, int row0, int d,
                                                          float* __restrict__ x_own, const float* __restrict__ gain,
                                                          float eps, uint32_t epoch, uint32_t* status, long long budget,
                                                          int dbg) {
-  rownorm_body<T, NW, NCH, false>(pp, rank, world, part_off, xb_off, rows, row0, d, x_own, gain, eps, epoch, status,
-                                  budget, dbg);
+  // up to four ranks a row's loads all go out together (8 in flight per thread keep the links busy with one CTA per
+  // SM); with eight ranks that many would not fit the register cap, so each chunk's eight loads are summed as they arrive
+  rownorm_body<T, NW, NCH, false, (NW > 4)>(pp, rank, world, part_off, xb_off, rows, row0, d, x_own, gain, eps, epoch,
+                                            status, budget, dbg);
 }
 
 // ---- the same exchange through the NVLink switch (multimem) -----------------------------------------------------
@@ -719,7 +743,7 @@ int32_t comm_peer_reduce_norm(void* comm, int T, int d, int dtype, bool reduce, 
 
 // The exchange over `T` rows whose partial products start `part_rel` bytes and whose gathered rows start `xb_rel`
 // bytes into the row-shard area of every rank's exchange memory.  lean: the form that runs beside compute kernels
-// (one CTA per SM, 80 registers).
+// (one CTA per SM, 96 registers).
 int32_t comm_peer_reduce_norm_at(void* comm, int T, int d, int dtype, bool reduce, float* x_own, const float* gain,
                                  float eps, size_t part_rel, size_t xb_rel, bool lean, cudaStream_t stream) {
   Comm* c = reinterpret_cast<Comm*>(comm);
@@ -901,6 +925,9 @@ int32_t b200_comm_init_rank(const void* id128, int32_t rank, int32_t world, void
   c->world = world;
   const int budget_m = env_int("B200_PEER_WAIT_MCYCLES", 4000);  // millions of SM clocks
   c->wait_budget = (long long)(budget_m > 0 ? budget_m : 4000) * 1000000LL;
+  const int poll_ns = env_int("B200_PEER_POLL_NS", -1);
+  if (poll_ns >= 0 && cudaMemcpyToSymbol(g_poll_ns, &poll_ns, sizeof(int)) != cudaSuccess)
+    return fail(B200_ERR_CUDA, "setting the flag poll pause failed");
   setup_peer_memory(c);
   *comm = c;
   return B200_OK;
@@ -924,6 +951,9 @@ int32_t b200_comm_init_rank_ex(const void* id128, int32_t rank, int32_t world, i
   c->world = world;
   const int budget_m = env_int("B200_PEER_WAIT_MCYCLES", 4000);  // millions of SM clocks
   c->wait_budget = (long long)(budget_m > 0 ? budget_m : 4000) * 1000000LL;
+  const int poll_ns = env_int("B200_PEER_POLL_NS", -1);
+  if (poll_ns >= 0 && cudaMemcpyToSymbol(g_poll_ns, &poll_ns, sizeof(int)) != cudaSuccess)
+    return fail(B200_ERR_CUDA, "setting the flag poll pause failed");
   if (own_peer_memory) setup_peer_memory(c);
   *comm = c;
   return B200_OK;

@@ -310,6 +310,7 @@ __global__ void __launch_bounds__(256) splitk_reduce_kernel(const float* __restr
   float v[16];
 #pragma unroll
   for (int i = 0; i < 16; ++i) v[i] = 0.f;
+#pragma unroll 4  // the loads of four K ranges in flight together; the sum stays in range order
   for (int s = 0; s < splits; ++s) {
     const float* p = partial + ((size_t)s * M + m) * N + n;
     float a[8], b[8];

@@ -699,6 +699,29 @@ int32_t b200_plan_cached(const B200LlamaConfig* cfg, int32_t tp_rank, int32_t tp
   return B200_OK;
 }
 
+// Run-time options of a plan.  "tp_pipeline": 1 = the tensor-parallel prefill runs two halves of the batch with
+// the exchange of one beside the compute of the other, 0 = one batch with the exchange between the kernels.  Every
+// rank of the communicator must hold the same value whenever b200_forward runs (the exchange kernels pair up in
+// launch order); which of the two is faster depends on the rank count and on how busy the NVLink fabric is, so a
+// caller may time both during warm-up and keep the faster one.
+int32_t b200_plan_set_option(B200Plan* p, const char* name, int32_t value) {
+  if (!p || !name) return fail(B200_ERR_INVALID_ARG, "null argument");
+  if (!strcmp(name, "tp_pipeline")) {
+    p->tp_pipeline = value != 0;
+    return B200_OK;
+  }
+  return fail(B200_ERR_INVALID_ARG, "unknown plan option '%s'", name);
+}
+
+int32_t b200_plan_get_option(const B200Plan* p, const char* name, int32_t* value) {
+  if (!p || !name || !value) return fail(B200_ERR_INVALID_ARG, "null argument");
+  if (!strcmp(name, "tp_pipeline")) {
+    *value = p->tp_pipeline ? 1 : 0;
+    return B200_OK;
+  }
+  return fail(B200_ERR_INVALID_ARG, "unknown plan option '%s'", name);
+}
+
 int32_t b200_packed_weight_bytes(const B200Plan* p, int32_t with_t, size_t* bytes) {
   if (!p || !bytes) return fail(B200_ERR_INVALID_ARG, "null argument");
   *bytes = with_t ? p->wlt.total : p->wl.total;

@@ -156,9 +156,19 @@ B200_API int32_t b200_plan_destroy(B200Plan* plan);
  * created on first use, shared afterwards, destroyed at process exit.  This is what a custom-call handler uses, which
  * is handed attributes and buffers on every call and has no place to keep a handle; it stands for the reference's
  * registry of compiled kernels keyed by an identifier (enzyme_call.cc:173,263,282: a map behind a reader/writer
- * lock).  Safe to call from several threads; plans are immutable after creation. */
+ * lock).  Safe to call from several threads; plans are immutable after creation apart from b200_plan_set_option, which
+ * a caller sharing a plan between threads must not call while another thread launches through it. */
 B200_API int32_t b200_plan_cached(const B200LlamaConfig* cfg, int32_t tp_rank, int32_t tp_size, void* comm,
                                   B200Plan** out);
+
+/* Run-time options of a plan, by name.  "tp_pipeline": 1 = the tensor-parallel prefill (b200_forward with tp_size > 1
+ * over peer memory) runs two halves of the batch so that one half's exchange crosses NVLink beside the other half's
+ * GEMMs and attention, 0 = one batch with the exchange between the kernels (default: 1 from four ranks on, or the
+ * B200_TP_PIPELINE environment variable).  Every rank of the communicator must hold the same value whenever
+ * b200_forward runs.  Results do not depend on it.  Unknown names: B200_ERR_INVALID_ARG.  The reference has no
+ * counterpart (its options travel as pass-pipeline strings, primitives.py:56-115). */
+B200_API int32_t b200_plan_set_option(B200Plan* plan, const char* name, int32_t value);
+B200_API int32_t b200_plan_get_option(const B200Plan* plan, const char* name, int32_t* value);
 
 /* Bytes of the packed weight buffer for this rank; with_transposed != 0 adds
  * the transposed copies the backward pass contracts against. */

@@ -108,6 +108,26 @@ def main():
     torch.cuda.synchronize()
     err = float((got_r.cpu() - ref_r[..., rank * vl:(rank + 1) * vl]).abs().max() / ref_r.abs().max())
     assert err < 2e-2, ("tp forward, 2000 tokens", err)
+    # the warm-up tuner times both exchange schedules; all ranks keep the same one; either gives the same logits
+    tok_dev = tokens.int().cuda()
+    res = plan.tune_tensor_parallel(tok_dev)
+    assert res["tp_pipeline"] in (0, 1) and plan.get_option("tp_pipeline") == res["tp_pipeline"], res
+    assert res["one_batch_ms"] > 0 and res["two_halves_ms"] > 0, res
+    agreed = torch.tensor([res["tp_pipeline"], -res["tp_pipeline"]], device="cuda")
+    dist.all_reduce(agreed, op=dist.ReduceOp.MAX)
+    assert int(agreed[0]) == -int(agreed[1]), "ranks disagree on the exchange schedule"
+    for mode in (0, 1):
+        plan.set_option("tp_pipeline", mode)
+        got_m = plan.forward(tok_dev)
+        torch.cuda.synchronize()
+        err = float((got_m.cpu() - ref[..., rank * vl:(rank + 1) * vl]).abs().max() / ref.abs().max())
+        assert err < 2e-2, ("tp forward after tuning", mode, err)
+        assert float((got_m - got).abs().max()) <= 1e-3 * float(ref.abs().max()), ("schedules differ", mode)
+    try:
+        plan.set_option("no_such_option", 1)
+        raise AssertionError("an unknown option must be refused")
+    except B.B200Error as e:
+        assert e.status == 1
     assert B.device_status() == 0
     plan.close()
     del os.environ["B200_TP_PIPELINE"]

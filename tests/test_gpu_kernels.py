@@ -62,8 +62,9 @@ def test_gemm_bf16_random_and_bf16_out(impl):
 
 @pytest.mark.parametrize("ta,tb", [(False, False), (True, False), (False, True), (True, True)])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-def test_gemm_transposed_operands(ta, tb, dtype):
-    M, N, K = 200, 144, 136
+@pytest.mark.parametrize("M,N,K", [(200, 144, 136),      # few tiles: the 32-row form of the FFMA kernel, ragged edges
+                                   (2312, 1088, 72)])    # 19 x 17 tiles: its 128-row form
+def test_gemm_transposed_operands(ta, tb, dtype, M, N, K):
     a = _ints((K, M) if ta else (M, K), 3, dtype=dtype)
     b = _ints((K, N) if tb else (N, K), 4, dtype=dtype)
     y = B.gemm(a, b, ta=ta, tb=tb, out_dtype=torch.float32 if dtype == torch.float32 else torch.float32)

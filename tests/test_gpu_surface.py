@@ -216,3 +216,19 @@ def test_token_jvp_all_inputs_matches_oracle(pos):
                 sum((gw[k].double().cpu() * dw[k]).sum() for k in dw))
     assert abs(lhs - rhs) < 1e-3 * max(1.0, abs(lhs))
     p.close()
+
+
+def test_plan_options_round_trip():
+    import b200_llama as B
+    cfg = dict(O.CONFIGS["c1"], n_layers=1)
+    p = B.Plan(cfg, torch.float32)
+    for v in (1, 0):
+        p.set_option("tp_pipeline", v)
+        assert p.get_option("tp_pipeline") == v
+    for call in (lambda: p.set_option("no_such_option", 1), lambda: p.get_option("no_such_option")):
+        with pytest.raises(B.B200Error) as e:
+            call()
+        assert e.value.status == 1
+    # a plan on one GPU has nothing to tune
+    assert p.tune_tensor_parallel(torch.zeros(1, 8, dtype=torch.int32, device="cuda"))["tp_pipeline"] == 0
+    p.close()
