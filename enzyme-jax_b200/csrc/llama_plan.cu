@@ -627,10 +627,11 @@ int32_t b200_plan_create(const B200LlamaConfig* cfg, int32_t tp_rank, int32_t tp
     // Chunked projections with the all-reduce of chunk c overlapping the GEMM of chunk c+1 measured SLOWER
     // than one all-reduce per block on 4 GPUs (45.3 ms vs 48.9 / 54.1 ms for 2 / 4 chunks), so the default is 1.
     p->row_shard = env_int("B200_TP_ROW_SHARD", 1) != 0;
-    // Two halves in flight pay from four ranks on (measured at the 7B shape: 30.1 against 34.0 ms per step at four
-    // ranks; at two ranks the exchange is a sixth of the step and the compute kernels lose more to the kernel running
-    // beside them than the overlap wins: 61.0 against 54.5 ms).  B200_TP_PIPELINE = 0 / 1 forces the choice.
-    p->tp_pipeline = env_int("B200_TP_PIPELINE", tp_size >= 4 ? 1 : 0) != 0;
+    // Two halves in flight hide the exchange but halve the rows of every GEMM and put a second kernel on the SMs; at
+    // the 7B shape that won on one 4-GPU box (30.1 against 34.0 ms per step) and lost on three others (36-37 against
+    // 34-35 ms) and at two ranks (57-61 against 54.5 ms).  So it is off unless asked for (B200_TP_PIPELINE = 1) or
+    // chosen by a caller that timed both (b200_plan_set_option).
+    p->tp_pipeline = env_int("B200_TP_PIPELINE", 0) != 0;
     p->reserve_sms = env_int("B200_TP_RESERVE_SMS", 0);
     p->tp_chunks = env_int("B200_TP_CHUNKS", 1);
     if (p->tp_chunks < 1) p->tp_chunks = 1;

@@ -82,7 +82,7 @@ struct B200Plan {
   cudaEvent_t ev_fork[8] = {}, ev_join[8] = {};
   int reserve_sms = 0;
   int tp_chunks = 1;
-  bool tp_pipeline = true;  // ... and runs two halves of the batch so that one half's exchange overlaps the other's compute
+  bool tp_pipeline = false;  // ... and runs two halves of the batch so that one half's exchange overlaps the other's compute
   bool row_shard = true;  // tensor-parallel prefill keeps T/tp residual rows per rank when peer memory is up
   float* rope_cos = nullptr;  // [seq_len, hs/2], owned by the plan
   float* rope_sin = nullptr;

@@ -163,8 +163,8 @@ B200_API int32_t b200_plan_cached(const B200LlamaConfig* cfg, int32_t tp_rank, i
 
 /* Run-time options of a plan, by name.  "tp_pipeline": 1 = the tensor-parallel prefill (b200_forward with tp_size > 1
  * over peer memory) runs two halves of the batch so that one half's exchange crosses NVLink beside the other half's
- * GEMMs and attention, 0 = one batch with the exchange between the kernels (default: 1 from four ranks on, or the
- * B200_TP_PIPELINE environment variable).  Every rank of the communicator must hold the same value whenever
+ * GEMMs and attention, 0 = one batch with the exchange between the kernels (the default, unless the B200_TP_PIPELINE
+ * environment variable says 1).  Every rank of the communicator must hold the same value whenever
  * b200_forward runs.  Results do not depend on it.  Unknown names: B200_ERR_INVALID_ARG.  The reference has no
  * counterpart (its options travel as pass-pipeline strings, primitives.py:56-115). */
 B200_API int32_t b200_plan_set_option(B200Plan* plan, const char* name, int32_t value);

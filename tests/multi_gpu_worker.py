@@ -59,7 +59,7 @@ def main():
     # an odd batch (cannot be split into two halves), and an even batch with the two-half pipeline forced on
     for env_off, nb in ((None, 3), ("B200_TP_PIPELINE", 2)):
         if env_off:
-            os.environ[env_off] = "1"   # the two-half pipeline is the default from four ranks on: force it here
+            os.environ[env_off] = "1"   # the two-half pipeline is off by default: force it here
         w = {k: v.bfloat16() for k, v in O.make_weights(cfg, 3, torch.float32, std=0.05).items()}
         tokens = O.make_tokens(cfg, nb, 128, 4)
         ref = O.forward_sequence(tokens, cfg, {k: v.double() for k, v in w.items()})
@@ -87,7 +87,7 @@ def main():
     assert err < 2e-2, ("tp forward, all-reduce path", err)
     plan.close()
     del os.environ["B200_TP_ROW_SHARD"]
-    # 2 x 1024 tokens, with the two-half pipeline on (the form four ranks and more run by default)
+    # 2 x 1024 tokens, with the two-half pipeline on
     os.environ["B200_TP_PIPELINE"] = "1"
     cfg_long = dict(cfg, seq_len=1024)
     w = {k: v.bfloat16() for k, v in O.make_weights(cfg_long, 8, torch.float32, std=0.05).items()}
