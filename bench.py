@@ -559,6 +559,9 @@ def run_prefill(args, rank, world, local, B, dist):
                                            "second stream beside the other half's GEMMs and attention")
         elif fused:
             line["config"]["exchange"] += "; one batch, the exchange between the kernels"
+        if fused and plan.get_option("tp_push_last"):
+            line["config"]["exchange"] += ("; the Wo / W2 GEMMs store each band of rows of their partial product "
+                                           "straight into its owner's memory, tile by tile")
         if tuned:
             line["config"]["exchange"] += (f" (chosen by timing both before the warm-up: one batch "
                                            f"{tuned['one_batch_ms']:.2f} ms, two halves {tuned['two_halves_ms']:.2f} ms)")

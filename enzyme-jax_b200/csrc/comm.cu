@@ -402,18 +402,34 @@ struct RowRegs {
   float4 x[NCH][E / 4];
 };
 
+// Where rank r's partial product of a row lives.  Pulled form: in rank r's own partial region, at the row's index in
+// [T].  Pushed form (push_rows > 0: the producing GEMM stored every row band straight into its owner's memory): in
+// THIS rank's region, slot r, at the row's index inside the band.
+struct PartSrc {
+  const uint8_t* base;
+  size_t row;
+};
+__device__ __forceinline__ PartSrc part_src(const PeerPtrs& pp, int r, int self, int only, size_t grow, int row0,
+                                            int push_rows) {
+  if (push_rows > 0) return PartSrc{reinterpret_cast<const uint8_t*>(pp.buf[self]), (size_t)r * push_rows + (grow - row0)};
+  return PartSrc{reinterpret_cast<const uint8_t*>(pp.buf[only >= 0 ? only : r]), grow};
+}
+
 template <typename T, int NW, int NCH>
 __device__ __forceinline__ void rownorm_load(RowRegs<T, NW, NCH>& g, const PeerPtrs& pp, int world, size_t part_off,
-                                             size_t grow, int d, const float* xr, int n_chunks, int only = -1) {
+                                             size_t grow, int d, const float* xr, int n_chunks, int only, int self,
+                                             int row0, int push_rows) {
   constexpr int E = 16 / sizeof(T);
 #pragma unroll
   for (int k = 0; k < NCH; ++k) {
     const int c = threadIdx.x + k * 256;
     if (c < n_chunks) {
-      const size_t off = part_off + (grow * d + (size_t)c * E) * sizeof(T);
 #pragma unroll
       for (int r = 0; r < NW; ++r)
-        if (r < world) g.part[r][k] = load16_sys(reinterpret_cast<const uint8_t*>(pp.buf[only >= 0 ? only : r]) + off);
+        if (r < world) {
+          const PartSrc ps = part_src(pp, r, self, only, grow, row0, push_rows);
+          g.part[r][k] = load16_sys(ps.base + part_off + (ps.row * d + (size_t)c * E) * sizeof(T));
+        }
 #pragma unroll
       for (int i = 0; i < E / 4; ++i) g.x[k][i] = *reinterpret_cast<const float4*>(xr + c * E + 4 * i);
     }
@@ -428,6 +444,7 @@ __device__ __forceinline__ void rownorm_body(const PeerPtrs& pp, int rank, int w
   constexpr int E = 16 / sizeof(T);  // elements per 16-byte chunk
   constexpr bool REDUCE = NW > 0;
   const int only = (dbg & 1) ? rank : -1;  // measurement aid: every load from this rank's own buffer
+  const int push_rows = (dbg & 4) ? rows : 0;  // the partial products were pushed into this rank's slots
   __shared__ float red[32];
   __shared__ int s_last;
   uint32_t* my_flags = pp.flags[rank];
@@ -443,13 +460,14 @@ __device__ __forceinline__ void rownorm_body(const PeerPtrs& pp, int rank, int w
     RowRegs<T, LEAN ? 0 : NW, LEAN ? 1 : NCH> cur, nxt;
     int row = blockIdx.x;
     if (!LEAN && row < rows)
-      rownorm_load(cur, pp, world, part_off, (size_t)(row0 + row), d, x_own + (size_t)row * d, n_chunks, only);
+      rownorm_load(cur, pp, world, part_off, (size_t)(row0 + row), d, x_own + (size_t)row * d, n_chunks, only, rank, row0, push_rows);
     for (; row < rows; row += gridDim.x) {
       const size_t grow = (size_t)(row0 + row);
       float* xr = x_own + (size_t)row * d;
       const int next = row + gridDim.x;
       if (PREFETCH && !LEAN && next < rows)
-        rownorm_load(nxt, pp, world, part_off, (size_t)(row0 + next), d, x_own + (size_t)next * d, n_chunks, only);
+        rownorm_load(nxt, pp, world, part_off, (size_t)(row0 + next), d, x_own + (size_t)next * d, n_chunks, only, rank, row0,
+                     push_rows);
       float v[NCH][E];
       float ss = 0.f;
 #pragma unroll
@@ -460,10 +478,12 @@ __device__ __forceinline__ void rownorm_body(const PeerPtrs& pp, int rank, int w
           uint4 part[NW > 0 ? NW : 1];
           float4 xk[E / 4];
           if constexpr (LEAN) {
-            const size_t off = part_off + (grow * d + (size_t)c * E) * sizeof(T);
 #pragma unroll
             for (int r = 0; r < NW; ++r)
-              if (r < world) part[r] = load16_sys(reinterpret_cast<const uint8_t*>(pp.buf[only >= 0 ? only : r]) + off);
+              if (r < world) {
+                const PartSrc ps = part_src(pp, r, rank, only, grow, row0, push_rows);
+                part[r] = load16_sys(ps.base + part_off + (ps.row * d + (size_t)c * E) * sizeof(T));
+              }
 #pragma unroll
             for (int i = 0; i < E / 4; ++i) xk[i] = *reinterpret_cast<const float4*>(xr + c * E + 4 * i);
           } else {
@@ -516,7 +536,8 @@ __device__ __forceinline__ void rownorm_body(const PeerPtrs& pp, int rank, int w
       } else if (PREFETCH) {
         cur = nxt;
       } else if (next < rows) {
-        rownorm_load(cur, pp, world, part_off, (size_t)(row0 + next), d, x_own + (size_t)next * d, n_chunks, only);
+        rownorm_load(cur, pp, world, part_off, (size_t)(row0 + next), d, x_own + (size_t)next * d, n_chunks, only, rank, row0,
+                     push_rows);
       }
     }
   }
@@ -735,17 +756,41 @@ bool comm_peer_rowshard_buffers(void* comm, size_t bytes_each, void** part, void
   return true;
 }
 
+// In-switch reduction halves the bytes on every link from four ranks on ((world + 1) / world of the buffer each way
+// instead of 2 (world - 1) / world); it was never faster on the boxes this was measured on (200 us against 118 us per
+// exchange of 64 MiB between two ranks, 216 against 197 us among four), so it is off unless B200_TP_MULTIMEM = 1.
+static bool use_multimem(const Comm* c) {
+  static const int mc_env = env_int("B200_TP_MULTIMEM", -1);
+  return c->pm.mc && mc_env > 0;
+}
+
 int32_t comm_peer_reduce_norm(void* comm, int T, int d, int dtype, bool reduce, float* x_own, const float* gain,
-                              float eps, cudaStream_t stream) {
+                              float eps, cudaStream_t stream, bool pushed) {
   const size_t each = align_up((size_t)T * d * (dtype == B200_BF16 ? 2 : 4), 256);
-  return comm_peer_reduce_norm_at(comm, T, d, dtype, reduce, x_own, gain, eps, 0, each, false, stream);
+  return comm_peer_reduce_norm_at(comm, T, d, dtype, reduce, x_own, gain, eps, 0, each, false, stream, pushed);
+}
+
+// Where a pushed store of a [T, d] partial product goes: bases[o] is slot `rank` of rank o's partial region, a
+// [T / world, d] matrix, for every rank o (this one included).  False when the exchange cannot take pushed partials
+// (no peer memory, in-switch reduction selected, rows not a multiple of 32).
+bool comm_peer_push_bases(void* comm, int T, int d, int dtype, void** bases) {
+  if (!comm) return false;
+  Comm* c = reinterpret_cast<Comm*>(comm);
+  const size_t es = dtype == B200_BF16 ? 2 : 4;
+  if (!c->pm.on || use_multimem(c) || T % c->world || (T / c->world) % 32 || c->world > 8) return false;
+  if (c->pm.bytes < 2 * kOneShotMaxBytes + 2 * align_up((size_t)T * d * es, 256)) return false;
+  const size_t rows = (size_t)(T / c->world);
+  for (int o = 0; o < c->world; ++o)
+    bases[o] = reinterpret_cast<uint8_t*>(c->pm.buf[o]) + 2 * kOneShotMaxBytes + (size_t)c->rank * rows * d * es;
+  return true;
 }
 
 // The exchange over `T` rows whose partial products start `part_rel` bytes and whose gathered rows start `xb_rel`
 // bytes into the row-shard area of every rank's exchange memory.  lean: the form that runs beside compute kernels
 // (one CTA per SM, 96 registers).
 int32_t comm_peer_reduce_norm_at(void* comm, int T, int d, int dtype, bool reduce, float* x_own, const float* gain,
-                                 float eps, size_t part_rel, size_t xb_rel, bool lean, cudaStream_t stream) {
+                                 float eps, size_t part_rel, size_t xb_rel, bool lean, cudaStream_t stream,
+                                 bool pushed) {
   Comm* c = reinterpret_cast<Comm*>(comm);
   if (!c || !c->pm.on) return fail(B200_ERR_INVALID_ARG, "peer memory is not set up for this communicator");
   const size_t es = dtype == B200_BF16 ? 2 : 4;
@@ -769,12 +814,9 @@ int32_t comm_peer_reduce_norm_at(void* comm, int T, int d, int dtype, bool reduc
   if (n_chunks > 1024)
     return fail(B200_ERR_BAD_SHAPE, "row-sharded exchange: rows of %d elements exceed 16 KB", d);
   const int nw = !reduce ? 0 : c->world <= 2 ? 2 : c->world <= 4 ? 4 : 8;
-  // In-switch reduction halves the bytes on every link from four ranks on ((world + 1) / world of the buffer each
-  // way instead of 2 (world - 1) / world); between two ranks it only adds the loop through the switch (measured
-  // 200 us against 118 us per exchange of 64 MiB).  B200_TP_MULTIMEM = 0 / 1 forces the choice.
-  static const int mc_env = env_int("B200_TP_MULTIMEM", -1);
-  const bool use_mc = mc_env >= 0 ? mc_env != 0 : false;
-  if (c->pm.mc && use_mc) {
+  const bool use_mc = use_multimem(c);
+  if (use_mc && pushed) return fail(B200_ERR_UNSUPPORTED, "pushed partial products and in-switch reduction exclude each other");
+  if (use_mc) {
     int grid_mc = sm_count() * (lean ? 1 : 4);
     if (grid_mc > rows) grid_mc = rows;
 #define B200_ROWNORM_MC(TT, NCH)                                                                                    \
@@ -800,7 +842,8 @@ int32_t comm_peer_reduce_norm_at(void* comm, int T, int d, int dtype, bool reduc
   // registers of one row's loads: NW * NCH * 4 (partials) + NCH * (4 or 8) (residual); two sets fit below about 72
   const int regs_row = (nw > 0 ? nw : 1) * nch * 4 + nch * (int)(16 / es);
   static const int pf_env = env_int("B200_ROWNORM_PREFETCH", -1);  // -1: decide by the register estimate
-  static const int dbg = env_int("B200_EXCH_LOCAL_ONLY", 0);       // measurement aid: 1 loads, 2 stores stay on this GPU
+  static const int dbg_env = env_int("B200_EXCH_LOCAL_ONLY", 0);   // measurement aid: 1 loads, 2 stores stay on this GPU
+  const int dbg = (dbg_env & 3) | (pushed ? 4 : 0);                // bit 2: partial products sit in this rank's slots
   const bool prefetch = pf_env >= 0 ? pf_env != 0 : regs_row <= 72;
 #define B200_ROWNORM(TT, NW, NCH)                                                                                    \
   do {                                                                                                               \

@@ -166,7 +166,15 @@ struct GemmArgs {
   size_t splitk_bytes = 0;
   // upper bound on the persistent grid (0 = every SM); lets a collective on another stream keep some SMs
   int max_ctas = 0;
+  // Row-parallel projection of a tensor-parallel plan: rows [o * push_rows, (o + 1) * push_rows) of the output are
+  // stored to push_base[o], a [push_rows, N] matrix of row pitch epi.ldo (memory of rank o, mapped into this
+  // process), instead of epi.out: the partial product crosses NVLink tile by tile while the GEMM still computes.
+  // Only the CTA-pair tensor kernel with the plain store does this; ask gemm_push_supported first.
+  int push_rows = 0;
+  void* push_base[8] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
 };
+// whether launch_gemm(g, impl) would take the kernel that honours push_rows / push_base
+bool gemm_push_supported(const GemmArgs& g, int impl);
 // Scratch that lets the tensor-core kernel split K whenever it wants to for an M x N output.
 inline size_t gemm_splitk_scratch_bytes(int M, int N) { return (size_t)32 * M * N * sizeof(float); }
 

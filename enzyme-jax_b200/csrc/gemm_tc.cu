@@ -479,6 +479,13 @@ int32_t launch_splitk_reduce(const GemmArgs& g, int splits, cudaStream_t stream)
   return B200_OK;
 }
 
+bool gemm_push_supported(const GemmArgs& g, int impl) {
+  static const int use_pair = env_int("B200_GEMM_PAIR", 1);
+  const bool tc = impl == 1 || (impl != 2 && gemm_tc_supports(g));
+  return tc && use_pair && gemm_tc2_supports(g) && g.kind == EPI_STORE && !g.ta && !g.tb && g.push_rows > 0 &&
+         g.push_rows % 32 == 0 && g.M % g.push_rows == 0 && g.M / g.push_rows <= 8;
+}
+
 int32_t launch_gemm(const GemmArgs& g, int impl, cudaStream_t stream) {
   const bool tc = impl == 1 || (impl != 2 && gemm_tc_supports(g));
   // B200_GEMM_PAIR=0 keeps every problem on the single-CTA kernel
@@ -488,6 +495,8 @@ int32_t launch_gemm(const GemmArgs& g, int impl, cudaStream_t stream) {
   const bool pair_t = tc && !pair && use_pair && pair_mn && gemm_tc2_mn_supports(g);
   ProfScope prof(!tc ? PROF_GEMM_SIMT : (pair || pair_t) ? PROF_GEMM_PAIR : PROF_GEMM_TC,
                  2.0 * g.M * (double)g.N * g.K, stream);
+  if (g.push_rows > 0 && !pair)
+    return fail(B200_ERR_UNSUPPORTED, "pushed store needs the CTA-pair tensor kernel (M=%d N=%d K=%d)", g.M, g.N, g.K);
   if (!tc) return launch_gemm_simt(g, stream);
   if (pair) return launch_gemm_tc2(g, stream);
   if (pair_t) return launch_gemm_tc2_mn(g, stream);

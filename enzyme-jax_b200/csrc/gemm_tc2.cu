@@ -101,6 +101,11 @@ __device__ __forceinline__ void mma_pair_commit(uint64_t* bar) {
                : "memory");
 }
 
+// Output maps of a pushed store (GemmArgs::push_rows): one [push_rows, N] matrix per destination rank.
+struct alignas(64) PushMaps {
+  CUtensorMap m[8];
+};
+
 // MN: both operands are MN-major (A stored [K, M], B stored [K, N]: the weight-gradient products dY^T X).  Their
 // tiles arrive as boxes of 64 columns x 64 k-rows and are described to the MMA as MN-major.  `splits` > 1 cuts K
 // into that many ranges handled as separate work items whose fp32 partial tiles go to rows split * split_rows + m
@@ -110,7 +115,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(P_THREADS, 1)
     gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                     const __grid_constant__ CUtensorMap tmO, const __grid_constant__ CUtensorMap tmR,
                     const __grid_constant__ CUtensorMap tmG, const __grid_constant__ CUtensorMap tmU, int M, int N,
-                    int K, EpiParams ep, int splits, int split_rows, uint32_t* status) {
+                    int K, EpiParams ep, int splits, int split_rows, uint32_t* status,
+                    const __grid_constant__ PushMaps pm, int push_rows) {
   using Cfg = PairCfg<BN, KIND>;
   constexpr int S = Cfg::kStages;
   extern __shared__ uint8_t smem_raw[];
@@ -264,6 +270,17 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(P_THREADS, 1)
       const int n0 = nt * BN;
       const int mrow0 = m0 + q * 32;  // first row of this warp's boxes; rows past M are clipped by the store
       const int yrow0 = mrow0 + split * split_rows;  // row of the output map (partial sums: one M-row band per split)
+      // where this warp's boxes go: the output map, or - pushed store - the map of the rank that owns these rows
+      const CUtensorMap* out_map = &tmO;
+      int out_y = yrow0, out_rows = 0x7fffffff;
+      if constexpr (KIND == EPI_STORE && !MN) {
+        if (push_rows > 0) {
+          const int dst = yrow0 / push_rows;  // push_rows is a multiple of 32: a box never straddles two destinations
+          out_rows = M;                       // no destination owns rows past M: such a box is not stored at all
+          out_map = &pm.m[dst < 8 ? dst : 7];
+          out_y = yrow0 - dst * push_rows;
+        }
+      }
       const int m = mrow0 + lane;
       const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * Cfg::kAccStride);
       const EpiRow erow = epi_row_begin<KIND>(ep, m < M ? m : 0);
@@ -354,7 +371,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(P_THREADS, 1)
               ptx::fence_proxy_async();
               __syncwarp();
               if (lane == 0) {
-                ptx::tma_store_2d(&tmO, stg + (uint32_t)((ring % NBUF) * BUFB), n0 + c, yrow0);
+                if (yrow0 < out_rows) ptx::tma_store_2d(out_map, stg + (uint32_t)((ring % NBUF) * BUFB), n0 + c, out_y);
                 ptx::tma_store_commit();
               }
               ++ring;
@@ -380,7 +397,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(P_THREADS, 1)
                 ptx::fence_proxy_async();
                 __syncwarp();
                 if (lane == 0) {
-                  ptx::tma_store_2d(&tmO, stg + (uint32_t)((ring % NBUF) * BUFB), n0 + c - 32, yrow0);
+                  if (yrow0 < out_rows)
+                    ptx::tma_store_2d(out_map, stg + (uint32_t)((ring % NBUF) * BUFB), n0 + c - 32, out_y);
                   ptx::tma_store_commit();
                 }
                 ++ring;
@@ -562,8 +580,25 @@ int32_t launch_pair_cfg(const GemmArgs& g, cudaStream_t stream, int splits = 1) 
   int pairs = max_pairs;
   if (g.max_ctas > 0 && g.max_ctas / 2 < pairs) pairs = g.max_ctas / 2;
   if (pairs > items) pairs = items;
+  PushMaps pm;
+  for (int i = 0; i < 8; ++i) pm.m[i] = tmO;
+  int push_rows = 0;
+  if (g.push_rows > 0) {
+    if constexpr (MN || KIND != EPI_STORE) {
+      return fail(B200_ERR_UNSUPPORTED, "pushed store: only the plain store epilogue of K-major operands");
+    } else {
+      if (g.push_rows % 32 || g.M % g.push_rows || g.M / g.push_rows > 8)
+        return fail(B200_ERR_UNSUPPORTED, "pushed store: %d rows in bands of %d", g.M, g.push_rows);
+      for (int o = 0; o < g.M / g.push_rows; ++o) {
+        if (!g.push_base[o] || !aligned16(g.push_base[o]))
+          return fail(B200_ERR_MISALIGNED, "pushed store: destination %d", o);
+        B200_TRY(make_map_out(&pm.m[o], g.push_base[o], g.push_rows, g.N, g.epi.ldo, (int)sizeof(TOut), 128));
+      }
+      push_rows = g.push_rows;
+    }
+  }
   B200_CUDA_OK(launch_pdl(kern, dim3(2 * pairs), dim3(P_THREADS), Cfg::kSmemBytes, stream, tmA, tmB, tmO, tmR, tmG,
-                          tmU, g.M, g.N, g.K, g.epi, splits, MN ? g.M : 0, device_status_word()));
+                          tmU, g.M, g.N, g.K, g.epi, splits, MN ? g.M : 0, device_status_word(), pm, push_rows));
   B200_LAUNCH_OK("gemm_tc2_kernel");
   return B200_OK;
 }

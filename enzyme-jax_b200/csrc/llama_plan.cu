@@ -245,6 +245,34 @@ static int32_t forward_row_sharded(B200Plan* p, const int32_t* tokens, int B, in
   const float* g_fin = reinterpret_cast<const float*>(w + wl.g_final);
   const float eps = p->cfg.rms_eps;
   float* x_own = a.x_in;  // [T, d] in the workspace; the first T/tp rows hold this rank's residual rows
+  // Pushed partial products: the Wo / W2 GEMMs store every row band straight into the memory of the rank that owns
+  // it (slot = this rank), tile by tile while they compute, so the reduce-scatter half of the exchange crosses NVLink
+  // under the GEMM and the exchange kernel sums from local memory.  Needs the CTA-pair kernel for both shapes.
+  void* push_base[8] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
+  bool push = p->tp_push && comm_peer_push_bases(p->comm, T, d, p->dtype, push_base);
+  auto proj_args = [&](const void* A, int lda, const void* W, int ldw, int K) {
+    GemmArgs g;
+    g.A = A; g.B = W; g.M = T; g.N = d; g.K = K; g.lda = lda; g.ldb = ldw;
+    g.in_dtype = p->dtype; g.out_dtype = p->dtype; g.kind = EPI_STORE;
+    g.epi.out = part; g.epi.ldo = d;
+    return g;
+  };
+  if (push) {
+    for (int which = 0; which < 2 && push; ++which) {
+      GemmArgs g = which ? proj_args(a.hg, hl, w, hl, hl) : proj_args(a.o, dl, w, dl, dl);
+      g.push_rows = rows;
+      push = gemm_push_supported(g, p->gemm_impl);
+    }
+  }
+  p->tp_push_last = push ? 1 : 0;
+  auto row_parallel = [&](const void* A, int lda, const void* W, int ldw, int K) -> int32_t {
+    GemmArgs g = proj_args(A, lda, W, ldw, K);
+    if (push) {
+      g.push_rows = rows;
+      for (int o = 0; o < p->tp_size; ++o) g.push_base[o] = push_base[o];
+    }
+    return launch_gemm(g, p->gemm_impl, stream);
+  };
   B200_TRY(launch_embed(tokens + row0, w + wl.emb, p->dtype, x_own, rows, d, p->V, stream));
   B200_TRY(comm_peer_reduce_norm(p->comm, T, d, p->dtype, false, x_own, g_att, eps, stream));
   for (int l = 0; l < p->L; ++l) {
@@ -273,24 +301,16 @@ static int32_t forward_row_sharded(B200Plan* p, const int32_t* tokens, int B, in
       at.ldq = 3 * dl; at.ldkv = 3 * dl; at.ldo = dl; at.dtype = p->dtype;
       B200_TRY(launch_attn_fwd(at, p->attn_impl, stream));
     }
-    {
-      EpiParams e;
-      e.out = part; e.ldo = d;
-      B200_TRY(gemm(*p, a.o, dl, w + o.wo, dl, T, d, dl, EPI_STORE, p->dtype, e, stream));
-    }
-    B200_TRY(comm_peer_reduce_norm(p->comm, T, d, p->dtype, true, x_own, g_ffn + (size_t)l * d, eps, stream));
+    B200_TRY(row_parallel(a.o, dl, w + o.wo, dl, dl));
+    B200_TRY(comm_peer_reduce_norm(p->comm, T, d, p->dtype, true, x_own, g_ffn + (size_t)l * d, eps, stream, push));
     {
       EpiParams e;
       e.out = a.hg; e.ldo = hl;
       B200_TRY(gemm(*p, xbg, d, w + o.w13, d, T, 2 * hl, d, EPI_SWIGLU, p->dtype, e, stream));
     }
-    {
-      EpiParams e;
-      e.out = part; e.ldo = d;
-      B200_TRY(gemm(*p, a.hg, hl, w + o.w2, hl, T, d, hl, EPI_STORE, p->dtype, e, stream));
-    }
+    B200_TRY(row_parallel(a.hg, hl, w + o.w2, hl, hl));
     const float* g_next = l + 1 < p->L ? g_att + (size_t)(l + 1) * d : g_fin;
-    B200_TRY(comm_peer_reduce_norm(p->comm, T, d, p->dtype, true, x_own, g_next, eps, stream));
+    B200_TRY(comm_peer_reduce_norm(p->comm, T, d, p->dtype, true, x_own, g_next, eps, stream, push));
   }
   if (logits) {
     EpiParams e;
@@ -442,7 +462,10 @@ static int32_t forward_impl(B200Plan* p, const int32_t* tokens, int B, int S, co
       // two halves of the batch in flight when the batch splits into two equal sets of sequences whose rows divide
       // over the ranks
       if (p->tp_pipeline && B % 2 == 0 && (B / 2 * S) % p->tp_size == 0 && ((size_t)(B / 2) * S * p->d * p->esize) % 256 == 0)
+      {
+        p->tp_push_last = 0;
         return forward_row_sharded_pipelined(p, tokens, B, S, w, wl, logits, kv_out, acts.layer[0], part, xbg, stream);
+      }
       return forward_row_sharded(p, tokens, B, S, w, wl, logits, kv_out, acts.layer[0], part, xbg, stream);
     }
   }
@@ -632,6 +655,7 @@ int32_t b200_plan_create(const B200LlamaConfig* cfg, int32_t tp_rank, int32_t tp
     // 34-35 ms) and at two ranks (57-61 against 54.5 ms).  So it is off unless asked for (B200_TP_PIPELINE = 1) or
     // chosen by a caller that timed both (b200_plan_set_option).
     p->tp_pipeline = env_int("B200_TP_PIPELINE", 0) != 0;
+    p->tp_push = env_int("B200_TP_PUSH", 1) != 0;  // 0: the exchange kernel pulls the partial products itself
     p->reserve_sms = env_int("B200_TP_RESERVE_SMS", 0);
     p->tp_chunks = env_int("B200_TP_CHUNKS", 1);
     if (p->tp_chunks < 1) p->tp_chunks = 1;
@@ -704,11 +728,17 @@ int32_t b200_plan_cached(const B200LlamaConfig* cfg, int32_t tp_rank, int32_t tp
 // the exchange of one beside the compute of the other, 0 = one batch with the exchange between the kernels.  Every
 // rank of the communicator must hold the same value whenever b200_forward runs (the exchange kernels pair up in
 // launch order); which of the two is faster depends on the rank count and on how busy the NVLink fabric is, so a
-// caller may time both during warm-up and keep the faster one.
+// caller may time both during warm-up and keep the faster one.  "tp_push": 1 (default) = the row-parallel projections
+// of that prefill store their partial products straight into the memory of the ranks that own the rows, 0 = into
+// local memory, from where the exchange kernel pulls them; same value on every rank.
 int32_t b200_plan_set_option(B200Plan* p, const char* name, int32_t value) {
   if (!p || !name) return fail(B200_ERR_INVALID_ARG, "null argument");
   if (!strcmp(name, "tp_pipeline")) {
     p->tp_pipeline = value != 0;
+    return B200_OK;
+  }
+  if (!strcmp(name, "tp_push")) {
+    p->tp_push = value != 0;
     return B200_OK;
   }
   return fail(B200_ERR_INVALID_ARG, "unknown plan option '%s'", name);
@@ -718,6 +748,14 @@ int32_t b200_plan_get_option(const B200Plan* p, const char* name, int32_t* value
   if (!p || !name || !value) return fail(B200_ERR_INVALID_ARG, "null argument");
   if (!strcmp(name, "tp_pipeline")) {
     *value = p->tp_pipeline ? 1 : 0;
+    return B200_OK;
+  }
+  if (!strcmp(name, "tp_push")) {
+    *value = p->tp_push ? 1 : 0;
+    return B200_OK;
+  }
+  if (!strcmp(name, "tp_push_last")) {  // read-only: whether the last tensor-parallel forward pushed its partial products
+    *value = p->tp_push_last;
     return B200_OK;
   }
   return fail(B200_ERR_INVALID_ARG, "unknown plan option '%s'", name);

@@ -82,6 +82,8 @@ struct B200Plan {
   cudaEvent_t ev_fork[8] = {}, ev_join[8] = {};
   int reserve_sms = 0;
   int tp_chunks = 1;
+  bool tp_push = true;       // row-parallel GEMMs store their partial product straight into the owners' memory
+  int tp_push_last = 0;      // whether the last tensor-parallel forward did so (it needs shapes the CTA-pair GEMM takes)
   bool tp_pipeline = false;  // ... and runs two halves of the batch so that one half's exchange overlaps the other's compute
   bool row_shard = true;  // tensor-parallel prefill keeps T/tp residual rows per rank when peer memory is up
   float* rope_cos = nullptr;  // [seq_len, hs/2], owned by the plan
@@ -110,10 +112,14 @@ int32_t comm_peer_allreduce_add(void* comm, size_t count, int dtype, const float
 // ranks, adds them to x_own (fp32 [T / world, d], in place; skipped when !reduce), and leaves gain * x * rinv of those
 // rows in every rank's gathered-activation region.  Its completion means the region of this rank is whole.
 bool comm_peer_rowshard_buffers(void* comm, size_t bytes_each, void** part, void** xb);
+// pushed: the partial products were stored by the producing GEMM straight into their owners' memory
+// (comm_peer_push_bases + GemmArgs::push_rows), so the kernel sums them from this rank's own slots.
 int32_t comm_peer_reduce_norm(void* comm, int T, int d, int dtype, bool reduce, float* x_own, const float* gain,
-                              float eps, cudaStream_t stream);
+                              float eps, cudaStream_t stream, bool pushed = false);
 int32_t comm_peer_reduce_norm_at(void* comm, int T, int d, int dtype, bool reduce, float* x_own, const float* gain,
-                                 float eps, size_t part_rel, size_t xb_rel, bool lean, cudaStream_t stream);
+                                 float eps, size_t part_rel, size_t xb_rel, bool lean, cudaStream_t stream,
+                                 bool pushed = false);
+bool comm_peer_push_bases(void* comm, int T, int d, int dtype, void** bases);
 int32_t launch_peer_wait_selftest(long long budget, uint32_t* reached_end, cudaStream_t stream);
 
 // Environment knobs (read once at plan creation): B200_GEMM_IMPL and

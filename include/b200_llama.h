@@ -165,7 +165,12 @@ B200_API int32_t b200_plan_cached(const B200LlamaConfig* cfg, int32_t tp_rank, i
  * over peer memory) runs two halves of the batch so that one half's exchange crosses NVLink beside the other half's
  * GEMMs and attention, 0 = one batch with the exchange between the kernels (the default, unless the B200_TP_PIPELINE
  * environment variable says 1).  Every rank of the communicator must hold the same value whenever
- * b200_forward runs.  Results do not depend on it.  Unknown names: B200_ERR_INVALID_ARG.  The reference has no
+ * b200_forward runs.  Results do not depend on it.  "tp_push": 1 (default, or B200_TP_PUSH) = the row-parallel
+ * projections (Wo, W2) of that prefill store every band of rows of their partial product straight into the memory of
+ * the rank that owns the rows, tile by tile while the GEMM computes, and the exchange kernel sums from local memory;
+ * 0 = they store locally and the exchange kernel pulls over NVLink; same value on every rank.  "tp_push_last"
+ * (get only): whether the last forward did push (it needs shapes the CTA-pair GEMM takes and T / tp_size a multiple
+ * of 32).  Unknown names: B200_ERR_INVALID_ARG.  The reference has no
  * counterpart (its options travel as pass-pipeline strings, primitives.py:56-115). */
 B200_API int32_t b200_plan_set_option(B200Plan* plan, const char* name, int32_t value);
 B200_API int32_t b200_plan_get_option(const B200Plan* plan, const char* name, int32_t* value);

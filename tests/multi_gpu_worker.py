@@ -131,6 +131,31 @@ def main():
     assert B.device_status() == 0
     plan.close()
     del os.environ["B200_TP_PIPELINE"]
+    # the widths of the 7B shape (2 layers, 2 x 1024 tokens): here the row-parallel projections run on the CTA-pair
+    # GEMM, which stores every band of rows of the partial product straight into its owner's memory (pushed store);
+    # the same forward with the pull form must give the same logits, and both the oracle's
+    cfg7 = dict(dim=4096, hidden_dim=11008, n_layers=2, n_heads=32, n_kv_heads=32, vocab_size=4096, seq_len=1024)
+    w = {k: v.bfloat16() for k, v in O.make_weights(cfg7, 21, torch.float32, std=0.02).items()}
+    tokens = O.make_tokens(cfg7, 2, 1024, 22)
+    ref = O.forward_sequence(tokens, cfg7, {k: v.float() for k, v in w.items()})
+    plan = B.Plan(cfg7, torch.bfloat16, tp_rank=rank, tp_size=world, comm=comm)
+    plan.pack_weights({k: v.cuda().contiguous() for k, v in w.items()})
+    del w
+    vl = cfg7["vocab_size"] // world
+    tok_dev = tokens.int().cuda()
+    outs = {}
+    for push in (1, 0):
+        plan.set_option("tp_push", push)
+        for _ in range(2):  # twice: the slots are reused by the next exchange
+            got = plan.forward(tok_dev)
+        torch.cuda.synchronize()
+        assert plan.get_option("tp_push_last") == push, ("pushed store taken?", push, plan.get_option("tp_push_last"))
+        err = float((got.cpu() - ref[..., rank * vl:(rank + 1) * vl]).abs().max() / ref.abs().max())
+        assert err < 2e-2, ("tp forward at the 7B widths", "push" if push else "pull", err)
+        outs[push] = got.clone()
+    assert torch.equal(outs[0], outs[1]), "pushed and pulled partial products must give the same logits"
+    assert B.device_status() == 0
+    plan.close()
     # data parallel: each rank differentiates its own sequences, gradients are summed over the ranks
     dtype = torch.float32
     w = O.make_weights(cfg, 5, torch.float32, std=0.05, gains_one=False)
