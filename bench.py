@@ -562,6 +562,9 @@ def run_prefill(args, rank, world, local, B, dist):
         if fused and plan.get_option("tp_push_last"):
             line["config"]["exchange"] += ("; the Wo / W2 GEMMs store each band of rows of their partial product "
                                            "straight into its owner's memory, tile by tile")
+        if fused and plan.get_option("tp_bands_last"):
+            line["config"]["exchange"] += ("; the QKV / W1|W3 / logits GEMMs wait for the gathered rows band by band, "
+                                           "starting on this rank's own")
         if tuned:
             line["config"]["exchange"] += (f" (chosen by timing both before the warm-up: one batch "
                                            f"{tuned['one_batch_ms']:.2f} ms, two halves {tuned['two_halves_ms']:.2f} ms)")

@@ -73,7 +73,7 @@ int32_t nccl_fail(const char* what, int rc) {
 }
 
 constexpr int kMaxPeers = 8;
-constexpr int kFlagWords = 64;  // [0..7] "partial ready" per source rank, [8..15] "slice written" per source rank, [32] CTA counter
+constexpr int kFlagWords = 64;  // [0..7] "partial ready" per source rank, [8..15] "slice written" per source rank, [32] CTA counter, [40..47] epoch ring
 
 struct PeerMem {
   bool on = false;
@@ -93,6 +93,11 @@ struct Comm {
   int rank = 0, world = 1;
   PeerMem pm;
   long long wait_budget = 4000000000LL;  // SM clocks a kernel waits for its peers before it gives up (B200_PEER_WAIT_MCYCLES)
+  // Copy-engine delivery of this rank's normed rows (comm_peer_reduce_norm_at with bands): a stream of its own, an
+  // event that follows the exchange kernel and one that follows the last copy of the latest exchange.
+  cudaStream_t ce_stream = nullptr;
+  cudaEvent_t ev_rows = nullptr, ev_sent = nullptr;
+  bool sent_pending = false;
 };
 
 namespace {
@@ -211,6 +216,7 @@ namespace {
 
 enum : uint32_t { ST_PEER_TIMEOUT = 1u << 12 };
 constexpr int kReadyBase = 0, kDoneBase = 8, kCounter = 32;
+constexpr int kEpochRing = 40;  // [40..47]: the epochs of the latest exchanges, sources of the copy-engine flag copies
 constexpr long long kPeerWaitCycles = 4000000000LL;
 
 __device__ __forceinline__ void flag_store_sys(uint32_t* p, uint32_t v) {
@@ -529,7 +535,7 @@ __device__ __forceinline__ void rownorm_body(const PeerPtrs& pp, int rank, int w
           const size_t off = xb_off + (grow * d + (size_t)c * E) * sizeof(T);
 #pragma unroll
           for (int r = 0; r < kMaxPeers; ++r)
-            if (r < world && (!(dbg & 2) || r == rank)) *reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(pp.buf[r]) + off) = out;
+            if (r < world && (!(dbg & 18) || r == rank)) *reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(pp.buf[r]) + off) = out;
         }
       }
       if constexpr (LEAN) {
@@ -549,11 +555,18 @@ __device__ __forceinline__ void rownorm_body(const PeerPtrs& pp, int rank, int w
     if (s_last) {
       my_flags[kCounter] = 0u;
       __threadfence_system();
-      for (int r = 0; r < world; ++r) flag_store_sys(pp.flags[r] + kDoneBase + rank, epoch);
+      if (dbg & 16) {
+        // copy-engine delivery: the rows are whole in THIS rank's region only; copies that the host queued behind
+        // this kernel carry them and then this epoch (from the ring) to the peers
+        my_flags[kEpochRing + (epoch & 7u)] = epoch;
+        flag_store_sys(my_flags + kDoneBase + rank, epoch);
+      } else {
+        for (int r = 0; r < world; ++r) flag_store_sys(pp.flags[r] + kDoneBase + rank, epoch);
+      }
     }
   }
   __syncthreads();
-  if (s_last && ok) wait_all_peers(my_flags, kDoneBase, world, epoch, status, budget);
+  if (s_last && ok && !(dbg & 8)) wait_all_peers(my_flags, kDoneBase, world, epoch, status, budget);
 }
 
 template <typename T, int NW, int NCH, bool PREFETCH>
@@ -759,15 +772,25 @@ bool comm_peer_rowshard_buffers(void* comm, size_t bytes_each, void** part, void
 // In-switch reduction halves the bytes on every link from four ranks on ((world + 1) / world of the buffer each way
 // instead of 2 (world - 1) / world); it was never faster on the boxes this was measured on (200 us against 118 us per
 // exchange of 64 MiB between two ranks, 216 against 197 us among four), so it is off unless B200_TP_MULTIMEM = 1.
+// Work queued on the copy stream by an earlier exchange reads this rank's gathered rows: whatever overwrites them or
+// frees the memory goes behind it.
+static int32_t join_copies(Comm* c, cudaStream_t stream) {
+  if (c->sent_pending) {
+    B200_CUDA_OK(cudaStreamWaitEvent(stream, c->ev_sent, 0));
+    c->sent_pending = false;
+  }
+  return B200_OK;
+}
+
 static bool use_multimem(const Comm* c) {
   static const int mc_env = env_int("B200_TP_MULTIMEM", -1);
   return c->pm.mc && mc_env > 0;
 }
 
 int32_t comm_peer_reduce_norm(void* comm, int T, int d, int dtype, bool reduce, float* x_own, const float* gain,
-                              float eps, cudaStream_t stream, bool pushed) {
+                              float eps, cudaStream_t stream, bool pushed, PeerBands* bands) {
   const size_t each = align_up((size_t)T * d * (dtype == B200_BF16 ? 2 : 4), 256);
-  return comm_peer_reduce_norm_at(comm, T, d, dtype, reduce, x_own, gain, eps, 0, each, false, stream, pushed);
+  return comm_peer_reduce_norm_at(comm, T, d, dtype, reduce, x_own, gain, eps, 0, each, false, stream, pushed, bands);
 }
 
 // Where a pushed store of a [T, d] partial product goes: bases[o] is slot `rank` of rank o's partial region, a
@@ -790,13 +813,14 @@ bool comm_peer_push_bases(void* comm, int T, int d, int dtype, void** bases) {
 // (one CTA per SM, 96 registers).
 int32_t comm_peer_reduce_norm_at(void* comm, int T, int d, int dtype, bool reduce, float* x_own, const float* gain,
                                  float eps, size_t part_rel, size_t xb_rel, bool lean, cudaStream_t stream,
-                                 bool pushed) {
+                                 bool pushed, PeerBands* bands) {
   Comm* c = reinterpret_cast<Comm*>(comm);
   if (!c || !c->pm.on) return fail(B200_ERR_INVALID_ARG, "peer memory is not set up for this communicator");
   const size_t es = dtype == B200_BF16 ? 2 : 4;
   if (T % c->world || ((size_t)d * es) % 16 || d % 4)
     return fail(B200_ERR_BAD_SHAPE, "row-sharded exchange: %d rows over %d ranks, row of %d elements", T, c->world, d);
   B200_TRY(reject_capture(stream, "the tensor-parallel exchange over peer memory"));
+  B200_TRY(join_copies(c, stream));
   ProfScope prof(PROF_COMM, (double)T * d * es, stream);
   PeerPtrs pp;
   for (int r = 0; r < kMaxPeers; ++r) {
@@ -843,7 +867,26 @@ int32_t comm_peer_reduce_norm_at(void* comm, int T, int d, int dtype, bool reduc
   const int regs_row = (nw > 0 ? nw : 1) * nch * 4 + nch * (int)(16 / es);
   static const int pf_env = env_int("B200_ROWNORM_PREFETCH", -1);  // -1: decide by the register estimate
   static const int dbg_env = env_int("B200_EXCH_LOCAL_ONLY", 0);   // measurement aid: 1 loads, 2 stores stay on this GPU
-  const int dbg = (dbg_env & 3) | (pushed ? 4 : 0);                // bit 2: partial products sit in this rank's slots
+  // bit 2: partial products sit in this rank's slots; bit 3: the consumer waits for the peers' rows, not this kernel
+  // bit 4: the kernel leaves its normed rows in this rank's region only and the copy engines deliver them (below)
+  static const int ce_env = env_int("B200_TP_COPY_ENGINE", 1);
+  bool ce = bands && ce_env && c->world > 1;
+  if (ce && !c->ce_stream) {
+    if (cudaStreamCreateWithFlags(&c->ce_stream, cudaStreamNonBlocking) != cudaSuccess ||
+        cudaEventCreateWithFlags(&c->ev_rows, cudaEventDisableTiming) != cudaSuccess ||
+        cudaEventCreateWithFlags(&c->ev_sent, cudaEventDisableTiming) != cudaSuccess) {
+      cudaGetLastError();
+      return fail(B200_ERR_CUDA, "creating the copy stream of the tensor-parallel exchange failed");
+    }
+  }
+  const int dbg = (dbg_env & 3) | (pushed ? 4 : 0) | (bands ? 8 : 0) | (ce ? 16 : 0);
+  if (bands) {
+    bands->flags = c->pm.flags[c->rank] + kDoneBase;
+    bands->epoch = epoch;
+    bands->rows = rows;
+    bands->first = c->rank;
+    bands->budget = c->wait_budget;
+  }
   const bool prefetch = pf_env >= 0 ? pf_env != 0 : regs_row <= 72;
 #define B200_ROWNORM(TT, NW, NCH)                                                                                    \
   do {                                                                                                               \
@@ -879,6 +922,26 @@ int32_t comm_peer_reduce_norm_at(void* comm, int T, int d, int dtype, bool reduc
 #undef B200_ROWNORM_NCH
 #undef B200_ROWNORM
   B200_LAUNCH_OK("peer_rownorm_kernel");
+  if (ce) {
+    // This rank's normed rows, then the epoch, to every peer by copies on a stream of their own: they cross NVLink
+    // on the copy engines while the GEMM that consumes the gathered rows already works on this rank's band.  One
+    // copy per destination and word; copies of one stream complete in order, so a peer that sees the epoch has
+    // the rows.
+    B200_CUDA_OK(cudaEventRecord(c->ev_rows, stream));
+    B200_CUDA_OK(cudaStreamWaitEvent(c->ce_stream, c->ev_rows, 0));
+    const size_t row_bytes = (size_t)d * es;
+    const uint8_t* src = reinterpret_cast<const uint8_t*>(c->pm.buf[c->rank]) + xb_off + (size_t)row0 * row_bytes;
+    const uint32_t* epoch_src = c->pm.flags[c->rank] + kEpochRing + (epoch & 7u);
+    for (int i = 1; i < c->world; ++i) {
+      const int r = (c->rank + i) % c->world;
+      uint8_t* dst = reinterpret_cast<uint8_t*>(c->pm.buf[r]) + xb_off + (size_t)row0 * row_bytes;
+      B200_CUDA_OK(cudaMemcpyAsync(dst, src, (size_t)rows * row_bytes, cudaMemcpyDeviceToDevice, c->ce_stream));
+      B200_CUDA_OK(cudaMemcpyAsync(c->pm.flags[r] + kDoneBase + c->rank, epoch_src, sizeof(uint32_t),
+                                   cudaMemcpyDeviceToDevice, c->ce_stream));
+    }
+    B200_CUDA_OK(cudaEventRecord(c->ev_sent, c->ce_stream));
+    c->sent_pending = true;
+  }
   return B200_OK;
 }
 
@@ -1069,6 +1132,12 @@ int32_t b200_comm_destroy(void* comm) {
       cudaFree(token);
     }
     cudaGetLastError();
+  }
+  if (c->ce_stream) {
+    cudaStreamSynchronize(c->ce_stream);
+    cudaStreamDestroy(c->ce_stream);
+    cudaEventDestroy(c->ev_rows);
+    cudaEventDestroy(c->ev_sent);
   }
   free_peer_memory(c);
   const int rc = a.comm_destroy(c->nccl);

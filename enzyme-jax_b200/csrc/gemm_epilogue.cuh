@@ -172,7 +172,17 @@ struct GemmArgs {
   // Only the CTA-pair tensor kernel with the plain store does this; ask gemm_push_supported first.
   int push_rows = 0;
   void* push_base[8] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
+  // Column-parallel projection of a tensor-parallel plan whose A operand arrives in bands of band_rows rows, band o
+  // written by rank o: before it first loads rows of band o the kernel waits (bounded by band_budget SM clocks)
+  // until band_flags[o] has reached band_epoch, and it starts with the tiles of band band_first, whose rows are
+  // already there.  Only the CTA-pair tensor kernel does this; ask gemm_bands_supported first.
+  const uint32_t* band_flags = nullptr;
+  uint32_t band_epoch = 0;
+  int band_rows = 0, band_first = 0;
+  long long band_budget = 0;
 };
+// whether launch_gemm(g, impl) would take the kernel that honours band_flags (see GemmArgs)
+bool gemm_bands_supported(const GemmArgs& g, int impl);
 // whether launch_gemm(g, impl) would take the kernel that honours push_rows / push_base
 bool gemm_push_supported(const GemmArgs& g, int impl);
 // Scratch that lets the tensor-core kernel split K whenever it wants to for an M x N output.

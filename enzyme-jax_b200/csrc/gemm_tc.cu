@@ -479,6 +479,13 @@ int32_t launch_splitk_reduce(const GemmArgs& g, int splits, cudaStream_t stream)
   return B200_OK;
 }
 
+bool gemm_bands_supported(const GemmArgs& g, int impl) {
+  static const int use_pair = env_int("B200_GEMM_PAIR", 1);
+  const bool tc = impl == 1 || (impl != 2 && gemm_tc_supports(g));
+  return tc && use_pair && gemm_tc2_supports(g) && !g.ta && !g.tb && g.band_rows > 0 && g.band_rows % 256 == 0 &&
+         g.M % g.band_rows == 0 && g.M / g.band_rows <= 8;
+}
+
 bool gemm_push_supported(const GemmArgs& g, int impl) {
   static const int use_pair = env_int("B200_GEMM_PAIR", 1);
   const bool tc = impl == 1 || (impl != 2 && gemm_tc_supports(g));
@@ -495,6 +502,8 @@ int32_t launch_gemm(const GemmArgs& g, int impl, cudaStream_t stream) {
   const bool pair_t = tc && !pair && use_pair && pair_mn && gemm_tc2_mn_supports(g);
   ProfScope prof(!tc ? PROF_GEMM_SIMT : (pair || pair_t) ? PROF_GEMM_PAIR : PROF_GEMM_TC,
                  2.0 * g.M * (double)g.N * g.K, stream);
+  if (g.band_flags && !pair)
+    return fail(B200_ERR_UNSUPPORTED, "banded A operand needs the CTA-pair tensor kernel (M=%d N=%d K=%d)", g.M, g.N, g.K);
   if (g.push_rows > 0 && !pair)
     return fail(B200_ERR_UNSUPPORTED, "pushed store needs the CTA-pair tensor kernel (M=%d N=%d K=%d)", g.M, g.N, g.K);
   if (!tc) return launch_gemm_simt(g, stream);

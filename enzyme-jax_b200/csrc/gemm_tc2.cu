@@ -101,9 +101,24 @@ __device__ __forceinline__ void mma_pair_commit(uint64_t* bar) {
                : "memory");
 }
 
+__device__ __forceinline__ uint32_t ld_acquire_sys_u32(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+
 // Output maps of a pushed store (GemmArgs::push_rows): one [push_rows, N] matrix per destination rank.
 struct alignas(64) PushMaps {
   CUtensorMap m[8];
+};
+
+// Bands of A rows that other ranks deliver (GemmArgs::band_flags).
+struct BandWait {
+  const uint32_t* flags = nullptr;  // [bands]: band o is whole once flags[o] has reached `epoch`
+  uint32_t epoch = 0;
+  int rows = 0;     // rows per band, a multiple of the 256-row tile
+  int mt_rot = 0;   // row tiles are visited starting at this one (the first tile of the band that is already there)
+  long long budget = 0;
 };
 
 // MN: both operands are MN-major (A stored [K, M], B stored [K, N]: the weight-gradient products dY^T X).  Their
@@ -116,7 +131,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(P_THREADS, 1)
                     const __grid_constant__ CUtensorMap tmO, const __grid_constant__ CUtensorMap tmR,
                     const __grid_constant__ CUtensorMap tmG, const __grid_constant__ CUtensorMap tmU, int M, int N,
                     int K, EpiParams ep, int splits, int split_rows, uint32_t* status,
-                    const __grid_constant__ PushMaps pm, int push_rows) {
+                    const __grid_constant__ PushMaps pm, int push_rows, BandWait bw) {
   using Cfg = PairCfg<BN, KIND>;
   constexpr int S = Cfg::kStages;
   extern __shared__ uint8_t smem_raw[];
@@ -175,13 +190,35 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(P_THREADS, 1)
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
+      uint32_t bands_seen = 0;  // bit o: band o of the A operand is known to be whole
       for (int item = pair; item < num_items && ok; item += n_pairs) {
         const int tile = item % num_tiles, split = item / num_tiles;
         const int kb0 = (int)((long)split * num_kb / splits), kb1 = (int)((long)(split + 1) * num_kb / splits);
         int mt, nt;
         tile_coords(tile, m_tiles, n_tiles, 8, mt, nt);
+        if (bw.flags) mt = (mt + bw.mt_rot) % m_tiles;
         const int m0 = mt * (2 * PM) + (int)rank * PM;
         const int n0 = nt * BN + (int)rank * (BN / 2);
+        if (bw.flags) {
+          // rows of a band another rank writes: wait for that rank's word, once per band (bounded; acquire at
+          // system scope, then order the bulk loads of this thread behind it)
+          const int band = m0 / bw.rows;
+          if (!((bands_seen >> band) & 1u)) {
+            const long long t0 = clock64();
+            while ((int32_t)(ld_acquire_sys_u32(bw.flags + band) - bw.epoch) < 0) {
+              __nanosleep(64);
+              if (*abort_flag || clock64() - t0 > bw.budget) {
+                atomicOr(status, (uint32_t)ST_PAIR_PRODUCER);
+                *abort_flag = 1u;
+                ok = false;
+                break;
+              }
+            }
+            if (!ok) break;
+            asm volatile("fence.proxy.async;" ::: "memory");
+            bands_seen |= 1u << band;
+          }
+        }
         for (int kb = kb0; kb < kb1; ++kb) {
           ok = ptx::mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag, status, ST_PAIR_PRODUCER);
           if (!ok) break;
@@ -266,6 +303,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(P_THREADS, 1)
       const int tile = item % num_tiles, split = item / num_tiles;
       int mt, nt;
       tile_coords(tile, m_tiles, n_tiles, 8, mt, nt);
+      if (bw.flags) mt = (mt + bw.mt_rot) % m_tiles;
       const int m0 = mt * (2 * PM) + (int)rank * PM;
       const int n0 = nt * BN;
       const int mrow0 = m0 + q * 32;  // first row of this warp's boxes; rows past M are clipped by the store
@@ -597,8 +635,19 @@ int32_t launch_pair_cfg(const GemmArgs& g, cudaStream_t stream, int splits = 1) 
       push_rows = g.push_rows;
     }
   }
+  BandWait bw;
+  if (g.band_flags) {
+    if (MN || splits != 1 || g.band_rows <= 0 || g.band_rows % (2 * PM) || g.M % g.band_rows || g.M / g.band_rows > 8 ||
+        g.band_first < 0 || g.band_first >= g.M / g.band_rows)
+      return fail(B200_ERR_UNSUPPORTED, "banded A operand: %d rows in bands of %d", g.M, g.band_rows);
+    bw.flags = g.band_flags;
+    bw.epoch = g.band_epoch;
+    bw.rows = g.band_rows;
+    bw.mt_rot = g.band_first * (g.band_rows / (2 * PM));
+    bw.budget = g.band_budget > 0 ? g.band_budget : 4000000000LL;
+  }
   B200_CUDA_OK(launch_pdl(kern, dim3(2 * pairs), dim3(P_THREADS), Cfg::kSmemBytes, stream, tmA, tmB, tmO, tmR, tmG,
-                          tmU, g.M, g.N, g.K, g.epi, splits, MN ? g.M : 0, device_status_word(), pm, push_rows));
+                          tmU, g.M, g.N, g.K, g.epi, splits, MN ? g.M : 0, device_status_word(), pm, push_rows, bw));
   B200_LAUNCH_OK("gemm_tc2_kernel");
   return B200_OK;
 }

@@ -175,10 +175,14 @@ void carve_forward(const B200Plan& p, Arena& a, int B, int S, bool keep, FwdActs
 
 // ---- forward ---------------------------------------------------------------------
 static int32_t gemm(const B200Plan& p, const void* A, int lda, const void* B, int ldb, int M, int N, int K, int kind,
-                    int out_dtype, const EpiParams& epi, cudaStream_t stream) {
+                    int out_dtype, const EpiParams& epi, cudaStream_t stream, const PeerBands* bands = nullptr) {
   GemmArgs g;
   g.A = A; g.B = B; g.M = M; g.N = N; g.K = K; g.lda = lda; g.ldb = ldb;
   g.in_dtype = p.dtype; g.out_dtype = out_dtype; g.kind = kind; g.epi = epi;
+  if (bands && bands->flags) {  // A arrives band by band from the other ranks: the kernel waits for each band itself
+    g.band_flags = bands->flags; g.band_epoch = bands->epoch; g.band_rows = bands->rows; g.band_first = bands->first;
+    g.band_budget = bands->budget;
+  }
   return launch_gemm(g, p.gemm_impl, stream);
 }
 
@@ -265,6 +269,27 @@ static int32_t forward_row_sharded(B200Plan* p, const int32_t* tokens, int B, in
     }
   }
   p->tp_push_last = push ? 1 : 0;
+  // Gathered rows consumed band by band: the exchange kernel returns once this rank's rows are delivered, and the
+  // column-parallel GEMM that follows starts on the band that is already here and waits for every other band just
+  // before it first loads rows of it, so the all-gather half of the exchange crosses NVLink under that GEMM.  Needs
+  // the CTA-pair kernel for all three consumers.
+  bool bands = p->tp_bands && rows % 256 == 0;
+  if (bands) {
+    const int ns[3] = {3 * dl, 2 * hl, p->V_loc};
+    const int kinds[3] = {EPI_ROPE, EPI_SWIGLU, EPI_STORE};
+    for (int i = 0; i < (logits ? 3 : 2) && bands; ++i) {
+      GemmArgs g;
+      g.A = xbg; g.B = w; g.M = T; g.N = ns[i]; g.K = d; g.lda = d; g.ldb = d;
+      g.in_dtype = p->dtype; g.out_dtype = i == 2 ? B200_F32 : p->dtype; g.kind = kinds[i];
+      g.epi.out = i == 0 ? a.qkv : i == 1 ? a.hg : (void*)logits;
+      g.epi.ldo = i == 1 ? hl : ns[i];
+      if (i == 0) { g.epi.rope_cos = p->rope_cos; g.epi.rope_sin = p->rope_sin; g.epi.head_size = p->hs; }
+      g.band_rows = rows;
+      bands = gemm_bands_supported(g, p->gemm_impl);
+    }
+  }
+  p->tp_bands_last = bands ? 1 : 0;
+  PeerBands pb;
   auto row_parallel = [&](const void* A, int lda, const void* W, int ldw, int K) -> int32_t {
     GemmArgs g = proj_args(A, lda, W, ldw, K);
     if (push) {
@@ -274,7 +299,7 @@ static int32_t forward_row_sharded(B200Plan* p, const int32_t* tokens, int B, in
     return launch_gemm(g, p->gemm_impl, stream);
   };
   B200_TRY(launch_embed(tokens + row0, w + wl.emb, p->dtype, x_own, rows, d, p->V, stream));
-  B200_TRY(comm_peer_reduce_norm(p->comm, T, d, p->dtype, false, x_own, g_att, eps, stream));
+  B200_TRY(comm_peer_reduce_norm(p->comm, T, d, p->dtype, false, x_own, g_att, eps, stream, false, bands ? &pb : nullptr));
   for (int l = 0; l < p->L; ++l) {
     const LayerOffsets& o = wl.layer[l];
     {
@@ -282,7 +307,7 @@ static int32_t forward_row_sharded(B200Plan* p, const int32_t* tokens, int B, in
       e.out = a.qkv; e.ldo = 3 * dl;
       e.rope_cos = p->rope_cos; e.rope_sin = p->rope_sin;
       e.seq_len = S; e.pos_base = 0; e.head_size = p->hs; e.rope_cols = 2 * dl;
-      B200_TRY(gemm(*p, xbg, d, w + o.wqkv, d, T, 3 * dl, d, EPI_ROPE, p->dtype, e, stream));
+      B200_TRY(gemm(*p, xbg, d, w + o.wqkv, d, T, 3 * dl, d, EPI_ROPE, p->dtype, e, stream, &pb));
     }
     if (kv_out) {
       uint8_t* dst = reinterpret_cast<uint8_t*>(kv_out) + (size_t)l * 2 * T * dl * p->esize;
@@ -302,20 +327,25 @@ static int32_t forward_row_sharded(B200Plan* p, const int32_t* tokens, int B, in
       B200_TRY(launch_attn_fwd(at, p->attn_impl, stream));
     }
     B200_TRY(row_parallel(a.o, dl, w + o.wo, dl, dl));
-    B200_TRY(comm_peer_reduce_norm(p->comm, T, d, p->dtype, true, x_own, g_ffn + (size_t)l * d, eps, stream, push));
+    B200_TRY(comm_peer_reduce_norm(p->comm, T, d, p->dtype, true, x_own, g_ffn + (size_t)l * d, eps, stream, push,
+                                   bands ? &pb : nullptr));
     {
       EpiParams e;
       e.out = a.hg; e.ldo = hl;
-      B200_TRY(gemm(*p, xbg, d, w + o.w13, d, T, 2 * hl, d, EPI_SWIGLU, p->dtype, e, stream));
+      B200_TRY(gemm(*p, xbg, d, w + o.w13, d, T, 2 * hl, d, EPI_SWIGLU, p->dtype, e, stream, &pb));
     }
     B200_TRY(row_parallel(a.hg, hl, w + o.w2, hl, hl));
     const float* g_next = l + 1 < p->L ? g_att + (size_t)(l + 1) * d : g_fin;
-    B200_TRY(comm_peer_reduce_norm(p->comm, T, d, p->dtype, true, x_own, g_next, eps, stream, push));
+    // the last exchange has a consumer only when logits are asked for; without one it waits for the peers itself
+    const bool last = l + 1 == p->L;
+    B200_TRY(comm_peer_reduce_norm(p->comm, T, d, p->dtype, true, x_own, g_next, eps, stream, push,
+                                   bands && (!last || logits) ? &pb : nullptr));
+    if (last && !logits) pb = PeerBands{};
   }
   if (logits) {
     EpiParams e;
     e.out = logits; e.ldo = p->V_loc;
-    B200_TRY(gemm(*p, xbg, d, w + wl.wcls, d, T, p->V_loc, d, EPI_STORE, B200_F32, e, stream));
+    B200_TRY(gemm(*p, xbg, d, w + wl.wcls, d, T, p->V_loc, d, EPI_STORE, B200_F32, e, stream, &pb));
   }
   return B200_OK;
 }
@@ -464,6 +494,7 @@ static int32_t forward_impl(B200Plan* p, const int32_t* tokens, int B, int S, co
       if (p->tp_pipeline && B % 2 == 0 && (B / 2 * S) % p->tp_size == 0 && ((size_t)(B / 2) * S * p->d * p->esize) % 256 == 0)
       {
         p->tp_push_last = 0;
+        p->tp_bands_last = 0;
         return forward_row_sharded_pipelined(p, tokens, B, S, w, wl, logits, kv_out, acts.layer[0], part, xbg, stream);
       }
       return forward_row_sharded(p, tokens, B, S, w, wl, logits, kv_out, acts.layer[0], part, xbg, stream);
@@ -656,6 +687,7 @@ int32_t b200_plan_create(const B200LlamaConfig* cfg, int32_t tp_rank, int32_t tp
     // chosen by a caller that timed both (b200_plan_set_option).
     p->tp_pipeline = env_int("B200_TP_PIPELINE", 0) != 0;
     p->tp_push = env_int("B200_TP_PUSH", 1) != 0;  // 0: the exchange kernel pulls the partial products itself
+    p->tp_bands = env_int("B200_TP_BANDS", 1) != 0;  // 0: the exchange kernel waits for all gathered rows itself
     p->reserve_sms = env_int("B200_TP_RESERVE_SMS", 0);
     p->tp_chunks = env_int("B200_TP_CHUNKS", 1);
     if (p->tp_chunks < 1) p->tp_chunks = 1;
@@ -741,6 +773,10 @@ int32_t b200_plan_set_option(B200Plan* p, const char* name, int32_t value) {
     p->tp_push = value != 0;
     return B200_OK;
   }
+  if (!strcmp(name, "tp_bands")) {
+    p->tp_bands = value != 0;
+    return B200_OK;
+  }
   return fail(B200_ERR_INVALID_ARG, "unknown plan option '%s'", name);
 }
 
@@ -752,6 +788,14 @@ int32_t b200_plan_get_option(const B200Plan* p, const char* name, int32_t* value
   }
   if (!strcmp(name, "tp_push")) {
     *value = p->tp_push ? 1 : 0;
+    return B200_OK;
+  }
+  if (!strcmp(name, "tp_bands")) {
+    *value = p->tp_bands ? 1 : 0;
+    return B200_OK;
+  }
+  if (!strcmp(name, "tp_bands_last")) {  // read-only
+    *value = p->tp_bands_last;
     return B200_OK;
   }
   if (!strcmp(name, "tp_push_last")) {  // read-only: whether the last tensor-parallel forward pushed its partial products

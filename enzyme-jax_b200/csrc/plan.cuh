@@ -82,7 +82,9 @@ struct B200Plan {
   cudaEvent_t ev_fork[8] = {}, ev_join[8] = {};
   int reserve_sms = 0;
   int tp_chunks = 1;
+  bool tp_bands = true;      // column-parallel GEMMs wait for the gathered rows band by band instead of the exchange kernel
   bool tp_push = true;       // row-parallel GEMMs store their partial product straight into the owners' memory
+  int tp_bands_last = 0;     // whether the last tensor-parallel forward consumed the gathered rows band by band
   int tp_push_last = 0;      // whether the last tensor-parallel forward did so (it needs shapes the CTA-pair GEMM takes)
   bool tp_pipeline = false;  // ... and runs two halves of the batch so that one half's exchange overlaps the other's compute
   bool row_shard = true;  // tensor-parallel prefill keeps T/tp residual rows per rank when peer memory is up
@@ -114,11 +116,20 @@ int32_t comm_peer_allreduce_add(void* comm, size_t count, int dtype, const float
 bool comm_peer_rowshard_buffers(void* comm, size_t bytes_each, void** part, void** xb);
 // pushed: the partial products were stored by the producing GEMM straight into their owners' memory
 // (comm_peer_push_bases + GemmArgs::push_rows), so the kernel sums them from this rank's own slots.
+// bands: when given, the kernel does NOT end by waiting for the peers' rows; it returns as soon as this rank's rows
+// are delivered and *bands says how the consumer can wait band by band itself (GemmArgs::band_flags): flags[o]
+// reaches `epoch` once rank o's rows are whole in this rank's gathered region.
+struct PeerBands {
+  const uint32_t* flags = nullptr;
+  uint32_t epoch = 0;
+  int rows = 0, first = 0;
+  long long budget = 0;
+};
 int32_t comm_peer_reduce_norm(void* comm, int T, int d, int dtype, bool reduce, float* x_own, const float* gain,
-                              float eps, cudaStream_t stream, bool pushed = false);
+                              float eps, cudaStream_t stream, bool pushed = false, PeerBands* bands = nullptr);
 int32_t comm_peer_reduce_norm_at(void* comm, int T, int d, int dtype, bool reduce, float* x_own, const float* gain,
                                  float eps, size_t part_rel, size_t xb_rel, bool lean, cudaStream_t stream,
-                                 bool pushed = false);
+                                 bool pushed = false, PeerBands* bands = nullptr);
 bool comm_peer_push_bases(void* comm, int T, int d, int dtype, void** bases);
 int32_t launch_peer_wait_selftest(long long budget, uint32_t* reached_end, cudaStream_t stream);
 

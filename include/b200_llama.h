@@ -170,7 +170,11 @@ B200_API int32_t b200_plan_cached(const B200LlamaConfig* cfg, int32_t tp_rank, i
  * the rank that owns the rows, tile by tile while the GEMM computes, and the exchange kernel sums from local memory;
  * 0 = they store locally and the exchange kernel pulls over NVLink; same value on every rank.  "tp_push_last"
  * (get only): whether the last forward did push (it needs shapes the CTA-pair GEMM takes and T / tp_size a multiple
- * of 32).  Unknown names: B200_ERR_INVALID_ARG.  The reference has no
+ * of 32).  "tp_bands": 1 (default, or B200_TP_BANDS) = the exchange kernel returns once this rank's rows are
+ * delivered and the column-parallel projection that follows (QKV, W1|W3, logits) starts on those rows and waits, with
+ * a bounded wait, for every other rank's band of rows just before it first loads from it, 0 = the exchange kernel
+ * waits for all ranks; same value on every rank; "tp_bands_last" (get only) as above.  Unknown names:
+ * B200_ERR_INVALID_ARG.  The reference has no
  * counterpart (its options travel as pass-pipeline strings, primitives.py:56-115). */
 B200_API int32_t b200_plan_set_option(B200Plan* plan, const char* name, int32_t value);
 B200_API int32_t b200_plan_get_option(const B200Plan* plan, const char* name, int32_t* value);

@@ -134,7 +134,7 @@ def main():
     # the widths of the 7B shape (2 layers, 2 x 1024 tokens): here the row-parallel projections run on the CTA-pair
     # GEMM, which stores every band of rows of the partial product straight into its owner's memory (pushed store);
     # the same forward with the pull form must give the same logits, and both the oracle's
-    cfg7 = dict(dim=4096, hidden_dim=11008, n_layers=2, n_heads=32, n_kv_heads=32, vocab_size=4096, seq_len=1024)
+    cfg7 = dict(dim=4096, hidden_dim=11008, n_layers=2, n_heads=32, n_kv_heads=32, vocab_size=32768, seq_len=1024)
     w = {k: v.bfloat16() for k, v in O.make_weights(cfg7, 21, torch.float32, std=0.02).items()}
     tokens = O.make_tokens(cfg7, 2, 1024, 22)
     ref = O.forward_sequence(tokens, cfg7, {k: v.float() for k, v in w.items()})
@@ -143,17 +143,23 @@ def main():
     del w
     vl = cfg7["vocab_size"] // world
     tok_dev = tokens.int().cuda()
+    # ... and the column-parallel projections wait for the gathered rows band by band (the exchange kernel returns
+    # once this rank's rows are delivered); every combination of the two must give the same logits
     outs = {}
-    for push in (1, 0):
+    for push, bands in ((1, 1), (0, 1), (1, 0), (0, 0)):
         plan.set_option("tp_push", push)
-        for _ in range(2):  # twice: the slots are reused by the next exchange
+        plan.set_option("tp_bands", bands)
+        for _ in range(3):  # repeatedly: slots, gathered rows and flag words are reused by the next exchange
             got = plan.forward(tok_dev)
         torch.cuda.synchronize()
         assert plan.get_option("tp_push_last") == push, ("pushed store taken?", push, plan.get_option("tp_push_last"))
+        assert plan.get_option("tp_bands_last") == bands, ("banded consumers taken?", bands)
         err = float((got.cpu() - ref[..., rank * vl:(rank + 1) * vl]).abs().max() / ref.abs().max())
-        assert err < 2e-2, ("tp forward at the 7B widths", "push" if push else "pull", err)
-        outs[push] = got.clone()
-    assert torch.equal(outs[0], outs[1]), "pushed and pulled partial products must give the same logits"
+        assert err < 2e-2, ("tp forward at the 7B widths", push, bands, err)
+        outs[(push, bands)] = got.clone()
+        assert B.device_status() == 0, (push, bands)
+    for k, v in outs.items():
+        assert torch.equal(v, outs[(0, 0)]), ("pushed / banded forms must give the same logits as the plain form", k)
     assert B.device_status() == 0
     plan.close()
     # data parallel: each rank differentiates its own sequences, gradients are summed over the ranks
