@@ -406,11 +406,10 @@ def run_prefill(args, rank, world, local, B, dist):
         launches_per_forward = (B.launch_count() - l_before) // (2 * n_bufs)
     last_dev = torch.empty(batch, plan.vocab_local, dtype=torch.float32, device=dev)
 
-    # Tensor parallel: time the two forms of the exchange schedule before the warm-up and keep the faster one (all
-    # ranks agree on it); B200_TP_PIPELINE pins the choice instead.
+    # Tensor parallel: --tune-tp times the two exchange schedules (one batch / two halves in flight) before the
+    # warm-up and keeps the faster one on every rank; without it the plan's default (one batch) runs.
     tuned = None
-    if tp > 1 and comm.peer_memory() and "B200_TP_PIPELINE" not in os.environ \
-            and os.environ.get("B200_TP_ROW_SHARD", "1") != "0":
+    if args.tune_tp and tp > 1 and comm.peer_memory() and os.environ.get("B200_TP_ROW_SHARD", "1") != "0":
         tuned = plan.tune_tensor_parallel(dev_tokens[0], logits)
 
     def step_resident(i):
@@ -810,6 +809,8 @@ def main():
     ap.add_argument("--workload", default="c4", choices=sorted(WORKLOADS))
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--tune-tp", action="store_true",
+                    help="tensor parallel: time both exchange schedules before the warm-up and run the faster one")
     ap.add_argument("--batch", type=int, default=0, help="override the batch per rank (profiling on a small case)")
     ap.add_argument("--layers", type=int, default=0, help="override the layer count (profiling on a small case)")
     ap.add_argument("--no-graph", action="store_true", help="launch every kernel eagerly instead of replaying a CUDA graph")
