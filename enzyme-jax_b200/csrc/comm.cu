@@ -959,6 +959,7 @@ int32_t comm_peer_allreduce_add(void* comm, size_t count, int dtype, const float
   if ((count * es) % 16 || count * es > c->pm.bytes - 2 * kOneShotMaxBytes)
     return fail(B200_ERR_BAD_SHAPE, "peer all-reduce: bad size");
   B200_TRY(reject_capture(stream, "the tensor-parallel all-reduce over peer memory"));
+  B200_TRY(join_copies(c, stream));  // a flag copy of an earlier exchange must not land behind this kernel's flags
   ProfScope prof(PROF_COMM, (double)count * es, stream);
   const bool small = count * es <= kOneShotMaxBytes;
   PeerPtrs pp;
