@@ -154,6 +154,9 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(P_THREADS, 1)
   const int num_tiles = m_tiles * n_tiles;
   const int num_kb = (K + PK - 1) / PK;
   const int num_items = num_tiles * splits;  // item = (tile, K range): tile = item % num_tiles, split = item / num_tiles
+  // row tiles per raster group (tiles of a group are visited before the next group: the A panel of the group stays
+  // in L2); with a banded A operand a group does not reach into the next band, which arrives later
+  const int raster_rows = bw.flags && bw.rows / (2 * PM) < 8 ? bw.rows / (2 * PM) : 8;
   constexpr int kMnBox = 64 * PK * 2;        // bytes of one MN-major box: 64 columns x 64 k-rows
 
   if (threadIdx.x == 0) {
@@ -195,7 +198,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(P_THREADS, 1)
         const int tile = item % num_tiles, split = item / num_tiles;
         const int kb0 = (int)((long)split * num_kb / splits), kb1 = (int)((long)(split + 1) * num_kb / splits);
         int mt, nt;
-        tile_coords(tile, m_tiles, n_tiles, 8, mt, nt);
+        tile_coords(tile, m_tiles, n_tiles, raster_rows, mt, nt);
         if (bw.flags) mt = (mt + bw.mt_rot) % m_tiles;
         const int m0 = mt * (2 * PM) + (int)rank * PM;
         const int n0 = nt * BN + (int)rank * (BN / 2);
@@ -302,7 +305,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(P_THREADS, 1)
     for (int item = pair; item < num_items && ok; item += n_pairs) {
       const int tile = item % num_tiles, split = item / num_tiles;
       int mt, nt;
-      tile_coords(tile, m_tiles, n_tiles, 8, mt, nt);
+      tile_coords(tile, m_tiles, n_tiles, raster_rows, mt, nt);
       if (bw.flags) mt = (mt + bw.mt_rot) % m_tiles;
       const int m0 = mt * (2 * PM) + (int)rank * PM;
       const int n0 = nt * BN;
